@@ -1,0 +1,107 @@
+"""Pins the CPU oracle (oracle/cbl_oracle.py) against fixtures produced by running the reference
+implementation (tests/golden/make_golden.py). Bit-exact for integers and decoded weights."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import cbl_oracle as orc
+
+G = Path(__file__).resolve().parent / "golden"
+
+
+def test_pack_unpack_matches_reference_for_every_bit_width():
+    z = np.load(G / "bits.npz")
+    for bits in (1, 8, 10, 12, 13, 14, 16):
+        v, w = z[f"vals_{bits}"], z[f"words_{bits}"]
+        got = orc.pack_bits(v, bits)
+        assert got.dtype == np.int32 and got.shape == w.shape
+        assert np.array_equal(got, w)
+        assert np.array_equal(orc.unpack_bits(w, bits, v.shape[1]), v)
+
+
+def test_bit_layout_known_answers():
+    z = np.load(G / "bits.npz")
+    # value 1 at index 0 -> bit 0; value 1 at index 1 with 10-bit tags -> bit 10
+    assert np.array_equal(orc.pack_bits(z["kat_a_vals"], 10), z["kat_a_words"])
+    assert int(orc.pack_bits(z["kat_a_vals"], 10)[0, 0]) == (1 | (1 << 10))
+    # a tag straddling the word boundary: index 3 occupies stream bits 30..39
+    w = orc.pack_bits(z["kat_b_vals"], 10).view(np.uint32)
+    assert np.array_equal(w.view(np.int32), z["kat_b_words"])
+    assert int(w[0, 0]) == 0b11 << 30 and int(w[0, 1]) == 0b11111111
+
+
+def test_pack_rejects_out_of_range():
+    with pytest.raises(ValueError):
+        orc.pack_bits(np.array([[4096]]), 12)
+
+
+def test_seeded_column_orders_and_crc():
+    z = np.load(G / "perms.npz")
+    for C, M, seed in z["cases"]:
+        p = orc.seeded_perms(int(C), int(M), int(seed))
+        assert p.shape == (M, C) and np.array_equal(p[0], np.arange(C))
+        assert orc.perm_crc(p) == int(z[f"crc_{C}_{M}_{seed}"][0])
+        if C <= 896:
+            assert np.array_equal(p, z[f"perms_{C}_{M}_{seed}"])
+        else:
+            assert np.array_equal(p[1], z[f"perms_{C}_{M}_{seed}_row1"])
+            assert np.array_equal(p[-1], z[f"perms_{C}_{M}_{seed}_rowlast"])
+
+
+def test_decode_tensors_is_bit_exact_over_the_format_grid():
+    z = np.load(G / "decode.npz")
+    for i, (Gb, M, K, d) in enumerate(z["grid"]):
+        seed, R, C = (int(v) for v in z[f"seed_{i}"])
+        bits = int(K).bit_length() - 1
+        tags = orc.unpack_bits(z[f"words_{i}"], bits, C // int(d))
+        rb = z[f"rb_{i}"] if f"rb_{i}" in z else None
+        rm = z[f"rm_{i}"] if f"rm_{i}" in z else None
+        perms = orc.seeded_perms(C, int(M), seed)
+        w = orc.decode_tensors(tags, z[f"table_{i}"], z[f"rs_{i}"], rb, rm, perms, int(K))
+        assert w.dtype == np.float32
+        assert np.array_equal(w, z[f"w_{i}"]), f"case {i}: G={Gb} M={M} K={K} d={d}"
+
+
+def test_codebook_decode_with_padding_and_permutation():
+    z = np.load(G / "codebook.npz")
+    pad, cols = (int(v) for v in z["pad"])
+    w = orc.codebook_decode(z["idx"], z["codebook"], z["row_scale"], pad, cols, z["perm"])
+    assert w.shape == (16, 100) and np.array_equal(w, z["decoded"])
+
+
+def test_assign_matches_reference():
+    z = np.load(G / "codebook.npz")
+    idx, err = orc.assign(z["assign_x"], z["assign_book"])
+    assert np.array_equal(idx, z["assign_idx"])
+    assert np.allclose(err, z["assign_err"], rtol=1e-5, atol=1e-6)
+
+
+def test_additive_two_book_decode_is_bit_exact():
+    z = np.load(G / "additive.npz")
+    w = orc.additive_decode(z["A"], z["B"], z["ta"], z["tb"], z["rs"])
+    assert np.array_equal(w, z["dense"])
+
+
+def test_linear_reference_product_and_stored_bytes():
+    z = np.load(G / "linear.npz")
+    R, C, K, d, M = 48, 896, 4096, 8, 16
+    tags = orc.unpack_bits(z["words"], 12, C // d)
+    w = orc.decode_tensors(tags, z["table"], z["rs"], None, z["rm"], orc.seeded_perms(C, M, 1), K)
+    assert float(w.astype(np.float64).sum()) == float(z["dense_sum"][0])
+    y = orc.linear_ref(z["x"], w)
+    assert orc.max_rel_err(y, z["y"]) < 1e-6
+    stored = z["words"].nbytes + z["table"].nbytes + z["rs"].nbytes
+    assert stored == int(z["stored_bytes"][0])
+
+
+def test_synth_matrix_round_trip():
+    m = orc.synth_matrix(20, 128, seed=3, M=4)
+    assert np.array_equal(orc.unpack_bits(m["words"][0], 12, 16), m["tags"][0])
+    w = orc.synth_decode(m)
+    assert w.shape == (20, 128) and np.isfinite(w).all()
+    t = __import__("torch")
+    y = orc.cpu_linear_torch(t.from_numpy(m["words"][0]), t.from_numpy(m["table"][0]), t.from_numpy(m["row_scale"]),
+                             t.ones(1, 128), 12, 8).numpy()
+    m1 = orc.synth_matrix(20, 128, seed=3, M=1)
+    assert np.allclose(y[0], orc.synth_decode(m1).sum(1), rtol=1e-5, atol=1e-6)
