@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Benchmark of the codebook-linear decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+
+Workload (N = 1): the Qwen2.5-7B-shaped decode GEMV set at batch 1 - 28 layers x {q 3584x3584,
+k/v 512x3584, o 3584x3584, gate/up 18944x3584, down 3584x18944} = 196 matrices, each with its own
+4096 x 8 fp16 codebook, 12-bit packed tags and fp16 row scales; synthetic random tags/books (seeded),
+x ~ N(0,1) bf16. One step = y = W x for all 196 matrices (1.24 GB of packed weights, far larger
+than L2, so every step streams from HBM). The metric is achieved HBM GB/s on the algorithmic bytes
+(packed tags + codebooks + row scales + activations in/out).
+
+With N > 1 every matrix is tensor-parallel sharded (q/k/v/gate/up by rows, o/down by columns with
+an NCCL all-reduce of the partial outputs) and the same total set is processed by the N ranks
+("strong" scaling).
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# Qwen2.5-7B block linears: (name, R, C, kind) kind: "col" = split rows under TP, "row" = split columns
+SHAPES_7B = [("q", 3584, 3584, "col"), ("k", 512, 3584, "col"), ("v", 512, 3584, "col"), ("o", 3584, 3584, "row"),
+             ("gate", 18944, 3584, "col"), ("up", 18944, 3584, "col"), ("down", 3584, 18944, "row")]
+LAYERS_7B = 28
+METRIC = "codebook_gemv_hbm_gbs_batch1"
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM bytes per launch of the batch-1 kernel on the 18944 x 3584 shape from one ncu capture
+# (profiles/gemv_l8_gate_7b.md: dram__bytes_read.sum + dram__bytes_write.sum), and the algorithmic
+# bytes of that launch; traffic of other launches is scaled by their algorithmic bytes.
+NCU_TRAFFIC_GATE = (12_939_008 + 0, 12_833_792 + 3584 * 2 + 18944 * 2)
+
+
+def measured_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def algorithmic_bytes(R: int, C: int, B: int = 1) -> int:
+    W = (C // 8 * 12 + 31) // 32
+    return R * W * 4 + 4096 * 8 * 2 + R * 2 + B * C * 2 + B * R * 2
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self._stop_evt = index, [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def stop(self) -> dict:
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ----------------------------------------------------------------------------------------- reference arm
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference's CPU execution of the path (unpack + decode + fp32 matmul in CPU torch, all host
+    threads), on a bounded sample of the same workload: one matrix per distinct shape per step, scaled
+    to the full set by the shape counts."""
+    if rank != 0:
+        return
+    from oracle import cbl_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    g = torch.Generator().manual_seed(0)
+    sample = []
+    for name, R, C, _ in SHAPES_7B:
+        if name in ("v", "o", "up"):
+            continue                      # same shapes as k, q, gate
+        Rs = min(R, 2048)                 # bounded sample: at most 2048 rows of each shape
+        W = (C // 8 * 12 + 31) // 32
+        words = torch.randint(-2**31, 2**31 - 1, (Rs, W), dtype=torch.int32, generator=g)
+        table = torch.randn(4096, 8, generator=g).half()
+        rs = (torch.rand(Rs, generator=g) * 0.02 + 0.01).half()
+        x = torch.randn(1, C, generator=g).bfloat16()
+        count = {"q": 2, "k": 2, "gate": 2, "down": 1}[name] * LAYERS_7B
+        sample.append((words, table, rs, x, R, C, Rs, count))
+
+    def step() -> float:
+        """Seconds the full 196-matrix set would take, extrapolated from the sampled rows."""
+        total = 0.0
+        for words, table, rs, x, R, C, Rs, count in sample:
+            t0 = time.perf_counter()
+            orc.cpu_linear_torch(words, table, rs, x, 12, 8)
+            total += (time.perf_counter() - t0) * (R / Rs) * count
+        return total
+
+    for _ in range(args.warmup):
+        step()
+    ts = [step() for _ in range(args.steps)]
+    t = sum(ts) / len(ts)
+    total_bytes = sum(algorithmic_bytes(R, C) for _, R, C, _ in SHAPES_7B) * LAYERS_7B
+    val = total_bytes / t / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen2.5-7b decode GEMV set (196 codebook matrices), batch 1", "timing": "host wall clock"},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                             "sample": "<=2048 rows of one matrix per distinct shape (q, k, gate, down) per step, scaled by rows and counts"},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------- our arm
+def build_set(dev, rank: int, world: int, batch: int):
+    """The rank's share of the 196 matrices as PackedLinear objects (random tags generated on the device)."""
+    from quantexperiments_b200.linear import PackedLinear
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    lins, kinds, total_bytes = [], [], 0
+    for layer in range(LAYERS_7B):
+        for name, R, C, kind in SHAPES_7B:
+            r, c = R, C
+            if world > 1:
+                if kind == "col":
+                    r = max(R // world, 1) if R % world == 0 else R       # k/v at TP 8: 512 / 8 = 64 rows
+                else:
+                    c = C // world
+            W = (c // 8 * 12 + 31) // 32
+            words = torch.randint(-2**31, 2**31 - 1, (r, W), dtype=torch.int32, device=dev, generator=g)
+            table = torch.randn(4096, 8, device=dev, generator=g).half()
+            rs = (torch.rand(r, device=dev, generator=g) * 0.02 + 0.01).half()
+            perms = torch.arange(c, device=dev)[None]
+            lin = PackedLinear(words, table, rs, None, None, perms, 4096, 8)
+            lin.l8 if (batch == 1 and lin.use_l8()) else lin.t16.xp_buffer(batch)
+            lins.append(lin)
+            kinds.append(kind)
+            total_bytes += algorithmic_bytes(r, c, batch)
+    return lins, kinds, total_bytes
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> None:
+    import torch.distributed as dist
+    from quantexperiments_b200 import kernels  # noqa: F401  (fails loudly if libcbl.so is missing)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B = args.batch
+    lins, kinds, rank_bytes = build_set(dev, rank, world, B)
+    g = torch.Generator(device=dev).manual_seed(7)
+    xs = {c: torch.randn(B, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
+    ys = {r: torch.empty(B, r, device=dev, dtype=torch.bfloat16) for r in {l.R for l in lins}}
+
+    def launch(lin, x, y):
+        if B == 1:
+            lin.gemv(x[0], y[0])
+        else:
+            lin.t16.run(x, y, B)
+
+    def step_kernels():
+        for lin, kind in zip(lins, kinds):
+            y = ys[lin.R]
+            launch(lin, xs[lin.C], y)
+            if world > 1 and kind == "row":
+                dist.all_reduce(y)
+
+    launches_per_step = sum(1 if (B == 1 and lin.use_l8()) else 2 for lin in lins)
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        step_kernels()
+        stream.synchronize()
+        graph = None
+        if world == 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_kernels()
+        run = graph.replay if graph is not None else step_kernels
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
+        for _ in range(max(args.warmup, 3)):
+            run()
+        barrier()
+        sampler = ClockSampler(physical_gpu_index(local_rank))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+
+        # dominant kernel alone: the batch-1 table-lookup kernel over its matrices, timed with events
+        roof = None
+        if world == 1 and B == 1:
+            big = [lin for lin in lins if lin.use_l8()]
+            gk = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gk, stream=stream):
+                for lin in big:
+                    lin.gemv(xs[lin.C][0], ys[lin.R][0])
+            for _ in range(3):
+                gk.replay()
+            torch.cuda.synchronize(dev)
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for _ in range(args.steps):
+                gk.replay()
+            k1.record(stream)
+            torch.cuda.synchronize(dev)
+            per_launch_s = k0.elapsed_time(k1) * 1e-3 / (args.steps * len(big))
+            alg = sum(algorithmic_bytes(lin.R, lin.C) for lin in big) / len(big)
+            peak, src = measured_peak()
+            achieved = alg / per_launch_s / 1e9
+            roof = {"bound": "hbm", "kernel": "k_gemv_l8", "achieved": achieved, "peak": peak, "peak_source": src, "unit": "GB/s",
+                    "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
+                    "traffic": alg * NCU_TRAFFIC_GATE[0] / NCU_TRAFFIC_GATE[1], "algorithmic_bytes_per_launch": alg,
+                    "us_per_launch": per_launch_s * 1e6, "launches_timed": args.steps * len(big)}
+
+        # end to end through the public call with HOST buffers: pinned x -> device, products, y -> host
+        hx = {c: torch.randn(B, c).bfloat16().pin_memory() for c in xs}
+        hy = {r: torch.empty(B, r, dtype=torch.bfloat16).pin_memory() for r in ys}
+        h2d = sum(B * lin.C * 2 for lin in lins)
+        d2h = sum(B * lin.R * 2 for lin in lins)
+
+        def step_e2e():
+            for lin, kind in zip(lins, kinds):
+                x, y = xs[lin.C], ys[lin.R]
+                x.copy_(hx[lin.C], non_blocking=True)
+                launch(lin, x, y)
+                if world > 1 and kind == "row":
+                    dist.all_reduce(y)
+                hy[lin.R].copy_(y, non_blocking=True)
+            stream.synchronize()
+
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(args.steps):
+            step_e2e()
+        t1.record(stream)
+        barrier()
+        ms_e2e = t0.elapsed_time(t1)
+
+    # max over ranks, whole-job bytes
+    tv = torch.tensor([ms, ms_e2e, float(rank_bytes)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax = tv.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = tv.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, ms_e2e, total_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        total_bytes = float(rank_bytes)
+    if rank != 0:
+        return
+    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    line = {"metric": METRIC if B == 1 else f"codebook_gemv_hbm_gbs_batch{B}", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b decode GEMV set (196 codebook matrices, d=8, K=4096, 12-bit tags), batch {B}",
+                       "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 (1.24 GB of packed weights per step)",
+                       "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step" if world == 1 else "eager + NCCL all-reduce"},
+            "clocks": clocks, "gpu_launches": launches_per_step * args.steps * world,
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                    "ms_per_step": ms_e2e / args.steps}}
+    if roof is not None:
+        line["roofline"] = roof
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline_sample()
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_sample() -> dict:
+    """The reference's CPU path (oracle port) timed on this host's cores on a bounded sample."""
+    from oracle import cbl_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(0)
+    t_total = 0.0
+    for name, R, C, count in (("q", 3584, 3584, 2), ("k", 512, 3584, 2), ("gate", 18944, 3584, 2), ("down", 3584, 18944, 1)):
+        Rs = min(R, 1024)
+        W = (C // 8 * 12 + 31) // 32
+        words = torch.randint(-2**31, 2**31 - 1, (Rs, W), dtype=torch.int32, generator=g)
+        table = torch.randn(4096, 8, generator=g).half()
+        rs = (torch.rand(Rs, generator=g) * 0.02 + 0.01).half()
+        x = torch.randn(1, C, generator=g).bfloat16()
+        orc.cpu_linear_torch(words[:64], table, rs[:64], x, 12, 8)
+        t0 = time.perf_counter()
+        orc.cpu_linear_torch(words, table, rs, x, 12, 8)
+        t_total += (time.perf_counter() - t0) * (R / Rs) * count * LAYERS_7B
+    total_bytes = sum(algorithmic_bytes(R, C) for _, R, C, _ in SHAPES_7B) * LAYERS_7B
+    return {"value": total_bytes / t_total / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "1024 rows of one matrix per distinct shape (q, k, gate, down), scaled by rows and counts to the 196-matrix set"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+/*
+ * cbl.h - C ABI of libcbl: the codebook-linear hot path on B200 (sm_100a).
+ *
+ * The library executes one storage format: an [R, C] weight matrix cut into chunks of d values
+ * along the input dimension, every chunk replaced by a log2(K)-bit tag into a table of fp16
+ * codewords, an fp16 scale per row, optionally a second summed table ("additive" books) and
+ * per-row seeded column orders.  The format is the one defined by the reference project
+ * angryslavemerchant/QuantExperiments in shapequant/packed.py:1-27.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless a comment says otherwise; plain C types only;
+ *   - every function returns an int status: CBL_OK or a negative cbl_status; nothing throws,
+ *     traps or aborts, and nothing allocates or frees device memory: the caller owns all
+ *     buffers and passes work space explicitly (sizes come from the *_bytes() queries);
+ *   - work is enqueued on the CUDA stream given (a cudaStream_t cast to cbl_stream); functions
+ *     return after the launch, they do not synchronise;
+ *   - a reference citation "replaces file:line" names the reference function whose role the
+ *     entry point takes (paths are inside the reference repository).
+ */
+#ifndef CBL_H
+#define CBL_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* cbl_stream;
+
+typedef enum cbl_status {
+    CBL_OK = 0,
+    CBL_EINVAL = -1,        /* bad argument (null pointer, negative size, misaligned buffer) */
+    CBL_EUNSUPPORTED = -2,  /* a shape or format variant this kernel does not execute */
+    CBL_ECUDA = -3,         /* a CUDA runtime call failed; cbl_last_cuda_error() has the code */
+    CBL_ETIMEOUT = -4       /* a bounded device-side wait expired (reported by status words) */
+} cbl_status;
+
+typedef enum cbl_dtype { CBL_F32 = 0, CBL_F16 = 1, CBL_BF16 = 2 } cbl_dtype;
+
+/* Library version (major*10000 + minor*100 + patch) and the SM architecture it was built for. */
+int cbl_version(void);
+int cbl_built_for_sm(void);
+const char* cbl_status_string(int status);
+int cbl_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * The file layout (device copy of the tensors of one matrix, shapequant/packed.py:8-16):
+ *   tags      int32 [R, W]    little-endian bit stream of `bits`-bit tags per row, W words
+ *   table     fp16  [G*K, d]  codewords
+ *   row_scale fp16  [R]
+ *   row_book  uint8 [R]       codebook of each row, or NULL when G == 1
+ *   row_mask  uint8 [R]       column order of each row, or NULL when M == 1
+ *   perms     int32 [M, C]    the column orders (regenerated from the seed on the host), or NULL
+ * books == 2 adds a second tag plane and table whose codewords are summed with the first
+ * (tests/test_proto_runs.py:135-144 of the reference); G must be 1 in that case.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct cbl_packed {
+    int32_t R, C, d, bits, G, M, books, W;
+    const int32_t* tags;
+    const int32_t* tags2;
+    const void* table;
+    const void* table2;
+    const void* row_scale;
+    const uint8_t* row_book;
+    const uint8_t* row_mask;
+    const int32_t* perms;
+} cbl_packed;
+
+/* Dense decode of rows [r0, r1) into out[(r - r0) * ld + c], c in the original column order:
+ *   u = fp32(table[row_book[r]*K + tag]) (+ fp32(table2[tag2]))   rounded to fp32
+ *   w[r, perms[row_mask[r]][j*d + i]] = round_to(dtype, u * fp32(row_scale[r]))
+ * Bit-exact with the reference decode for f32 and one round-to-nearest of it for f16 / bf16.
+ * Any d in 1..16, bits in 1..16.
+ * replaces shapequant/packed.py:259-270 (decode_tensors), shapequant/codebook.py:277-289 (decode),
+ *          shapequant/kernels/cuda_dequant.py:79-103 (dequant, incl. its rows=(r0, r1) range),
+ *          shapequant/kernels/batched_runs.py:935-961 (dequant_tile, fp16 / bf16 output). */
+int cbl_dequant(const cbl_packed* m, void* out, int dtype, int64_t ld, int32_t r0, int32_t r1, cbl_stream s);
+
+/* Unpacked tags of plane `plane` (0 or 1) as int32 [R, C/d].
+ * replaces shapequant/packed.py:80-90 (unpack_bits) / :246-248 (PackedFile.local_tags). */
+int cbl_unpack_tags(const cbl_packed* m, int plane, int32_t* out, cbl_stream s);
+
+/* ------------------------------------------------------------------------------------------
+ * Row-tile layout ("t16") for the small-batch product: rows are grouped by column order into
+ * tiles of 16 (tile_rows[tile*16 + i] = source row or -1), tags re-ordered so that every lane of
+ * a warp reads its own tags with 128-bit loads.  d = 8, bits = 12, G = 1 only.
+ * replaces shapequant/kernels/batched_runs.py:643-677 (tile_words) and
+ *          shapequant/kernels/proto_runs.py:322-336, 380-388 (pack_lane_major, make_tiles).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct cbl_t16 {
+    int32_t R, C, books, M, ntile, nsuper;
+    const void* words;         /* uint4 [books][ntile][nsuper][3][32] */
+    const int32_t* tile_rows;  /* [ntile * 16], -1 = padding row */
+    const int32_t* tile_mask;  /* [ntile] column order of the tile, NULL when M == 1 */
+    const void* table;         /* fp16 [4096, 8] */
+    const void* table2;        /* fp16 [4096, 8] when books == 2 */
+    const void* row_scale;     /* fp16 [R], indexed by source row */
+} cbl_t16;
+
+size_t cbl_t16_bytes(int32_t ntile, int32_t C, int32_t books);
+int cbl_repack_t16(const cbl_packed* m, const int32_t* tile_rows, int32_t ntile, void* out, cbl_stream s);
+
+/* Activations for cbl_gemv_t16: x [B, C] (row stride ldx, f16 or bf16) -> xp fp16
+ * [M][Bpad][Cpad] with xp[m][b][c] = x[b][perms[m][c]], zero padded (Bpad = B rounded up to 8,
+ * Cpad = C rounded up to 512).
+ * replaces shapequant/kernels/proto_runs.py:500-502 (prep_x). */
+size_t cbl_prep_x_bytes(int32_t B, int32_t C, int32_t M);
+int cbl_prep_x(const void* x, int xdtype, int32_t B, int32_t C, int64_t ldx, const int32_t* perms, int32_t M,
+               void* xp, cbl_stream s);
+
+/* y[b*ldy + r] = round_to(ydtype, row_scale[r] * sum_c W[r, c] * x[b, c]) for b < B <= 64,
+ * tensor-core (mma.sync) product with fp32 accumulation straight from the packed tags.
+ * replaces shapequant/kernels/batched_runs.py:745-771 (RunsBatch.run) and, for B = 1 with column
+ *          orders or two books, shapequant/kernels/proto_runs.py:412-473, 505-571 (gemv_additive, gemv). */
+int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y, int ydtype, int64_t ldy, cbl_stream s);
+
+/* ------------------------------------------------------------------------------------------
+ * Column-tile layout ("l8") for the batch-1 product by activation-side tables: per tile of 8
+ * chunk columns the kernel computes T[c][e] = <table[e], x_chunk_c> once (tensor cores) into
+ * shared memory and every weight chunk becomes one 4-byte table read and one add.
+ * d = 8, bits = 12, G = 1, M = 1; books = 2 is stored as a second run of tiles.
+ * replaces shapequant/kernels/gemv.py:142-162 (PackedLinear.gemv) and
+ *          shapequant/kernels/proto_runs.py:505-571 (gemv) for batch 1.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct cbl_l8 {
+    int32_t R, C, books, ntile, Rpad;   /* ntile counts both books' tiles; Rpad = R rounded up to 4 */
+    const void* words;                  /* uint32 [ntile][3][Rpad] */
+    const void* table;
+    const void* table2;
+    const void* row_scale;
+} cbl_l8;
+
+size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books);
+int cbl_repack_l8(const cbl_packed* m, void* out, cbl_stream s);
+
+/* Work space of cbl_gemv_l8: fp32 row accumulators and arrival counters.  It must be zero before
+ * the first call; every call leaves it zero again.  Calls that share a work space must not
+ * overlap on the device. */
+size_t cbl_gemv_l8_workspace_bytes(int32_t R);
+int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CBL_H */

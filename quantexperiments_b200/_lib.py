@@ -1,0 +1,87 @@
+"""ctypes binding of libcbl.so (the C ABI declared in include/cbl.h).
+
+There is no fallback: if the shared object is missing or lacks a symbol, importing this module
+raises. Build it with `python -m quantexperiments_b200.build`."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcbl.so"
+
+OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT = 0, -1, -2, -3, -4
+F32, F16, BF16 = 0, 1, 2
+
+
+class CblError(RuntimeError):
+    """A libcbl entry point returned a negative status."""
+
+    def __init__(self, fn: str, status: int, detail: str):
+        super().__init__(f"{fn}: {detail} (status {status})")
+        self.status = status
+
+
+class Packed(Structure):
+    """struct cbl_packed: the file layout of one matrix, device pointers."""
+    _fields_ = [("R", c_int32), ("C", c_int32), ("d", c_int32), ("bits", c_int32), ("G", c_int32), ("M", c_int32),
+                ("books", c_int32), ("W", c_int32), ("tags", c_void_p), ("tags2", c_void_p), ("table", c_void_p),
+                ("table2", c_void_p), ("row_scale", c_void_p), ("row_book", c_void_p), ("row_mask", c_void_p),
+                ("perms", c_void_p)]
+
+
+class T16(Structure):
+    """struct cbl_t16: row-tile layout for the small-batch product."""
+    _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("M", c_int32), ("ntile", c_int32),
+                ("nsuper", c_int32), ("words", c_void_p), ("tile_rows", c_void_p), ("tile_mask", c_void_p),
+                ("table", c_void_p), ("table2", c_void_p), ("row_scale", c_void_p)]
+
+
+class L8(Structure):
+    """struct cbl_l8: column-tile layout for the batch-1 product."""
+    _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("ntile", c_int32), ("Rpad", c_int32),
+                ("words", c_void_p), ("table", c_void_p), ("table2", c_void_p), ("row_scale", c_void_p)]
+
+
+# name -> (restype, argtypes); every symbol include/cbl.h declares
+SIGNATURES = {
+    "cbl_version": (c_int, []),
+    "cbl_built_for_sm": (c_int, []),
+    "cbl_status_string": (c_char_p, [c_int]),
+    "cbl_last_cuda_error": (c_int, []),
+    "cbl_dequant": (c_int, [POINTER(Packed), c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p]),
+    "cbl_unpack_tags": (c_int, [POINTER(Packed), c_int, c_void_p, c_void_p]),
+    "cbl_t16_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_repack_t16": (c_int, [POINTER(Packed), c_void_p, c_int32, c_void_p, c_void_p]),
+    "cbl_prep_x_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_prep_x": (c_int, [c_void_p, c_int, c_int32, c_int32, c_int64, c_void_p, c_int32, c_void_p, c_void_p]),
+    "cbl_gemv_t16": (c_int, [POINTER(T16), c_void_p, c_int32, c_void_p, c_int, c_int64, c_void_p]),
+    "cbl_l8_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_repack_l8": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
+    "cbl_gemv_l8_workspace_bytes": (c_size_t, [c_int32]),
+    "cbl_gemv_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+}
+
+
+def _load() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(f"{LIB_PATH} is missing: run `python -m quantexperiments_b200.build` "
+                          "(there is no CPU or PyTorch fallback for these kernels)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the library lacks a declared symbol
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+
+
+def check(fn: str, status: int) -> None:
+    if status == OK:
+        return
+    detail = lib.cbl_status_string(status).decode()
+    if status == ECUDA:
+        detail += f" (cudaError {lib.cbl_last_cuda_error()})"
+    raise CblError(fn, status, detail)

@@ -1,0 +1,264 @@
+// Dense decode, tag unpacking and the load-time re-layouts (file layout -> kernel layouts).
+#include "cbl_common.cuh"
+
+int g_cbl_last_cuda_error = 0;
+
+extern "C" int cbl_version(void) { return 100; }
+extern "C" int cbl_built_for_sm(void) { return 100; }
+extern "C" int cbl_last_cuda_error(void) { return g_cbl_last_cuda_error; }
+extern "C" const char* cbl_status_string(int status) {
+    switch (status) {
+        case CBL_OK: return "ok";
+        case CBL_EINVAL: return "invalid argument";
+        case CBL_EUNSUPPORTED: return "unsupported shape or format variant";
+        case CBL_ECUDA: return "CUDA runtime error";
+        case CBL_ETIMEOUT: return "bounded device-side wait expired";
+        default: return "unknown status";
+    }
+}
+
+int cbl_sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int check_packed(const cbl_packed* m) {
+    if (!m || !m->tags || !m->table || !m->row_scale) return CBL_EINVAL;
+    if (m->R < 0 || m->C <= 0 || m->d < 1 || m->d > 16 || m->bits < 1 || m->bits > 16) return CBL_EINVAL;
+    if (m->C % m->d) return CBL_EINVAL;
+    if (m->G < 1 || m->M < 1 || (m->books != 1 && m->books != 2)) return CBL_EINVAL;
+    if ((int64_t)m->W * 32 < (int64_t)(m->C / m->d) * m->bits) return CBL_EINVAL;
+    if (m->books == 2 && (!m->tags2 || !m->table2 || m->G != 1)) return CBL_EINVAL;
+    if (m->G > 1 && !m->row_book) return CBL_EINVAL;
+    if (m->M > 1 && (!m->row_mask || !m->perms)) return CBL_EINVAL;
+    return CBL_OK;
+}
+
+// ------------------------------------------------------------------------------------ dense decode
+//
+// One thread per chunk.  u = fp32(cw) [+ fp32(cw2)] rounded, then u * fp32(row_scale) rounded, then
+// one rounding to the output type: the order of shapequant/packed.py:266 and masks.py:193-200.
+template <typename OutT, int D, bool VEC>
+__global__ void __launch_bounds__(256) k_dequant(cbl_packed m, OutT* __restrict__ out, int64_t ld, int r0, int64_t nchunks_total) {
+    int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= nchunks_total) return;
+    const int d = (D > 0) ? D : m.d;
+    const int nch = m.C / d;
+    int rr = (int)(gi / nch);
+    int j = (int)(gi - (int64_t)rr * nch);
+    int r = r0 + rr;
+    const uint32_t K = 1u << m.bits;
+    uint32_t tag = cbl_read_tag(m.tags + (int64_t)r * m.W, m.W, j, m.bits);
+    if (m.row_book) tag += (uint32_t)m.row_book[r] * K;
+    const __half* cw = (const __half*)m.table + (int64_t)tag * d;
+    const __half* cw2 = nullptr;
+    if (m.books == 2) cw2 = (const __half*)m.table2 + (int64_t)cbl_read_tag(m.tags2 + (int64_t)r * m.W, m.W, j, m.bits) * d;
+    const float rs = __half2float(((const __half*)m.row_scale)[r]);
+    const int32_t* perm = (m.M > 1) ? m.perms + (int64_t)m.row_mask[r] * m.C : nullptr;
+    OutT* orow = out + (int64_t)rr * ld;
+    if (VEC && D == 8) {
+        // M == 1, 8 values per chunk: one 16-byte table read, contiguous aligned stores
+        uint4 q = __ldg((const uint4*)cw);
+        const __half2* h = (const __half2*)&q;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+        if (cw2) {
+            uint4 q2 = __ldg((const uint4*)cw2);
+            const __half2* h2 = (const __half2*)&q2;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 f = __half22float2(h2[i]);
+                v[2 * i] = __fadd_rn(v[2 * i], f.x);
+                v[2 * i + 1] = __fadd_rn(v[2 * i + 1], f.y);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(v[i], rs);
+        OutT* o = orow + j * 8;
+        if (sizeof(OutT) == 4) {
+            float4* o4 = (float4*)o;
+            o4[0] = make_float4(v[0], v[1], v[2], v[3]);
+            o4[1] = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+            union { uint4 u; OutT t[8]; } pk;
+#pragma unroll
+            for (int i = 0; i < 8; i++) pk.t[i] = cbl_cvt_out<OutT>(v[i]);
+            *(uint4*)o = pk.u;
+        }
+    } else {
+        for (int i = 0; i < d; i++) {
+            float u = __half2float(cw[i]);
+            if (cw2) u = __fadd_rn(u, __half2float(cw2[i]));
+            u = __fmul_rn(u, rs);
+            int c = j * d + i;
+            if (perm) c = perm[c];
+            orow[c] = cbl_cvt_out<OutT>(u);
+        }
+    }
+}
+
+template <typename OutT>
+static int launch_dequant(const cbl_packed* m, void* out, int64_t ld, int r0, int r1, cudaStream_t st) {
+    int64_t n = (int64_t)(r1 - r0) * (m->C / m->d);
+    if (n == 0) return CBL_OK;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return CBL_EUNSUPPORTED;
+    bool vec = m->M == 1 && m->d == 8 && (ld % 8 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)m->table % 16 == 0) &&
+               (m->books == 1 || (uintptr_t)m->table2 % 16 == 0);
+    if (vec) k_dequant<OutT, 8, true><<<(unsigned)blocks, 256, 0, st>>>(*m, (OutT*)out, ld, r0, n);
+    else k_dequant<OutT, 0, false><<<(unsigned)blocks, 256, 0, st>>>(*m, (OutT*)out, ld, r0, n);
+    return cbl_check_launch();
+}
+
+extern "C" int cbl_dequant(const cbl_packed* m, void* out, int dtype, int64_t ld, int32_t r0, int32_t r1, cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (r0 < 0 || r1 < r0 || r1 > m->R || ld < m->C) return CBL_EINVAL;
+    if (r0 == r1) return CBL_OK;
+    if (!out) return CBL_EINVAL;
+    cudaStream_t st = (cudaStream_t)s;
+    switch (dtype) {
+        case CBL_F32: return launch_dequant<float>(m, out, ld, r0, r1, st);
+        case CBL_F16: return launch_dequant<__half>(m, out, ld, r0, r1, st);
+        case CBL_BF16: return launch_dequant<__nv_bfloat16>(m, out, ld, r0, r1, st);
+        default: return CBL_EINVAL;
+    }
+}
+
+// ------------------------------------------------------------------------------------ tags
+__global__ void __launch_bounds__(256) k_unpack(cbl_packed m, const int32_t* __restrict__ words, int32_t* __restrict__ out, int64_t n) {
+    int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= n) return;
+    int nch = m.C / m.d;
+    int r = (int)(gi / nch), j = (int)(gi - (int64_t)r * nch);
+    out[gi] = (int32_t)cbl_read_tag(words + (int64_t)r * m.W, m.W, j, m.bits);
+}
+
+extern "C" int cbl_unpack_tags(const cbl_packed* m, int plane, int32_t* out, cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (!out || plane < 0 || plane >= m->books) return CBL_EINVAL;
+    int64_t n = (int64_t)m->R * (m->C / m->d);
+    if (n == 0) return CBL_OK;
+    k_unpack<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)s>>>(*m, plane ? m->tags2 : m->tags, out, n);
+    return cbl_check_launch();
+}
+
+// ------------------------------------------------------------------------------------ t16 layout
+//
+// Lane (g = lane >> 2, t = lane & 3) of the warp that owns a 16-row tile multiplies rows g and
+// g + 8; in step s of a super-step it takes chunk column (ss*16 + s)*4 + t.  Its 32 tags of one
+// super-step (i = 2*s + h, h = 0: row g, h = 1: row g + 8) form a 384-bit little-endian stream
+// stored as three uint4 at [book][tile][ss][q][lane].
+static int t16_nsuper(int C) { return cbl_ceil_div(C / 8, 64); }
+
+extern "C" size_t cbl_t16_bytes(int32_t ntile, int32_t C, int32_t books) {
+    if (ntile < 0 || C <= 0 || books < 1) return 0;
+    return (size_t)books * ntile * t16_nsuper(C) * 3 * 32 * 16;
+}
+
+__global__ void __launch_bounds__(128) k_repack_t16(cbl_packed m, const int32_t* __restrict__ tile_rows, int ntile, int nsuper,
+                                                    uint4* __restrict__ out, int64_t nthreads) {
+    int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= nthreads) return;
+    int lane = (int)(gi & 31);
+    int64_t rest = gi >> 5;
+    int ss = (int)(rest % nsuper);
+    rest /= nsuper;
+    int tile = (int)(rest % ntile);
+    int book = (int)(rest / ntile);
+    int g = lane >> 2, t = lane & 3;
+    const int nch = m.C / 8;
+    const int32_t* words = book ? m.tags2 : m.tags;
+    int rows[2] = {tile_rows[tile * 16 + g], tile_rows[tile * 16 + g + 8]};
+    uint32_t w[13];
+#pragma unroll
+    for (int i = 0; i < 13; i++) w[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        int sidx = i >> 1, h = i & 1;
+        int chunk = (ss * 16 + sidx) * 4 + t;
+        uint32_t tag = 0;
+        if (rows[h] >= 0 && chunk < nch) tag = cbl_read_tag(words + (int64_t)rows[h] * m.W, m.W, chunk, 12);
+        int bit = 12 * i;
+        w[bit >> 5] |= tag << (bit & 31);
+        if ((bit & 31) > 20) w[(bit >> 5) + 1] |= tag >> (32 - (bit & 31));
+    }
+    uint4* o = out + (((int64_t)book * ntile + tile) * nsuper + ss) * 96 + lane;
+    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[32] = make_uint4(w[4], w[5], w[6], w[7]);
+    o[64] = make_uint4(w[8], w[9], w[10], w[11]);
+}
+
+extern "C" int cbl_repack_t16(const cbl_packed* m, const int32_t* tile_rows, int32_t ntile, void* out, cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (m->d != 8 || m->bits != 12 || m->G != 1) return CBL_EUNSUPPORTED;
+    if (!tile_rows || !out || ntile < 0 || ((uintptr_t)out % 16)) return CBL_EINVAL;
+    int nsuper = t16_nsuper(m->C);
+    int64_t n = (int64_t)m->books * ntile * nsuper * 32;
+    if (n == 0) return CBL_OK;
+    k_repack_t16<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)s>>>(*m, tile_rows, ntile, nsuper, (uint4*)out, n);
+    return cbl_check_launch();
+}
+
+// ------------------------------------------------------------------------------------ l8 layout
+//
+// Tile v covers chunk columns 8*(v % ntile1) .. +7 of book v / ntile1.  Row r's 8 tags of the tile
+// form a 96-bit little-endian stream; word k of that stream is stored at [v][k][r], so that four
+// consecutive rows' k-th words are one aligned 128-bit load.
+extern "C" size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books) {
+    if (R < 0 || C <= 0 || books < 1) return 0;
+    size_t Rpad = ((size_t)R + 3) / 4 * 4;
+    return (size_t)books * cbl_ceil_div(C / 8, 8) * 3 * Rpad * 4;
+}
+
+__global__ void __launch_bounds__(256) k_repack_l8(cbl_packed m, int ntile1, int Rpad, uint32_t* __restrict__ out, int64_t nthreads) {
+    int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= nthreads) return;
+    int r = (int)(gi % Rpad);
+    int v = (int)(gi / Rpad);
+    int book = v / ntile1, tile = v % ntile1;
+    const int nch = m.C / 8;
+    const int32_t* words = book ? m.tags2 : m.tags;
+    uint32_t w[4] = {0, 0, 0, 0};
+    if (r < m.R) {
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            int chunk = tile * 8 + c;
+            uint32_t tag = chunk < nch ? cbl_read_tag(words + (int64_t)r * m.W, m.W, chunk, 12) : 0u;
+            int bit = 12 * c;
+            w[bit >> 5] |= tag << (bit & 31);
+            if ((bit & 31) > 20) w[(bit >> 5) + 1] |= tag >> (32 - (bit & 31));
+        }
+    }
+    uint32_t* o = out + (int64_t)v * 3 * Rpad + r;
+    o[0] = w[0];
+    o[Rpad] = w[1];
+    o[2 * (int64_t)Rpad] = w[2];
+}
+
+extern "C" int cbl_repack_l8(const cbl_packed* m, void* out, cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (m->d != 8 || m->bits != 12 || m->G != 1 || m->M != 1) return CBL_EUNSUPPORTED;
+    if (!out || ((uintptr_t)out % 16)) return CBL_EINVAL;
+    int ntile1 = cbl_ceil_div(m->C / 8, 8);
+    int Rpad = (m->R + 3) / 4 * 4;
+    int64_t n = (int64_t)m->books * ntile1 * Rpad;
+    if (n == 0) return CBL_OK;
+    k_repack_l8<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)s>>>(*m, ntile1, Rpad, (uint32_t*)out, n);
+    return cbl_check_launch();
+}

@@ -1,0 +1,255 @@
+"""Device-side matrices and kernel launchers over libcbl (thin, allocation-aware Python).
+
+DeviceMatrix  the file layout resident on the GPU: dense decode, tag unpacking
+T16Matrix     row-tile re-layout + tensor-core product for batches up to 64 (column orders and
+              two summed books supported)
+L8Matrix      column-tile re-layout + batch-1 product by activation-side tables
+
+All launches go to torch's current CUDA stream; outputs can be caller-provided so that steady-state
+calls allocate nothing (CUDA-graph capturable)."""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import lib
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.dtype) -> int:
+    try:
+        return _DT[t]
+    except KeyError:
+        raise ValueError(f"dtype {t} is not supported (float32, float16, bfloat16)") from None
+
+
+class DeviceMatrix:
+    """One packed matrix in the file layout on a CUDA device (tags int32 [R, W], table fp16
+    [G*K, d], row_scale fp16 [R], optional row_book / row_mask uint8 [R], perms int32 [M, C];
+    optional second tag plane + table for two summed books)."""
+
+    def __init__(self, tags, table, row_scale, row_book=None, row_mask=None, perms=None, *, K: int, d: int,
+                 C: int | None = None, device="cuda", tags2=None, table2=None):
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise ValueError("DeviceMatrix lives on a CUDA device; there is no CPU path")
+        self.device = dev
+        self.K, self.d = int(K), int(d)
+        self.bits = int(math.log2(K))
+        if 1 << self.bits != K:
+            raise ValueError(f"K={K} is not a power of two")
+        self.tags = tags.to(dev, torch.int32).contiguous()
+        dev = self.device = self.tags.device          # normalised ("cuda" -> "cuda:0")
+        self.R, self.W = self.tags.shape
+        self.table = table.to(dev, torch.float16).contiguous()
+        if self.table.shape[1] != d or self.table.shape[0] % K:
+            raise ValueError(f"table shape {tuple(self.table.shape)} does not fit K={K}, d={d}")
+        self.G = self.table.shape[0] // K
+        self.row_scale = row_scale.to(dev, torch.float16).contiguous()
+        self.row_book = None if row_book is None else row_book.to(dev, torch.uint8).contiguous()
+        if self.G > 1 and self.row_book is None:
+            raise ValueError("G > 1 needs row_book")
+        self.M = 1 if (perms is None or row_mask is None) else int(perms.shape[0])
+        self.row_mask = row_mask.to(dev, torch.uint8).contiguous() if self.M > 1 else None
+        self.perms = perms.to(dev, torch.int32).contiguous() if self.M > 1 else None
+        self.C = int(C) if C is not None else (int(perms.shape[1]) if perms is not None else (self.W * 32 // self.bits) * d)
+        if self.C % d or self.W * 32 < (self.C // d) * self.bits:
+            raise ValueError(f"C={self.C} does not fit d={d}, W={self.W}, bits={self.bits}")
+        self.nch = self.C // d
+        self.books = 1 if tags2 is None else 2
+        self.tags2 = None if tags2 is None else tags2.to(dev, torch.int32).contiguous()
+        self.table2 = None if table2 is None else table2.to(dev, torch.float16).contiguous()
+        if self.books == 2 and (self.table2 is None or self.tags2.shape != self.tags.shape or self.G != 1):
+            raise ValueError("two summed books need tags2 and table2 of matching shape and G = 1")
+
+    @classmethod
+    def tags_only(cls, words: torch.Tensor, bits: int, n: int) -> "DeviceMatrix":
+        """A matrix with a dummy one-value table, for unpacking a tag stream."""
+        dev = words.device
+        return cls(words, torch.zeros(1 << bits, 1, dtype=torch.float16, device=dev),
+                   torch.ones(words.shape[0], dtype=torch.float16, device=dev), K=1 << bits, d=1, C=n, device=dev)
+
+    def struct(self) -> _lib.Packed:
+        return _lib.Packed(self.R, self.C, self.d, self.bits, self.G, self.M, self.books, self.W, _ptr(self.tags),
+                           _ptr(self.tags2), _ptr(self.table), _ptr(self.table2), _ptr(self.row_scale),
+                           _ptr(self.row_book), _ptr(self.row_mask), _ptr(self.perms))
+
+    def stored_bytes(self) -> int:
+        """Bytes a product must stream: tags, tables, row scales (the definition of the reference's
+        PackedLinear.stored_bytes, shapequant/kernels/gemv.py:172-175)."""
+        ts = [self.tags, self.table, self.row_scale, self.tags2, self.table2]
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+    def dequant(self, out: torch.Tensor | None = None, dtype: torch.dtype = torch.float32,
+                rows: tuple[int, int] | None = None) -> torch.Tensor:
+        """Dense [r1 - r0, C] decode, bit-exact with the reference decode (fp32) or one rounding of
+        it (fp16 / bf16). `out` may be a larger flat scratch buffer (its first (r1-r0)*C elements are used)."""
+        r0, r1 = rows if rows is not None else (0, self.R)
+        n = (r1 - r0) * self.C
+        if out is None:
+            res = torch.empty(r1 - r0, self.C, dtype=dtype, device=self.device)
+        else:
+            if out.numel() < n or not out.is_contiguous() or out.device != self.device:
+                raise ValueError("out must be a contiguous buffer on the matrix's device with room for the rows")
+            res = out.view(-1)[:n].view(r1 - r0, self.C)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_dequant", lib.cbl_dequant(ctypes.byref(self.struct()), res.data_ptr(), _dt(res.dtype),
+                                                      self.C, r0, r1, _stream()))
+        return res
+
+    def unpack(self, plane: int = 0) -> torch.Tensor:
+        out = torch.empty(self.R, self.nch, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_unpack_tags", lib.cbl_unpack_tags(ctypes.byref(self.struct()), plane, out.data_ptr(), _stream()))
+        return out
+
+
+def _need_fast(dm: DeviceMatrix) -> None:
+    if dm.d != 8 or dm.bits != 12 or dm.G != 1:
+        raise ValueError(f"the product kernels execute d=8, 12-bit tags, one codebook per matrix "
+                         f"(got d={dm.d}, bits={dm.bits}, G={dm.G})")
+
+
+class T16Matrix:
+    """Row-tile layout: rows grouped by column order into tiles of 16; run() multiplies a batch."""
+
+    BMAX = 64
+
+    def __init__(self, dm: DeviceMatrix):
+        _need_fast(dm)
+        self.dm, self.R, self.C, self.M, self.books, self.device = dm, dm.R, dm.C, dm.M, dm.books, dm.device
+        # tiles: rows of one column order, padded with -1 to whole tiles (the reference groups rows
+        # by order the same way, shapequant/kernels/proto_runs.py:380-388)
+        if dm.M > 1:
+            mask = dm.row_mask.cpu().to(torch.int64)
+            rows, tmask = [], []
+            for m in range(dm.M):
+                r = torch.nonzero(mask == m).flatten()
+                if r.numel() == 0:
+                    continue
+                pad = (-r.numel()) % 16
+                rows.append(torch.cat([r, torch.full((pad,), -1, dtype=torch.int64)]))
+                tmask += [m] * ((r.numel() + pad) // 16)
+            tile_rows = torch.cat(rows) if rows else torch.empty(0, dtype=torch.int64)
+            self.tile_mask = torch.tensor(tmask, dtype=torch.int32, device=dm.device)
+        else:
+            pad = (-dm.R) % 16
+            tile_rows = torch.cat([torch.arange(dm.R), torch.full((pad,), -1, dtype=torch.int64)])
+            self.tile_mask = None
+        self.tile_rows = tile_rows.to(torch.int32).to(dm.device).contiguous()
+        self.ntile = self.tile_rows.numel() // 16
+        self.nsuper = -(-dm.nch // 64)
+        nbytes = lib.cbl_t16_bytes(self.ntile, dm.C, dm.books)
+        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        with torch.cuda.device(dm.device):
+            _lib.check("cbl_repack_t16", lib.cbl_repack_t16(ctypes.byref(dm.struct()), self.tile_rows.data_ptr(), self.ntile,
+                                                            self.words.data_ptr(), _stream()))
+        self._xp: dict[int, torch.Tensor] = {}
+
+    def struct(self) -> _lib.T16:
+        dm = self.dm
+        return _lib.T16(self.R, self.C, self.books, self.M, self.ntile, self.nsuper, _ptr(self.words), _ptr(self.tile_rows),
+                        _ptr(self.tile_mask), _ptr(dm.table), _ptr(dm.table2), _ptr(dm.row_scale))
+
+    def nbytes(self) -> int:
+        return self.words.numel() * 4 + self.tile_rows.numel() * 4
+
+    def xp_buffer(self, B: int) -> torch.Tensor:
+        """Staging buffer for the fp16 (permuted, padded) activations of a batch of B; cached per
+        padded batch size so that repeated calls allocate nothing."""
+        nb = -(-B // 8)
+        buf = self._xp.get(nb)
+        if buf is None:
+            buf = self._xp[nb] = torch.empty(lib.cbl_prep_x_bytes(B, self.C, self.M) // 2, dtype=torch.float16, device=self.device)
+        return buf
+
+    def run(self, X: torch.Tensor, Y: torch.Tensor | None = None, B: int | None = None) -> torch.Tensor:
+        """Y [B, R] = X [B, C] . W^T. X f16 / bf16 / f32 with unit column stride; Y f16 / bf16 / f32
+        with unit column stride (e.g. a column slice of a wider output; its row stride is passed on)."""
+        if X.dim() == 1:
+            X = X[None]
+        B = X.shape[0] if B is None else B
+        if B < 1 or B > self.BMAX:
+            raise ValueError(f"batch {B} outside 1..{self.BMAX}")
+        if X.shape[-1] != self.C or X.stride(-1) != 1 or X.device != self.device:
+            raise ValueError("X must be [B, C] with unit column stride on the matrix's device")
+        if Y is None:
+            Y = torch.empty(B, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape[-1] != self.R or Y.stride(-1) != 1:
+            raise ValueError("Y must be [B, R] with unit column stride")
+        ldy = Y.stride(0) if Y.dim() == 2 else self.R
+        xp = self.xp_buffer(B)
+        with torch.cuda.device(self.device):
+            s = _stream()
+            _lib.check("cbl_prep_x", lib.cbl_prep_x(X.data_ptr(), _dt(X.dtype), B, self.C, X.stride(0), _ptr(self.dm.perms), self.M,
+                                                    xp.data_ptr(), s))
+            _lib.check("cbl_gemv_t16", lib.cbl_gemv_t16(ctypes.byref(self.struct()), xp.data_ptr(), B, Y.data_ptr(), _dt(Y.dtype),
+                                                        ldy, s))
+        return Y
+
+
+_WORKSPACES: dict[tuple, torch.Tensor] = {}
+
+
+def l8_workspace(device: torch.device, R: int) -> torch.Tensor:
+    """Zero-initialised work space shared by every L8 product on (device, current stream): the kernel
+    leaves it zero. Products that may overlap on the device (different streams) get distinct buffers."""
+    key = (device.index, _stream())
+    need = lib.cbl_gemv_l8_workspace_bytes(R)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _WORKSPACES[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+    return ws
+
+
+class L8Matrix:
+    """Column-tile layout for the batch-1 product by activation-side tables (one column order)."""
+
+    def __init__(self, dm: DeviceMatrix):
+        _need_fast(dm)
+        if dm.M != 1:
+            raise ValueError("the table-lookup product supports one column order (M = 1)")
+        self.dm, self.R, self.C, self.books, self.device = dm, dm.R, dm.C, dm.books, dm.device
+        self.Rpad = (dm.R + 3) // 4 * 4
+        self.ntile = dm.books * (-(-dm.nch // 8))
+        nbytes = lib.cbl_l8_bytes(dm.R, dm.C, dm.books)
+        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        with torch.cuda.device(dm.device):
+            _lib.check("cbl_repack_l8", lib.cbl_repack_l8(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
+
+    def struct(self) -> _lib.L8:
+        dm = self.dm
+        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, _ptr(self.words), _ptr(dm.table), _ptr(dm.table2),
+                       _ptr(dm.row_scale))
+
+    def nbytes(self) -> int:
+        return self.words.numel() * 4
+
+    def run(self, x: torch.Tensor, y: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+        """y [R] = W . x for x [C] (f16 / bf16 / f32, contiguous)."""
+        x = x.reshape(-1)
+        if x.numel() != self.C or not x.is_contiguous() or x.device != self.device:
+            raise ValueError("x must be a contiguous [C] vector on the matrix's device")
+        if y is None:
+            y = torch.empty(self.R, dtype=x.dtype, device=self.device)
+        yv = y.reshape(-1)
+        if yv.numel() != self.R or not yv.is_contiguous():
+            raise ValueError("y must be a contiguous [R] vector")
+        ws = workspace if workspace is not None else l8_workspace(self.device, self.R)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_l8", lib.cbl_gemv_l8(ctypes.byref(self.struct()), x.data_ptr(), _dt(x.dtype), yv.data_ptr(),
+                                                      _dt(y.dtype), ws.data_ptr(), _stream()))
+        return y

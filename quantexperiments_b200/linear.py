@@ -1,0 +1,176 @@
+"""The packed-linear call surfaces of the reference, backed by libcbl.
+
+PackedLinear   mirrors shapequant/kernels/gemv.py:107-175 (from_packed, gemv, dense, forward, stored_bytes)
+RunsLin        mirrors shapequant/kernels/decode_e2e.py:405-443 (run(x, y) into a caller-provided buffer)
+runs_linear    mirrors shapequant/runtime.py:41-51
+RunsBatch      mirrors shapequant/kernels/batched_runs.py:680-771 (run(X, Y, B))
+
+Differences that a caller can observe: the product kernels execute the benchmark format (d = 8,
+12-bit tags, one 4096-entry book per matrix, optionally a second summed book and seeded column
+orders) instead of the reference's d = 4 fast path, accumulate in fp32 throughout (no table
+pre-scaling against fp16 overflow is needed), and apply column orders inside the kernels: callers
+pass the plain activation vector, not permuted copies.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .kernels import DeviceMatrix, L8Matrix, T16Matrix
+
+# rows from which the batch-1 product uses activation-side tables instead of codeword lookups
+L8_MIN_ROWS = 2048
+
+
+def _is_capturing() -> bool:
+    return torch.cuda.is_current_stream_capturing()
+
+
+class _Scratch:
+    """Per-device dense scratch shared by every large-M product (grown outside graph capture)."""
+    bufs: dict = {}
+
+    @classmethod
+    def get(cls, n: int, dev, dtype) -> torch.Tensor:
+        key = (str(dev), dtype)
+        b = cls.bufs.get(key)
+        if b is None or b.numel() < n:
+            b = cls.bufs[key] = torch.empty(n, dtype=dtype, device=dev)
+        return b
+
+
+class PackedLinear(torch.nn.Module):
+    """A block linear run from packed tensors: one token -> batch-1 kernel, up to 64 tokens -> the
+    small-batch tensor-core kernel, more -> decode to 16 bit + GEMM. Constructor arguments follow the
+    reference (words, table, row_scale, row_book, row_mask, perms, K, d, bias)."""
+
+    def __init__(self, words, table, row_scale, row_book, row_mask, perms, K: int, d: int, bias=None,
+                 words2=None, table2=None):
+        super().__init__()
+        dev = words.device
+        if dev.type != "cuda":
+            raise ValueError("PackedLinear needs CUDA tensors (no CPU path)")
+        C = perms.shape[1] if perms is not None else None
+        has_mask = row_mask is not None and perms is not None and perms.shape[0] > 1
+        self.dm = DeviceMatrix(words, table, row_scale, row_book, row_mask if has_mask else None,
+                               perms if has_mask else None, K=K, d=d, C=C, device=dev, tags2=words2, table2=table2)
+        self.R, self.C, self.K, self.d, self.W = self.dm.R, self.dm.C, K, d, self.dm.W
+        self.bits, self.nch, self.has_mask = self.dm.bits, self.dm.nch, has_mask
+        self.bias = bias
+        self._t16: T16Matrix | None = None
+        self._l8: L8Matrix | None = None
+
+    @classmethod
+    def from_packed(cls, pf, name: str, device="cuda", bias=None, **kw):
+        m = pf.meta[name]
+        t = pf.tensors(name)
+        return cls(t["tags"].to(device), t["table"].to(device), t["row_scale"].to(device),
+                   t["row_book"].to(device) if "row_book" in t else None,
+                   t["row_mask"].to(device) if "row_mask" in t else None,
+                   pf.perms(name).to(device), m["K"], m["d"], bias=bias, **kw)
+
+    # lazily built kernel layouts (a second copy of the tags in the kernel's order)
+    @property
+    def t16(self) -> T16Matrix:
+        if self._t16 is None:
+            self._t16 = T16Matrix(self.dm)
+        return self._t16
+
+    @property
+    def l8(self) -> L8Matrix:
+        if self._l8 is None:
+            self._l8 = L8Matrix(self.dm)
+        return self._l8
+
+    def use_l8(self) -> bool:
+        return self.dm.M == 1 and self.R >= L8_MIN_ROWS
+
+    def gemv(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x [C] (fp16 / bf16 / fp32, contiguous) -> y [R] in x's dtype (or `out`'s)."""
+        if self.use_l8():
+            return self.l8.run(x, out)
+        y = out if out is not None else torch.empty(self.R, dtype=x.dtype, device=x.device)
+        self.t16.run(x.reshape(1, -1), y.reshape(1, -1), 1)
+        return y
+
+    def dense(self) -> torch.Tensor:
+        """fp32 [R, C] reference-exact decode."""
+        return self.dm.dequant(dtype=torch.float32)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        n = math.prod(lead)
+        if n == 1:
+            y = self.gemv(x.reshape(-1).contiguous()).reshape(*lead, self.R)
+        elif n == 0:
+            y = x.new_empty(*lead, self.R)
+        elif n <= T16Matrix.BMAX:
+            y = self.t16.run(x.reshape(n, self.C).contiguous()).reshape(*lead, self.R)
+        else:
+            x2 = x.reshape(n, self.C)
+            dt = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
+            w = self.dm.dequant(_Scratch.get(self.R * self.C, x.device, dt))
+            y = (x2.to(dt) @ w.t()).to(x.dtype).reshape(*lead, self.R)
+        return y if self.bias is None else y + self.bias
+
+    def stored_bytes(self) -> int:
+        return self.dm.stored_bytes()
+
+
+class RunsLin:
+    """Engine linear: run(x, y) writes y [R] (or [B, R]) into a caller-provided buffer; no allocation
+    and no host synchronisation in run(), so a decode step can be captured in one CUDA graph."""
+
+    def __init__(self, lin: PackedLinear):
+        self.lin, self.R, self.C = lin, lin.R, lin.C
+        self.perms = lin.dm.perms
+        if lin.use_l8():
+            lin.l8          # build the layouts now, not inside a captured region
+        else:
+            lin.t16.xp_buffer(1)
+
+    def run(self, x: torch.Tensor, y: torch.Tensor, epi=None):
+        if epi is not None:
+            raise NotImplementedError("fused epilogues are not part of this path")
+        if x.dim() == 1 or x.shape[0] == 1:
+            self.lin.gemv(x.reshape(-1), y.reshape(-1))
+        else:
+            self.lin.t16.run(x, y)
+
+    def nbytes(self) -> int:
+        return self.lin.stored_bytes()
+
+
+def runs_linear(pf, name: str, dev="cuda", **_ignored) -> RunsLin:
+    """One packed matrix of a PackedFile as an engine linear (keyword arguments that tune the
+    reference's launch geometry are accepted and ignored)."""
+    m = pf.meta[name]
+    if m["d"] != 8 or m["K"] != 4096 or m["G"] != 1:
+        raise ValueError(f"{name}: the kernels execute d=8, K=4096, G=1 (d={m['d']}, K={m['K']}, G={m['G']})")
+    return RunsLin(PackedLinear.from_packed(pf, name, device=dev))
+
+
+class RunsBatch:
+    """Batched launcher for one matrix: run(X [B, C], Y [B, R]) for any B <= bmax. X fp16 or bf16
+    contiguous; Y fp16 / bf16 with unit column stride, e.g. a column slice of a wider stacked output
+    (its row stride is passed through)."""
+
+    def __init__(self, lin: PackedLinear | RunsLin, bmax: int = 32, **_ignored):
+        self.lin = lin.lin if isinstance(lin, RunsLin) else lin
+        if bmax > T16Matrix.BMAX:
+            raise ValueError(f"bmax {bmax} over {T16Matrix.BMAX}")
+        self.R, self.C, self.bmax = self.lin.R, self.lin.C, bmax
+        self.t16 = self.lin.t16
+        for b in range(1, bmax + 1, 8):
+            self.t16.xp_buffer(b)
+
+    def run(self, X: torch.Tensor, Y: torch.Tensor, B: int | None = None) -> torch.Tensor:
+        B = X.shape[0] if B is None else B
+        ok = (torch.float16, torch.bfloat16)
+        if not (B <= self.bmax and X.is_contiguous() and X.dtype in ok and Y.dtype in ok):
+            raise ValueError("RunsBatch.run: B <= bmax, X contiguous, X and Y fp16 or bf16")
+        if Y.stride(-1) != 1 or Y.shape[-1] != self.R:
+            raise ValueError("RunsBatch.run: Y must be [B, R] with unit column stride")
+        return self.t16.run(X, Y, B)

@@ -1,0 +1,112 @@
+"""vLLM-free serving layer: stacked packed pieces (q|k|v, gate|up) behind one forward(), a handle
+registry and the `shapequant::linear` torch custom op.
+
+Mirrors shapequant/vllm_ext/core.py of the reference: PackedShards (:212-486: from_packed, forward,
+dense, nbytes, R, C), register (:622-624) and linear_op with its fake implementation (:693-702), so
+that vLLM's LinearMethod.apply can stay `torch.ops.shapequant.linear(x, handle)`.
+
+Dispatch on the number of tokens M: 1 -> batch-1 kernel per piece, <= bmax -> small-batch
+tensor-core kernel per piece, each writing its column slice of the stacked output; larger ->
+per-piece decode to x's 16-bit dtype into a shared scratch followed by a GEMM into the slice."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import T16Matrix
+from ..linear import PackedLinear, _Scratch
+
+BMAX = T16Matrix.BMAX
+
+
+class PackedShards:
+    def __init__(self, lins: list[PackedLinear], *, bmax: int = BMAX, **_ignored):
+        if not lins:
+            raise ValueError("no pieces")
+        C = {lin.C for lin in lins}
+        if len(C) != 1:
+            raise ValueError(f"stacked pieces disagree on the input size: {sorted(C)}")
+        if bmax > BMAX:
+            raise ValueError(f"bmax {bmax} over {BMAX}")
+        self.lins = lins
+        self.C = C.pop()
+        self.Rs = [lin.R for lin in lins]
+        self.R = sum(self.Rs)
+        self.offs = [sum(self.Rs[:i]) for i in range(len(lins))]
+        self.bmax = self.cross = bmax
+        self.device = lins[0].dm.device
+        self.sq_name = ""
+        for lin in lins:                       # build kernel layouts and staging buffers up front
+            if lin.use_l8():
+                lin.l8
+            for b in range(1, bmax + 1, 8):
+                lin.t16.xp_buffer(b)
+        _Scratch.get(max(self.Rs) * self.C, self.device, torch.bfloat16)
+
+    @classmethod
+    def from_packed(cls, pf, names: list[str], dev="cuda", **kw) -> "PackedShards":
+        return cls([PackedLinear.from_packed(pf, n, device=dev) for n in names], **kw)
+
+    def nbytes(self) -> int:
+        n = 0
+        for lin in self.lins:
+            n += lin.stored_bytes()
+            n += lin._t16.nbytes() if lin._t16 is not None else 0
+            n += lin._l8.nbytes() if lin._l8 is not None else 0
+        return n
+
+    def dense(self) -> torch.Tensor:
+        """fp16 [R, C] (testing)."""
+        return torch.cat([lin.dm.dequant(dtype=torch.float16) for lin in self.lins])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x [..., C] -> [..., R] in x's dtype."""
+        shp = x.shape
+        x2 = x.reshape(-1, self.C)
+        M = x2.shape[0]
+        if M == 0:
+            y = x2.new_empty(0, self.R)
+        elif M <= self.cross:
+            xin = x2 if x2.dtype in (torch.float16, torch.bfloat16) else x2.to(torch.bfloat16)
+            y = self._small(xin.contiguous(), M)
+        else:
+            xin = x2 if x2.dtype in (torch.float16, torch.bfloat16) else x2.to(torch.bfloat16)
+            y = self._large(xin.contiguous())
+        return y.to(x.dtype).view(*shp[:-1], self.R)
+
+    def _small(self, x: torch.Tensor, M: int) -> torch.Tensor:
+        y = torch.empty(M, self.R, dtype=x.dtype, device=x.device)
+        for lin, off, R in zip(self.lins, self.offs, self.Rs):
+            if M == 1 and lin.use_l8():
+                lin.l8.run(x[0], y[0, off:off + R])
+            else:
+                lin.t16.run(x, y[:, off:off + R], M)
+        return y
+
+    def _large(self, x: torch.Tensor) -> torch.Tensor:
+        scratch = _Scratch.get(max(self.Rs) * self.C, x.device, x.dtype)
+        y = torch.empty(x.shape[0], self.R, dtype=x.dtype, device=x.device)
+        for lin, off, R in zip(self.lins, self.offs, self.Rs):
+            w = lin.dm.dequant(scratch)
+            torch.mm(x, w.t(), out=y[:, off:off + R])     # the GEMM finishes before the scratch is reused (one stream)
+        return y
+
+
+# ------------------------------------------------------------------ torch custom op
+
+_REGISTRY: list = []
+
+
+def register(ps) -> int:
+    _REGISTRY.append(ps)
+    return len(_REGISTRY) - 1
+
+
+@torch.library.custom_op("shapequant::linear", mutates_args=())
+def linear_op(x: torch.Tensor, handle: int) -> torch.Tensor:
+    return _REGISTRY[handle].forward(x)
+
+
+@linear_op.register_fake
+def _(x: torch.Tensor, handle: int) -> torch.Tensor:
+    return x.new_empty(*x.shape[:-1], _REGISTRY[handle].R)

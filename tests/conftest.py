@@ -9,3 +9,9 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); deselect with -m 'not gpu'")
+
+
+def pytest_sessionstart(session):
+    """The tests bind the in-tree shared library; (re)build it when a source is newer."""
+    from quantexperiments_b200.build import build
+    build()

@@ -1,0 +1,307 @@
+"""GPU parity tests: every kernel, called through the C ABI, against the CPU oracle and the
+reference-generated fixtures. Decoded weights are compared bit for bit; products against an fp32
+matmul on the reference-decoded weights with max|got - ref| / max|ref| <= 1e-3 for fp32 outputs
+(16-bit outputs add their own rounding of at most half an ulp: 2^-8 for bf16, 2^-11 for fp16, of the element's magnitude)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cbl_oracle as orc
+
+pytestmark = pytest.mark.gpu
+G = Path(__file__).resolve().parent / "golden"
+TOL = 1e-3
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def _dm(m, device="cuda"):
+    from quantexperiments_b200.kernels import DeviceMatrix
+    two = m["books"] == 2
+    return DeviceMatrix(_t(m["words"][0]), _t(m["table"][0]), _t(m["row_scale"]), None,
+                        None if m["row_mask"] is None else _t(m["row_mask"]), None if m["M"] == 1 else _t(m["perms"]),
+                        K=m["K"], d=m["d"], C=m["C"], device=device, tags2=_t(m["words"][1]) if two else None,
+                        table2=_t(m["table"][1]) if two else None)
+
+
+def _out_tol(dtype):
+    return TOL + {torch.float32: 0.0, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}[dtype]
+
+
+# ------------------------------------------------------------------------------------------ decode
+def test_decode_matches_reference_fixtures_bit_for_bit():
+    from quantexperiments_b200.kernels import DeviceMatrix
+    z = np.load(G / "decode.npz")
+    for i, (Gb, M, K, d) in enumerate(z["grid"]):
+        seed, R, C = (int(v) for v in z[f"seed_{i}"])
+        rb = _t(z[f"rb_{i}"]) if f"rb_{i}" in z else None
+        rm = _t(z[f"rm_{i}"]) if f"rm_{i}" in z else None
+        perms = _t(orc.seeded_perms(C, int(M), seed)) if M > 1 else None
+        dm = DeviceMatrix(_t(z[f"words_{i}"]), _t(z[f"table_{i}"]), _t(z[f"rs_{i}"]), rb, rm, perms, K=int(K), d=int(d), C=C)
+        w = dm.dequant(dtype=torch.float32)
+        assert torch.equal(w.cpu(), _t(z[f"w_{i}"])), f"case {i}: G={Gb} M={M} K={K} d={d}"
+        bits = int(K).bit_length() - 1
+        assert np.array_equal(dm.unpack().cpu().numpy(), orc.unpack_bits(z[f"words_{i}"], bits, C // int(d)))
+
+
+def test_two_book_decode_matches_reference_fixture():
+    from quantexperiments_b200.kernels import DeviceMatrix
+    z = np.load(G / "additive.npz")
+    ta, tb = orc.pack_bits(z["ta"], 12), orc.pack_bits(z["tb"], 12)
+    dm = DeviceMatrix(_t(ta), _t(z["A"]), _t(z["rs"]), K=4096, d=8, C=512, tags2=_t(tb), table2=_t(z["B"]))
+    assert torch.equal(dm.dequant(dtype=torch.float32).cpu(), _t(z["dense"]))
+
+
+@pytest.mark.parametrize("R,C,books,M", [(40, 512, 1, 1), (33, 1024, 2, 4), (100, 3584, 1, 16), (4864, 896, 1, 1)])
+def test_decode_16bit_outputs_are_one_rounding_of_the_fp32_decode(R, C, books, M):
+    m = orc.synth_matrix(R, C, seed=R + C, books=books, M=M)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    assert torch.equal(dm.dequant(dtype=torch.float32).cpu(), _t(ref))
+    assert torch.equal(dm.dequant(dtype=torch.float16).cpu(), _t(orc.round_to(ref, "f16")))
+    assert torch.equal(dm.dequant(dtype=torch.bfloat16).cpu(), orc.round_to(ref, "bf16"))
+
+
+def test_decode_row_range_into_a_larger_scratch_leaves_the_rest_untouched():
+    m = orc.synth_matrix(70, 256, seed=5)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    buf = torch.full((70 * 256 + 100,), float("nan"), dtype=torch.float16, device="cuda")
+    got = dm.dequant(buf, rows=(13, 61))
+    assert got.shape == (48, 256)
+    assert torch.equal(got.cpu(), _t(orc.round_to(ref[13:61], "f16")))
+    assert torch.isnan(buf[48 * 256:]).all()
+    assert dm.dequant(rows=(7, 7)).shape == (0, 256)
+
+
+def test_decode_rejects_unsupported_arguments():
+    from quantexperiments_b200 import _lib
+    m = orc.synth_matrix(8, 64, seed=1)
+    dm = _dm(m)
+    with pytest.raises(_lib.CblError):
+        dm.dequant(rows=(0, 9))
+    with pytest.raises(ValueError):
+        dm.dequant(dtype=torch.int32)
+
+
+def test_packed_file_decodes_on_the_gpu_exactly(tmp_path):
+    from quantexperiments_b200 import packed
+    g = torch.Generator().manual_seed(3)
+    R, C, K, d, M = 24, 128, 4096, 8, 4
+    tags = torch.randint(0, K, (R, C // d), generator=g)
+    table = torch.randn(K, d, generator=g).half()
+    rs = torch.rand(R, generator=g).half()
+    rm = torch.randint(0, M, (R,), generator=g)
+    packed.save(tmp_path / "q.safetensors", {"m": packed.pack_matrix(tags, table, rs, d=d, K=K, M=M, seed=5, row_mask=rm)},
+                base_model="test/base")
+    pf = packed.PackedFile(tmp_path / "q.safetensors")
+    ref = orc.decode_tensors(tags.numpy(), table.numpy(), rs.numpy(), None, rm.numpy(), orc.seeded_perms(C, M, 5), K)
+    assert torch.equal(pf.decode("m").cpu(), _t(ref))
+    assert torch.equal(pf.local_tags("m").cpu(), tags)
+    w = packed.decode_tensors(tags, table, rs, None, rm, pf.perms("m"), K)
+    assert torch.equal(w.cpu(), _t(ref))
+
+
+# ------------------------------------------------------------------------------------------ small-batch product
+@pytest.mark.parametrize("R,C", [(512, 3584), (300, 18944), (256, 4864), (128, 256), (17, 896)])
+@pytest.mark.parametrize("books,M", [(1, 1), (1, 16), (2, 1), (2, 16)])
+def test_small_batch_product_matches_fp32_matmul(R, C, books, M):
+    from quantexperiments_b200.kernels import T16Matrix
+    m = orc.synth_matrix(R, C, seed=R * 7 + C + books + M, books=books, M=M)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    t16 = T16Matrix(dm)
+    g = torch.Generator().manual_seed(R)
+    for B in (1, 4, 8, 13, 64):
+        x = torch.randn(B, C, generator=g).bfloat16()
+        yref = orc.linear_ref(x.float().numpy(), ref)
+        y = torch.full((B, R), float("nan"), device="cuda")
+        t16.run(x.cuda(), y)
+        assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL, (B, orc.max_rel_err(y.cpu().numpy(), yref))
+    x = torch.randn(5, C, generator=g).half()
+    yref = orc.linear_ref(x.float().numpy(), ref)
+    for dt in (torch.bfloat16, torch.float16):
+        y = t16.run(x.cuda(), torch.empty(5, R, dtype=dt, device="cuda"))
+        assert orc.max_rel_err(y.float().cpu().numpy(), yref) < _out_tol(dt)
+
+
+def test_small_batch_product_writes_a_column_slice_and_nothing_else():
+    from quantexperiments_b200.kernels import T16Matrix
+    m = orc.synth_matrix(48, 512, seed=9)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    x = torch.randn(6, 512, generator=torch.Generator().manual_seed(2)).bfloat16()
+    wide = torch.full((6, 200), float("nan"), device="cuda")
+    T16Matrix(dm).run(x.cuda(), wide[:, 100:148])
+    yref = orc.linear_ref(x.float().numpy(), ref)
+    assert orc.max_rel_err(wide[:, 100:148].cpu().numpy(), yref) < TOL
+    assert torch.isnan(wide[:, :100]).all() and torch.isnan(wide[:, 148:]).all()
+
+
+def test_small_batch_product_is_deterministic_and_survives_outliers():
+    from quantexperiments_b200.kernels import T16Matrix
+    m = orc.synth_matrix(256, 3584, seed=4)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    t16 = T16Matrix(dm)
+    x = torch.randn(8, 3584, generator=torch.Generator().manual_seed(0)).half()
+    x[:, ::97] = 5536.0           # magnitudes that overflow fp16 products summed in half precision
+    ys = [t16.run(x.cuda()).clone() for _ in range(3)]
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])
+    y = t16.run(x.cuda(), torch.empty(8, 256, device="cuda"))
+    assert torch.isfinite(y).all()
+    assert orc.max_rel_err(y.cpu().numpy(), orc.linear_ref(x.float().numpy(), ref)) < TOL
+
+
+# ------------------------------------------------------------------------------------------ batch-1 product
+@pytest.mark.parametrize("R,C,books", [(4864, 896, 1), (3584, 3584, 1), (2051, 1024, 1), (512, 3584, 1), (2304, 1000 * 8, 2),
+                                        (4, 64, 1), (1030, 72, 2)])
+def test_batch1_product_matches_fp32_matmul(R, C, books):
+    from quantexperiments_b200.kernels import L8Matrix
+    m = orc.synth_matrix(R, C, seed=R + 3 * C + books, books=books)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    g = torch.Generator().manual_seed(C)
+    for it in range(3):           # repeated calls: the shared work space must return to zero every time
+        x = torch.randn(C, generator=g).bfloat16()
+        yref = orc.linear_ref(x.float().numpy()[None], ref)[0]
+        y = torch.full((R,), float("nan"), device="cuda")
+        l8.run(x.cuda(), y)
+        assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL, (it, orc.max_rel_err(y.cpu().numpy(), yref))
+    for dt in (torch.bfloat16, torch.float16):
+        y = l8.run(x.cuda(), torch.empty(R, dtype=dt, device="cuda"))
+        assert orc.max_rel_err(y.float().cpu().numpy(), yref) < _out_tol(dt)
+    from quantexperiments_b200.kernels import l8_workspace
+    assert int(l8_workspace(dm.device, R).count_nonzero()) == 0
+
+
+def test_batch1_product_survives_outliers_and_extreme_scales():
+    from quantexperiments_b200.kernels import L8Matrix
+    m = orc.synth_matrix(2048, 3584, seed=8)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    x = torch.randn(3584, generator=torch.Generator().manual_seed(1))
+    x[::97] = 5536.0
+    for xs in (x.half(), (x * 1e30).bfloat16(), (x * 1e-20).bfloat16()):
+        yref = orc.linear_ref(xs.float().numpy()[None], ref)[0]
+        y = l8.run(xs.cuda(), torch.empty(2048, device="cuda"))
+        assert torch.isfinite(y).all()
+        assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
+
+
+def test_full_size_shapes_by_linearity_and_agreement_between_kernels():
+    """At the benchmark's largest shapes the oracle is too slow to run whole; check size-independent
+    properties: W(x1 + x2) = W x1 + W x2, the two kernels agree, and a sample of rows matches the oracle."""
+    from quantexperiments_b200.kernels import DeviceMatrix, L8Matrix, T16Matrix
+    for R, C in ((18944, 3584), (3584, 18944)):
+        g = torch.Generator(device="cuda").manual_seed(R)
+        W = (C // 8 * 12 + 31) // 32
+        words = torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device="cuda", generator=g)
+        table = torch.randn(4096, 8, device="cuda", generator=g).half()
+        rs = (torch.rand(R, device="cuda", generator=g) * 0.02 + 0.01).half()
+        dm = DeviceMatrix(words, table, rs, K=4096, d=8, C=C)
+        l8, t16 = L8Matrix(dm), T16Matrix(dm)
+        x1 = torch.randn(C, device="cuda", generator=g).half().float()
+        x2 = torch.randn(C, device="cuda", generator=g).half().float()
+        f = lambda x: l8.run(x, torch.empty(R, device="cuda"))
+        ya, yb, yab = f(x1), f(x2), f((x1 + x2).half().float())
+        scale = float(yab.abs().max())
+        x12 = (x1 + x2).half().float()
+        assert float((f(x12) - yab).abs().max()) == 0.0 or float((f(x12) - yab).abs().max()) / scale < 1e-5
+        lin_err = float((ya + yb - f(x1 + x2)).abs().max()) / scale
+        assert lin_err < TOL
+        yt = t16.run(x12[None], torch.empty(1, R, device="cuda"))[0]
+        assert float((yt - yab).abs().max()) / scale < TOL
+        rows = torch.randint(0, R, (64,), generator=torch.Generator().manual_seed(0))
+        tags = orc.unpack_bits(words[rows.cuda()].cpu().numpy(), 12, C // 8)
+        wref = orc.decode_tensors(tags, table.cpu().numpy(), rs[rows.cuda()].cpu().numpy(), None, None, np.arange(C)[None], 4096)
+        assert torch.equal(dm.dequant(rows=(int(rows[0]), int(rows[0]) + 1)).cpu()[0], _t(wref[0]))
+        yref = orc.linear_ref(x12.cpu().numpy()[None], wref)[0]
+        assert float(np.abs(yab[rows.cuda()].cpu().numpy() - yref).max()) / scale < TOL
+
+
+# ------------------------------------------------------------------------------------------ call surfaces
+def test_packed_linear_matches_reference_fixture_and_dispatches_by_token_count():
+    from quantexperiments_b200.linear import PackedLinear
+    z = np.load(G / "linear.npz")
+    R, C, K, d, M = 48, 896, 4096, 8, 16
+    lin = PackedLinear(_t(z["words"]).cuda(), _t(z["table"]).cuda(), _t(z["rs"]).cuda(), None, _t(z["rm"]).cuda(),
+                       _t(orc.seeded_perms(C, M, 1)).cuda(), K, d)
+    assert lin.stored_bytes() == int(z["stored_bytes"][0])
+    assert float(lin.dense().double().sum()) == float(z["dense_sum"][0])
+    x = _t(z["x"]).cuda()
+    y = lin(x)                                    # 3 tokens -> small-batch kernel
+    assert orc.max_rel_err(y.cpu().numpy(), z["y"]) < TOL
+    y1 = lin(x[:1])                               # 1 token -> batch-1 path
+    assert orc.max_rel_err(y1.cpu().numpy(), z["y"][:1]) < TOL
+    xb = torch.randn(2, 40, C, device="cuda", dtype=torch.bfloat16)      # 80 tokens -> decode + GEMM
+    yb = lin(xb)
+    ref = xb.float().reshape(80, C) @ lin.dense().T
+    assert yb.shape == (2, 40, R) and orc.max_rel_err(yb.float().reshape(80, R).cpu().numpy(), ref.cpu().numpy()) < 1e-2
+    assert lin(x[:0]).shape == (0, R)
+    with pytest.raises(ValueError):
+        PackedLinear(_t(z["words"]), _t(z["table"]), _t(z["rs"]), None, None, None, K, d)      # CPU tensors
+
+
+def test_runs_lin_and_runs_batch_write_into_caller_buffers_and_capture_in_a_graph():
+    from quantexperiments_b200.linear import PackedLinear, RunsBatch, RunsLin
+    m = orc.synth_matrix(2304, 896, seed=21)
+    ref = orc.synth_decode(m)
+    lin = PackedLinear(_t(m["words"][0]).cuda(), _t(m["table"][0]).cuda(), _t(m["row_scale"]).cuda(), None, None,
+                       torch.arange(896)[None].cuda(), 4096, 8)
+    rl, rb = RunsLin(lin), RunsBatch(lin, bmax=32)
+    x = torch.randn(896, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0)).bfloat16()
+    X = torch.randn(32, 896, device="cuda").bfloat16()
+    y, Y = torch.empty(2304, device="cuda", dtype=torch.bfloat16), torch.empty(32, 2304, device="cuda", dtype=torch.bfloat16)
+    rl.run(x, y)
+    rb.run(X, Y, 32)
+    torch.cuda.synchronize()
+    y0, Y0 = y.clone(), Y.clone()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        rl.run(x, y)
+        rb.run(X, Y, 32)
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            rl.run(x, y)
+            rb.run(X, Y, 32)
+        y.zero_(), Y.zero_()
+        g.replay()
+        s.synchronize()
+    assert orc.max_rel_err(y.float().cpu().numpy(), orc.linear_ref(x.float().cpu().numpy()[None], ref)[0]) < _out_tol(torch.bfloat16)
+    assert torch.equal(Y, Y0)
+    assert orc.max_rel_err(y.float().cpu().numpy(), y0.float().cpu().numpy()) < 1e-2
+    with pytest.raises(ValueError):
+        rb.run(X.float(), Y, 32)
+
+
+def test_packed_shards_and_custom_op(tmp_path):
+    from quantexperiments_b200 import packed
+    from quantexperiments_b200.vllm_ext import core
+    g = torch.Generator().manual_seed(0)
+    C, K, d = 512, 4096, 8
+    mats, refs = {}, []
+    for name, R in (("l.q_proj", 2048), ("l.k_proj", 64), ("l.v_proj", 64)):
+        tags = torch.randint(0, K, (R, C // d), generator=g)
+        table = torch.randn(K, d, generator=g).half()
+        rs = (torch.rand(R, generator=g) * 0.02 + 0.01).half()
+        mats[name] = packed.pack_matrix(tags, table, rs, d=d, K=K, seed=1)
+        refs.append(orc.decode_tensors(tags.numpy(), table.numpy(), rs.numpy(), None, None, np.arange(C)[None], K))
+    packed.save(tmp_path / "m.safetensors", mats, base_model="test/base")
+    pf = packed.PackedFile(tmp_path / "m.safetensors")
+    ps = core.PackedShards.from_packed(pf, list(mats), dev="cuda", bmax=32)
+    wref = np.concatenate(refs)
+    assert ps.R == 2176 and ps.C == C and ps.nbytes() > 0
+    assert torch.equal(ps.dense().cpu(), _t(wref.astype(np.float16)))
+    h = core.register(ps)
+    for M in (1, 5, 32, 100):
+        x = torch.randn(M, C, device="cuda", dtype=torch.bfloat16)
+        y = torch.ops.shapequant.linear(x, h)
+        assert y.shape == (M, 2176) and y.dtype == torch.bfloat16
+        ref = orc.linear_ref(x.float().cpu().numpy(), wref)
+        assert orc.max_rel_err(y.float().cpu().numpy(), ref) < (_out_tol(torch.bfloat16) if M <= 32 else 1e-2)
+    assert torch.ops.shapequant.linear(torch.empty(0, C, device="cuda", dtype=torch.bfloat16), h).shape == (0, 2176)
+    # opaque to the compiler, like the reference's op (fullgraph trace through the fake implementation)
+    fn = torch.compile(lambda t: torch.ops.shapequant.linear(t, h) * 2, backend="aot_eager", fullgraph=True)
+    x = torch.randn(3, C, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(fn(x), torch.ops.shapequant.linear(x, h) * 2)

@@ -1,0 +1,98 @@
+"""CPU-only tests: host-side format code against the reference-generated fixtures, and that the C-ABI
+library loads and exports every symbol include/cbl.h declares (no compute calls without a GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from quantexperiments_b200 import _lib, packed
+
+ROOT = Path(__file__).resolve().parent.parent
+G = ROOT / "tests" / "golden"
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = (ROOT / "include" / "cbl.h").read_text()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = set(re.findall(r"\b(cbl_[a-z0-9_]+)\s*\(", hdr))
+    assert len(declared) >= 15
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared:
+        assert hasattr(lib, name), f"libcbl.so lacks {name}"
+    assert declared == set(_lib.SIGNATURES), "ctypes signatures and header disagree"
+
+
+def test_library_identity_and_status_strings():
+    assert _lib.lib.cbl_built_for_sm() == 100
+    assert _lib.lib.cbl_version() >= 100
+    assert _lib.lib.cbl_status_string(0) == b"ok"
+    assert b"unsupported" in _lib.lib.cbl_status_string(_lib.EUNSUPPORTED)
+
+
+def test_size_queries_match_the_layout_arithmetic():
+    lib = _lib.lib
+    # t16: [books][ntile][nsuper][3][32] uint4, nsuper = ceil(C/8/64)
+    assert lib.cbl_t16_bytes(224, 3584, 1) == 224 * 7 * 3 * 32 * 16
+    assert lib.cbl_t16_bytes(10, 896, 2) == 2 * 10 * 2 * 3 * 32 * 16
+    # l8: [ntile][3][Rpad] words
+    assert lib.cbl_l8_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
+    assert lib.cbl_l8_bytes(4863, 896, 2) == 2 * 14 * 3 * 4864 * 4
+    assert lib.cbl_prep_x_bytes(3, 896, 16) == 16 * 8 * 1024 * 2 + 16 * 8 * 4
+    assert lib.cbl_gemv_l8_workspace_bytes(18944) >= 18944 * 4 + 37 * 4
+
+
+def test_null_and_bad_arguments_are_rejected_without_a_device():
+    lib = _lib.lib
+    p = _lib.Packed(R=4, C=16, d=8, bits=12, G=1, M=1, books=1, W=1)
+    assert lib.cbl_dequant(ctypes.byref(p), None, _lib.F32, 16, 0, 4, None) == _lib.EINVAL
+    assert lib.cbl_gemv_l8(None, None, 0, None, 0, None, None) == _lib.EINVAL
+    assert lib.cbl_prep_x(None, _lib.BF16, 1, 8, 8, None, 1, None, None) == _lib.EINVAL
+
+
+def test_host_pack_bits_matches_reference_fixtures():
+    z = np.load(G / "bits.npz")
+    for bits in (1, 8, 10, 12, 13, 14, 16):
+        v = torch.from_numpy(z[f"vals_{bits}"].astype(np.int64))
+        w = packed.pack_bits(v, bits)
+        assert w.dtype == torch.int32 and np.array_equal(w.numpy(), z[f"words_{bits}"])
+        assert torch.equal(packed.unpack_bits(w, bits, v.shape[1]), v)
+    with pytest.raises(ValueError):
+        packed.pack_bits(torch.tensor([[1 << 12]]), 12)
+
+
+def test_host_column_orders_and_crc_match_reference_fixtures():
+    z = np.load(G / "perms.npz")
+    for C, M, seed in z["cases"]:
+        p = packed.seeded_perms(int(C), int(M), torch.Generator(device="cpu").manual_seed(int(seed)))
+        assert packed.perm_crc(p) == int(z[f"crc_{C}_{M}_{seed}"][0])
+
+
+def test_packed_file_round_trip_metadata(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    R, C, K, d, M = 12, 64, 4096, 8, 4
+    tags = torch.randint(0, K, (R, C // d), generator=g)
+    table = torch.randn(K, d, generator=g).half()
+    rs = torch.rand(R, generator=g).half()
+    rm = torch.randint(0, M, (R,), generator=g)
+    t, meta = packed.pack_matrix(tags, table, rs, d=d, K=K, M=M, seed=11, row_mask=rm)
+    # storage bits: tags + table + scales + row_mask bytes + 32 for the seed (reference formula)
+    assert meta["bits"] == R * 3 * 32 + K * d * 16 + R * 16 + R * 8 + 32
+    summary = packed.save(tmp_path / "q.safetensors", {"model.layers.0.mlp.up_proj": (t, meta)}, base_model="test/base")
+    assert summary["format"] == packed.FORMAT and summary["matrices"] == 1
+    pf = packed.PackedFile(tmp_path / "q.safetensors")
+    tt = pf.tensors("model.layers.0.mlp.up_proj")
+    assert set(tt) == {"tags", "table", "row_scale", "row_mask"}
+    assert torch.equal(packed.unpack_bits(tt["tags"], 12, C // d), tags)
+    assert pf.perms("model.layers.0.mlp.up_proj").shape == (M, C)
+    pf.meta["model.layers.0.mlp.up_proj"]["perm_crc"] ^= 1
+    with pytest.raises(RuntimeError):
+        pf.perms("model.layers.0.mlp.up_proj")
+
+
+def test_device_matrix_refuses_cpu():
+    from quantexperiments_b200.kernels import DeviceMatrix
+    with pytest.raises(ValueError):
+        DeviceMatrix(torch.zeros(2, 3, dtype=torch.int32), torch.zeros(4096, 8), torch.ones(2), K=4096, d=8, device="cpu")
