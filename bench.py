@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the batch-1 kernel on the 18944 x 3584 shape from one ncu capture
 # (profiles/gemv_l8_gate_7b.md: dram__bytes_read.sum + dram__bytes_write.sum), and the algorithmic
 # bytes of that launch; traffic of other launches is scaled by their algorithmic bytes.
-NCU_TRAFFIC_GATE = (12_939_008 + 0, 12_833_792 + 3584 * 2 + 18944 * 2)
+NCU_TRAFFIC_GATE = (12_902_912 + 0, 12_833_792 + 3584 * 2 + 18944 * 2)
 
 
 def measured_peak() -> tuple[float, str]:

@@ -127,19 +127,30 @@ int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y, int ydtyp
 typedef struct cbl_l8 {
     int32_t R, C, books, ntile, Rpad;   /* ntile counts both books' tiles; Rpad = R rounded up to 4 */
     const void* words;                  /* uint32 [ntile][3][Rpad] */
-    const void* table;
-    const void* table2;
+    const void* frag;                   /* the 4096 x 8 book in tensor-core fragment order (cbl_repack_book) */
+    const void* frag2;                  /* second book when books == 2 */
     const void* row_scale;
 } cbl_l8;
 
 size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books);
 int cbl_repack_l8(const cbl_packed* m, void* out, cbl_stream s);
 
-/* Work space of cbl_gemv_l8: fp32 row accumulators and arrival counters.  It must be zero before
+/* A 4096 x 8 fp16 book re-ordered so that one 128-bit load per lane yields the mma.m16n8k8 A fragments
+ * of two 16-codeword blocks (64 KB, done once at load time; no counterpart in the reference, whose
+ * kernels copy the book to shared memory as stored: shapequant/kernels/cuda_gemv.py:129-141). */
+size_t cbl_book_frag_bytes(void);
+int cbl_repack_book(const void* table, void* out, cbl_stream s);
+
+/* Work space of cbl_gemv_l8: fp32 row accumulators and a status word.  It must be zero before
  * the first call; every call leaves it zero again.  Calls that share a work space must not
  * overlap on the device. */
 size_t cbl_gemv_l8_workspace_bytes(int32_t R);
 int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s);
+
+/* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
+ * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.
+ * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
+int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s);
 
 #ifdef __cplusplus
 }

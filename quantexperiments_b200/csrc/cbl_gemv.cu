@@ -8,7 +8,7 @@
 //                 T[c][e] = <book[e], x_c> for all 4096 codewords (mma.sync m16n8k8, fp32 results in
 //                 shared memory); every weight chunk then costs one 4-byte shared-memory read and
 //                 one add.  Row sums are accumulated across tiles with vector reductions in L2 and
-//                 finished (row scale, output rounding) by the last block to arrive per 512 rows.
+//                 finished (row scale, output rounding, re-zeroing) by a second small kernel.
 #include <utility>
 #include <cstdlib>
 #include "cbl_common.cuh"
@@ -257,16 +257,19 @@ extern "C" int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y
 }
 
 // ------------------------------------------------------------------------------------ l8 product
-constexpr int L8_RB_ROWS = 512;           // rows per arrival block
+//
+// Work decomposition: the (tile, row group) pairs of a matrix, tile-major, are cut into gridDim.x equal
+// contiguous ranges (a row group = 4 rows).  A thread block walks its range NT groups at a time; the
+// groups' tag words are staged by bulk copies (cp.async.bulk + mbarrier) into a ring of shared-memory
+// stages that runs L8_STAGES iterations ahead, across tile boundaries and across the table builds.
 constexpr int L8_COL_WORDS = 4096 + 4;    // column stride of the table in words: the pad keeps the build's stores conflict-free
-constexpr int L8_GROUPS_PER_BLOCK = L8_RB_ROWS / 4;
-constexpr int L8_MAX_WIN = 1024;          // arrival blocks one thread block can finish per segment pass
+constexpr int L8_RING_BYTES = 73728;      // 3 planes x 16 bytes x (NT * stages) groups
+constexpr uint32_t L8_WAIT_LIMIT = 1u << 20;   // mbarrier polls before a wait gives up
 
 extern "C" size_t cbl_gemv_l8_workspace_bytes(int32_t R) {
     if (R < 0) return 0;
     size_t Rpad = ((size_t)R + 3) / 4 * 4;
-    size_t nblk = (Rpad / 4 + L8_GROUPS_PER_BLOCK - 1) / L8_GROUPS_PER_BLOCK;
-    return Rpad * 4 + nblk * 4 + 16;
+    return Rpad * 4 + 16;
 }
 
 __device__ __forceinline__ float l8_row_sum(uint32_t a, uint32_t b, uint32_t c, uint32_t lut) {
@@ -282,138 +285,225 @@ __device__ __forceinline__ float l8_row_sum(uint32_t a, uint32_t b, uint32_t c, 
     return ((s0 + s1) + (s2 + s3)) + ((s4 + s5) + (s6 + s7));
 }
 
+__device__ __forceinline__ void l8_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void l8_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void l8_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Bounded wait for a phase of an mbarrier; false when the limit ran out.
+__device__ __forceinline__ bool l8_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < L8_WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+#ifdef CBL_TRACE
+// Debug builds only: per-block phase timestamps (ns) for offline inspection.
+__device__ unsigned long long g_cbl_trace[1024 * 16];
+__device__ __forceinline__ unsigned long long cbl_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define CBL_MARK(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) g_cbl_trace[blockIdx.x * 16 + (i)] = cbl_now(); } while (0)
+extern "C" int cbl_trace_read(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_cbl_trace, sizeof(g_cbl_trace)); }
+#else
+#define CBL_MARK(i) do { } while (0)
+#endif
+
 template <int NT>
-__global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restrict__ x, int xdtype, void* __restrict__ y,
-                                                   int ydtype, float* __restrict__ acc, unsigned int* __restrict__ cnt) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    float* s_lut = (float*)smem;                         // [8][L8_COL_WORDS]
-    __shared__ int s_win[L8_MAX_WIN];
-    __shared__ int s_nwin;
+__global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restrict__ x, int xdtype, float* __restrict__ acc,
+                                                   unsigned int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int STAGES = L8_RING_BYTES / (NT * 48);
     constexpr int NWARP = NT / 32, NIT = 256 / NWARP;
+    float* s_lut = (float*)smem;                                   // [8][L8_COL_WORDS]
+    unsigned char* s_ring = smem + 8 * L8_COL_WORDS * 4;           // [STAGES][3][NT] uint4
+    __shared__ __align__(8) unsigned long long s_bar[STAGES];
+    __shared__ uint32_t s_b0[32];                                  // B fragment of the tile's activations, per lane
+    __shared__ float s_inv;
+    __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ngroups = m.Rpad >> 2;
     const int ntile1 = m.ntile / m.books;
     const int nch = m.C >> 3;
-    const int64_t total = (int64_t)m.ntile * ngroups;
-    const int64_t a = total * blockIdx.x / gridDim.x, e = total * (blockIdx.x + 1) / gridDim.x;
-    if (a >= e) return;
-    const int tile_first = (int)(a / ngroups), tile_last = (int)((e - 1) / ngroups);
-    const uint32_t lut = cbl_smem_u32(s_lut);
-    if (tid == 0) s_nwin = 0;
-
-    for (int tile = tile_first; tile <= tile_last; tile++) {
-        const int g_lo = (tile == tile_first) ? (int)(a - (int64_t)tile * ngroups) : 0;
-        const int g_hi = (tile == tile_last) ? (int)(e - (int64_t)tile * ngroups) : ngroups;
-        // first tags of this segment: in flight while the table is built
-        const uint4* wp = (const uint4*)m.words + (int64_t)tile * 3 * ngroups;
-        int gi = g_lo + tid;
-        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
-        if (gi < g_hi) {
-            w0 = cbl_ldg_stream(wp + gi);
-            w1 = cbl_ldg_stream(wp + ngroups + gi);
-            w2 = cbl_ldg_stream(wp + 2 * ngroups + gi);
+    // This block's contiguous range [a, e) of (tile, row group) pairs, tile-major.  With at least as many
+    // tiles as blocks a block takes whole tiles; otherwise every tile is cut into equal row ranges, one per
+    // block, so that each block builds exactly one table.
+    int64_t a, e;
+    {
+        const int nb = (int)gridDim.x, b = (int)blockIdx.x;
+        if (m.ntile >= nb) {
+            const int base = m.ntile / nb, extra = m.ntile % nb;
+            const int t0 = b * base + min(b, extra), t1 = t0 + base + (b < extra ? 1 : 0);
+            a = (int64_t)t0 * ngroups;
+            e = (int64_t)t1 * ngroups;
+        } else {
+            const int base = nb / m.ntile, extra = nb % m.ntile;
+            int tl, part, nparts;
+            if (b < extra * (base + 1)) { tl = b / (base + 1); part = b % (base + 1); nparts = base + 1; }
+            else { const int bb = b - extra * (base + 1); tl = extra + bb / base; part = bb % base; nparts = base; }
+            a = (int64_t)tl * ngroups + (int64_t)ngroups * part / nparts;
+            e = (int64_t)tl * ngroups + (int64_t)ngroups * (part + 1) / nparts;
         }
-        // ---- build T[c][e] for the tile's 8 chunk columns
-        {
-            const int book = tile / ntile1, ctile = tile - book * ntile1;
-            const __half* table = (const __half*)(book ? m.table2 : m.table);
-            const int chunk = ctile * 8 + g;              // B fragment: k = 2t, 2t+1 of column n = g
-            float x0 = 0.f, x1 = 0.f;
+    }
+    if (a >= e) return;
+    CBL_MARK(0);
+    const int tile_first = (int)(a / ngroups), tile_last = (int)((e - 1) / ngroups);
+    const int gA = (int)(a - (int64_t)tile_first * ngroups), gE = (int)(e - (int64_t)tile_last * ngroups);
+    const uint32_t lut = cbl_smem_u32(s_lut), ring = cbl_smem_u32(s_ring), bar0 = cbl_smem_u32(s_bar);
+    // iterations of this block: each covers up to NT row groups of one tile
+    int nit = 0;
+    for (int tile = tile_first; tile <= tile_last; tile++) {
+        const int lo = tile == tile_first ? gA : 0, hi = tile == tile_last ? gE : ngroups;
+        nit += (hi - lo + NT - 1) / NT;
+    }
+    if (tid == 0) {
+        s_abort = 0;
+        for (int i = 0; i < STAGES; i++) l8_mbar_init(bar0 + 8 * i, 3);      // one arrival per tag plane
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // Producers: lane 0 of warps 0..2 each stage one of the three tag planes; every producer keeps its
+    // own cursor over the block's iterations.  Consumers: all threads.
+    const bool producer = lane == 0 && warp < 3;
+    int ptile = tile_first, pg = gA, pit = 0;
+    auto issue = [&]() {
+        const int hi = ptile == tile_last ? gE : ngroups;
+        const int n = min(NT, hi - pg);
+        const int stage = pit % STAGES;
+        const uint32_t bar = bar0 + 8 * stage, dst = ring + stage * (NT * 48) + warp * (NT * 16);
+        l8_mbar_expect_tx(bar, (uint32_t)n * 16u);
+        l8_bulk_g2s(dst, (const uint4*)m.words + ((int64_t)ptile * 3 + warp) * ngroups + pg, (uint32_t)n * 16u, bar);
+        pg += NT;
+        if (pg >= hi) { ptile++; pg = 0; }
+        pit++;
+    };
+    if (producer) issue();                                 // stage 0 now; the others after the first book reads are in flight
+    CBL_MARK(7);
+    // Per-tile inputs of the table build: the book's A fragments (two 16-codeword blocks per lane and load)
+    // and, in one warp only, the tile's 64 activations (every block reads the same few lines: keep the
+    // request count low).  B fragment: k = 2t, 2t+1 of column n = g.
+    constexpr int XWARP = 3;
+    uint4 af[NIT / 2];
+    float x0 = 0.f, x1 = 0.f;
+    auto request = [&](int tl) {
+        const int book = tl / ntile1, ctile = tl - book * ntile1;
+        const uint4* fr = (const uint4*)(book ? m.frag2 : m.frag);
+#pragma unroll
+        for (int i = 0; i < NIT / 2; i++) af[i] = __ldg(fr + (warp + i * NWARP) * 32 + lane);
+        if (warp == XWARP) {
+            const int chunk = ctile * 8 + g;
+            x0 = x1 = 0.f;
             if (chunk < nch) {
                 x0 = cbl_load_in(x, xdtype, (int64_t)chunk * 8 + 2 * t);
                 x1 = cbl_load_in(x, xdtype, (int64_t)chunk * 8 + 2 * t + 1);
             }
-            float mx = fmaxf(fabsf(x0), fabsf(x1));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            // power-of-two pre-scale so that fp16(x * sc) neither overflows nor underflows; undone on the fp32 result
-            const int k = cbl_scale_exp(mx);
-            const float sc = ldexpf(1.f, -k), inv = ldexpf(1.f, k);
-            __half2 xb = __floats2half2_rn(x0 * sc, x1 * sc);
-            const uint32_t b0 = *(const uint32_t*)&xb;
-            const uint32_t* tw = (const uint32_t*)table;   // 4 words per codeword
-            uint32_t a0[NIT], a1[NIT];
-#pragma unroll
-            for (int i = 0; i < NIT; i++) {
-                const int e0 = (warp + i * NWARP) * 16;
-                a0[i] = __ldg(tw + (e0 + g) * 4 + t);
-                a1[i] = __ldg(tw + (e0 + g + 8) * 4 + t);
-            }
-            __syncthreads();                               // every reader of the previous table is done
-#pragma unroll
-            for (int i = 0; i < NIT; i++) {
-                const int e0 = (warp + i * NWARP) * 16;
-                float c[4];
-                cbl_mma1688(c, a0[i], a1[i], b0);
-                float* p = s_lut + (2 * t) * L8_COL_WORDS + e0 + g;
-                p[0] = c[0] * inv;
-                p[L8_COL_WORDS] = c[1] * inv;
-                p[8] = c[2] * inv;
-                p[L8_COL_WORDS + 8] = c[3] * inv;
-            }
-            __syncthreads();
         }
-        // ---- one table read per weight chunk
-        while (gi < g_hi) {
-            const int gn = gi + NT;
-            uint4 n0 = w0, n1 = w1, n2 = w2;
-            if (gn < g_hi) {
-                n0 = cbl_ldg_stream(wp + gn);
-                n1 = cbl_ldg_stream(wp + ngroups + gn);
-                n2 = cbl_ldg_stream(wp + 2 * ngroups + gn);
+    };
+    request(tile_first);
+
+    int tile = tile_first, cg = gA, built = -1;
+    bool aborted = false;
+    for (int it = 0; it < nit; it++) {
+        const int hi = tile == tile_last ? gE : ngroups;
+        if (tile != built) {
+            // ---- build T[c][e] for the tile's 8 chunk columns (its fragments and activations were requested
+            // before the previous tile's lookups, or before the loop for the first tile)
+            if (it == 0 && producer)
+                for (int i = 1; i < STAGES && i < nit; i++) issue();
+            if (warp == XWARP) {
+                float mx = fmaxf(fabsf(x0), fabsf(x1));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                // power-of-two pre-scale so that fp16(x * sc) neither overflows nor underflows; undone on the fp32 result
+                const int k = cbl_scale_exp(mx);
+                const float sc = ldexpf(1.f, -k);
+                __half2 xb = __floats2half2_rn(x0 * sc, x1 * sc);
+                s_b0[lane] = *(const uint32_t*)&xb;
+                if (lane == 0) s_inv = ldexpf(1.f, k);
             }
+            __syncthreads();                               // every reader of the previous table is done; s_b0 is published
+            const uint32_t b0 = s_b0[lane];
+            const float inv = s_inv;
+            if (it == 0) CBL_MARK(10);
+#pragma unroll
+            for (int i = 0; i < NIT / 2; i++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int e0 = ((warp + i * NWARP) * 2 + h) * 16;
+                    float c[4];
+                    cbl_mma1688(c, h ? af[i].z : af[i].x, h ? af[i].w : af[i].y, b0);
+                    float* p = s_lut + (2 * t) * L8_COL_WORDS + e0 + g;
+                    p[0] = c[0] * inv;
+                    p[L8_COL_WORDS] = c[1] * inv;
+                    p[8] = c[2] * inv;
+                    p[L8_COL_WORDS + 8] = c[3] * inv;
+                }
+            }
+            built = tile;
+            if (tile < tile_last) request(tile + 1);       // in flight during this tile's lookups
+            __syncthreads();
+            if (it == 0) CBL_MARK(1);
+        }
+        const int stage = it % STAGES;
+        const int n = min(NT, hi - cg);
+        if (!l8_mbar_wait(bar0 + 8 * stage, (uint32_t)(it / STAGES) & 1u)) s_abort = 1;
+        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
+        if (tid < n) {
+            const uint32_t src = ring + stage * (NT * 48) + tid * 16;
+            w0 = cbl_lds128(src);
+            w1 = cbl_lds128(src + NT * 16);
+            w2 = cbl_lds128(src + 2 * NT * 16);
+        }
+        __syncthreads();                                   // the stage has been read by everyone: refill it
+        if (it == 0) CBL_MARK(2);
+        if (s_abort) { aborted = true; break; }
+        if (producer && pit < nit) issue();
+        if (tid < n) {
             float r0 = l8_row_sum(w0.x, w1.x, w2.x, lut);
             float r1 = l8_row_sum(w0.y, w1.y, w2.y, lut);
             float r2 = l8_row_sum(w0.z, w1.z, w2.z, lut);
             float r3 = l8_row_sum(w0.w, w1.w, w2.w, lut);
-            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(acc + 4 * (int64_t)gi), "f"(r0), "f"(r1), "f"(r2), "f"(r3)
+            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(acc + 4 * (int64_t)(cg + tid)), "f"(r0), "f"(r1), "f"(r2),
+                         "f"(r3)
                          : "memory");
-            w0 = n0; w1 = n1; w2 = n2;
-            gi = gn;
         }
-        // ---- arrival accounting per block of 512 rows; the thread block completing a count finishes those rows
-        __threadfence();
-        __syncthreads();
-        const int b_lo = g_lo / L8_GROUPS_PER_BLOCK, b_hi = (g_hi - 1) / L8_GROUPS_PER_BLOCK;
-        for (int base = b_lo; base <= b_hi; base += L8_MAX_WIN) {
-            for (int rb = base + tid; rb <= b_hi && rb < base + L8_MAX_WIN; rb += NT) {
-                const int lo = max(g_lo, rb * L8_GROUPS_PER_BLOCK), hi = min(g_hi, (rb + 1) * L8_GROUPS_PER_BLOCK);
-                const unsigned int n = (unsigned int)(hi - lo);
-                const unsigned int expect = (unsigned int)m.ntile * (unsigned int)(min(ngroups, (rb + 1) * L8_GROUPS_PER_BLOCK) - rb * L8_GROUPS_PER_BLOCK);
-                const unsigned int old = atomicAdd(cnt + rb, n);
-                if (old + n == expect) s_win[atomicAdd(&s_nwin, 1)] = rb;
-            }
-            __syncthreads();
-            const int nwin = s_nwin;
-            if (nwin) {
-                __threadfence();
-                const int nelem = nwin * L8_RB_ROWS;
-                for (int i0 = tid; i0 < nelem; i0 += 4 * NT) {
-                    float v[4];
-                    int row[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int i = i0 + u * NT;
-                        row[u] = -1;
-                        if (i < nelem) {
-                            const int r = s_win[i / L8_RB_ROWS] * L8_RB_ROWS + (i % L8_RB_ROWS);
-                            if (r < m.Rpad) { row[u] = r; v[u] = __ldcg(acc + r); }
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        if (row[u] < 0) continue;
-                        __stcg(acc + row[u], 0.f);
-                        if (row[u] < m.R) cbl_store_out(y, ydtype, row[u], v[u] * __half2float(((const __half*)m.row_scale)[row[u]]));
-                    }
-                }
-                for (int i = tid; i < nwin; i += NT) __stcg(cnt + s_win[i], 0u);
-            }
-            __syncthreads();
-            if (tid == 0) s_nwin = 0;
-            __syncthreads();
+        cg += NT;
+        if (cg >= hi) { tile++; cg = 0; }
+    }
+    if (aborted) {
+        // a staged copy never completed: report, give the copies still in flight a bounded time, leave
+        if (tid == 0) {
+            atomicExch(status, 1u);
+            for (int i = 0; i < STAGES; i++) (void)l8_mbar_wait(bar0 + 8 * i, 0u);
         }
+        return;
+    }
+    CBL_MARK(3);
+}
+
+// y[r] = round(row_scale[r] * acc[r]); acc[r] = 0.  Four rows per thread.
+__global__ void __launch_bounds__(256) k_l8_finish(float4* __restrict__ acc, const __half* __restrict__ row_scale, void* __restrict__ y,
+                                                   int ydtype, int R, int ngroups) {
+    const int gi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= ngroups) return;
+    const float4 v = __ldcg(acc + gi);
+    __stcg(acc + gi, make_float4(0.f, 0.f, 0.f, 0.f));
+    const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const int r = gi * 4 + u;
+        if (r < R) cbl_store_out(y, ydtype, r, vv[u] * __half2float(row_scale[r]));
     }
 }
 
@@ -422,14 +512,35 @@ static int l8_threads() {
     if (!v) {
         const char* e = getenv("CBL_L8_THREADS");
         v = e ? atoi(e) : 512;
-        if (v != 256 && v != 512 && v != 1024) v = 512;
+        if (v != 256 && v != 512) v = 512;
     }
     return v;
 }
 
+// Book in mma.m16n8k8 A-fragment order: uint4 [128][32] = {a0, a1 of codeword block 2p, a0, a1 of block 2p+1}
+// for lane (g, t): a0 = codeword (16*blk + g) values 2t, 2t+1; a1 = codeword (16*blk + g + 8) values 2t, 2t+1.
+__global__ void __launch_bounds__(256) k_repack_book(const uint32_t* __restrict__ table, uint4* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;       // 0 .. 4095
+    const int lane = i & 31, p = i >> 5, g = lane >> 2, t = lane & 3;
+    uint4 v;
+    v.x = table[((2 * p) * 16 + g) * 4 + t];
+    v.y = table[((2 * p) * 16 + g + 8) * 4 + t];
+    v.z = table[((2 * p + 1) * 16 + g) * 4 + t];
+    v.w = table[((2 * p + 1) * 16 + g + 8) * 4 + t];
+    out[i] = v;
+}
+
+extern "C" size_t cbl_book_frag_bytes(void) { return 65536; }
+
+extern "C" int cbl_repack_book(const void* table, void* out, cbl_stream s) {
+    if (!table || !out || ((uintptr_t)table % 4) || ((uintptr_t)out % 16)) return CBL_EINVAL;
+    k_repack_book<<<16, 256, 0, (cudaStream_t)s>>>((const uint32_t*)table, (uint4*)out);
+    return cbl_check_launch();
+}
+
 template <int NT>
 static int launch_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cudaStream_t st) {
-    const size_t smem = (size_t)8 * L8_COL_WORDS * 4;
+    const size_t smem = (size_t)8 * L8_COL_WORDS * 4 + L8_RING_BYTES;
     static bool attr_set[64] = {};
     int dev = 0;
     CBL_CUDA(cudaGetDevice(&dev));
@@ -438,32 +549,43 @@ static int launch_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int yd
         attr_set[dev] = true;
     }
     const int ngroups = m->Rpad / 4;
-    int64_t total = (int64_t)m->ntile * ngroups;
+    // one block per SM at most; a tile is cut into row ranges of at least 128 groups (512 rows) each
     int grid = cbl_sm_count();
-    // a block should own at least ~2 groups per thread, or the table build dominates
-    int64_t cap = total / (2 * NT);
-    if (cap < 1) cap = 1;
-    if (grid > cap) grid = (int)cap;
+    int parts = ngroups / 128;
+    if (parts < 1) parts = 1;
+    if ((int64_t)m->ntile * parts < grid) grid = m->ntile * parts;
     float* acc = (float*)workspace;
-    unsigned int* cnt = (unsigned int*)((char*)workspace + (size_t)m->Rpad * 4);
-    k_gemv_l8<NT><<<grid, NT, smem, st>>>(*m, x, xdtype, y, ydtype, acc, cnt);
+    unsigned int* status = (unsigned int*)((char*)workspace + (size_t)m->Rpad * 4);
+    k_gemv_l8<NT><<<grid, NT, smem, st>>>(*m, x, xdtype, acc, status);
+    int rc = cbl_check_launch();
+    if (rc) return rc;
+    k_l8_finish<<<cbl_ceil_div(ngroups, 256), 256, 0, st>>>((float4*)acc, (const __half*)m->row_scale, y, ydtype, m->R, ngroups);
     return cbl_check_launch();
 }
 
 extern "C" int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s) {
-    if (!m || !m->words || !m->table || !m->row_scale || !x || !y || !workspace) return CBL_EINVAL;
+    if (!m || !m->words || !m->frag || !m->row_scale || !x || !y || !workspace) return CBL_EINVAL;
     if (m->books != 1 && m->books != 2) return CBL_EINVAL;
-    if (m->books == 2 && !m->table2) return CBL_EINVAL;
+    if (m->books == 2 && !m->frag2) return CBL_EINVAL;
     if (m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4) return CBL_EINVAL;
     if (m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
     if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
     if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
-    if (((uintptr_t)m->words % 16) || ((uintptr_t)workspace % 16) || ((uintptr_t)m->table % 4)) return CBL_EINVAL;
+    if (((uintptr_t)m->words % 16) || ((uintptr_t)workspace % 16) || ((uintptr_t)m->frag % 16)) return CBL_EINVAL;
+    if (m->books == 2 && ((uintptr_t)m->frag2 % 16)) return CBL_EINVAL;
     if (m->R == 0) return CBL_OK;
     cudaStream_t st = (cudaStream_t)s;
-    switch (l8_threads()) {
-        case 256: return launch_l8<256>(m, x, xdtype, y, ydtype, workspace, st);
-        case 1024: return launch_l8<1024>(m, x, xdtype, y, ydtype, workspace, st);
-        default: return launch_l8<512>(m, x, xdtype, y, ydtype, workspace, st);
-    }
+    if (l8_threads() == 256) return launch_l8<256>(m, x, xdtype, y, ydtype, workspace, st);
+    return launch_l8<512>(m, x, xdtype, y, ydtype, workspace, st);
+}
+
+// Reads the status word a product leaves in its work space (0 = ok, nonzero = a bounded device-side
+// wait expired and the output is invalid).  Synchronises the stream.
+extern "C" int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s) {
+    if (!workspace || R < 0) return CBL_EINVAL;
+    size_t Rpad = ((size_t)R + 3) / 4 * 4;
+    unsigned int v = 0;
+    CBL_CUDA(cudaMemcpyAsync(&v, (const char*)workspace + Rpad * 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
+    return v ? CBL_ETIMEOUT : CBL_OK;
 }

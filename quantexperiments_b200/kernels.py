@@ -227,16 +227,27 @@ class L8Matrix:
         self.ntile = dm.books * (-(-dm.nch // 8))
         nbytes = lib.cbl_l8_bytes(dm.R, dm.C, dm.books)
         self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        self.frag = torch.empty(lib.cbl_book_frag_bytes() // 4, dtype=torch.int32, device=dm.device)
+        self.frag2 = torch.empty_like(self.frag) if dm.books == 2 else None
         with torch.cuda.device(dm.device):
             _lib.check("cbl_repack_l8", lib.cbl_repack_l8(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
+            _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table.data_ptr(), self.frag.data_ptr(), _stream()))
+            if dm.books == 2:
+                _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table2.data_ptr(), self.frag2.data_ptr(), _stream()))
 
     def struct(self) -> _lib.L8:
         dm = self.dm
-        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, _ptr(self.words), _ptr(dm.table), _ptr(dm.table2),
+        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, _ptr(self.words), _ptr(self.frag), _ptr(self.frag2),
                        _ptr(dm.row_scale))
 
     def nbytes(self) -> int:
-        return self.words.numel() * 4
+        return self.words.numel() * 4 + self.frag.numel() * 4 * self.books
+
+    def status(self, workspace: torch.Tensor | None = None) -> None:
+        """Synchronises and raises CblError if a bounded device-side wait of an earlier run() expired."""
+        ws = workspace if workspace is not None else l8_workspace(self.device, self.R)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_l8_status", lib.cbl_gemv_l8_status(ws.data_ptr(), self.R, _stream()))
 
     def run(self, x: torch.Tensor, y: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
         """y [R] = W . x for x [C] (f16 / bf16 / f32, contiguous)."""

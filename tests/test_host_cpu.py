@@ -41,7 +41,7 @@ def test_size_queries_match_the_layout_arithmetic():
     assert lib.cbl_l8_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
     assert lib.cbl_l8_bytes(4863, 896, 2) == 2 * 14 * 3 * 4864 * 4
     assert lib.cbl_prep_x_bytes(3, 896, 16) == 16 * 8 * 1024 * 2 + 16 * 8 * 4
-    assert lib.cbl_gemv_l8_workspace_bytes(18944) >= 18944 * 4 + 37 * 4
+    assert lib.cbl_gemv_l8_workspace_bytes(18944) >= 18944 * 4 + 4
 
 
 def test_null_and_bad_arguments_are_rejected_without_a_device():
