@@ -130,6 +130,8 @@ typedef struct cbl_l8 {
     const void* frag;                   /* the 4096 x 8 book in tensor-core fragment order (cbl_repack_book) */
     const void* frag2;                  /* second book when books == 2 */
     const void* row_scale;
+    const void* table;                  /* the book as stored, fp16 [4096, 8] (used by cbl_gemm_l8) */
+    const void* table2;
 } cbl_l8;
 
 size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books);
@@ -151,6 +153,19 @@ int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype,
  * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
 int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s);
+
+/* ------------------------------------------------------------------------------------------
+ * Prefill product on the same column-tile layout: y[t*ldy + r] = round_to(ydtype, row_scale[r] *
+ * sum_c W[r, c] * x[t*ldx + c]) for t < ntok.  W tiles are decoded into shared memory and multiplied
+ * with tcgen05.mma (fp16 x fp16, fp32 accumulation in tensor memory); x is staged as fp16 with a
+ * power-of-two scale per token in `stage` (cbl_gemm_stage_bytes).  `workspace`: at least 4 bytes,
+ * zero; a nonzero word afterwards means a bounded device-side wait expired (output invalid).
+ * books = 1 only.
+ * replaces shapequant/kernels/runs_gemm.py:471-514 (gemm: fused dequant + GEMM with mma.sync) and the
+ *          dequant + cuBLAS large-M path of shapequant/vllm_ext/core.py:386-420. */
+size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C);
+int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                void* stage, void* workspace, cbl_stream s);
 
 #ifdef __cplusplus
 }

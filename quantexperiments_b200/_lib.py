@@ -41,7 +41,8 @@ class T16(Structure):
 class L8(Structure):
     """struct cbl_l8: column-tile layout for the batch-1 product."""
     _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("ntile", c_int32), ("Rpad", c_int32),
-                ("words", c_void_p), ("frag", c_void_p), ("frag2", c_void_p), ("row_scale", c_void_p)]
+                ("words", c_void_p), ("frag", c_void_p), ("frag2", c_void_p), ("row_scale", c_void_p),
+                ("table", c_void_p), ("table2", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/cbl.h declares
@@ -63,6 +64,8 @@ SIGNATURES = {
     "cbl_repack_book": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cbl_gemv_l8_workspace_bytes": (c_size_t, [c_int32]),
     "cbl_gemv_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "cbl_gemm_stage_bytes": (c_size_t, [c_int32, c_int32]),
+    "cbl_gemm_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
 }
 

@@ -1,0 +1,294 @@
+// Prefill product Y[tokens, R] = X[tokens, C] . W^T with W decoded on the fly into shared memory and
+// multiplied on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// One thread block computes a 256-token x 256-row tile: two 128 x 256 fp32 accumulators fill the 512
+// TMEM columns.  Per 64-wide k-block
+//   - one thread brings the activations (fp16, two 128 x 64 boxes) in with TMA, 128-byte swizzled;
+//   - 256 decode threads, one per W row, read the row's eight 12-bit tags, fetch the eight 16-byte
+//     codewords from the 64 KB book in shared memory and store them into the K-major 128-byte
+//     swizzled B tile (one codeword = one 16-byte swizzle unit), then fence to the async proxy;
+//   - one thread issues 2 x 4 tcgen05.mma (M 128, N 256, K 16, fp16 x fp16 -> fp32) and commits to
+//     the stage's "empty" barrier.
+// The epilogue reads TMEM with tcgen05.ld, applies the fp16 row scale and the token's power-of-two
+// activation scale, rounds once and writes Y.  Every wait is bounded; a wait that expires sets the
+// status word and lets the block drain and free its tensor memory.
+#include <cuda.h>
+#include "cbl_common.cuh"
+
+namespace {
+
+constexpr int GM_BM = 256;                 // tokens per tile (2 accumulators of 128)
+constexpr int GM_BN = 256;                 // W rows per tile (UMMA N)
+constexpr int GM_BK = 64;                  // k-block: 8 chunks, one 128-byte swizzled row
+constexpr int GM_STAGES = 2;
+constexpr int GM_A_BYTES = 128 * GM_BK * 2;            // one 128-token box
+constexpr int GM_STAGE_BYTES = 2 * GM_A_BYTES + GM_BN * GM_BK * 2;   // 64 KB
+constexpr int GM_SMEM = 65536 + GM_STAGES * GM_STAGE_BYTES;           // book + stages
+constexpr int GM_DECODE_WARPS = 8, GM_THREADS = (GM_DECODE_WARPS + 2) * 32;
+constexpr uint32_t GM_WAIT_LIMIT = 1u << 20;   // mbarrier polls before a wait gives up
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < GM_WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart (descriptor version 1).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __restrict__ xinv, int ntok, void* __restrict__ y, int ydtype,
+          int64_t ldy, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_bar[3 * GM_STAGES + 1];   // full_a, full_b, empty per stage; tmem_full
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r0 = blockIdx.x * GM_BN, tok0 = blockIdx.y * GM_BM;
+    const int nkb = m.ntile;                                  // books == 1: one tile of the l8 layout per k-block
+    const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
+    auto full_a = [&](int s) { return bar0 + 8u * s; };
+    auto full_b = [&](int s) { return bar0 + 8u * (GM_STAGES + s); };
+    auto empty = [&](int s) { return bar0 + 8u * (2 * GM_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (3 * GM_STAGES);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < GM_STAGES; s++) {
+            mbar_init(full_a(s), 1);
+            mbar_init(full_b(s), GM_DECODE_WARPS);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == GM_DECODE_WARPS) {                            // this warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // the book: 4096 codewords of 16 bytes
+    if (warp < GM_DECODE_WARPS) {
+        const uint4* t0 = (const uint4*)m.table;
+        uint4* dst = (uint4*)smem;
+        for (int i = tid; i < 4096; i += GM_DECODE_WARPS * 32) dst[i] = __ldg(t0 + i);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == GM_DECODE_WARPS) {
+        // ---------------- TMA producer of the activations
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % GM_STAGES;
+                if (!mbar_wait(empty(s), ((kb / GM_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+                mbar_expect_tx(full_a(s), 2 * GM_A_BYTES);
+                const uint32_t dst = sbase + 65536 + s * GM_STAGE_BYTES;
+                tma_load_2d(dst, &xmap, kb * GM_BK, tok0, full_a(s));
+                tma_load_2d(dst + GM_A_BYTES, &xmap, kb * GM_BK, tok0 + 128, full_a(s));
+            }
+        }
+    } else if (warp == GM_DECODE_WARPS + 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f16 x f16 -> f32, K-major both
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % GM_STAGES;
+                const uint32_t par = (kb / GM_STAGES) & 1;
+                ok = mbar_wait(full_a(s), par) && mbar_wait(full_b(s), par);
+                if (!ok) { s_abort = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = sbase + 65536 + s * GM_STAGE_BYTES, b_addr = a_addr + 2 * GM_A_BYTES;
+#pragma unroll
+                for (int tb = 0; tb < 2; tb++) {
+#pragma unroll
+                    for (int kk = 0; kk < GM_BK / 16; kk++) {
+                        const uint64_t da = umma_desc_sw128(a_addr + tb * GM_A_BYTES + kk * 32);
+                        const uint64_t db = umma_desc_sw128(b_addr + kk * 32);
+                        umma_f16(tmem + tb * GM_BN, da, db, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                }
+                umma_commit(empty(s));
+            }
+            umma_commit(tmem_full);       // arrives when every MMA issued so far has completed
+        }
+    } else {
+        // ---------------- decode: thread t owns W row r0 + t of the tile
+        const int row = r0 + tid;
+        const bool live = row < m.Rpad;
+        const uint32_t* wp = (const uint32_t*)m.words + row;
+        uint32_t wa = 0, wb = 0, wc = 0;
+        if (live) { wa = __ldg(wp); wb = __ldg(wp + m.Rpad); wc = __ldg(wp + 2 * (int64_t)m.Rpad); }
+        const uint32_t sw = (uint32_t)(tid & 7);
+        const uint32_t rowoff = (uint32_t)(tid >> 3) * 1024u + sw * 128u;
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % GM_STAGES;
+            uint32_t na = 0, nb = 0, nc = 0;
+            if (live && kb + 1 < nkb) {
+                const uint32_t* np = wp + (int64_t)(kb + 1) * 3 * m.Rpad;
+                na = __ldg(np); nb = __ldg(np + m.Rpad); nc = __ldg(np + 2 * (int64_t)m.Rpad);
+            }
+            if (!mbar_wait(empty(s), ((kb / GM_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+            const uint32_t bdst = sbase + 65536 + s * GM_STAGE_BYTES + 2 * GM_A_BYTES + rowoff;
+            uint32_t off[8];
+            off[0] = (wa << 4) & 0xFFF0u;
+            off[1] = (wa >> 8) & 0xFFF0u;
+            off[2] = __funnelshift_r(wa, wb, 20) & 0xFFF0u;
+            off[3] = wb & 0xFFF0u;
+            off[4] = (wb >> 12) & 0xFFF0u;
+            off[5] = __funnelshift_r(wb, wc, 24) & 0xFFF0u;
+            off[6] = (wc >> 4) & 0xFFF0u;
+            off[7] = (wc >> 16) & 0xFFF0u;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const uint4 cw = cbl_lds128(sbase + off[c]);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bdst + (((uint32_t)c ^ sw) << 4)), "r"(cw.x), "r"(cw.y), "r"(cw.z),
+                             "r"(cw.w)
+                             : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_b(s));
+            wa = na; wb = nb; wc = nc;
+        }
+        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).. of accumulator w/4
+        const bool ok = mbar_wait(tmem_full, 0);
+        if (!ok) s_abort = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3, tb = warp >> 2;
+        const int tok = tok0 + tb * 128 + q * 32 + lane;
+        const float tsc = (tok < ntok) ? xinv[tok] : 0.f;
+        if (ok) {
+            for (int c0 = 0; c0 < GM_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(tb * GM_BN + c0), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (tok < ntok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int r = r0 + c0 + j;
+                        if (r < m.R) {
+                            const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
+                            cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, __uint_as_float(v[j]) * tsc * rs);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    if (warp == GM_DECODE_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_tiled_fn get_encode() {
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)p;
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Staging of the activations for cbl_gemm_l8: fp16 [Mpad8][Cpad512] followed by fp32 [Mpad8] inverse scales
+// (the layout cbl_prep_x writes for one column order).
+extern "C" size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C) { return cbl_prep_x_bytes(ntok, C, 1); }
+
+extern "C" int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                           void* stage, void* workspace, cbl_stream s) {
+    if (!m || !m->words || !m->table || !m->row_scale || !x || !y || !stage || !workspace) return CBL_EINVAL;
+    if (m->books != 1) return CBL_EUNSUPPORTED;
+    if (m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+    if (ntok <= 0 || ldx < m->C || ldy < m->R) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (((uintptr_t)stage % 16) || ((uintptr_t)m->table % 16) || ((uintptr_t)workspace % 4)) return CBL_EINVAL;
+    cudaStream_t st = (cudaStream_t)s;
+    int rc = cbl_prep_x(x, xdtype, ntok, m->C, ldx, nullptr, 1, stage, s);
+    if (rc) return rc;
+    const int Mpad = (ntok + 7) / 8 * 8, Cpad = (m->C + 511) / 512 * 512;
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return CBL_ECUDA;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)Cpad, (cuuint64_t)Mpad};
+    const cuuint64_t strides[1] = {(cuuint64_t)Cpad * 2};
+    const cuuint32_t box[2] = {GM_BK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, stage, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        g_cbl_last_cuda_error = (int)cr;
+        return CBL_ECUDA;
+    }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_gemm_l8, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
+        attr_set[dev] = true;
+    }
+    const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
+    dim3 grid(cbl_ceil_div(m->R, GM_BN), cbl_ceil_div(ntok, GM_BM));
+    k_gemm_l8<<<grid, GM_THREADS, GM_SMEM, st>>>(map, *m, xinv, ntok, y, ydtype, ldy, (unsigned int*)workspace);
+    return cbl_check_launch();
+}

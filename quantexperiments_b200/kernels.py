@@ -238,10 +238,38 @@ class L8Matrix:
     def struct(self) -> _lib.L8:
         dm = self.dm
         return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, _ptr(self.words), _ptr(self.frag), _ptr(self.frag2),
-                       _ptr(dm.row_scale))
+                       _ptr(dm.row_scale), _ptr(dm.table), _ptr(dm.table2))
 
     def nbytes(self) -> int:
         return self.words.numel() * 4 + self.frag.numel() * 4 * self.books
+
+    _stage: dict = {}
+
+    def gemm(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
+        """Y [T, R] = X [T, C] . W^T on the tensor cores (prefill). X f16 / bf16 / f32 with unit column
+        stride; Y f16 / bf16 / f32 with unit column stride (its row stride is passed through)."""
+        if self.books != 1:
+            raise ValueError("the prefill product executes one book per matrix")
+        if X.dim() != 2 or X.shape[1] != self.C or X.stride(1) != 1 or X.device != self.device:
+            raise ValueError("X must be [T, C] with unit column stride on the matrix's device")
+        T = X.shape[0]
+        if Y is None:
+            Y = torch.empty(T, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape != (T, self.R) or Y.stride(1) != 1:
+            raise ValueError("Y must be [T, R] with unit column stride")
+        if T == 0:
+            return Y
+        need = lib.cbl_gemm_stage_bytes(T, self.C)
+        key = (self.device.index, _stream())
+        st = L8Matrix._stage.get(key)
+        if st is None or st.numel() < need:
+            st = L8Matrix._stage[key] = torch.empty(need, dtype=torch.uint8, device=self.device)
+        ws = l8_workspace(self.device, self.R)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemm_l8", lib.cbl_gemm_l8(ctypes.byref(self.struct()), X.data_ptr(), _dt(X.dtype), T, X.stride(0),
+                                                      Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
+                                                      ws.data_ptr() + self.Rpad * 4, _stream()))
+        return Y
 
     def status(self, workspace: torch.Tensor | None = None) -> None:
         """Synchronises and raises CblError if a bounded device-side wait of an earlier run() expired."""
