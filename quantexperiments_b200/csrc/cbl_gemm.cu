@@ -85,7 +85,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 
 __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __restrict__ xinv, int ntok, void* __restrict__ y, int ydtype,
-          int64_t ldy, unsigned int* __restrict__ status) {
+          int64_t ldy, int vec_ok, unsigned int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) unsigned long long s_bar[3 * GM_STAGES + 1];   // full_a, full_b, empty per stage; tmem_full
     __shared__ uint32_t s_tmem;
@@ -166,17 +166,22 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
         const int row = r0 + tid;
         const bool live = row < m.Rpad;
         const uint32_t* wp = (const uint32_t*)m.words + row;
-        uint32_t wa = 0, wb = 0, wc = 0;
-        if (live) { wa = __ldg(wp); wb = __ldg(wp + m.Rpad); wc = __ldg(wp + 2 * (int64_t)m.Rpad); }
+        // this row's tag words of the current and the next two k-blocks (three words each)
+        uint32_t wa = 0, wb = 0, wc = 0, na = 0, nb = 0, nc = 0, fa = 0, fb = 0, fc = 0;
+        auto load_tags = [&](int kb, uint32_t& a, uint32_t& b, uint32_t& c) {
+            a = b = c = 0;
+            if (live && kb < nkb) {
+                const uint32_t* p = wp + (int64_t)kb * 3 * m.Rpad;
+                a = __ldg(p); b = __ldg(p + m.Rpad); c = __ldg(p + 2 * (int64_t)m.Rpad);
+            }
+        };
+        load_tags(0, wa, wb, wc);
+        load_tags(1, na, nb, nc);
         const uint32_t sw = (uint32_t)(tid & 7);
         const uint32_t rowoff = (uint32_t)(tid >> 3) * 1024u + sw * 128u;
         for (int kb = 0; kb < nkb; kb++) {
             const int s = kb % GM_STAGES;
-            uint32_t na = 0, nb = 0, nc = 0;
-            if (live && kb + 1 < nkb) {
-                const uint32_t* np = wp + (int64_t)(kb + 1) * 3 * m.Rpad;
-                na = __ldg(np); nb = __ldg(np + m.Rpad); nc = __ldg(np + 2 * (int64_t)m.Rpad);
-            }
+            load_tags(kb + 2, fa, fb, fc);
             if (!mbar_wait(empty(s), ((kb / GM_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
             const uint32_t bdst = sbase + 65536 + s * GM_STAGE_BYTES + 2 * GM_A_BYTES + rowoff;
             uint32_t off[8];
@@ -199,6 +204,7 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
             __syncwarp();
             if (lane == 0) mbar_arrive(full_b(s));
             wa = na; wb = nb; wc = nc;
+            na = fa; nb = fb; nc = fc;
         }
         // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).. of accumulator w/4
         const bool ok = mbar_wait(tmem_full, 0);
@@ -212,10 +218,38 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(tb * GM_BN + c0), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (tok < ntok) {
+                const int rbase = r0 + c0;
+                if (tok >= ntok || rbase >= m.R) continue;
+                if (vec_ok && rbase + 32 <= m.R) {
+                    // 32 consecutive outputs of this token: row scales as four 16-byte loads, outputs as 16-byte stores
+                    union { uint4 u[4]; __half h[32]; } rsv;
+                    const uint4* rp = (const uint4*)((const __half*)m.row_scale + rbase);
 #pragma unroll
+                    for (int j = 0; j < 4; j++) rsv.u[j] = __ldg(rp + j);
+                    float o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * tsc * __half2float(rsv.h[j]);
+                    if (ydtype == CBL_F32) {
+                        float4* dst = (float4*)((float*)y + (int64_t)tok * ldy + rbase);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    } else {
+                        union { uint4 u[4]; __nv_bfloat16 b[32]; __half h[32]; } pk;
+                        if (ydtype == CBL_BF16) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) pk.b[j] = __float2bfloat16_rn(o[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) pk.h[j] = __float2half_rn(o[j]);
+                        }
+                        uint4* dst = (uint4*)((char*)y + ((int64_t)tok * ldy + rbase) * 2);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) dst[j] = pk.u[j];
+                    }
+                } else {
+#pragma unroll 1
                     for (int j = 0; j < 32; j++) {
-                        const int r = r0 + c0 + j;
+                        const int r = rbase + j;
                         if (r < m.R) {
                             const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
                             cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, __uint_as_float(v[j]) * tsc * rs);
@@ -289,6 +323,8 @@ extern "C" int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t n
     }
     const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
     dim3 grid(cbl_ceil_div(m->R, GM_BN), cbl_ceil_div(ntok, GM_BM));
-    k_gemm_l8<<<grid, GM_THREADS, GM_SMEM, st>>>(map, *m, xinv, ntok, y, ydtype, ldy, (unsigned int*)workspace);
+    const int esz = ydtype == CBL_F32 ? 4 : 2;
+    const int vec_ok = ((uintptr_t)y % 16 == 0) && ((ldy * esz) % 16 == 0) && ((uintptr_t)m->row_scale % 16 == 0);
+    k_gemm_l8<<<grid, GM_THREADS, GM_SMEM, st>>>(map, *m, xinv, ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace);
     return cbl_check_launch();
 }

@@ -1,6 +1,7 @@
 """The packed-linear call surfaces of the reference, backed by libcbl.
 
-PackedLinear   mirrors shapequant/kernels/gemv.py:107-175 (from_packed, gemv, dense, forward, stored_bytes)
+PackedLinear   mirrors shapequant/kernels/gemv.py:107-175 (from_packed, gemv, dense, forward, stored_bytes);
+               more than 64 tokens run the fused decode + tcgen05 GEMM (the role of shapequant/kernels/runs_gemm.py:471-514)
 RunsLin        mirrors shapequant/kernels/decode_e2e.py:405-443 (run(x, y) into a caller-provided buffer)
 runs_linear    mirrors shapequant/runtime.py:41-51
 RunsBatch      mirrors shapequant/kernels/batched_runs.py:680-771 (run(X, Y, B))
@@ -43,7 +44,7 @@ class _Scratch:
 
 class PackedLinear(torch.nn.Module):
     """A block linear run from packed tensors: one token -> batch-1 kernel, up to 64 tokens -> the
-    small-batch tensor-core kernel, more -> decode to 16 bit + GEMM. Constructor arguments follow the
+    small-batch tensor-core kernel, more -> fused decode + tcgen05 GEMM. Constructor arguments follow the
     reference (words, table, row_scale, row_book, row_mask, perms, K, d, bias)."""
 
     def __init__(self, words, table, row_scale, row_book, row_mask, perms, K: int, d: int, bias=None,
@@ -87,6 +88,10 @@ class PackedLinear(torch.nn.Module):
     def use_l8(self) -> bool:
         return self.dm.M == 1 and self.R >= L8_MIN_ROWS
 
+    def use_gemm(self) -> bool:
+        """The fused tensor-core prefill kernel executes one column order and one book."""
+        return self.dm.M == 1 and self.dm.books == 1
+
     def gemv(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [C] (fp16 / bf16 / fp32, contiguous) -> y [R] in x's dtype (or `out`'s)."""
         if self.use_l8():
@@ -108,7 +113,10 @@ class PackedLinear(torch.nn.Module):
             y = x.new_empty(*lead, self.R)
         elif n <= T16Matrix.BMAX:
             y = self.t16.run(x.reshape(n, self.C).contiguous()).reshape(*lead, self.R)
+        elif self.use_gemm():
+            y = self.l8.gemm(x.reshape(n, self.C)).reshape(*lead, self.R)
         else:
+            # column orders or two books: decode to 16 bit into the shared scratch, then a library GEMM
             x2 = x.reshape(n, self.C)
             dt = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
             w = self.dm.dequant(_Scratch.get(self.R * self.C, x.device, dt))

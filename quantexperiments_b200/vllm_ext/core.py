@@ -7,7 +7,8 @@ that vLLM's LinearMethod.apply can stay `torch.ops.shapequant.linear(x, handle)`
 
 Dispatch on the number of tokens M: 1 -> batch-1 kernel per piece, <= bmax -> small-batch
 tensor-core kernel per piece, each writing its column slice of the stacked output; larger ->
-per-piece decode to x's 16-bit dtype into a shared scratch followed by a GEMM into the slice."""
+the fused decode + tcgen05 GEMM per piece into its slice (pieces with column orders or two books:
+decode to x's 16-bit dtype into a shared scratch followed by a library GEMM)."""
 
 from __future__ import annotations
 
@@ -37,7 +38,7 @@ class PackedShards:
         self.device = lins[0].dm.device
         self.sq_name = ""
         for lin in lins:                       # build kernel layouts and staging buffers up front
-            if lin.use_l8():
+            if lin.use_l8() or lin.use_gemm():
                 lin.l8
             for b in range(1, bmax + 1, 8):
                 lin.t16.xp_buffer(b)
@@ -87,8 +88,11 @@ class PackedShards:
         scratch = _Scratch.get(max(self.Rs) * self.C, x.device, x.dtype)
         y = torch.empty(x.shape[0], self.R, dtype=x.dtype, device=x.device)
         for lin, off, R in zip(self.lins, self.offs, self.Rs):
-            w = lin.dm.dequant(scratch)
-            torch.mm(x, w.t(), out=y[:, off:off + R])     # the GEMM finishes before the scratch is reused (one stream)
+            if lin.use_gemm():
+                lin.l8.gemm(x, y[:, off:off + R])         # fused decode + tcgen05 GEMM straight into the column slice
+            else:
+                w = lin.dm.dequant(scratch)
+                torch.mm(x, w.t(), out=y[:, off:off + R])  # the GEMM finishes before the scratch is reused (one stream)
         return y
 
 

@@ -219,6 +219,49 @@ def test_full_size_shapes_by_linearity_and_agreement_between_kernels():
         assert float(np.abs(yab[rows.cuda()].cpu().numpy() - yref).max()) / scale < TOL
 
 
+# ------------------------------------------------------------------------------------------ prefill product
+@pytest.mark.parametrize("R,C,T", [(256, 64, 128), (512, 896, 300), (300, 1024, 77), (4864, 896, 513), (1024, 3584, 2048),
+                                   (259, 72, 1)])
+def test_prefill_product_matches_fp32_matmul(R, C, T):
+    from quantexperiments_b200.kernels import L8Matrix
+    m = orc.synth_matrix(R, C, seed=R + C + T)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    X = torch.randn(T, C, generator=torch.Generator().manual_seed(T)).bfloat16()
+    yref = orc.linear_ref(X.float().numpy(), ref)
+    Y = torch.full((T, R), float("nan"), device="cuda")
+    l8.gemm(X.cuda(), Y)
+    l8.status()
+    assert orc.max_rel_err(Y.cpu().numpy(), yref) < TOL
+    for dt in (torch.bfloat16, torch.float16):
+        Y = l8.gemm(X.cuda(), torch.empty(T, R, dtype=dt, device="cuda"))
+        assert orc.max_rel_err(Y.float().cpu().numpy(), yref) < _out_tol(dt)
+
+
+def test_prefill_product_writes_a_column_slice_and_survives_outliers():
+    from quantexperiments_b200.kernels import L8Matrix
+    m = orc.synth_matrix(256, 512, seed=12)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    X = torch.randn(100, 512, generator=torch.Generator().manual_seed(3)).bfloat16()
+    X[:, ::61] = 5536.0
+    X[7] *= 1e30
+    X[9] *= 1e-25
+    yref = orc.linear_ref(X.float().numpy(), ref)
+    wide = torch.full((100, 777), float("nan"), device="cuda")       # odd row stride: the scalar store path
+    l8.gemm(X.cuda(), wide[:, 300:556])
+    got = wide[:, 300:556].cpu().numpy()
+    assert np.isfinite(got).all()
+    for t in range(100):          # per token: scales differ by 55 orders of magnitude
+        assert orc.max_rel_err(got[t], yref[t]) < TOL
+    assert torch.isnan(wide[:, :300]).all() and torch.isnan(wide[:, 556:]).all()
+    wide16 = torch.full((100, 768), float("nan"), device="cuda", dtype=torch.bfloat16)   # aligned slice: vector stores
+    l8.gemm(X.cuda(), wide16[:, 256:512])
+    assert torch.isnan(wide16[:, :256]).all() and torch.isnan(wide16[:, 512:]).all()
+    for t in range(100):
+        assert orc.max_rel_err(wide16[t, 256:512].float().cpu().numpy(), yref[t]) < _out_tol(torch.bfloat16)
+
+
 # ------------------------------------------------------------------------------------------ call surfaces
 def test_packed_linear_matches_reference_fixture_and_dispatches_by_token_count():
     from quantexperiments_b200.linear import PackedLinear
@@ -233,7 +276,7 @@ def test_packed_linear_matches_reference_fixture_and_dispatches_by_token_count()
     assert orc.max_rel_err(y.cpu().numpy(), z["y"]) < TOL
     y1 = lin(x[:1])                               # 1 token -> batch-1 path
     assert orc.max_rel_err(y1.cpu().numpy(), z["y"][:1]) < TOL
-    xb = torch.randn(2, 40, C, device="cuda", dtype=torch.bfloat16)      # 80 tokens -> decode + GEMM
+    xb = torch.randn(2, 40, C, device="cuda", dtype=torch.bfloat16)      # 80 tokens, column orders -> decode + library GEMM
     yb = lin(xb)
     ref = xb.float().reshape(80, C) @ lin.dense().T
     assert yb.shape == (2, 40, R) and orc.max_rel_err(yb.float().reshape(80, R).cpu().numpy(), ref.cpu().numpy()) < 1e-2
