@@ -176,15 +176,19 @@ class T16Matrix:
             buf = self._xp[nb] = torch.empty(lib.cbl_prep_x_bytes(B, self.C, self.M) // 2, dtype=torch.float16, device=self.device)
         return buf
 
-    def run(self, X: torch.Tensor, Y: torch.Tensor | None = None, B: int | None = None) -> torch.Tensor:
+    def run(self, X: torch.Tensor, Y: torch.Tensor | None = None, B: int | None = None, wide: bool = False) -> torch.Tensor:
         """Y [B, R] = X [B, C] . W^T. X f16 / bf16 / f32 with unit column stride; Y f16 / bf16 / f32
-        with unit column stride (e.g. a column slice of a wider output; its row stride is passed on)."""
+        with unit column stride (e.g. a column slice of a wider output; its row stride is passed on).
+        wide=True (matrices with column orders only): X is wider than C and the column orders index
+        into the wide rows (a tensor-parallel input shard that reads the full activation vector)."""
         if X.dim() == 1:
             X = X[None]
         B = X.shape[0] if B is None else B
         if B < 1 or B > self.BMAX:
             raise ValueError(f"batch {B} outside 1..{self.BMAX}")
-        if X.shape[-1] != self.C or X.stride(-1) != 1 or X.device != self.device:
+        if wide and self.M == 1:
+            raise ValueError("wide activations need column orders")
+        if (X.shape[-1] != self.C and not wide) or X.stride(-1) != 1 or X.device != self.device:
             raise ValueError("X must be [B, C] with unit column stride on the matrix's device")
         if Y is None:
             Y = torch.empty(B, self.R, dtype=X.dtype, device=self.device)

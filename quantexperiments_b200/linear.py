@@ -104,23 +104,29 @@ class PackedLinear(torch.nn.Module):
         """fp32 [R, C] reference-exact decode."""
         return self.dm.dequant(dtype=torch.float32)
 
+    def forward_into(self, x2: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """y [n, R] (any of fp32 / fp16 / bf16, unit column stride) = x2 [n, C] . W^T, dispatched by n."""
+        n = x2.shape[0]
+        if n == 0:
+            return y
+        if n == 1 and self.use_l8() and y.is_contiguous():
+            self.l8.run(x2[0].contiguous(), y[0])
+        elif n <= T16Matrix.BMAX:
+            self.t16.run(x2.contiguous(), y, n)
+        elif self.use_gemm():
+            self.l8.gemm(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
+        else:
+            # column orders or two books: decode to 16 bit into the shared scratch, then a library GEMM
+            dt = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
+            w = self.dm.dequant(_Scratch.get(self.R * self.C, x2.device, dt))
+            y.copy_(x2.to(dt) @ w.t())
+        return y
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         n = math.prod(lead)
-        if n == 1:
-            y = self.gemv(x.reshape(-1).contiguous()).reshape(*lead, self.R)
-        elif n == 0:
-            y = x.new_empty(*lead, self.R)
-        elif n <= T16Matrix.BMAX:
-            y = self.t16.run(x.reshape(n, self.C).contiguous()).reshape(*lead, self.R)
-        elif self.use_gemm():
-            y = self.l8.gemm(x.reshape(n, self.C)).reshape(*lead, self.R)
-        else:
-            # column orders or two books: decode to 16 bit into the shared scratch, then a library GEMM
-            x2 = x.reshape(n, self.C)
-            dt = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
-            w = self.dm.dequant(_Scratch.get(self.R * self.C, x.device, dt))
-            y = (x2.to(dt) @ w.t()).to(x.dtype).reshape(*lead, self.R)
+        y = self.forward_into(x.reshape(n, self.C), torch.empty(n, self.R, dtype=x.dtype, device=x.device))
+        y = y.reshape(*lead, self.R)
         return y if self.bias is None else y + self.bias
 
     def stored_bytes(self) -> int:

@@ -1,0 +1,165 @@
+"""Tensor-parallel sharding of packed matrices (new design: the reference refuses tensor parallelism,
+shapequant/vllm_ext/plugin.py:198-199).
+
+Column-parallel linears (q, k, v, gate, up) split the OUTPUT rows: every row carries its own tags,
+scale and column-order id, so a rank keeps a contiguous row range plus a full copy of the book(s).
+Row-parallel linears (o, down) split the INPUT dimension at chunk boundaries: a rank keeps, for every
+row, the tags of its chunk range (re-packed into its own bit stream), all row scales and the book(s),
+and produces partial outputs that are summed across ranks (NCCL all-reduce over NVLink).
+
+With several column orders (M > 1) a chunk range of a row-parallel matrix reads activations at
+arbitrary global columns; the shard then keeps perms[:, c0:c1] (global indices) and is fed the FULL
+activation vector (all-gathered by the caller), see RowParallelLinear.
+
+The shard_* functions work on the file-layout tensors (CPU or GPU) and are pure index arithmetic, so
+they are tested on CPU ranks; the linears launch the CUDA kernels."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .packed import pack_bits, unpack_bits
+
+
+def row_range(R: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows of a column-parallel shard. R must split evenly (vLLM's rule); a KV projection with fewer
+    heads than ranks is replicated by the caller instead (rank // (world // n_kv_heads))."""
+    if R % world:
+        raise ValueError(f"{R} rows do not split evenly over {world} ranks")
+    n = R // world
+    return rank * n, (rank + 1) * n
+
+
+def col_range(C: int, d: int, rank: int, world: int) -> tuple[int, int]:
+    """Columns of a row-parallel shard, cut at chunk boundaries."""
+    nch = C // d
+    if nch % world:
+        raise ValueError(f"{nch} chunks do not split evenly over {world} ranks")
+    n = nch // world
+    return rank * n * d, (rank + 1) * n * d
+
+
+def shard_rows(t: dict, meta: dict, r0: int, r1: int) -> tuple[dict, dict]:
+    """File-layout tensors + metadata of rows [r0, r1) of a matrix (tags, row_scale, row_book,
+    row_mask sliced; table and column orders unchanged)."""
+    out = {"tags": t["tags"][r0:r1].contiguous(), "table": t["table"], "row_scale": t["row_scale"][r0:r1].contiguous()}
+    for k in ("row_book", "row_mask"):
+        if k in t:
+            out[k] = t[k][r0:r1].contiguous()
+    for k in ("tags2", "table2"):
+        if k in t:
+            out[k] = t[k][r0:r1].contiguous() if k == "tags2" else t[k]
+    m = dict(meta, R=r1 - r0)
+    return out, m
+
+
+def _slice_stream(words: torch.Tensor, bits: int, nch: int, j0: int, j1: int) -> torch.Tensor:
+    """Bit stream of chunks [j0, j1) of every row. Word-aligned ranges are sliced in place (all
+    Qwen2.5 shapes at TP 2/4/8); anything else goes through unpack + pack."""
+    n = j1 - j0
+    if (j0 * bits) % 32 == 0 and ((n * bits) % 32 == 0 or j1 == nch):
+        w0 = j0 * bits // 32
+        return words[:, w0:w0 + (n * bits + 31) // 32].contiguous()
+    tags = unpack_bits(words.cpu(), bits, nch)[:, j0:j1]
+    return pack_bits(tags, bits).to(words.device)
+
+
+def shard_cols(t: dict, meta: dict, c0: int, c1: int, perms: torch.Tensor | None = None) -> tuple[dict, dict, torch.Tensor | None]:
+    """File-layout tensors + metadata of input columns [c0, c1) (chunk aligned) of a matrix, and the
+    shard's column orders (global activation indices) when the matrix has several."""
+    d, K = meta["d"], meta["K"]
+    if c0 % d or c1 % d:
+        raise ValueError("column ranges must be cut at chunk boundaries")
+    bits = int(math.log2(K))
+    nch = meta["C"] // d
+    out = {"tags": _slice_stream(t["tags"], bits, nch, c0 // d, c1 // d), "table": t["table"], "row_scale": t["row_scale"]}
+    if "tags2" in t:
+        out["tags2"] = _slice_stream(t["tags2"], bits, nch, c0 // d, c1 // d)
+        out["table2"] = t["table2"]
+    for k in ("row_book", "row_mask"):
+        if k in t:
+            out[k] = t[k]
+    m = dict(meta, C=c1 - c0)
+    p = None if perms is None else perms[:, c0:c1].contiguous()
+    return out, m, p
+
+
+class ColumnParallelLinear:
+    """Rank-local part of a column-parallel packed linear: y_local [..., R / world] = x . W[r0:r1]^T.
+    No communication; the caller gathers or consumes the sharded output."""
+
+    def __init__(self, t: dict, meta: dict, perms: torch.Tensor | None, rank: int, world: int, device="cuda"):
+        from .linear import PackedLinear
+        r0, r1 = row_range(meta["R"], rank, world)
+        ts, ms = shard_rows(t, meta, r0, r1)
+        self.r0, self.r1 = r0, r1
+        p = perms if perms is not None else torch.arange(meta["C"])[None]
+        self.lin = PackedLinear(ts["tags"].to(device), ts["table"].to(device), ts["row_scale"].to(device),
+                                ts["row_book"].to(device) if "row_book" in ts else None,
+                                ts["row_mask"].to(device) if "row_mask" in ts else None, p.to(device), ms["K"], ms["d"],
+                                words2=ts["tags2"].to(device) if "tags2" in ts else None,
+                                table2=ts["table2"].to(device) if "table2" in ts else None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.lin(x)
+
+    __call__ = forward
+
+
+class RowParallelLinear:
+    """Rank-local part of a row-parallel packed linear plus the sum over ranks:
+    y = sum_ranks x[..., c0:c1] . W[:, c0:c1]^T. `x` is the rank's slice [..., C / world] when the
+    matrix has one column order, or the full [..., C] vector when it has several (the shard's column
+    orders index the full vector). reduce=False returns the partial product (for callers that
+    reduce themselves, e.g. vLLM's RowParallelLinear)."""
+
+    def __init__(self, t: dict, meta: dict, perms: torch.Tensor | None, rank: int, world: int, device="cuda", group=None):
+        from .kernels import DeviceMatrix, T16Matrix
+        from .linear import PackedLinear
+        c0, c1 = col_range(meta["C"], meta["d"], rank, world)
+        multi = meta["M"] > 1
+        ts, ms, ps = shard_cols(t, meta, c0, c1, perms if multi else None)
+        self.c0, self.c1, self.group, self.world, self.multi = c0, c1, group, world, multi
+        self.R, self.C_full = meta["R"], meta["C"]
+        if not multi:
+            self.lin = PackedLinear(ts["tags"].to(device), ts["table"].to(device), ts["row_scale"].to(device),
+                                    ts["row_book"].to(device) if "row_book" in ts else None, None,
+                                    torch.arange(c1 - c0)[None].to(device), ms["K"], ms["d"],
+                                    words2=ts["tags2"].to(device) if "tags2" in ts else None,
+                                    table2=ts["table2"].to(device) if "table2" in ts else None)
+        else:
+            # column orders: the small-batch kernel gathers x through perms[:, c0:c1] from the full vector
+            self.dm = DeviceMatrix(ts["tags"], ts["table"], ts["row_scale"], None, ts["row_mask"], ps, K=ms["K"], d=ms["d"],
+                                   C=c1 - c0, device=device, tags2=ts.get("tags2"), table2=ts.get("table2"))
+            self.t16 = T16Matrix(self.dm)
+
+    def partial(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 partial product [..., R] of this rank's column range."""
+        lead = x.shape[:-1]
+        n = math.prod(lead)
+        y = torch.empty(n, self.R, dtype=torch.float32, device=x.device)
+        if not self.multi:
+            self.lin.forward_into(x.reshape(n, self.c1 - self.c0), y)
+        else:
+            if n > T16Matrix_BMAX():
+                raise ValueError("row-parallel matrices with column orders run batches up to 64 tokens")
+            if n:
+                self.t16.run(x.reshape(n, self.C_full).contiguous(), y, n, wide=True)
+        return y.reshape(*lead, self.R)
+
+    def forward(self, x: torch.Tensor, reduce: bool = True) -> torch.Tensor:
+        """Partials are kept in fp32 through the all-reduce and rounded to x's dtype once."""
+        y = self.partial(x)
+        if reduce and self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(y, group=self.group)
+        return y.to(x.dtype)
+
+    __call__ = forward
+
+
+def T16Matrix_BMAX() -> int:
+    from .kernels import T16Matrix
+    return T16Matrix.BMAX

@@ -1,0 +1,121 @@
+"""Tensor-parallel sharding: host-side index arithmetic on CPU ranks (gloo, world size 2) and the
+sharded kernels on one GPU (ranks emulated one after another)."""
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import cbl_oracle as orc
+from quantexperiments_b200 import tp
+
+
+def _file_tensors(m):
+    t = {"tags": torch.from_numpy(m["words"][0]), "table": torch.from_numpy(m["table"][0]), "row_scale": torch.from_numpy(m["row_scale"])}
+    if m["books"] == 2:
+        t["tags2"], t["table2"] = torch.from_numpy(m["words"][1]), torch.from_numpy(m["table"][1])
+    if m["row_mask"] is not None:
+        t["row_mask"] = torch.from_numpy(m["row_mask"])
+    meta = {"R": m["R"], "C": m["C"], "d": m["d"], "K": m["K"], "G": 1, "M": m["M"]}
+    return t, meta, torch.from_numpy(m["perms"])
+
+
+def _oracle_decode(t, meta, perms_global, c0=0):
+    """fp32 decode of a shard by the oracle; a column shard of a matrix with column orders is returned
+    in the shard's own chunk order (its activations are gathered through perms_global[:, c0:c1])."""
+    bits = int(meta["K"]).bit_length() - 1
+    nch = meta["C"] // meta["d"]
+    tags = orc.unpack_bits(t["tags"].numpy(), bits, nch)
+    ident = np.arange(meta["C"])[None]
+    if "tags2" in t:
+        tags2 = orc.unpack_bits(t["tags2"].numpy(), bits, nch)
+        return orc.additive_decode(t["table"].numpy(), t["table2"].numpy(), tags, tags2, t["row_scale"].numpy())
+    return orc.decode_tensors(tags, t["table"].numpy(), t["row_scale"].numpy(), None, None, ident, meta["K"])
+
+
+def _rank_main(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        for books, M in ((1, 1), (2, 1), (1, 4)):
+            m = orc.synth_matrix(32, 768, seed=5 + books + M, books=books, M=M)
+            t, meta, perms = _file_tensors(m)
+            wfull = orc.synth_decode(m)
+            x = torch.randn(3, 768, generator=torch.Generator().manual_seed(1)).bfloat16().float()
+            yfull = orc.linear_ref(x.numpy(), wfull)
+            # column-parallel: rows split, outputs concatenated by all_gather
+            r0, r1 = tp.row_range(meta["R"], rank, world)
+            ts, ms = tp.shard_rows(t, meta, r0, r1)
+            assert ts["tags"].shape[0] == r1 - r0 and ms["R"] == r1 - r0
+            y_loc = torch.from_numpy(yfull[:, r0:r1].copy())
+            parts = [torch.empty_like(y_loc) for _ in range(world)]
+            dist.all_gather(parts, y_loc)
+            assert np.allclose(torch.cat(parts, 1).numpy(), yfull)
+            if M == 1:
+                w_loc = _oracle_decode(ts, ms, perms)
+                assert np.array_equal(w_loc, wfull[r0:r1])
+            # row-parallel: columns split at chunk boundaries, partial products summed by all_reduce
+            c0, c1 = tp.col_range(meta["C"], meta["d"], rank, world)
+            ts, ms, ps = tp.shard_cols(t, meta, c0, c1, perms if M > 1 else None)
+            assert ms["C"] == c1 - c0 and ts["tags"].shape[1] == orc.words_per_row((c1 - c0) // 8, 12)
+            u_loc = _oracle_decode(ts, ms, perms)            # chunk order of the shard
+            if M == 1:
+                assert np.array_equal(u_loc, wfull[:, c0:c1])
+                part = orc.linear_ref(x.numpy()[:, c0:c1], u_loc)
+            else:
+                # y[b, r] = sum_c u[r, c] * x[b, perms[mask[r]][c0 + c]]: gather the full x per row's order
+                rm = t["row_mask"].numpy().astype(np.int64)
+                xg = x.numpy()[:, ps.numpy()[rm]]            # [B, R, Cs]
+                part = np.einsum("brc,rc->br", xg, u_loc).astype(np.float32)
+            y = torch.from_numpy(part.copy())
+            dist.all_reduce(y)
+            assert orc.max_rel_err(y.numpy(), yfull) < 1e-5, (books, M)
+        (Path(tmp) / f"ok{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharding_on_two_cpu_ranks(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_unaligned_column_ranges_are_repacked():
+    m = orc.synth_matrix(6, 8 * 10, seed=2)          # 10 chunks of 12 bits: ranges not word aligned
+    t, meta, _ = _file_tensors(m)
+    ts, ms, _ = tp.shard_cols(t, meta, 24, 56)       # chunks 3..6
+    tags = orc.unpack_bits(ts["tags"].numpy(), 12, 4)
+    assert np.array_equal(tags, m["tags"][0][:, 3:7])
+    with pytest.raises(ValueError):
+        tp.shard_cols(t, meta, 4, 16)
+    with pytest.raises(ValueError):
+        tp.row_range(10, 0, 4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("books,M", [(1, 1), (2, 1), (1, 16), (2, 16)])
+def test_sharded_linears_on_one_gpu(world, books, M):
+    R, C = 2304 * 2 if M == 1 else 256, 1024
+    m = orc.synth_matrix(R, C, seed=world + books + M, books=books, M=M)
+    t, meta, perms = _file_tensors(m)
+    wfull = orc.synth_decode(m)
+    for B in (1, 5, 80 if M == 1 else 40):
+        x = torch.randn(B, C, generator=torch.Generator().manual_seed(B)).bfloat16()
+        yfull = orc.linear_ref(x.float().numpy(), wfull)
+        cols = [tp.ColumnParallelLinear(t, meta, perms if M > 1 else None, r, world)(x.cuda()) for r in range(world)]
+        ycat = torch.cat(cols, 1).float().cpu().numpy()
+        assert orc.max_rel_err(ycat, yfull) < 1e-3 + 2.0 ** -8
+        acc = torch.zeros(B, R, device="cuda")
+        for r in range(world):
+            rp = tp.RowParallelLinear(t, meta, perms if M > 1 else None, r, world)
+            xin = x.cuda() if M > 1 else x[:, rp.c0:rp.c1].contiguous().cuda()
+            part = rp.partial(xin)
+            assert part.dtype == torch.float32
+            acc += part
+        tol = 1e-3 if (B <= 64 or books == 1) else 1e-2      # >64 tokens with two books: 16-bit decode + library GEMM
+        assert orc.max_rel_err(acc.cpu().numpy(), yfull) < tol, (world, books, M, B)
