@@ -12,12 +12,35 @@ decode to x's 16-bit dtype into a shared scratch followed by a library GEMM)."""
 
 from __future__ import annotations
 
+import re
+
 import torch
 
 from ..kernels import T16Matrix
 from ..linear import PackedLinear, _Scratch
 
 BMAX = T16Matrix.BMAX
+
+# vLLM fuses some HF projections into one layer; the packed file keeps the HF pieces
+STACKED = {"self_attn.qkv_proj": ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"),
+           "mlp.gate_up_proj": ("mlp.gate_proj", "mlp.up_proj")}
+_LAYER = re.compile(r"(?:^|\.)layers\.(\d+)\.(.+)$")
+
+
+def packed_pieces(prefix: str, names) -> list[str] | None:
+    """Packed matrix names (model.layers.N.<kind>) that make up the vLLM layer at `prefix`, or None
+    when the layer is not packed (same rule as shapequant/vllm_ext/core.py:127-142)."""
+    m = _LAYER.search(prefix)
+    if m is None:
+        return None
+    i, suffix = m.group(1), m.group(2)
+    pieces = [f"model.layers.{i}.{s}" for s in STACKED.get(suffix, (suffix,))]
+    have = [p in names for p in pieces]
+    if all(have):
+        return pieces
+    if any(have):
+        raise ValueError(f"{prefix}: only some of its pieces are packed ({pieces})")
+    return None
 
 
 class PackedShards:

@@ -119,3 +119,56 @@ def test_sharded_linears_on_one_gpu(world, books, M):
             acc += part
         tol = 1e-3 if (B <= 64 or books == 1) else 1e-2      # >64 tokens with two books: 16-bit decode + library GEMM
         assert orc.max_rel_err(acc.cpu().numpy(), yfull) < tol, (world, books, M, B)
+
+
+def test_vllm_plugin_registers_the_method_and_pickles():
+    pytest.importorskip("vllm")
+    import pickle
+    from quantexperiments_b200.vllm_ext import plugin
+    cfg = plugin.ShapeQuantConfig.from_config({"packed_file": "x.packed", "bmax": 32, "layout": "tile", "tune": True})
+    assert cfg.get_name() == "shapequant" and cfg.bmax == 32 and cfg.get_min_capability() == 100
+    assert pickle.loads(pickle.dumps(cfg)).packed_file == "x.packed"
+    with pytest.raises(ValueError):
+        plugin.ShapeQuantConfig("x.packed", embed_head="packed")
+    from quantexperiments_b200.vllm_ext import core
+    names = {"model.layers.3.self_attn.q_proj", "model.layers.3.self_attn.k_proj", "model.layers.3.self_attn.v_proj"}
+    assert core.packed_pieces("model.layers.3.self_attn.qkv_proj", names) == sorted(names, key=lambda n: "qkv".index(n[-6]))
+    assert core.packed_pieces("model.layers.3.mlp.down_proj", names) is None
+    with pytest.raises(ValueError):
+        core.packed_pieces("model.layers.3.self_attn.qkv_proj", {"model.layers.3.self_attn.q_proj"})
+
+
+@pytest.mark.gpu
+def test_vllm_layer_shards_under_tensor_parallelism(tmp_path):
+    pytest.importorskip("vllm")
+    from quantexperiments_b200 import packed
+    from quantexperiments_b200.vllm_ext import plugin
+    g = torch.Generator().manual_seed(0)
+    K, d = 4096, 8
+    mats, ref = {}, {}
+    for name, R, C in (("model.layers.0.self_attn.q_proj", 2048, 512), ("model.layers.0.self_attn.k_proj", 256, 512),
+                       ("model.layers.0.self_attn.v_proj", 256, 512), ("model.layers.0.self_attn.o_proj", 512, 2048)):
+        tags = torch.randint(0, K, (R, C // d), generator=g)
+        table = torch.randn(K, d, generator=g).half()
+        rs = (torch.rand(R, generator=g) * 0.02 + 0.01).half()
+        mats[name] = packed.pack_matrix(tags, table, rs, d=d, K=K, seed=1)
+        ref[name] = orc.decode_tensors(tags.numpy(), table.numpy(), rs.numpy(), None, None, np.arange(C)[None], K)
+    packed.save(tmp_path / "m.packed", mats, base_model="test/base")
+    pf = packed.PackedFile(tmp_path / "m.packed")
+    world = 2
+    qkv = [n for n in mats if n.endswith(("q_proj", "k_proj", "v_proj"))]
+    x = torch.randn(5, 512, generator=g).bfloat16()
+    outs = [plugin.build_shards(pf, qkv, input_size_per_partition=512, output_partition_sizes=[1024, 128, 128], input_size=512,
+                                output_size=2560, rank=r, world=world, device="cuda", bmax=32).forward(x.cuda()).float().cpu()
+            for r in range(world)]
+    for i, (name, off, n) in enumerate(zip(qkv, (0, 1024, 1152), (1024, 128, 128))):
+        full = orc.linear_ref(x.float().numpy(), ref[name])
+        got = torch.cat([o[:, off:off + n] for o in outs], 1).numpy()
+        assert orc.max_rel_err(got, full) < 1e-3 + 2.0 ** -8, name
+    xo = torch.randn(5, 2048, generator=g).bfloat16()
+    acc = 0
+    for r in range(world):
+        ps = plugin.build_shards(pf, ["model.layers.0.self_attn.o_proj"], input_size_per_partition=1024, output_partition_sizes=[512],
+                                 input_size=2048, output_size=512, rank=r, world=world, device="cuda", bmax=32)
+        acc = acc + ps.forward(xo[:, r * 1024:(r + 1) * 1024].contiguous().cuda().float()).cpu()
+    assert orc.max_rel_err(acc.numpy(), orc.linear_ref(xo.float().numpy(), ref["model.layers.0.self_attn.o_proj"])) < 1e-3 + 2.0 ** -7
