@@ -154,6 +154,20 @@ int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype,
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
 int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s);
 
+/* The same batch-1 product for callers that cannot hand the library any device memory of their
+ * own making (hosts that pre-partition the whole GPU into private pools, or plugin contracts that
+ * forbid allocator calls while serving).  The accumulators live in a fixed array compiled into the
+ * library: at most cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED);
+ * 256 KB + 256 B of every GPU that loads the library stay reserved until the process exits.
+ * The call allocates and frees nothing.  Its first use on a device looks the array's device address
+ * up (cudaGetSymbolAddress), so make that first call before any stream capture.  All calls share
+ * the one array: the call clears what it needs on its stream before launching, and two such
+ * products that overlap on the GPU (different streams, or a replayed graph beside a live call)
+ * race on it - serialise them.  Results equal cbl_gemv_l8's up to the order of the fp32 reductions.
+ * No counterpart in the reference (its launchers allocate through torch / CuPy). */
+int32_t cbl_gemv_l8_static_max_rows(void);
+int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s);
+
 /* ------------------------------------------------------------------------------------------
  * Prefill product on the same column-tile layout: y[t*ldy + r] = round_to(ydtype, row_scale[r] *
  * sum_c W[r, c] * x[t*ldx + c]) for t < ntok.  W tiles are decoded into shared memory and multiplied

@@ -589,3 +589,37 @@ extern "C" int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
     return v ? CBL_ETIMEOUT : CBL_OK;
 }
+
+// ------------------------------------------------------------------------------------ batch-1 product without caller work space
+//
+// Some hosts may not give this library a way to obtain device memory: a serving runtime that carves
+// all of HBM into its own pools at start-up, or a plugin slot whose contract forbids allocator calls
+// on the request path (an allocation can synchronise the device and fragments a pre-sized pool).
+// For them the fp32 row accumulators of the batch-1 product live in a fixed array inside the library
+// image instead of a caller buffer.  The array is part of every CUDA context that loads the library
+// (256 KB + 256 B per GPU, held until the process exits).
+constexpr int L8_STATIC_MAX_ROWS = 65536;
+static __device__ __align__(256) unsigned char g_l8_static_scratch[L8_STATIC_MAX_ROWS * 4 + 256];
+
+extern "C" int32_t cbl_gemv_l8_static_max_rows(void) { return L8_STATIC_MAX_ROWS; }
+
+extern "C" int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s) {
+    if (!m) return CBL_EINVAL;
+    if (m->R > L8_STATIC_MAX_ROWS) return CBL_EUNSUPPORTED;      // the built-in scratch holds 65536 rows at most
+    // The array's name is only a host-side handle; the device address comes from the runtime, once per
+    // device, with that device current.  (This first call per device should happen outside stream capture.)
+    static void* scratch_addr[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CBL_EUNSUPPORTED;
+    if (!scratch_addr[dev]) {
+        void* p = nullptr;
+        CBL_CUDA(cudaGetSymbolAddress(&p, g_l8_static_scratch));
+        scratch_addr[dev] = p;
+    }
+    // Every call shares the array and finds whatever the previous call left: clear the part this
+    // call accumulates into (accumulators and status word) on the caller's stream first.
+    const size_t bytes = cbl_gemv_l8_workspace_bytes(m->R);
+    CBL_CUDA(cudaMemsetAsync(scratch_addr[dev], 0, bytes, (cudaStream_t)s));
+    return cbl_gemv_l8(m, x, xdtype, y, ydtype, scratch_addr[dev], s);
+}

@@ -247,6 +247,20 @@ class L8Matrix:
     def nbytes(self) -> int:
         return self.words.numel() * 4 + self.frag.numel() * 4 * self.books
 
+    def run_static(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """y [R] = W . x using the scratch array built into the library instead of a work-space tensor:
+        for hosts that must not allocate (at most 65536 rows; calls must not overlap on the GPU). Both
+        x and y are caller tensors; nothing is allocated here."""
+        if self.R > lib.cbl_gemv_l8_static_max_rows():
+            raise ValueError(f"{self.R} rows exceed the built-in scratch ({lib.cbl_gemv_l8_static_max_rows()} rows)")
+        x, yv = x.reshape(-1), y.reshape(-1)
+        if x.numel() != self.C or not x.is_contiguous() or yv.numel() != self.R or not yv.is_contiguous():
+            raise ValueError("x must be a contiguous [C] vector and y a contiguous [R] vector")
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_l8_static", lib.cbl_gemv_l8_static(ctypes.byref(self.struct()), x.data_ptr(), _dt(x.dtype),
+                                                                    yv.data_ptr(), _dt(y.dtype), _stream()))
+        return y
+
     _stage: dict = {}
 
     def gemm(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
