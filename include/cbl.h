@@ -149,6 +149,15 @@ int cbl_repack_book(const void* table, void* out, cbl_stream s);
 size_t cbl_gemv_l8_workspace_bytes(int32_t R);
 int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s);
 
+/* Up to 4 matrices that read the same activation vector (q|k|v, gate|up) as ONE launch: their tiles
+ * form one work list, so launch, table-build and tail latencies are paid once.  ys[i] receives matrix
+ * i's output; the work space must hold the sum of cbl_gemv_l8_workspace_bytes(R_i) bytes, zero on
+ * entry, left zero.
+ * replaces the merged q|k|v and gate|up launches of shapequant/kernels/decode_e2e.py:453-485
+ *          (merge_runs) and the per-piece loop of shapequant/vllm_ext/core.py:376-384 (_small). */
+int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
+                      void* workspace, cbl_stream s);
+
 /* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
  * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */

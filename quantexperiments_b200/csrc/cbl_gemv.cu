@@ -319,8 +319,19 @@ extern "C" int cbl_trace_read(unsigned long long* host) { return (int)cudaMemcpy
 #define CBL_MARK(i) do { } while (0)
 #endif
 
+// Up to L8_MAX_GROUP matrices that share one activation vector (q|k|v, gate|up) run as ONE launch:
+// their tiles form one list, the work split and the tag ring run across matrix boundaries.
+constexpr int L8_MAX_GROUP = 4;
+struct L8Launch {
+    int n;                         // matrices in the group
+    int tile0[L8_MAX_GROUP + 1];   // prefix sums of their tile counts
+    cbl_l8 m[L8_MAX_GROUP];
+    float* acc[L8_MAX_GROUP];      // fp32 row accumulators of each matrix (zero on entry)
+    void* y[L8_MAX_GROUP];
+};
+
 template <int NT>
-__global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restrict__ x, int xdtype, float* __restrict__ acc,
+__global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const void* __restrict__ x, int xdtype,
                                                    unsigned int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int STAGES = L8_RING_BYTES / (NT * 48);
@@ -333,38 +344,40 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int ngroups = m.Rpad >> 2;
-    const int ntile1 = m.ntile / m.books;
-    const int nch = m.C >> 3;
-    // This block's contiguous range [a, e) of (tile, row group) pairs, tile-major.  With at least as many
-    // tiles as blocks a block takes whole tiles; otherwise every tile is cut into equal row ranges, one per
-    // block, so that each block builds exactly one table.
-    int64_t a, e;
+    const int ntile = P.tile0[P.n];
+    // This block's tiles [tile_first, tile_last] and row-group ranges: with at least as many tiles as
+    // blocks a block takes whole tiles; otherwise every tile is cut into equal row ranges, one per block,
+    // so that each block builds exactly one table.  part/nparts describe the cut of a single tile.
+    int tile_first, tile_last, part = 0, nparts = 1;
     {
         const int nb = (int)gridDim.x, b = (int)blockIdx.x;
-        if (m.ntile >= nb) {
-            const int base = m.ntile / nb, extra = m.ntile % nb;
-            const int t0 = b * base + min(b, extra), t1 = t0 + base + (b < extra ? 1 : 0);
-            a = (int64_t)t0 * ngroups;
-            e = (int64_t)t1 * ngroups;
+        if (ntile >= nb) {
+            const int base = ntile / nb, extra = ntile % nb;
+            tile_first = b * base + min(b, extra);
+            tile_last = tile_first + base + (b < extra ? 1 : 0) - 1;
         } else {
-            const int base = nb / m.ntile, extra = nb % m.ntile;
-            int tl, part, nparts;
-            if (b < extra * (base + 1)) { tl = b / (base + 1); part = b % (base + 1); nparts = base + 1; }
-            else { const int bb = b - extra * (base + 1); tl = extra + bb / base; part = bb % base; nparts = base; }
-            a = (int64_t)tl * ngroups + (int64_t)ngroups * part / nparts;
-            e = (int64_t)tl * ngroups + (int64_t)ngroups * (part + 1) / nparts;
+            const int base = nb / ntile, extra = nb % ntile;
+            if (b < extra * (base + 1)) { tile_first = b / (base + 1); part = b % (base + 1); nparts = base + 1; }
+            else { const int bb = b - extra * (base + 1); tile_first = extra + bb / base; part = bb % base; nparts = base; }
+            tile_last = tile_first;
         }
     }
-    if (a >= e) return;
+    if (tile_last < tile_first) return;
     CBL_MARK(0);
-    const int tile_first = (int)(a / ngroups), tile_last = (int)((e - 1) / ngroups);
-    const int gA = (int)(a - (int64_t)tile_first * ngroups), gE = (int)(e - (int64_t)tile_last * ngroups);
+    auto matrix_of = [&](int tl) { int mi = 0; while (mi + 1 < P.n && tl >= P.tile0[mi + 1]) mi++; return mi; };
+    // row groups [lo, hi) of tile tl that belong to this block
+    auto seg = [&](int tl, int& mi, int& lo, int& hi) {
+        mi = matrix_of(tl);
+        const int ng = P.m[mi].Rpad >> 2;
+        lo = (int)((int64_t)ng * part / nparts);
+        hi = (int)((int64_t)ng * (part + 1) / nparts);
+    };
     const uint32_t lut = cbl_smem_u32(s_lut), ring = cbl_smem_u32(s_ring), bar0 = cbl_smem_u32(s_bar);
     // iterations of this block: each covers up to NT row groups of one tile
     int nit = 0;
-    for (int tile = tile_first; tile <= tile_last; tile++) {
-        const int lo = tile == tile_first ? gA : 0, hi = tile == tile_last ? gE : ngroups;
+    for (int tl = tile_first; tl <= tile_last; tl++) {
+        int mi, lo, hi;
+        seg(tl, mi, lo, hi);
         nit += (hi - lo + NT - 1) / NT;
     }
     if (tid == 0) {
@@ -376,17 +389,20 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
     // Producers: lane 0 of warps 0..2 each stage one of the three tag planes; every producer keeps its
     // own cursor over the block's iterations.  Consumers: all threads.
     const bool producer = lane == 0 && warp < 3;
-    int ptile = tile_first, pg = gA, pit = 0;
+    int ptile = tile_first, pmi, plo, phi, pit = 0;
+    seg(ptile, pmi, plo, phi);
+    int pg = plo;
     auto issue = [&]() {
-        const int hi = ptile == tile_last ? gE : ngroups;
-        const int n = min(NT, hi - pg);
+        const cbl_l8& mm = P.m[pmi];
+        const int ng = mm.Rpad >> 2;
+        const int n = min(NT, phi - pg);
         const int stage = pit % STAGES;
         const uint32_t bar = bar0 + 8 * stage, dst = ring + stage * (NT * 48) + warp * (NT * 16);
         l8_mbar_expect_tx(bar, (uint32_t)n * 16u);
-        l8_bulk_g2s(dst, (const uint4*)m.words + ((int64_t)ptile * 3 + warp) * ngroups + pg, (uint32_t)n * 16u, bar);
+        l8_bulk_g2s(dst, (const uint4*)mm.words + ((int64_t)(ptile - P.tile0[pmi]) * 3 + warp) * ng + pg, (uint32_t)n * 16u, bar);
         pg += NT;
-        if (pg >= hi) { ptile++; pg = 0; }
         pit++;
+        if (pg >= phi && ptile < tile_last) { ptile++; seg(ptile, pmi, plo, phi); pg = plo; }
     };
     if (producer) issue();                                 // stage 0 now; the others after the first book reads are in flight
     CBL_MARK(7);
@@ -397,14 +413,17 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
     uint4 af[NIT / 2];
     float x0 = 0.f, x1 = 0.f;
     auto request = [&](int tl) {
-        const int book = tl / ntile1, ctile = tl - book * ntile1;
-        const uint4* fr = (const uint4*)(book ? m.frag2 : m.frag);
+        const int mi = matrix_of(tl);
+        const cbl_l8& mm = P.m[mi];
+        const int ntile1 = mm.ntile / mm.books, lt = tl - P.tile0[mi];
+        const int book = lt / ntile1, ctile = lt - book * ntile1;
+        const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
 #pragma unroll
         for (int i = 0; i < NIT / 2; i++) af[i] = __ldg(fr + (warp + i * NWARP) * 32 + lane);
         if (warp == XWARP) {
             const int chunk = ctile * 8 + g;
             x0 = x1 = 0.f;
-            if (chunk < nch) {
+            if (chunk < (mm.C >> 3)) {
                 x0 = cbl_load_in(x, xdtype, (int64_t)chunk * 8 + 2 * t);
                 x1 = cbl_load_in(x, xdtype, (int64_t)chunk * 8 + 2 * t + 1);
             }
@@ -412,10 +431,11 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
     };
     request(tile_first);
 
-    int tile = tile_first, cg = gA, built = -1;
+    int tile = tile_first, cmi, clo, chi, built = -1;
+    seg(tile, cmi, clo, chi);
+    int cg = clo;
     bool aborted = false;
     for (int it = 0; it < nit; it++) {
-        const int hi = tile == tile_last ? gE : ngroups;
         if (tile != built) {
             // ---- build T[c][e] for the tile's 8 chunk columns (its fragments and activations were requested
             // before the previous tile's lookups, or before the loop for the first tile)
@@ -456,7 +476,7 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
             if (it == 0) CBL_MARK(1);
         }
         const int stage = it % STAGES;
-        const int n = min(NT, hi - cg);
+        const int n = min(NT, chi - cg);
         if (!l8_mbar_wait(bar0 + 8 * stage, (uint32_t)(it / STAGES) & 1u)) s_abort = 1;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
         if (tid < n) {
@@ -474,12 +494,12 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
             float r1 = l8_row_sum(w0.y, w1.y, w2.y, lut);
             float r2 = l8_row_sum(w0.z, w1.z, w2.z, lut);
             float r3 = l8_row_sum(w0.w, w1.w, w2.w, lut);
-            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(acc + 4 * (int64_t)(cg + tid)), "f"(r0), "f"(r1), "f"(r2),
-                         "f"(r3)
+            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(P.acc[cmi] + 4 * (int64_t)(cg + tid)), "f"(r0), "f"(r1),
+                         "f"(r2), "f"(r3)
                          : "memory");
         }
         cg += NT;
-        if (cg >= hi) { tile++; cg = 0; }
+        if (cg >= chi && tile < tile_last) { tile++; seg(tile, cmi, clo, chi); cg = clo; }
     }
     if (aborted) {
         // a staged copy never completed: report, give the copies still in flight a bounded time, leave
@@ -492,29 +512,21 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(cbl_l8 m, const void* __restr
     CBL_MARK(3);
 }
 
-// y[r] = round(row_scale[r] * acc[r]); acc[r] = 0.  Four rows per thread.
-__global__ void __launch_bounds__(256) k_l8_finish(float4* __restrict__ acc, const __half* __restrict__ row_scale, void* __restrict__ y,
-                                                   int ydtype, int R, int ngroups) {
+// y[r] = round(row_scale[r] * acc[r]); acc[r] = 0.  Four rows per thread; blockIdx.y = matrix of the group.
+__global__ void __launch_bounds__(256) k_l8_finish(const __grid_constant__ L8Launch P, int ydtype) {
+    const int mi = blockIdx.y;
+    const cbl_l8& mm = P.m[mi];
     const int gi = blockIdx.x * blockDim.x + threadIdx.x;
-    if (gi >= ngroups) return;
+    if (gi >= (mm.Rpad >> 2)) return;
+    float4* acc = (float4*)P.acc[mi];
     const float4 v = __ldcg(acc + gi);
     __stcg(acc + gi, make_float4(0.f, 0.f, 0.f, 0.f));
     const float vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int u = 0; u < 4; u++) {
         const int r = gi * 4 + u;
-        if (r < R) cbl_store_out(y, ydtype, r, vv[u] * __half2float(row_scale[r]));
+        if (r < mm.R) cbl_store_out(P.y[mi], ydtype, r, vv[u] * __half2float(((const __half*)mm.row_scale)[r]));
     }
-}
-
-static int l8_threads() {
-    static int v = 0;
-    if (!v) {
-        const char* e = getenv("CBL_L8_THREADS");
-        v = e ? atoi(e) : 512;
-        if (v != 256 && v != 512) v = 512;
-    }
-    return v;
 }
 
 // Book in mma.m16n8k8 A-fragment order: uint4 [128][32] = {a0, a1 of codeword block 2p, a0, a1 of block 2p+1}
@@ -538,8 +550,29 @@ extern "C" int cbl_repack_book(const void* table, void* out, cbl_stream s) {
     return cbl_check_launch();
 }
 
+static int l8_threads() {
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("CBL_L8_THREADS");
+        v = e ? atoi(e) : 512;
+        if (v != 256 && v != 512) v = 512;
+    }
+    return v;
+}
+
+static int check_l8(const cbl_l8* m) {
+    if (!m || !m->words || !m->frag || !m->row_scale) return CBL_EINVAL;
+    if (m->books != 1 && m->books != 2) return CBL_EINVAL;
+    if (m->books == 2 && !m->frag2) return CBL_EINVAL;
+    if (m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4) return CBL_EINVAL;
+    if (m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+    if (((uintptr_t)m->words % 16) || ((uintptr_t)m->frag % 16)) return CBL_EINVAL;
+    if (m->books == 2 && ((uintptr_t)m->frag2 % 16)) return CBL_EINVAL;
+    return CBL_OK;
+}
+
 template <int NT>
-static int launch_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cudaStream_t st) {
+static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, unsigned int* status, cudaStream_t st) {
     const size_t smem = (size_t)8 * L8_COL_WORDS * 4 + L8_RING_BYTES;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -548,35 +581,58 @@ static int launch_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int yd
         CBL_CUDA(cudaFuncSetAttribute(k_gemv_l8<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev] = true;
     }
-    const int ngroups = m->Rpad / 4;
     // one block per SM at most; a tile is cut into row ranges of at least 128 groups (512 rows) each
+    int ntile = P.tile0[P.n], max_groups = 0, min_groups = 1 << 30;
+    for (int i = 0; i < P.n; i++) {
+        max_groups = max_groups > (P.m[i].Rpad >> 2) ? max_groups : (P.m[i].Rpad >> 2);
+        min_groups = min_groups < (P.m[i].Rpad >> 2) ? min_groups : (P.m[i].Rpad >> 2);
+    }
     int grid = cbl_sm_count();
-    int parts = ngroups / 128;
+    int parts = min_groups / 128;
     if (parts < 1) parts = 1;
-    if ((int64_t)m->ntile * parts < grid) grid = m->ntile * parts;
-    float* acc = (float*)workspace;
-    unsigned int* status = (unsigned int*)((char*)workspace + (size_t)m->Rpad * 4);
-    k_gemv_l8<NT><<<grid, NT, smem, st>>>(*m, x, xdtype, acc, status);
+    if ((int64_t)ntile * parts < grid) grid = ntile * parts;
+    k_gemv_l8<NT><<<grid, NT, smem, st>>>(P, x, xdtype, status);
     int rc = cbl_check_launch();
     if (rc) return rc;
-    k_l8_finish<<<cbl_ceil_div(ngroups, 256), 256, 0, st>>>((float4*)acc, (const __half*)m->row_scale, y, ydtype, m->R, ngroups);
+    k_l8_finish<<<dim3(cbl_ceil_div(max_groups, 256), P.n), 256, 0, st>>>(P, ydtype);
     return cbl_check_launch();
 }
 
-extern "C" int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s) {
-    if (!m || !m->words || !m->frag || !m->row_scale || !x || !y || !workspace) return CBL_EINVAL;
-    if (m->books != 1 && m->books != 2) return CBL_EINVAL;
-    if (m->books == 2 && !m->frag2) return CBL_EINVAL;
-    if (m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4) return CBL_EINVAL;
-    if (m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+extern "C" int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
+                                 void* workspace, cbl_stream s) {
+    if (!mats || !ys || !x || !workspace || n < 1) return CBL_EINVAL;
+    if (n > L8_MAX_GROUP) return CBL_EUNSUPPORTED;
     if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
     if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
-    if (((uintptr_t)m->words % 16) || ((uintptr_t)workspace % 16) || ((uintptr_t)m->frag % 16)) return CBL_EINVAL;
-    if (m->books == 2 && ((uintptr_t)m->frag2 % 16)) return CBL_EINVAL;
-    if (m->R == 0) return CBL_OK;
+    if ((uintptr_t)workspace % 16) return CBL_EINVAL;
+    L8Launch P;
+    P.n = 0;
+    P.tile0[0] = 0;
+    size_t off = 0;
+    for (int i = 0; i < n; i++) {
+        int rc = check_l8(mats + i);
+        if (rc) return rc;
+        if (mats[i].C != mats[0].C) return CBL_EINVAL;          // one shared activation vector
+        if (!ys[i]) return CBL_EINVAL;
+        if (mats[i].R == 0) continue;
+        P.m[P.n] = mats[i];
+        P.acc[P.n] = (float*)((char*)workspace + off);
+        P.y[P.n] = ys[i];
+        P.tile0[P.n + 1] = P.tile0[P.n] + mats[i].ntile;
+        off += (size_t)mats[i].Rpad * 4;
+        P.n++;
+    }
+    if (P.n == 0) return CBL_OK;
+    unsigned int* status = (unsigned int*)((char*)workspace + off);
     cudaStream_t st = (cudaStream_t)s;
-    if (l8_threads() == 256) return launch_l8<256>(m, x, xdtype, y, ydtype, workspace, st);
-    return launch_l8<512>(m, x, xdtype, y, ydtype, workspace, st);
+    if (l8_threads() == 256) return launch_l8<256>(P, x, xdtype, ydtype, status, st);
+    return launch_l8<512>(P, x, xdtype, ydtype, status, st);
+}
+
+extern "C" int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s) {
+    if (!m || !y) return CBL_EINVAL;
+    void* ys[1] = {y};
+    return cbl_gemv_l8_multi(m, 1, x, xdtype, ys, ydtype, workspace, s);
 }
 
 // Reads the status word a product leaves in its work space (0 = ok, nonzero = a bounded device-side

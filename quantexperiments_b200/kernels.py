@@ -208,11 +208,11 @@ class T16Matrix:
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
 
 
-def l8_workspace(device: torch.device, R: int) -> torch.Tensor:
+def l8_workspace(device: torch.device, R: int, nbytes: int = 0) -> torch.Tensor:
     """Zero-initialised work space shared by every L8 product on (device, current stream): the kernel
     leaves it zero. Products that may overlap on the device (different streams) get distinct buffers."""
     key = (device.index, _stream())
-    need = lib.cbl_gemv_l8_workspace_bytes(R)
+    need = max(lib.cbl_gemv_l8_workspace_bytes(R), nbytes)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         ws = _WORKSPACES[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
@@ -310,3 +310,38 @@ class L8Matrix:
             _lib.check("cbl_gemv_l8", lib.cbl_gemv_l8(ctypes.byref(self.struct()), x.data_ptr(), _dt(x.dtype), yv.data_ptr(),
                                                       _dt(y.dtype), ws.data_ptr(), _stream()))
         return y
+
+
+class L8Group:
+    """Up to four column-tile matrices that read the same activation vector (q|k|v, gate|up), run as
+    one launch: run(x, ys) writes each matrix's output into its own contiguous vector."""
+
+    MAX = 4
+
+    def __init__(self, mats: list[L8Matrix]):
+        if not 1 <= len(mats) <= self.MAX:
+            raise ValueError(f"a group holds 1..{self.MAX} matrices")
+        if len({m.C for m in mats}) != 1 or len({m.device for m in mats}) != 1:
+            raise ValueError("grouped matrices share the input size and the device")
+        self.mats, self.C, self.device = mats, mats[0].C, mats[0].device
+        self.Rs = [m.R for m in mats]
+        self._structs = (_lib.L8 * len(mats))(*[m.struct() for m in mats])
+        self._ys = (ctypes.c_void_p * len(mats))()
+        self.ws_bytes = sum(lib.cbl_gemv_l8_workspace_bytes(m.R) for m in mats)
+
+    def run(self, x: torch.Tensor, ys: list[torch.Tensor]) -> list[torch.Tensor]:
+        x = x.reshape(-1)
+        if x.numel() != self.C or not x.is_contiguous() or x.device != self.device:
+            raise ValueError("x must be a contiguous [C] vector on the matrices' device")
+        if len(ys) != len(self.mats):
+            raise ValueError("one output vector per matrix")
+        dt = ys[0].dtype
+        for i, (y, R) in enumerate(zip(ys, self.Rs)):
+            if y.numel() != R or not y.is_contiguous() or y.dtype != dt:
+                raise ValueError("outputs must be contiguous [R_i] vectors of one dtype")
+            self._ys[i] = y.data_ptr()
+        ws = l8_workspace(self.device, 0, self.ws_bytes)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_l8_multi", lib.cbl_gemv_l8_multi(self._structs, len(self.mats), x.data_ptr(), _dt(x.dtype), self._ys,
+                                                                  _dt(dt), ws.data_ptr(), _stream()))
+        return ys

@@ -16,8 +16,8 @@ import re
 
 import torch
 
-from ..kernels import T16Matrix
-from ..linear import PackedLinear, _Scratch
+from ..kernels import L8Group, T16Matrix
+from ..linear import L8_MIN_ROWS, PackedLinear, _Scratch
 
 BMAX = T16Matrix.BMAX
 
@@ -66,6 +66,10 @@ class PackedShards:
             for b in range(1, bmax + 1, 8):
                 lin.t16.xp_buffer(b)
         _Scratch.get(max(self.Rs) * self.C, self.device, torch.bfloat16)
+        # one token: all pieces in one launch when they share a column order and the stack is tall enough
+        self.group = None
+        if all(lin.dm.M == 1 for lin in lins) and self.R >= L8_MIN_ROWS and len(lins) <= L8Group.MAX:
+            self.group = L8Group([lin.l8 for lin in lins])
 
     @classmethod
     def from_packed(cls, pf, names: list[str], dev="cuda", **kw) -> "PackedShards":
@@ -100,6 +104,9 @@ class PackedShards:
 
     def _small(self, x: torch.Tensor, M: int) -> torch.Tensor:
         y = torch.empty(M, self.R, dtype=x.dtype, device=x.device)
+        if M == 1 and self.group is not None:
+            self.group.run(x[0], [y[0, off:off + R] for off, R in zip(self.offs, self.Rs)])
+            return y
         for lin, off, R in zip(self.lins, self.offs, self.Rs):
             if M == 1 and lin.use_l8():
                 lin.l8.run(x[0], y[0, off:off + R])

@@ -348,3 +348,21 @@ def test_packed_shards_and_custom_op(tmp_path):
     fn = torch.compile(lambda t: torch.ops.shapequant.linear(t, h) * 2, backend="aot_eager", fullgraph=True)
     x = torch.randn(3, C, device="cuda", dtype=torch.bfloat16)
     assert torch.equal(fn(x), torch.ops.shapequant.linear(x, h) * 2)
+
+
+@pytest.mark.parametrize("shapes,C", [([(3584, 1), (512, 1), (512, 1)], 896), ([(2304, 1), (2304, 2)], 512), ([(260, 1)], 64),
+                                      ([(128, 1), (128, 1), (128, 1), (4100, 1)], 1024)])
+def test_grouped_batch1_launch_matches_fp32_matmul(shapes, C):
+    from quantexperiments_b200.kernels import L8Group, L8Matrix
+    ms = [orc.synth_matrix(R, C, seed=R + i + books, books=books) for i, (R, books) in enumerate(shapes)]
+    grp = L8Group([L8Matrix(_dm(m)) for m in ms])
+    g = torch.Generator().manual_seed(C)
+    for it in range(2):
+        x = torch.randn(C, generator=g).bfloat16()
+        ys = [torch.full((m["R"],), float("nan"), device="cuda") for m in ms]
+        grp.run(x.cuda(), ys)
+        for m, y in zip(ms, ys):
+            yref = orc.linear_ref(x.float().numpy()[None], orc.synth_decode(m))[0]
+            assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
+    with pytest.raises(ValueError):
+        grp.run(x.cuda(), ys[:-1] + [ys[-1].double()] if len(ys) > 1 else [])
