@@ -190,6 +190,12 @@ size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C);
 int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
                 void* stage, void* workspace, cbl_stream s);
 
+/* The same product computed by clusters of two thread blocks with tcgen05.mma.cta_group::2 (512-token x
+ * 256-row tiles; each block decodes half of the weight tile).  Same arguments and results; measured
+ * slower than cbl_gemm_l8 on B200 at present, kept as the two-SM variant of the design. */
+int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                    void* stage, void* workspace, cbl_stream s);
+
 #ifdef __cplusplus
 }
 #endif

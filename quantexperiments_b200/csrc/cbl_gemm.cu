@@ -20,12 +20,13 @@ namespace {
 constexpr int GM_BM = 256;                 // tokens per tile (2 accumulators of 128)
 constexpr int GM_BN = 256;                 // W rows per tile (UMMA N)
 constexpr int GM_BK = 64;                  // k-block: 8 chunks, one 128-byte swizzled row
-constexpr int GM_STAGES = 2;
+constexpr int GM_A_STAGES = 3;             // activation (TMA) ring: 3 x 32 KB
+constexpr int GM_B_STAGES = 2;             // decoded weight ring: 2 x 32 KB
 constexpr int GM_A_BYTES = 128 * GM_BK * 2;            // one 128-token box
-constexpr int GM_STAGE_BYTES = 2 * GM_A_BYTES + GM_BN * GM_BK * 2;   // 64 KB
-constexpr int GM_SMEM = 65536 + GM_STAGES * GM_STAGE_BYTES;           // book + stages
+constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;
+constexpr int GM_SMEM = 65536 + GM_A_STAGES * 2 * GM_A_BYTES + GM_B_STAGES * GM_B_BYTES;   // book + rings = 224 KB
 constexpr int GM_DECODE_WARPS = 8, GM_THREADS = (GM_DECODE_WARPS + 2) * 32;
-constexpr uint32_t GM_WAIT_LIMIT = 1u << 20;   // mbarrier polls before a wait gives up
+constexpr uint32_t GM_WAIT_LIMIT = 1u << 24;   // mbarrier polls (a few tens of cycles each) before a wait gives up
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -36,10 +37,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Bounded wait for a phase of an mbarrier: a non-blocking test in a spin loop (the blocking try_wait form
+// adds wake-up latency to every pipeline hand-off); false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < GM_WAIT_LIMIT; i++) {
         uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(ok)
                      : "r"(bar), "r"(parity)
                      : "memory");
@@ -83,29 +86,71 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr));
 }
 
+// One token's 32 consecutive outputs: row scales as four 16-byte loads, outputs as 16-byte stores when aligned.
+__device__ __forceinline__ void gemm_store_row32(const uint32_t (&v)[32], int tok, int ntok, int rbase, const cbl_l8& m, float tsc,
+                                                 void* __restrict__ y, int ydtype, int64_t ldy, int vec_ok) {
+    if (tok >= ntok || rbase >= m.R) return;
+    if (vec_ok && rbase + 32 <= m.R) {
+        union { uint4 u[4]; __half h[32]; } rsv;
+        const uint4* rp = (const uint4*)((const __half*)m.row_scale + rbase);
+#pragma unroll
+        for (int j = 0; j < 4; j++) rsv.u[j] = __ldg(rp + j);
+        float o[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * tsc * __half2float(rsv.h[j]);
+        if (ydtype == CBL_F32) {
+            float4* dst = (float4*)((float*)y + (int64_t)tok * ldy + rbase);
+#pragma unroll
+            for (int j = 0; j < 8; j++) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        } else {
+            union { uint4 u[4]; __nv_bfloat16 b[32]; __half h[32]; } pk;
+            if (ydtype == CBL_BF16) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) pk.b[j] = __float2bfloat16_rn(o[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) pk.h[j] = __float2half_rn(o[j]);
+            }
+            uint4* dst = (uint4*)((char*)y + ((int64_t)tok * ldy + rbase) * 2);
+#pragma unroll
+            for (int j = 0; j < 4; j++) dst[j] = pk.u[j];
+        }
+    } else {
+#pragma unroll 1
+        for (int j = 0; j < 32; j++) {
+            const int r = rbase + j;
+            if (r < m.R) {
+                const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
+                cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, __uint_as_float(v[j]) * tsc * rs);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __restrict__ xinv, int ntok, void* __restrict__ y, int ydtype,
           int64_t ldy, int vec_ok, unsigned int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_bar[3 * GM_STAGES + 1];   // full_a, full_b, empty per stage; tmem_full
+    // barriers: full_a / empty_a per activation stage, full_b / empty_b per weight stage, tmem_full
+    __shared__ __align__(8) unsigned long long s_bar[2 * GM_A_STAGES + 2 * GM_B_STAGES + 1];
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // row tiles vary fastest across the grid: blocks that run together share one activation tile in L2
     const int r0 = blockIdx.x * GM_BN, tok0 = blockIdx.y * GM_BM;
     const int nkb = m.ntile;                                  // books == 1: one tile of the l8 layout per k-block
     const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
     auto full_a = [&](int s) { return bar0 + 8u * s; };
-    auto full_b = [&](int s) { return bar0 + 8u * (GM_STAGES + s); };
-    auto empty = [&](int s) { return bar0 + 8u * (2 * GM_STAGES + s); };
-    const uint32_t tmem_full = bar0 + 8u * (3 * GM_STAGES);
+    auto empty_a = [&](int s) { return bar0 + 8u * (GM_A_STAGES + s); };
+    auto full_b = [&](int s) { return bar0 + 8u * (2 * GM_A_STAGES + s); };
+    auto empty_b = [&](int s) { return bar0 + 8u * (2 * GM_A_STAGES + GM_B_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (2 * GM_A_STAGES + 2 * GM_B_STAGES);
+    const uint32_t a_base = sbase + 65536, b_base = a_base + GM_A_STAGES * 2 * GM_A_BYTES;
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < GM_STAGES; s++) {
-            mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), GM_DECODE_WARPS);
-            mbar_init(empty(s), 1);
-        }
+        for (int s = 0; s < GM_A_STAGES; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
+        for (int s = 0; s < GM_B_STAGES; s++) { mbar_init(full_b(s), GM_DECODE_WARPS); mbar_init(empty_b(s), 1); }
         mbar_init(tmem_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -125,13 +170,14 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
     const uint32_t tmem = s_tmem;
 
     if (warp == GM_DECODE_WARPS) {
-        // ---------------- TMA producer of the activations
+        // ---------------- TMA producer of the activations (its ring is deeper than the weights': the
+        // round trip through L2 is several k-blocks long)
         if (lane == 0) {
             for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % GM_STAGES;
-                if (!mbar_wait(empty(s), ((kb / GM_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+                const int s = kb % GM_A_STAGES;
+                if (!mbar_wait(empty_a(s), ((kb / GM_A_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
                 mbar_expect_tx(full_a(s), 2 * GM_A_BYTES);
-                const uint32_t dst = sbase + 65536 + s * GM_STAGE_BYTES;
+                const uint32_t dst = a_base + s * 2 * GM_A_BYTES;
                 tma_load_2d(dst, &xmap, kb * GM_BK, tok0, full_a(s));
                 tma_load_2d(dst + GM_A_BYTES, &xmap, kb * GM_BK, tok0 + 128, full_a(s));
             }
@@ -140,14 +186,11 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
         // ---------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f16 x f16 -> f32, K-major both
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % GM_STAGES;
-                const uint32_t par = (kb / GM_STAGES) & 1;
-                ok = mbar_wait(full_a(s), par) && mbar_wait(full_b(s), par);
-                if (!ok) { s_abort = 1; break; }
+            for (int kb = 0; kb < nkb; kb++) {
+                const int sa = kb % GM_A_STAGES, sb = kb % GM_B_STAGES;
+                if (!(mbar_wait(full_a(sa), (kb / GM_A_STAGES) & 1) && mbar_wait(full_b(sb), (kb / GM_B_STAGES) & 1))) { s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = sbase + 65536 + s * GM_STAGE_BYTES, b_addr = a_addr + 2 * GM_A_BYTES;
+                const uint32_t a_addr = a_base + sa * 2 * GM_A_BYTES, b_addr = b_base + sb * GM_B_BYTES;
 #pragma unroll
                 for (int tb = 0; tb < 2; tb++) {
 #pragma unroll
@@ -157,7 +200,8 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
                         umma_f16(tmem + tb * GM_BN, da, db, idesc, (kb | kk) ? 1u : 0u);
                     }
                 }
-                umma_commit(empty(s));
+                umma_commit(empty_a(sa));
+                umma_commit(empty_b(sb));
             }
             umma_commit(tmem_full);       // arrives when every MMA issued so far has completed
         }
@@ -180,10 +224,10 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
         const uint32_t sw = (uint32_t)(tid & 7);
         const uint32_t rowoff = (uint32_t)(tid >> 3) * 1024u + sw * 128u;
         for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % GM_STAGES;
+            const int s = kb % GM_B_STAGES;
             load_tags(kb + 2, fa, fb, fc);
-            if (!mbar_wait(empty(s), ((kb / GM_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
-            const uint32_t bdst = sbase + 65536 + s * GM_STAGE_BYTES + 2 * GM_A_BYTES + rowoff;
+            if (!mbar_wait(empty_b(s), ((kb / GM_B_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+            const uint32_t bdst = b_base + s * GM_B_BYTES + rowoff;
             uint32_t off[8];
             off[0] = (wa << 4) & 0xFFF0u;
             off[1] = (wa >> 8) & 0xFFF0u;
@@ -193,13 +237,14 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
             off[5] = __funnelshift_r(wb, wc, 24) & 0xFFF0u;
             off[6] = (wc >> 4) & 0xFFF0u;
             off[7] = (wc >> 16) & 0xFFF0u;
+            uint4 cw[8];
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const uint4 cw = cbl_lds128(sbase + off[c]);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bdst + (((uint32_t)c ^ sw) << 4)), "r"(cw.x), "r"(cw.y), "r"(cw.z),
-                             "r"(cw.w)
+            for (int c = 0; c < 8; c++) cw[c] = cbl_lds128(sbase + off[c]);      // all eight gathers in flight before the stores
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bdst + (((uint32_t)c ^ sw) << 4)), "r"(cw[c].x), "r"(cw[c].y),
+                             "r"(cw[c].z), "r"(cw[c].w)
                              : "memory");
-            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_b(s));
@@ -218,44 +263,7 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(tb * GM_BN + c0), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int rbase = r0 + c0;
-                if (tok >= ntok || rbase >= m.R) continue;
-                if (vec_ok && rbase + 32 <= m.R) {
-                    // 32 consecutive outputs of this token: row scales as four 16-byte loads, outputs as 16-byte stores
-                    union { uint4 u[4]; __half h[32]; } rsv;
-                    const uint4* rp = (const uint4*)((const __half*)m.row_scale + rbase);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) rsv.u[j] = __ldg(rp + j);
-                    float o[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * tsc * __half2float(rsv.h[j]);
-                    if (ydtype == CBL_F32) {
-                        float4* dst = (float4*)((float*)y + (int64_t)tok * ldy + rbase);
-#pragma unroll
-                        for (int j = 0; j < 8; j++) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                    } else {
-                        union { uint4 u[4]; __nv_bfloat16 b[32]; __half h[32]; } pk;
-                        if (ydtype == CBL_BF16) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) pk.b[j] = __float2bfloat16_rn(o[j]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) pk.h[j] = __float2half_rn(o[j]);
-                        }
-                        uint4* dst = (uint4*)((char*)y + ((int64_t)tok * ldy + rbase) * 2);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) dst[j] = pk.u[j];
-                    }
-                } else {
-#pragma unroll 1
-                    for (int j = 0; j < 32; j++) {
-                        const int r = rbase + j;
-                        if (r < m.R) {
-                            const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
-                            cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, __uint_as_float(v[j]) * tsc * rs);
-                        }
-                    }
-                }
+                gemm_store_row32(v, tok, ntok, r0 + c0, m, tsc, y, ydtype, ldy, vec_ok);
             }
         }
     }
@@ -265,6 +273,201 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
     if (warp == GM_DECODE_WARPS) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------ two-SM variant
+//
+// A cluster of two blocks computes a 512-token x 256-row tile with tcgen05.mma.cta_group::2 (M 256 split
+// over the two SMs, N 256).  Each block loads its own 2 x 128 tokens of activations and decodes only
+// HALF of the B tile (128 W rows), so the shared-memory cost of decoding per MMA cycle halves.  The MMA
+// is issued by the leader block (cluster rank 0); "full" barriers live in the leader and are signalled by
+// both blocks (TMA complete_tx and remote arrives), "empty" and "accumulators ready" are multicast
+// commits to both blocks.
+constexpr int G2_STAGES = 3;
+constexpr int G2_B_BYTES = 128 * GM_BK * 2;                              // this block's half of the B tile
+constexpr int G2_STAGE_BYTES = 2 * GM_A_BYTES + G2_B_BYTES;              // 48 KB
+constexpr int G2_SMEM = 65536 + G2_STAGES * G2_STAGE_BYTES;
+constexpr int G2_DECODE_WARPS = 4, G2_THREADS = (G2_DECODE_WARPS + 2) * 32;
+
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_f16_2sm(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(G2_THREADS, 1)
+k_gemm_l8_2sm(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __restrict__ xinv, int ntok, void* __restrict__ y, int ydtype,
+              int64_t ldy, int vec_ok, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_bar[3 * G2_STAGES + 1];   // full_a, full_b, empty per stage; tmem_full
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int r0 = (blockIdx.x >> 1) * GM_BN, tok_base = blockIdx.y * 512;
+    const int nkb = m.ntile;
+    const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
+    auto full_a = [&](int s) { return bar0 + 8u * s; };
+    auto full_b = [&](int s) { return bar0 + 8u * (G2_STAGES + s); };
+    auto empty = [&](int s) { return bar0 + 8u * (2 * G2_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (3 * G2_STAGES);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < G2_STAGES; s++) {
+            mbar_init(full_a(s), 1);                          // the leader's expect_tx arrival; bytes come from both blocks
+            mbar_init(full_b(s), 2 * G2_DECODE_WARPS);        // decode warps of both blocks
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == G2_DECODE_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    if (warp < G2_DECODE_WARPS) {
+        const uint4* t0 = (const uint4*)m.table;
+        uint4* dst = (uint4*)smem;
+        for (int i = tid; i < 4096; i += G2_DECODE_WARPS * 32) dst[i] = __ldg(t0 + i);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                        // both blocks' barriers and tensor memory exist
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == G2_DECODE_WARPS) {
+        // ---------------- TMA producer: this block's 2 x 128 tokens; completion lands on the leader's barrier
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % G2_STAGES;
+                if (!mbar_wait(empty(s), ((kb / G2_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+                if (rank == 0) mbar_expect_tx(full_a(s), 2 * 2 * GM_A_BYTES);
+                const uint32_t dst = sbase + 65536 + s * G2_STAGE_BYTES;
+                const uint32_t lead_bar = mapa_u32(full_a(s), 0);
+                tma_load_2d_2sm(dst, &xmap, kb * GM_BK, tok_base + (int)rank * 128, lead_bar);
+                tma_load_2d_2sm(dst + GM_A_BYTES, &xmap, kb * GM_BK, tok_base + 256 + (int)rank * 128, lead_bar);
+            }
+        }
+    } else if (warp == G2_DECODE_WARPS + 1) {
+        // ---------------- MMA issuer (leader block only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % G2_STAGES;
+                const uint32_t par = (kb / G2_STAGES) & 1;
+                if (!(mbar_wait(full_a(s), par) && mbar_wait(full_b(s), par))) { s_abort = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = sbase + 65536 + s * G2_STAGE_BYTES, b_addr = a_addr + 2 * GM_A_BYTES;
+#pragma unroll
+                for (int tb = 0; tb < 2; tb++) {
+#pragma unroll
+                    for (int kk = 0; kk < GM_BK / 16; kk++) {
+                        const uint64_t da = umma_desc_sw128(a_addr + tb * GM_A_BYTES + kk * 32);
+                        const uint64_t db = umma_desc_sw128(b_addr + kk * 32);
+                        umma_f16_2sm(tmem + tb * GM_BN, da, db, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                }
+                umma_commit_2sm(empty(s));
+            }
+            umma_commit_2sm(tmem_full);
+        }
+    } else {
+        // ---------------- decode: thread t owns W row r0 + 128*rank + t (this block's half of the B tile)
+        const int row = r0 + (int)rank * 128 + tid;
+        const bool live = row < m.Rpad;
+        const uint32_t* wp = (const uint32_t*)m.words + row;
+        uint32_t wa = 0, wb = 0, wc = 0, na = 0, nb = 0, nc = 0, fa = 0, fb = 0, fc = 0;
+        auto load_tags = [&](int kb, uint32_t& a, uint32_t& b, uint32_t& c) {
+            a = b = c = 0;
+            if (live && kb < nkb) {
+                const uint32_t* p = wp + (int64_t)kb * 3 * m.Rpad;
+                a = __ldg(p); b = __ldg(p + m.Rpad); c = __ldg(p + 2 * (int64_t)m.Rpad);
+            }
+        };
+        load_tags(0, wa, wb, wc);
+        load_tags(1, na, nb, nc);
+        const uint32_t sw = (uint32_t)(tid & 7);
+        const uint32_t rowoff = (uint32_t)(tid >> 3) * 1024u + sw * 128u;
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % G2_STAGES;
+            load_tags(kb + 2, fa, fb, fc);
+            if (!mbar_wait(empty(s), ((kb / G2_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+            const uint32_t bdst = sbase + 65536 + s * G2_STAGE_BYTES + 2 * GM_A_BYTES + rowoff;
+            uint32_t off[8];
+            off[0] = (wa << 4) & 0xFFF0u;
+            off[1] = (wa >> 8) & 0xFFF0u;
+            off[2] = __funnelshift_r(wa, wb, 20) & 0xFFF0u;
+            off[3] = wb & 0xFFF0u;
+            off[4] = (wb >> 12) & 0xFFF0u;
+            off[5] = __funnelshift_r(wb, wc, 24) & 0xFFF0u;
+            off[6] = (wc >> 4) & 0xFFF0u;
+            off[7] = (wc >> 16) & 0xFFF0u;
+            uint4 cw[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) cw[c] = cbl_lds128(sbase + off[c]);      // all eight gathers in flight before the stores
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bdst + (((uint32_t)c ^ sw) << 4)), "r"(cw[c].x), "r"(cw[c].y),
+                             "r"(cw[c].z), "r"(cw[c].w)
+                             : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(full_b(s), 0));
+            wa = na; wb = nb; wc = nc;
+            na = fa; nb = fb; nc = fc;
+        }
+        // ---------------- epilogue: warp q reads TMEM lanes 32q.. of both accumulators of this block
+        const bool ok = mbar_wait(tmem_full, 0);
+        if (!ok) s_abort = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3;
+        if (ok) {
+            for (int tb = 0; tb < 2; tb++) {
+                const int tok = tok_base + tb * 256 + (int)rank * 128 + q * 32 + lane;
+                const float tsc = (tok < ntok) ? xinv[tok] : 0.f;
+                for (int c0 = 0; c0 < GM_BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(tb * GM_BN + c0), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    gemm_store_row32(v, tok, ntok, r0 + c0, m, tsc, y, ydtype, ldy, vec_ok);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    cluster_sync_all();                                        // the peer no longer reads or signals this block's memory
+    if (warp == G2_DECODE_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -289,8 +492,8 @@ encode_tiled_fn get_encode() {
 // (the layout cbl_prep_x writes for one column order).
 extern "C" size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C) { return cbl_prep_x_bytes(ntok, C, 1); }
 
-extern "C" int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
-                           void* stage, void* workspace, cbl_stream s) {
+static int gemm_l8_impl(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                        void* stage, void* workspace, cbl_stream s, int two_sm) {
     if (!m || !m->words || !m->table || !m->row_scale || !x || !y || !stage || !workspace) return CBL_EINVAL;
     if (m->books != 1) return CBL_EUNSUPPORTED;
     if (m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
@@ -322,9 +525,42 @@ extern "C" int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t n
         attr_set[dev] = true;
     }
     const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
-    dim3 grid(cbl_ceil_div(m->R, GM_BN), cbl_ceil_div(ntok, GM_BM));
     const int esz = ydtype == CBL_F32 ? 4 : 2;
     const int vec_ok = ((uintptr_t)y % 16 == 0) && ((ldy * esz) % 16 == 0) && ((uintptr_t)m->row_scale % 16 == 0);
+    if (two_sm && ntok > GM_BM) {
+        static bool attr2_set[64] = {};
+        if (dev >= 0 && dev < 64 && !attr2_set[dev]) {
+            CBL_CUDA(cudaFuncSetAttribute(k_gemm_l8_2sm, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
+            attr2_set[dev] = true;
+        }
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * cbl_ceil_div(m->R, GM_BN), cbl_ceil_div(ntok, 512));
+        cfg.blockDim = dim3(G2_THREADS);
+        cfg.dynamicSmemBytes = G2_SMEM;
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_l8_2sm, map, *m, xinv, (int)ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace));
+        return cbl_check_launch();
+    }
+    dim3 grid(cbl_ceil_div(m->R, GM_BN), cbl_ceil_div(ntok, GM_BM));
     k_gemm_l8<<<grid, GM_THREADS, GM_SMEM, st>>>(map, *m, xinv, ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace);
     return cbl_check_launch();
+}
+
+extern "C" int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                           void* stage, void* workspace, cbl_stream s) {
+    return gemm_l8_impl(m, x, xdtype, ntok, ldx, y, ydtype, ldy, stage, workspace, s, 0);
+}
+
+// Same product with pairs of thread blocks on tcgen05.mma.cta_group::2 (each block decodes half of the
+// weight tile).  Token counts up to 256 run the one-block kernel.
+extern "C" int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                               void* stage, void* workspace, cbl_stream s) {
+    return gemm_l8_impl(m, x, xdtype, ntok, ldx, y, ydtype, ldy, stage, workspace, s, 1);
 }

@@ -364,6 +364,9 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
     }
     if (tile_last < tile_first) return;
     CBL_MARK(0);
+    // Programmatic dependent launch: let the next kernel in the stream (the finish kernel) get resident now;
+    // this kernel itself waits for its predecessor only where it first touches data that depends on it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     auto matrix_of = [&](int tl) { int mi = 0; while (mi + 1 < P.n && tl >= P.tile0[mi + 1]) mi++; return mi; };
     // row groups [lo, hi) of tile tl that belong to this block
     auto seg = [&](int tl, int& mi, int& lo, int& hi) {
@@ -420,6 +423,7 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
         const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
 #pragma unroll
         for (int i = 0; i < NIT / 2; i++) af[i] = __ldg(fr + (warp + i * NWARP) * 32 + lane);
+        if (tl == tile_first) asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the accumulators come from earlier kernels
         if (warp == XWARP) {
             const int chunk = ctile * 8 + g;
             x0 = x1 = 0.f;
@@ -514,6 +518,8 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
 
 // y[r] = round(row_scale[r] * acc[r]); acc[r] = 0.  Four rows per thread; blockIdx.y = matrix of the group.
 __global__ void __launch_bounds__(256) k_l8_finish(const __grid_constant__ L8Launch P, int ydtype) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // every partial sum of the product kernel has landed
     const int mi = blockIdx.y;
     const cbl_l8& mm = P.m[mi];
     const int gi = blockIdx.x * blockDim.x + threadIdx.x;
@@ -591,10 +597,23 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, u
     int parts = min_groups / 128;
     if (parts < 1) parts = 1;
     if ((int64_t)ntile * parts < grid) grid = ntile * parts;
-    k_gemv_l8<NT><<<grid, NT, smem, st>>>(P, x, xdtype, status);
-    int rc = cbl_check_launch();
-    if (rc) return rc;
-    k_l8_finish<<<dim3(cbl_ceil_div(max_groups, 256), P.n), 256, 0, st>>>(P, ydtype);
+    static int pdl = -1;
+    if (pdl < 0) { const char* e = getenv("CBL_PDL"); pdl = (e && atoi(e) == 0) ? 0 : 1; }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_l8<NT>, P, x, xdtype, status));
+    cfg.gridDim = dim3(cbl_ceil_div(max_groups, 256), P.n);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_l8_finish, P, ydtype));
     return cbl_check_launch();
 }
 

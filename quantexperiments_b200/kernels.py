@@ -263,9 +263,10 @@ class L8Matrix:
 
     _stage: dict = {}
 
-    def gemm(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
+    def gemm(self, X: torch.Tensor, Y: torch.Tensor | None = None, two_sm: bool = False) -> torch.Tensor:
         """Y [T, R] = X [T, C] . W^T on the tensor cores (prefill). X f16 / bf16 / f32 with unit column
-        stride; Y f16 / bf16 / f32 with unit column stride (its row stride is passed through)."""
+        stride; Y f16 / bf16 / f32 with unit column stride (its row stride is passed through).
+        two_sm selects the cta_group::2 variant (pairs of thread blocks per tile)."""
         if self.books != 1:
             raise ValueError("the prefill product executes one book per matrix")
         if X.dim() != 2 or X.shape[1] != self.C or X.stride(1) != 1 or X.device != self.device:
@@ -284,9 +285,9 @@ class L8Matrix:
             st = L8Matrix._stage[key] = torch.empty(need, dtype=torch.uint8, device=self.device)
         ws = l8_workspace(self.device, self.R)
         with torch.cuda.device(self.device):
-            _lib.check("cbl_gemm_l8", lib.cbl_gemm_l8(ctypes.byref(self.struct()), X.data_ptr(), _dt(X.dtype), T, X.stride(0),
-                                                      Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
-                                                      ws.data_ptr() + self.Rpad * 4, _stream()))
+            fn = lib.cbl_gemm_l8_2sm if two_sm else lib.cbl_gemm_l8
+            _lib.check("cbl_gemm_l8", fn(ctypes.byref(self.struct()), X.data_ptr(), _dt(X.dtype), T, X.stride(0), Y.data_ptr(),
+                                         _dt(Y.dtype), Y.stride(0), st.data_ptr(), ws.data_ptr() + self.Rpad * 4, _stream()))
         return Y
 
     def status(self, workspace: torch.Tensor | None = None) -> None:

@@ -236,6 +236,10 @@ def test_prefill_product_matches_fp32_matmul(R, C, T):
     for dt in (torch.bfloat16, torch.float16):
         Y = l8.gemm(X.cuda(), torch.empty(T, R, dtype=dt, device="cuda"))
         assert orc.max_rel_err(Y.float().cpu().numpy(), yref) < _out_tol(dt)
+    Y = torch.full((T, R), float("nan"), device="cuda")
+    l8.gemm(X.cuda(), Y, two_sm=True)            # pairs of thread blocks (tcgen05 cta_group::2) above 256 tokens
+    l8.status()
+    assert orc.max_rel_err(Y.cpu().numpy(), yref) < TOL
 
 
 def test_prefill_product_writes_a_column_slice_and_survives_outliers():
