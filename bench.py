@@ -353,6 +353,100 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
+    """Prefill product of the same 196-matrix set: Y = X W^T for --tokens tokens per matrix on the tcgen05
+    kernel; metric TFLOPS = 2 * tokens * R * C summed over the matrices / time."""
+    import torch.distributed as dist
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    T = args.tokens
+    lins, kinds, _ = build_set(dev, rank, world, 64)
+    g = torch.Generator(device=dev).manual_seed(7)
+    xs = {c: torch.randn(T, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
+    ys = {r: torch.empty(T, r, device=dev, dtype=torch.bfloat16) for r in {l.R for l in lins}}
+    flops = sum(2.0 * T * l.R * l.C for l in lins)
+
+    def step():
+        for lin, kind in zip(lins, kinds):
+            lin.l8.gemm(xs[lin.C], ys[lin.R])
+            if world > 1 and kind == "row":
+                dist.all_reduce(ys[lin.R])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        barrier()
+        sampler = ClockSampler(physical_gpu_index(local_rank))
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        # end to end: the layer inputs come from pinned host memory, the last token's outputs go back
+        hx = {c: torch.randn(T, c).bfloat16().pin_memory() for c in xs}
+        hy = {r: torch.empty(r, dtype=torch.bfloat16).pin_memory() for r in ys}
+
+        def step_e2e():
+            for i, (lin, kind) in enumerate(zip(lins, kinds)):
+                if i % 7 in (0, 3, 4, 6):          # q, o, gate, down: a new activation tensor enters the layer
+                    xs[lin.C].copy_(hx[lin.C], non_blocking=True)
+                lin.l8.gemm(xs[lin.C], ys[lin.R])
+                if world > 1 and kind == "row":
+                    dist.all_reduce(ys[lin.R])
+                hy[lin.R].copy_(ys[lin.R][T - 1], non_blocking=True)
+            stream.synchronize()
+
+        step_e2e()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(max(args.steps // 4, 1)):
+            step_e2e()
+        t1.record(stream)
+        barrier()
+        ms_e2e = t0.elapsed_time(t1) / max(args.steps // 4, 1)
+    tv = torch.tensor([ms, ms_e2e, flops], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax, tsum = tv.clone(), tv.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, ms_e2e, flops = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    if rank != 0:
+        return
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    value = flops * args.steps / (ms * 1e-3) / 1e12
+    line = {"metric": "prefill_dequant_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b prefill dequant-GEMM set (196 codebook matrices), {T} tokens", "accumulate": "fp32",
+                       "activations": "bf16 in, fp16 on the tensor cores with a power-of-two scale per token", "output": "bf16",
+                       "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 per step"},
+            "clocks": clocks, "gpu_launches": 2 * len(lins) * args.steps * world,
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": sum(T * l.C * 2 for i, l in enumerate(lins) if i % 7 in (0, 3, 4, 6)) * world,
+                    "d2h_bytes_per_step": sum(l.R * 2 for l in lins) * world, "ms_per_step": ms_e2e},
+            "roofline": {"bound": "tensor", "kernel": "k_gemm_l8", "achieved": value / world, "peak": peak,
+                         "peak_source": "measured (sustained)" if peaks else "fallback", "unit": "TFLOP/s", "frac": value / world / peak,
+                         "frac_of_burst": value / world / float(peaks.get("bf16_tflops", 1590.0)), "traffic": None}}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline_sample() -> dict:
     """The reference's CPU path (oracle port) timed on this host's cores on a bounded sample."""
     from oracle import cbl_oracle as orc
@@ -382,6 +476,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill"],
+                    help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens")
+    ap.add_argument("--tokens", type=int, default=2048)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -395,7 +492,10 @@ def main() -> None:
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "prefill":
+            run_prefill(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist
