@@ -208,19 +208,28 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     from quantexperiments_b200.kernels import L8Group
     per_layer = len(SHAPES_7B)
     groups = []
+    arena = None
+    if B == 1 and world > 1:
+        # row-parallel products sum their partial outputs through peer memory inside the finish kernel
+        from quantexperiments_b200.tp import PeerArena, PeerReduceGemv
+        arena = PeerArena(8 << 20)
     if B == 1:
         for l0 in range(0, len(lins), per_layer):
             q, k, v, o, gate, up, down = lins[l0:l0 + per_layer]
             for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
                 outs = [torch.empty(m.R, device=dev, dtype=torch.bfloat16) for m in members]
-                groups.append((L8Group([m.l8 for m in members]), xs[members[0].C][0], outs, kind))
+                if arena is not None and kind == "row":
+                    groups.append((PeerReduceGemv(members[0].l8, arena), xs[members[0].C][0], outs, "fused"))
+                else:
+                    groups.append((L8Group([m.l8 for m in members]), xs[members[0].C][0], outs, kind))
 
     def step_kernels():
         if B == 1:
             for grp, x, outs, kind in groups:
-                grp.run(x, outs)
-                if world > 1 and kind == "row":
-                    dist.all_reduce(outs[0])
+                if kind == "fused":
+                    grp.run(x, outs[0])
+                else:
+                    grp.run(x, outs)
             return
         for lin, kind in zip(lins, kinds):
             y = ys[lin.R]
@@ -296,9 +305,10 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             if B == 1:
                 for gi, (grp, x, outs, kind) in enumerate(groups):
                     x.copy_(hx[x.numel()][0], non_blocking=True)
-                    grp.run(x, outs)
-                    if world > 1 and kind == "row":
-                        dist.all_reduce(outs[0])
+                    if kind == "fused":
+                        grp.run(x, outs[0])
+                    else:
+                        grp.run(x, outs)
                     for o, h in zip(outs, hys[gi % 4]):
                         h.copy_(o, non_blocking=True)
                 stream.synchronize()
@@ -342,7 +352,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"qwen2.5-7b decode GEMV set (196 codebook matrices, d=8, K=4096, 12-bit tags), batch {B}",
                        "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 (1.24 GB of packed weights per step)",
-                       "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step (q|k|v and gate|up grouped)" + ("" if world == 1 else " incl. NCCL all-reduce")},
+                       "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step (q|k|v and gate|up grouped)" + ("" if world == 1 else "; o/down summed over ranks through peer memory in the finish kernel")},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps * world,
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                     "ms_per_step": ms_e2e / args.steps}}

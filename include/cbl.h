@@ -158,6 +158,19 @@ int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype,
 int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
                       void* workspace, cbl_stream s);
 
+/* Row-split (tensor-parallel o / down) batch-1 product fused with the sum over ranks, without a
+ * collective library: each rank accumulates its chunk range locally, then one kernel per rank
+ * exchanges "ready" words with its peers (bounded wait), reads every rank's partial sums through
+ * peer pointers over NVLink, adds them in rank order (bit-identical on all ranks), scales, rounds and
+ * writes the full y on every rank.  peer_ws[r] = rank r's work space (symmetric allocation mapped
+ * into this process; cbl_gemv_l8_ar_workspace_bytes(R) bytes, zero before the first call, one work
+ * space per matrix).  All ranks must issue the same sequence of calls; the call number is kept in the
+ * work space by the kernels, so the launches can be captured in a CUDA graph and replayed.  At most
+ * 8 ranks.  New with tensor parallelism (the reference has none); replaces product + NCCL all-reduce. */
+size_t cbl_gemv_l8_ar_workspace_bytes(int32_t R);
+int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* const* peer_ws, int32_t rank,
+                   int32_t world, cbl_stream s);
+
 /* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
  * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */

@@ -6,7 +6,7 @@ raises. Build it with `python -m quantexperiments_b200.build`."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libcbl.so"
@@ -70,6 +70,8 @@ SIGNATURES = {
     "cbl_gemm_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "cbl_gemm_l8_2sm": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "cbl_gemv_l8_multi": (c_int, [POINTER(L8), c_int32, c_void_p, c_int, POINTER(c_void_p), c_int, c_void_p, c_void_p]),
+    "cbl_gemv_l8_ar_workspace_bytes": (c_size_t, [c_int32]),
+    "cbl_gemv_l8_ar": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, POINTER(c_void_p), c_int32, c_int32, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
 }
 

@@ -328,6 +328,8 @@ struct L8Launch {
     cbl_l8 m[L8_MAX_GROUP];
     float* acc[L8_MAX_GROUP];      // fp32 row accumulators of each matrix (zero on entry)
     void* y[L8_MAX_GROUP];
+    const uint32_t* calls;         // optional: completed-call counter; call e = *calls + 1 accumulates into
+    int64_t acc_stride;            // acc[0] + (e & 1) * acc_stride (two alternating buffers, see cbl_gemv_l8_ar)
 };
 
 template <int NT>
@@ -415,6 +417,7 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
     constexpr int XWARP = 3;
     uint4 af[NIT / 2];
     float x0 = 0.f, x1 = 0.f;
+    float* acc0 = P.acc[0];                                // may be redirected to the call's buffer (single-matrix launches)
     auto request = [&](int tl) {
         const int mi = matrix_of(tl);
         const cbl_l8& mm = P.m[mi];
@@ -423,7 +426,10 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
         const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
 #pragma unroll
         for (int i = 0; i < NIT / 2; i++) af[i] = __ldg(fr + (warp + i * NWARP) * 32 + lane);
-        if (tl == tile_first) asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the accumulators come from earlier kernels
+        if (tl == tile_first) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the accumulators come from earlier kernels
+            if (P.calls) acc0 += (int64_t)((__ldcg(P.calls) + 1u) & 1u) * P.acc_stride;
+        }
         if (warp == XWARP) {
             const int chunk = ctile * 8 + g;
             x0 = x1 = 0.f;
@@ -498,7 +504,7 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
             float r1 = l8_row_sum(w0.y, w1.y, w2.y, lut);
             float r2 = l8_row_sum(w0.z, w1.z, w2.z, lut);
             float r3 = l8_row_sum(w0.w, w1.w, w2.w, lut);
-            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(P.acc[cmi] + 4 * (int64_t)(cg + tid)), "f"(r0), "f"(r1),
+            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"((cmi ? P.acc[cmi] : acc0) + 4 * (int64_t)(cg + tid)), "f"(r0), "f"(r1),
                          "f"(r2), "f"(r3)
                          : "memory");
         }
@@ -578,7 +584,7 @@ static int check_l8(const cbl_l8* m) {
 }
 
 template <int NT>
-static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, unsigned int* status, cudaStream_t st) {
+static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, unsigned int* status, cudaStream_t st, bool finish = true) {
     const size_t smem = (size_t)8 * L8_COL_WORDS * 4 + L8_RING_BYTES;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -610,6 +616,7 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, u
     cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = smem;
     CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_l8<NT>, P, x, xdtype, status));
+    if (!finish) return cbl_check_launch();
     cfg.gridDim = dim3(cbl_ceil_div(max_groups, 256), P.n);
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = 0;
@@ -641,6 +648,8 @@ extern "C" int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, i
         off += (size_t)mats[i].Rpad * 4;
         P.n++;
     }
+    P.calls = nullptr;
+    P.acc_stride = 0;
     if (P.n == 0) return CBL_OK;
     unsigned int* status = (unsigned int*)((char*)workspace + off);
     cudaStream_t st = (cudaStream_t)s;
@@ -663,6 +672,140 @@ extern "C" int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s
     CBL_CUDA(cudaMemcpyAsync(&v, (const char*)workspace + Rpad * 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
     return v ? CBL_ETIMEOUT : CBL_OK;
+}
+
+// ------------------------------------------------------------------------------------ row-split product + all-reduce over peer memory
+//
+// Tensor-parallel o / down projections: every rank multiplies its chunk range into its own fp32
+// accumulators (the kernel above), then ONE kernel per rank finishes the job across GPUs without a
+// collective library: it publishes "my partial sums of call e are complete" to every peer (a word
+// stored into the peer's flag array over NVLink), waits - bounded - for the same word from every
+// peer, reads all ranks' partial sums with plain peer loads, adds them in rank order (so every rank
+// gets bit-identical results), applies the row scale and writes y.  Two accumulator buffers alternate
+// by call so that a rank never overwrites sums a peer may still be reading.  The call number e lives
+// in the work space and is advanced by the kernel itself, so a captured CUDA graph can be replayed.
+//
+// Work space of each rank (the same layout everywhere, allocated as symmetric memory by the caller,
+// zero before the first call): acc[0] | acc[1] (Rpad fp32 each) | flags (uint32 per rank) | status |
+// completed calls | block ticket.
+constexpr int L8_AR_MAX_RANKS = 8;
+constexpr uint32_t L8_AR_SPIN_LIMIT = 1u << 22;      // polls of a peer's flag before giving up (~1 s)
+
+struct L8AllReduce {
+    int rank, world, R, Rpad, ydtype;
+    int64_t acc_stride;                       // floats between the two accumulator buffers
+    const float* acc[L8_AR_MAX_RANKS];        // every rank's accumulator buffer 0 (peer pointers)
+    uint32_t* flags[L8_AR_MAX_RANKS];         // every rank's flag array
+    uint32_t* ctl;                            // this rank's {status, completed calls, ticket}
+    const __half* row_scale;
+    void* y;
+};
+
+extern "C" size_t cbl_gemv_l8_ar_workspace_bytes(int32_t R) {
+    if (R < 0) return 0;
+    size_t Rpad = ((size_t)R + 3) / 4 * 4;
+    return 2 * Rpad * 4 + L8_AR_MAX_RANKS * 4 + 32;
+}
+
+__global__ void __launch_bounds__(256) k_l8_finish_allreduce(const __grid_constant__ L8AllReduce A) {
+    __shared__ int s_ok;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // this rank's partial sums have landed
+    const int tid = threadIdx.x;
+    const uint32_t epoch = __ldcg(A.ctl + 1) + 1u;              // every block reads it before the last block advances it
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < A.world) {
+        // publish (one block does it), then wait for every peer's word of this call
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(A.flags[tid] + A.rank), "r"(epoch) : "memory");
+        }
+        const uint32_t* f = A.flags[A.rank] + tid;
+        bool seen = false;
+        for (uint32_t i = 0; i < L8_AR_SPIN_LIMIT && !seen; i++) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            seen = (int32_t)(v - epoch) >= 0;
+        }
+        if (!seen) s_ok = 0;
+    }
+    __syncthreads();
+    const int gi = blockIdx.x * blockDim.x + tid;
+    if (!s_ok) {                                                // a peer never arrived: report, do not touch y
+        if (tid == 0) atomicExch(A.ctl, 1u);
+    } else if (gi < (A.Rpad >> 2)) {
+        const int64_t cur = (int64_t)(epoch & 1u) * A.acc_stride, nxt = (int64_t)((epoch + 1u) & 1u) * A.acc_stride;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < A.world; r++) {
+            const float4 v = __ldcg((const float4*)(A.acc[r] + cur) + gi);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        __stcg((float4*)(const_cast<float*>(A.acc[A.rank]) + nxt) + gi, make_float4(0.f, 0.f, 0.f, 0.f));
+        const float vv[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int r = gi * 4 + u;
+            if (r < A.R) cbl_store_out(A.y, A.ydtype, r, vv[u] * __half2float(A.row_scale[r]));
+        }
+    }
+    // the last block to get here advances the call counter (all blocks have read it by then)
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(A.ctl + 2, 1u) == gridDim.x - 1) {
+            A.ctl[2] = 0u;
+            __stcg(A.ctl + 1, epoch);
+        }
+    }
+}
+
+extern "C" int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* const* peer_ws, int32_t rank,
+                              int32_t world, cbl_stream s) {
+    if (!m || !x || !y || !peer_ws) return CBL_EINVAL;
+    if (world < 1 || world > L8_AR_MAX_RANKS || rank < 0 || rank >= world) return CBL_EINVAL;
+    int rc = check_l8(m);
+    if (rc) return rc;
+    if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    for (int r = 0; r < world; r++)
+        if (!peer_ws[r] || ((uintptr_t)peer_ws[r] % 16)) return CBL_EINVAL;
+    if (m->R == 0) return CBL_OK;
+    const size_t accb = (size_t)m->Rpad * 4;
+    uint32_t* ctl = (uint32_t*)((char*)peer_ws[rank] + 2 * accb + L8_AR_MAX_RANKS * 4);
+    L8Launch P;
+    P.n = 1;
+    P.tile0[0] = 0;
+    P.tile0[1] = m->ntile;
+    P.m[0] = *m;
+    P.acc[0] = (float*)peer_ws[rank];
+    P.y[0] = y;
+    P.calls = ctl + 1;
+    P.acc_stride = m->Rpad;
+    L8AllReduce A;
+    A.rank = rank; A.world = world; A.R = m->R; A.Rpad = m->Rpad; A.ydtype = ydtype;
+    A.acc_stride = m->Rpad;
+    for (int r = 0; r < world; r++) {
+        A.acc[r] = (const float*)peer_ws[r];
+        A.flags[r] = (uint32_t*)((char*)peer_ws[r] + 2 * accb);
+    }
+    A.ctl = ctl;
+    A.row_scale = (const __half*)m->row_scale;
+    A.y = y;
+    cudaStream_t st = (cudaStream_t)s;
+    rc = (l8_threads() == 256) ? launch_l8<256>(P, x, xdtype, ydtype, ctl, st, false) : launch_l8<512>(P, x, xdtype, ydtype, ctl, st, false);
+    if (rc) return rc;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(cbl_ceil_div(m->Rpad >> 2, 256));
+    cfg.blockDim = dim3(256);
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_l8_finish_allreduce, A));
+    return cbl_check_launch();
 }
 
 // ------------------------------------------------------------------------------------ batch-1 product without caller work space

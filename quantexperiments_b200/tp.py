@@ -86,6 +86,60 @@ def shard_cols(t: dict, meta: dict, c0: int, c1: int, perms: torch.Tensor | None
     return out, m, p
 
 
+class PeerArena:
+    """One symmetric-memory allocation per rank, mapped into every rank of `group`, carved into
+    sub-buffers at identical offsets on all ranks (take() must be called in the same order everywhere).
+    Used by the row-parallel linears that sum their partial outputs through peer pointers."""
+
+    def __init__(self, nbytes: int, group=None, device=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.nbytes, self.used = nbytes, 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)                   # every rank's buffer is zero before anyone uses a peer's
+
+    def take(self, nbytes: int) -> list[int]:
+        """Per-rank addresses of a fresh zeroed sub-buffer (256-byte aligned)."""
+        off = (self.used + 255) // 256 * 256
+        if off + nbytes > self.nbytes:
+            raise ValueError("peer arena exhausted")
+        self.used = off + nbytes
+        return [p + off for p in self.ptrs]
+
+
+class PeerReduceGemv:
+    """Batch-1 product of one row-parallel shard fused with the sum over ranks through peer memory
+    (cbl_gemv_l8_ar): run(x_slice, y) leaves the full y on every rank. All ranks must create these
+    objects, and call run(), in the same order."""
+
+    def __init__(self, l8, arena: PeerArena):
+        import ctypes
+        from ._lib import lib
+        self.l8, self.rank, self.world = l8, arena.rank, arena.world
+        ptrs = arena.take(lib.cbl_gemv_l8_ar_workspace_bytes(l8.R))
+        self.ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        self._struct = l8.struct()
+
+    def run(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        import ctypes
+        from . import _lib
+        from .kernels import _dt, _stream
+        xv, yv = x.reshape(-1), y.reshape(-1)
+        if xv.numel() != self.l8.C or not xv.is_contiguous() or yv.numel() != self.l8.R or not yv.is_contiguous():
+            raise ValueError("x must be this rank's contiguous activation slice and y a contiguous [R] vector")
+        with torch.cuda.device(self.l8.device):
+            _lib.check("cbl_gemv_l8_ar", _lib.lib.cbl_gemv_l8_ar(ctypes.byref(self._struct), xv.data_ptr(), _dt(xv.dtype), yv.data_ptr(),
+                                                               _dt(y.dtype), self.ptrs, self.rank, self.world, _stream()))
+        return y
+
+
 class ColumnParallelLinear:
     """Rank-local part of a column-parallel packed linear: y_local [..., R / world] = x . W[r0:r1]^T.
     No communication; the caller gathers or consumes the sharded output."""
@@ -115,9 +169,11 @@ class RowParallelLinear:
     orders index the full vector). reduce=False returns the partial product (for callers that
     reduce themselves, e.g. vLLM's RowParallelLinear)."""
 
-    def __init__(self, t: dict, meta: dict, perms: torch.Tensor | None, rank: int, world: int, device="cuda", group=None):
+    def __init__(self, t: dict, meta: dict, perms: torch.Tensor | None, rank: int, world: int, device="cuda", group=None,
+                 arena: "PeerArena | None" = None):
         from .kernels import DeviceMatrix, T16Matrix
         from .linear import PackedLinear
+        self.rank, self.fused = rank, None
         c0, c1 = col_range(meta["C"], meta["d"], rank, world)
         multi = meta["M"] > 1
         ts, ms, ps = shard_cols(t, meta, c0, c1, perms if multi else None)
@@ -148,6 +204,20 @@ class RowParallelLinear:
             if n:
                 self.t16.run(x.reshape(n, self.C_full).contiguous(), y, n, wide=True)
         return y.reshape(*lead, self.R)
+
+    def attach(self, arena: "PeerArena") -> None:
+        """Reserve this matrix's peer work space (call on every rank, in the same order)."""
+        if self.multi or not self.lin.use_l8():
+            raise ValueError("the fused path runs single-order matrices with at least 2048 rows")
+        self.fused = PeerReduceGemv(self.lin.l8, arena)
+
+    def forward_fused(self, x: torch.Tensor, y: torch.Tensor | None = None) -> torch.Tensor:
+        """One token: product + sum over ranks through peer memory (no collective library call)."""
+        if getattr(self, "fused", None) is None:
+            raise ValueError("attach() a peer arena first")
+        if y is None:
+            y = torch.empty(self.R, dtype=x.dtype, device=x.device)
+        return self.fused.run(x, y)
 
     def forward(self, x: torch.Tensor, reduce: bool = True) -> torch.Tensor:
         """Partials are kept in fp32 through the all-reduce and rounded to x's dtype once."""

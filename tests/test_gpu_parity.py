@@ -370,3 +370,51 @@ def test_grouped_batch1_launch_matches_fp32_matmul(shapes, C):
             assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
     with pytest.raises(ValueError):
         grp.run(x.cuda(), ys[:-1] + [ys[-1].double()] if len(ys) > 1 else [])
+
+
+def test_peer_reduce_entry_point_with_one_rank_and_graph_replay():
+    """cbl_gemv_l8_ar with world = 1 (the rank is its own only peer): same result as the plain product,
+    and a captured graph can be replayed because the call number lives in the work space."""
+    import ctypes
+    from quantexperiments_b200 import _lib
+    from quantexperiments_b200.kernels import L8Matrix
+    m = orc.synth_matrix(3584, 896, seed=31)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    ws = torch.zeros(_lib.lib.cbl_gemv_l8_ar_workspace_bytes(3584), dtype=torch.uint8, device="cuda")
+    ptrs = (ctypes.c_void_p * 1)(ws.data_ptr())
+    st = l8.struct()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(896, generator=g).bfloat16().cuda()
+    y = torch.empty(3584, device="cuda")
+
+    def call():
+        rc = _lib.lib.cbl_gemv_l8_ar(ctypes.byref(st), x.data_ptr(), _lib.BF16, y.data_ptr(), _lib.F32, ptrs, 0, 1,
+                                     torch.cuda.current_stream().cuda_stream)
+        assert rc == _lib.OK
+
+    for it in range(3):
+        x.copy_(torch.randn(896, generator=g).bfloat16())
+        y.fill_(float("nan"))
+        call()
+        yref = orc.linear_ref(x.float().cpu().numpy()[None], ref)[0]
+        assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        call()
+        s.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=s):
+            call()
+            call()
+        for it in range(3):
+            x.copy_(torch.randn(896, generator=g).bfloat16().cuda())
+            y.fill_(float("nan"))
+            gr.replay()
+            s.synchronize()
+            yref = orc.linear_ref(x.float().cpu().numpy()[None], ref)[0]
+            assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
+    ctl = ws[2 * 3584 * 4 + 32:].view(torch.int32)[:3].cpu().tolist()
+    assert ctl[0] == 0 and ctl[1] == 3 + 1 + 6 and ctl[2] == 0           # status, completed calls (capture itself runs nothing), ticket
+    nxt = (ctl[1] + 1) & 1                                               # the buffer the next call accumulates into is zero
+    assert int(ws[nxt * 3584 * 4:(nxt + 1) * 3584 * 4].count_nonzero()) == 0

@@ -172,3 +172,40 @@ def test_vllm_layer_shards_under_tensor_parallelism(tmp_path):
                                  input_size=2048, output_size=512, rank=r, world=world, device="cuda", bmax=32)
         acc = acc + ps.forward(xo[:, r * 1024:(r + 1) * 1024].contiguous().cuda().float()).cpu()
     assert orc.max_rel_err(acc.numpy(), orc.linear_ref(xo.float().numpy(), ref["model.layers.0.self_attn.o_proj"])) < 1e-3 + 2.0 ** -7
+
+
+def _peer_rank_main(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        arena = tp.PeerArena(2 << 20)
+        for R, C in ((3584, 1024), (2304, 4096)):
+            m = orc.synth_matrix(R, C, seed=R + C)
+            t, meta, _ = _file_tensors(m)
+            wfull = orc.synth_decode(m)
+            rp = tp.RowParallelLinear(t, meta, None, rank, world)
+            rp.attach(arena)
+            g = torch.Generator().manual_seed(1)
+            for it in range(3):
+                x = torch.randn(C, generator=g).bfloat16()
+                y = rp.forward_fused(x[rp.c0:rp.c1].contiguous().cuda(), torch.empty(R, device="cuda"))
+                yref = orc.linear_ref(x.float().numpy()[None], wfull)[0]
+                assert orc.max_rel_err(y.cpu().numpy(), yref) < 1e-3
+                ys = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(ys, y)
+                assert all(torch.equal(ys[0], v) for v in ys)        # rank-ordered sum: identical bits everywhere
+        (Path(tmp) / f"ok{rank}").write_text("ok")
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_fused_row_parallel_product_over_peer_memory(tmp_path):
+    """Needs two GPUs in the box: two processes, partial sums exchanged through peer pointers by the finish kernel."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    port = 29500 + (os.getpid() % 2000) + 7
+    mp.spawn(_peer_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
