@@ -170,6 +170,10 @@ int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, 
 size_t cbl_gemv_l8_ar_workspace_bytes(int32_t R);
 int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* const* peer_ws, int32_t rank,
                    int32_t world, cbl_stream s);
+/* CBL_ETIMEOUT if, since the last query, a peer's word did not arrive within the bounded wait of a
+ * cbl_gemv_l8_ar call on this rank's work space (that call's output is invalid; the GPU context stays
+ * usable).  Synchronises the stream and clears the word. */
+int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s);
 
 /* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
  * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.

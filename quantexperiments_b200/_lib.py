@@ -72,6 +72,7 @@ SIGNATURES = {
     "cbl_gemv_l8_multi": (c_int, [POINTER(L8), c_int32, c_void_p, c_int, POINTER(c_void_p), c_int, c_void_p, c_void_p]),
     "cbl_gemv_l8_ar_workspace_bytes": (c_size_t, [c_int32]),
     "cbl_gemv_l8_ar": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, POINTER(c_void_p), c_int32, c_int32, c_void_p]),
+    "cbl_gemv_l8_ar_status": (c_int, [c_void_p, c_int32, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
 }
 

@@ -808,6 +808,20 @@ extern "C" int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* 
     return cbl_check_launch();
 }
 
+// Status of the last cbl_gemv_l8_ar calls on this rank's work space: CBL_ETIMEOUT if a peer's "ready" word
+// did not arrive within the bounded wait (the output of that call is invalid).  Synchronises the stream
+// and clears the status word.
+extern "C" int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s) {
+    if (!workspace || R < 0) return CBL_EINVAL;
+    size_t Rpad = ((size_t)R + 3) / 4 * 4;
+    char* p = (char*)workspace + 2 * Rpad * 4 + L8_AR_MAX_RANKS * 4;
+    unsigned int v = 0;
+    CBL_CUDA(cudaMemcpyAsync(&v, p, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
+    if (v) CBL_CUDA(cudaMemsetAsync(p, 0, 4, (cudaStream_t)s));
+    return v ? CBL_ETIMEOUT : CBL_OK;
+}
+
 // ------------------------------------------------------------------------------------ batch-1 product without caller work space
 //
 // Some hosts may not give this library a way to obtain device memory: a serving runtime that carves

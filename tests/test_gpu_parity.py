@@ -418,3 +418,33 @@ def test_peer_reduce_entry_point_with_one_rank_and_graph_replay():
     assert ctl[0] == 0 and ctl[1] == 3 + 1 + 6 and ctl[2] == 0           # status, completed calls (capture itself runs nothing), ticket
     nxt = (ctl[1] + 1) & 1                                               # the buffer the next call accumulates into is zero
     assert int(ws[nxt * 3584 * 4:(nxt + 1) * 3584 * 4].count_nonzero()) == 0
+
+
+def test_peer_reduce_reports_a_missing_peer_instead_of_hanging():
+    """A rank whose peer never publishes its word: the finish kernel's wait is bounded, the call returns,
+    the status query reports the time-out and the context keeps working (no fault, no hang)."""
+    import ctypes
+    import time
+    from quantexperiments_b200 import _lib
+    from quantexperiments_b200.kernels import L8Matrix
+    lib = _lib.lib
+    m = orc.synth_matrix(2048, 256, seed=3)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    l8 = L8Matrix(dm)
+    n = lib.cbl_gemv_l8_ar_workspace_bytes(2048)
+    ws = torch.zeros(2 * n + 512, dtype=torch.uint8, device="cuda")
+    off = (n + 255) // 256 * 256
+    ptrs = (ctypes.c_void_p * 2)(ws.data_ptr(), ws.data_ptr() + off)       # "rank 1" is never launched
+    x = torch.randn(256, generator=torch.Generator().manual_seed(0)).bfloat16().cuda()
+    y = torch.full((2048,), 7.0, device="cuda")
+    st = l8.struct()
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.time()
+    assert lib.cbl_gemv_l8_ar(ctypes.byref(st), x.data_ptr(), _lib.BF16, y.data_ptr(), _lib.F32, ptrs, 0, 2, stream) == _lib.OK
+    assert lib.cbl_gemv_l8_ar_status(ctypes.c_void_p(ws.data_ptr()), 2048, stream) == _lib.ETIMEOUT
+    assert time.time() - t0 < 60
+    assert torch.equal(y, torch.full_like(y, 7.0))                       # the output was left untouched
+    assert lib.cbl_gemv_l8_ar_status(ctypes.c_void_p(ws.data_ptr()), 2048, stream) == _lib.OK      # cleared
+    # the device is fine: an ordinary product right after
+    y2 = l8.run(x, torch.empty(2048, device="cuda"))
+    assert orc.max_rel_err(y2.cpu().numpy(), orc.linear_ref(x.float().cpu().numpy()[None], ref)[0]) < TOL
