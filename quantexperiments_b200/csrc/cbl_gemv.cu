@@ -11,6 +11,9 @@
 //                 finished (row scale, output rounding, re-zeroing) by a second small kernel.
 #include <utility>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <vector>
 #include "cbl_common.cuh"
 
 // ------------------------------------------------------------------------------------ activations
@@ -332,50 +335,93 @@ struct L8Launch {
     int64_t acc_stride;            // acc[0] + (e & 1) * acc_stride (two alternating buffers, see cbl_gemv_l8_ar)
 };
 
+// Work split.  The (tile, row group) pairs of the launch, tile-major over all its matrices, are cut into one
+// contiguous range per block: first tile + first group, last tile + end group, whole tiles in between.
+// The host plans the cut so that the SLOWEST block is as fast as possible under a simple cost model - a table
+// build costs about 0.8 lookup iterations, an iteration covers up to NT row groups of one tile - and passes
+// the ranges as a kernel parameter (blocks beyond the plan's count exit at once).
+constexpr int L8_MAX_BLOCKS = 160;
+struct L8Plan {
+    int nblocks;
+    int4 r[L8_MAX_BLOCKS];          // {tile_first, g_first, tile_last, g_end}
+};
+
+__host__ __device__ inline int l8_matrix_of(const L8Launch& P, int tl) {
+    int mi = 0;
+    while (mi + 1 < P.n && tl >= P.tile0[mi + 1]) mi++;
+    return mi;
+}
+
+// Greedy sweep: blocks take work in order, each up to a cost budget T.  Returns the number of blocks used
+// (and fills `out` if given); more than `maxb` means T is too small.
+static int l8_sweep(const L8Launch& P, int NT, double T, int maxb, L8Plan* out) {
+    const double B = 0.8;
+    const int ntile = P.tile0[P.n];
+    int nb = 0, t = 0, g = 0;
+    while (t < ntile) {
+        if (nb >= maxb) return maxb + 1;
+        double c = 0.0;
+        int4 r = make_int4(t, g, t, g);
+        while (t < ntile) {
+            const int ng = P.m[l8_matrix_of(P, t)].Rpad >> 2;
+            const int k = (int)(T - c - B + 1e-9);              // whole iterations that still fit
+            if (k < 1) {
+                if (c == 0.0) return maxb + 1;                     // even an empty block cannot afford one tile
+                break;
+            }
+            const int rem = ng - g;
+            const int take = rem < k * NT ? rem : k * NT;
+            c += B + (double)((take + NT - 1) / NT);
+            r.z = t;
+            r.w = g + take;
+            g += take;
+            if (g == ng) { t++; g = 0; } else break;
+        }
+        if (out) out->r[nb] = r;
+        nb++;
+    }
+    if (out) out->nblocks = nb;
+    return nb;
+}
+
+static void l8_make_plan(const L8Launch& P, int NT, int maxb, L8Plan* plan) {
+    double lo = 1.8, hi = 1.8;
+    for (int t = 0; t < P.tile0[P.n]; t++) hi += 0.8 + (double)(((P.m[l8_matrix_of(P, t)].Rpad >> 2) + NT - 1) / NT);
+    for (int it = 0; it < 40 && hi - lo > 0.01; it++) {
+        const double mid = 0.5 * (lo + hi);
+        if (l8_sweep(P, NT, mid, maxb, nullptr) <= maxb) hi = mid; else lo = mid;
+    }
+    l8_sweep(P, NT, hi, maxb, plan);
+}
+
 template <int NT>
-__global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const void* __restrict__ x, int xdtype,
-                                                   unsigned int* __restrict__ status) {
+__global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan,
+                                                   const void* __restrict__ x, int xdtype, unsigned int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int STAGES = L8_RING_BYTES / (NT * 48);
     constexpr int NWARP = NT / 32, NIT = 256 / NWARP;
     float* s_lut = (float*)smem;                                   // [8][L8_COL_WORDS]
     unsigned char* s_ring = smem + 8 * L8_COL_WORDS * 4;           // [STAGES][3][NT] uint4
-    __shared__ __align__(8) unsigned long long s_bar[STAGES];
+    __shared__ __align__(8) unsigned long long s_bar[2 * STAGES];  // full[STAGES] (tags landed), empty[STAGES] (every warp has read them)
     __shared__ uint32_t s_b0[32];                                  // B fragment of the tile's activations, per lane
     __shared__ float s_inv;
     __shared__ int s_abort;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int ntile = P.tile0[P.n];
-    // This block's tiles [tile_first, tile_last] and row-group ranges: with at least as many tiles as
-    // blocks a block takes whole tiles; otherwise every tile is cut into equal row ranges, one per block,
-    // so that each block builds exactly one table.  part/nparts describe the cut of a single tile.
-    int tile_first, tile_last, part = 0, nparts = 1;
-    {
-        const int nb = (int)gridDim.x, b = (int)blockIdx.x;
-        if (ntile >= nb) {
-            const int base = ntile / nb, extra = ntile % nb;
-            tile_first = b * base + min(b, extra);
-            tile_last = tile_first + base + (b < extra ? 1 : 0) - 1;
-        } else {
-            const int base = nb / ntile, extra = nb % ntile;
-            if (b < extra * (base + 1)) { tile_first = b / (base + 1); part = b % (base + 1); nparts = base + 1; }
-            else { const int bb = b - extra * (base + 1); tile_first = extra + bb / base; part = bb % base; nparts = base; }
-            tile_last = tile_first;
-        }
-    }
+    if ((int)blockIdx.x >= plan.nblocks) return;
+    const int4 rg = plan.r[blockIdx.x];
+    const int tile_first = rg.x, tile_last = rg.z;
     if (tile_last < tile_first) return;
     CBL_MARK(0);
     // Programmatic dependent launch: let the next kernel in the stream (the finish kernel) get resident now;
     // this kernel itself waits for its predecessor only where it first touches data that depends on it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    auto matrix_of = [&](int tl) { int mi = 0; while (mi + 1 < P.n && tl >= P.tile0[mi + 1]) mi++; return mi; };
+    auto matrix_of = [&](int tl) { return l8_matrix_of(P, tl); };
     // row groups [lo, hi) of tile tl that belong to this block
     auto seg = [&](int tl, int& mi, int& lo, int& hi) {
         mi = matrix_of(tl);
-        const int ng = P.m[mi].Rpad >> 2;
-        lo = (int)((int64_t)ng * part / nparts);
-        hi = (int)((int64_t)ng * (part + 1) / nparts);
+        lo = tl == tile_first ? rg.y : 0;
+        hi = tl == tile_last ? rg.w : (P.m[mi].Rpad >> 2);
     };
     const uint32_t lut = cbl_smem_u32(s_lut), ring = cbl_smem_u32(s_ring), bar0 = cbl_smem_u32(s_bar);
     // iterations of this block: each covers up to NT row groups of one tile
@@ -387,7 +433,10 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
     }
     if (tid == 0) {
         s_abort = 0;
-        for (int i = 0; i < STAGES; i++) l8_mbar_init(bar0 + 8 * i, 3);      // one arrival per tag plane
+        for (int i = 0; i < STAGES; i++) {
+            l8_mbar_init(bar0 + 8 * i, 3);                      // full: one arrival per tag plane
+            l8_mbar_init(bar0 + 8 * (STAGES + i), NWARP);       // empty: one arrival per consuming warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -424,8 +473,12 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
         const int ntile1 = mm.ntile / mm.books, lt = tl - P.tile0[mi];
         const int book = lt / ntile1, ctile = lt - book * ntile1;
         const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
+        // all blocks read the same 64 KB at the same time: start each block at a different eighth of the book
 #pragma unroll
-        for (int i = 0; i < NIT / 2; i++) af[i] = __ldg(fr + (warp + i * NWARP) * 32 + lane);
+        for (int i = 0; i < NIT / 2; i++) {
+            const int ii = (i + (int)blockIdx.x) % (NIT / 2);
+            af[i] = __ldg(fr + (warp + ii * NWARP) * 32 + lane);
+        }
         if (tl == tile_first) {
             asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the accumulators come from earlier kernels
             if (P.calls) acc0 += (int64_t)((__ldcg(P.calls) + 1u) & 1u) * P.acc_stride;
@@ -444,7 +497,6 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
     int tile = tile_first, cmi, clo, chi, built = -1;
     seg(tile, cmi, clo, chi);
     int cg = clo;
-    bool aborted = false;
     for (int it = 0; it < nit; it++) {
         if (tile != built) {
             // ---- build T[c][e] for the tile's 8 chunk columns (its fragments and activations were requested
@@ -470,7 +522,7 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
             for (int i = 0; i < NIT / 2; i++) {
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
-                    const int e0 = ((warp + i * NWARP) * 2 + h) * 16;
+                    const int e0 = ((warp + ((i + (int)blockIdx.x) % (NIT / 2)) * NWARP) * 2 + h) * 16;
                     float c[4];
                     cbl_mma1688(c, h ? af[i].z : af[i].x, h ? af[i].w : af[i].y, b0);
                     float* p = s_lut + (2 * t) * L8_COL_WORDS + e0 + g;
@@ -485,21 +537,28 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
             __syncthreads();
             if (it == 0) CBL_MARK(1);
         }
+        // Warps run through the stages on their own: no block-wide barrier per iteration.  A producer lane refills
+        // the stage of the previous iteration once every warp has released it.  After a wait has expired the
+        // loop only keeps its shape (the table builds contain block-wide barriers) and does no more work.
+        bool dead = *(volatile int*)&s_abort != 0;
         const int stage = it % STAGES;
         const int n = min(NT, chi - cg);
-        if (!l8_mbar_wait(bar0 + 8 * stage, (uint32_t)(it / STAGES) & 1u)) s_abort = 1;
+        if (producer && it >= 1 && pit < nit && !dead) {
+            if (l8_mbar_wait(bar0 + 8 * (STAGES + (it - 1) % STAGES), (uint32_t)((it - 1) / STAGES) & 1u)) issue();
+            else { s_abort = 1; dead = true; }
+        }
+        if (!dead && !l8_mbar_wait(bar0 + 8 * stage, (uint32_t)(it / STAGES) & 1u)) { s_abort = 1; dead = true; }
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
-        if (tid < n) {
+        if (!dead && tid < n) {
             const uint32_t src = ring + stage * (NT * 48) + tid * 16;
             w0 = cbl_lds128(src);
             w1 = cbl_lds128(src + NT * 16);
             w2 = cbl_lds128(src + 2 * NT * 16);
         }
-        __syncthreads();                                   // the stage has been read by everyone: refill it
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * (STAGES + stage)) : "memory");
         if (it == 0) CBL_MARK(2);
-        if (s_abort) { aborted = true; break; }
-        if (producer && pit < nit) issue();
-        if (tid < n) {
+        if (!dead && tid < n) {
             float r0 = l8_row_sum(w0.x, w1.x, w2.x, lut);
             float r1 = l8_row_sum(w0.y, w1.y, w2.y, lut);
             float r2 = l8_row_sum(w0.z, w1.z, w2.z, lut);
@@ -511,7 +570,8 @@ __global__ void __launch_bounds__(NT, 1) k_gemv_l8(const __grid_constant__ L8Lau
         cg += NT;
         if (cg >= chi && tile < tile_last) { tile++; seg(tile, cmi, clo, chi); cg = clo; }
     }
-    if (aborted) {
+    __syncthreads();
+    if (s_abort) {
         // a staged copy never completed: report, give the copies still in flight a bounded time, leave
         if (tid == 0) {
             atomicExch(status, 1u);
@@ -603,6 +663,22 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, u
     int parts = min_groups / 128;
     if (parts < 1) parts = 1;
     if ((int64_t)ntile * parts < grid) grid = ntile * parts;
+    if (grid > L8_MAX_BLOCKS) grid = L8_MAX_BLOCKS;
+    // plan cache: the cut depends only on the shapes of the group
+    static std::mutex mu;
+    static std::map<std::vector<int>, L8Plan> cache;
+    std::vector<int> key = {NT, grid, P.n};
+    for (int i = 0; i < P.n; i++) { key.push_back(P.m[i].ntile); key.push_back(P.m[i].Rpad); }
+    L8Plan plan;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it == cache.end()) {
+            l8_make_plan(P, NT, grid, &plan);
+            cache.emplace(key, plan);
+        } else plan = it->second;
+    }
+    const L8Launch& Q = P;
     static int pdl = -1;
     if (pdl < 0) { const char* e = getenv("CBL_PDL"); pdl = (e && atoi(e) == 0) ? 0 : 1; }
     cudaLaunchAttribute attr[1];
@@ -615,7 +691,7 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, u
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = smem;
-    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_l8<NT>, P, x, xdtype, status));
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_l8<NT>, Q, plan, x, xdtype, status));
     if (!finish) return cbl_check_launch();
     cfg.gridDim = dim3(cbl_ceil_div(max_groups, 256), P.n);
     cfg.blockDim = dim3(256);
