@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(256) k_prep_x(const void* __restrict__ x, int 
                                                 const int32_t* __restrict__ perms, int Bpad, int Cpad, __half* __restrict__ xp,
                                                 float* __restrict__ xinv) {
     __shared__ float s_max[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x % Bpad, m = blockIdx.x / Bpad;
     __half* dst = xp + (int64_t)blockIdx.x * Cpad;
     float mx = 0.f;
@@ -70,7 +72,17 @@ extern "C" int cbl_prep_x(const void* x, int xdtype, int32_t B, int32_t C, int64
     if (M > 1 && !perms) return CBL_EINVAL;
     int Bpad = (B + 7) / 8 * 8, Cpad = (C + 511) / 512 * 512;
     float* xinv = (float*)((__half*)xp + (int64_t)M * Bpad * Cpad);
-    k_prep_x<<<M * Bpad, 256, 0, (cudaStream_t)s>>>(x, xdtype, B, C, ldx, M > 1 ? perms : nullptr, Bpad, Cpad, (__half*)xp, xinv);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = (cudaStream_t)s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(M * Bpad);
+    cfg.blockDim = dim3(256);
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_prep_x, x, xdtype, (int)B, (int)C, ldx, M > 1 ? perms : (const int32_t*)nullptr, Bpad, Cpad,
+                                (__half*)xp, xinv));
     return cbl_check_launch();
 }
 
@@ -86,11 +98,12 @@ __device__ __forceinline__ uint32_t t16_tag_off(const uint32_t (&w)[12]) {
 
 template <int BOOKS, int NB, int S>
 __device__ __forceinline__ void t16_step(float (&acc)[NB][4], const uint32_t (&w)[BOOKS][12], uint32_t tbl,
-                                         const uint4* __restrict__ xrow, int64_t xstride8) {
-    // xrow points at chunk (ss*16)*4 + t of batch row g; step S adds 4 chunks
+                                         const uint4* __restrict__ xrow, int64_t xstride8, int rows_left) {
+    // xrow points at chunk (ss*16)*4 + t of batch row g; step S adds 4 chunks.  Lanes whose batch row does not
+    // exist (padding up to a multiple of 8) feed zeros without touching memory.
     uint4 xv[NB];
 #pragma unroll
-    for (int nb = 0; nb < NB; nb++) xv[nb] = __ldg(xrow + S * 4 + nb * xstride8);
+    for (int nb = 0; nb < NB; nb++) xv[nb] = (nb * 8 < rows_left) ? __ldg(xrow + S * 4 + nb * xstride8) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int bk = 0; bk < BOOKS; bk++) {
         uint4 c0 = cbl_lds128(tbl + bk * 65536u + t16_tag_off<2 * S>(w[bk]));
@@ -105,8 +118,9 @@ __device__ __forceinline__ void t16_step(float (&acc)[NB][4], const uint32_t (&w
 
 template <int BOOKS, int NB, int... S>
 __device__ __forceinline__ void t16_steps(float (&acc)[NB][4], const uint32_t (&w)[BOOKS][12], uint32_t tbl,
-                                          const uint4* __restrict__ xrow, int64_t xstride8, std::integer_sequence<int, S...>) {
-    (t16_step<BOOKS, NB, S>(acc, w, tbl, xrow, xstride8), ...);
+                                          const uint4* __restrict__ xrow, int64_t xstride8, int rows_left,
+                                          std::integer_sequence<int, S...>) {
+    (t16_step<BOOKS, NB, S>(acc, w, tbl, xrow, xstride8, rows_left), ...);
 }
 
 constexpr int T16_WARPS = 8;
@@ -127,6 +141,8 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
             for (int i = tid; i < 4096; i += T16_WARPS * 32) s_table[4096 + i] = __ldg(t1 + i);
         }
     }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // the staged activations come from the kernel before
     __syncthreads();
     const uint32_t tbl = cbl_smem_u32(s_table);
     const uint4* words = (const uint4*)m.words;
@@ -169,7 +185,7 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
                     }
                 }
             }
-            t16_steps<BOOKS, NB>(acc, w, tbl, xbase + (int64_t)ss * 64, xstride8, std::make_integer_sequence<int, 16>{});
+            t16_steps<BOOKS, NB>(acc, w, tbl, xbase + (int64_t)ss * 64, xstride8, B - g, std::make_integer_sequence<int, 16>{});
             if (sn < m.nsuper) {
 #pragma unroll
                 for (int bk = 0; bk < BOOKS; bk++)
@@ -216,7 +232,17 @@ static int launch_t16(const cbl_t16* m, const void* xp, int B, void* y, int ydty
     int grid = cbl_sm_count() * per_sm;
     if (grid > m->ntile) grid = m->ntile;
     int Bpad = NB * 8, Cpad = (m->C + 511) / 512 * 512;
-    k_gemv_t16<BOOKS, NB><<<grid, T16_WARPS * 32, smem, st>>>(*m, (const __half*)xp, B, Bpad, Cpad, y, ydtype, ldy);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(T16_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_t16<BOOKS, NB>, *m, (const __half*)xp, B, Bpad, Cpad, y, ydtype, ldy));
     return cbl_check_launch();
 }
 
