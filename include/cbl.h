@@ -200,7 +200,7 @@ int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int 
  * with tcgen05.mma (fp16 x fp16, fp32 accumulation in tensor memory); x is staged as fp16 with a
  * power-of-two scale per token in `stage` (cbl_gemm_stage_bytes).  `workspace`: at least 4 bytes,
  * zero; a nonzero word afterwards means a bounded device-side wait expired (output invalid).
- * books = 1 only.
+ * A second summed book runs as a second pass over the activation k-blocks into the same accumulators.
  * replaces shapequant/kernels/runs_gemm.py:471-514 (gemm: fused dequant + GEMM with mma.sync) and the
  *          dequant + cuBLAS large-M path of shapequant/vllm_ext/core.py:386-420. */
 size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C);

@@ -138,7 +138,9 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // row tiles vary fastest across the grid: blocks that run together share one activation tile in L2
     const int r0 = blockIdx.x * GM_BN, tok0 = blockIdx.y * GM_BM;
-    const int nkb = m.ntile;                                  // books == 1: one tile of the l8 layout per k-block
+    // one tile of the l8 layout per k-block; a second (summed) book is a second pass over the same activation
+    // k-blocks with the other book in shared memory: Y = X A^T + X B^T accumulates in the same tensor memory
+    const int nkb = m.ntile, nkb1 = m.ntile / m.books;
     const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
     auto full_a = [&](int s) { return bar0 + 8u * s; };
     auto empty_a = [&](int s) { return bar0 + 8u * (GM_A_STAGES + s); };
@@ -178,8 +180,9 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
                 if (!mbar_wait(empty_a(s), ((kb / GM_A_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
                 mbar_expect_tx(full_a(s), 2 * GM_A_BYTES);
                 const uint32_t dst = a_base + s * 2 * GM_A_BYTES;
-                tma_load_2d(dst, &xmap, kb * GM_BK, tok0, full_a(s));
-                tma_load_2d(dst + GM_A_BYTES, &xmap, kb * GM_BK, tok0 + 128, full_a(s));
+                const int kx = (kb >= nkb1 ? kb - nkb1 : kb) * GM_BK;
+                tma_load_2d(dst, &xmap, kx, tok0, full_a(s));
+                tma_load_2d(dst + GM_A_BYTES, &xmap, kx, tok0 + 128, full_a(s));
             }
         }
     } else if (warp == GM_DECODE_WARPS + 1) {
@@ -226,6 +229,14 @@ k_gemm_l8(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* __res
         for (int kb = 0; kb < nkb; kb++) {
             const int s = kb % GM_B_STAGES;
             load_tags(kb + 2, fa, fb, fc);
+            if (kb == nkb1 && m.books == 2) {
+                // switch books: every decode thread is done with the first one (barrier among the decode warps only)
+                asm volatile("bar.sync 1, %0;" ::"n"(GM_DECODE_WARPS * 32) : "memory");
+                const uint4* t1 = (const uint4*)m.table2;
+                uint4* dst = (uint4*)smem;
+                for (int i = tid; i < 4096; i += GM_DECODE_WARPS * 32) dst[i] = __ldg(t1 + i);
+                asm volatile("bar.sync 1, %0;" ::"n"(GM_DECODE_WARPS * 32) : "memory");
+            }
             if (!mbar_wait(empty_b(s), ((kb / GM_B_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
             const uint32_t bdst = b_base + s * GM_B_BYTES + rowoff;
             uint32_t off[8];
@@ -495,8 +506,10 @@ extern "C" size_t cbl_gemm_stage_bytes(int32_t ntok, int32_t C) { return cbl_pre
 static int gemm_l8_impl(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
                         void* stage, void* workspace, cbl_stream s, int two_sm) {
     if (!m || !m->words || !m->table || !m->row_scale || !x || !y || !stage || !workspace) return CBL_EINVAL;
-    if (m->books != 1) return CBL_EUNSUPPORTED;
-    if (m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+    if (m->books != 1 && m->books != 2) return CBL_EINVAL;
+    if (m->books == 2 && (!m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
+    if (m->books == 2 && two_sm) return CBL_EUNSUPPORTED;      // the two-SM variant executes one book
+    if (m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
     if (ntok <= 0 || ldx < m->C || ldy < m->R) return CBL_EINVAL;
     if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
     if (((uintptr_t)stage % 16) || ((uintptr_t)m->table % 16) || ((uintptr_t)workspace % 4)) return CBL_EINVAL;

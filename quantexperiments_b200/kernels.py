@@ -267,8 +267,8 @@ class L8Matrix:
         """Y [T, R] = X [T, C] . W^T on the tensor cores (prefill). X f16 / bf16 / f32 with unit column
         stride; Y f16 / bf16 / f32 with unit column stride (its row stride is passed through).
         two_sm selects the cta_group::2 variant (pairs of thread blocks per tile)."""
-        if self.books != 1:
-            raise ValueError("the prefill product executes one book per matrix")
+        if self.books != 1 and two_sm:
+            raise ValueError("the two-SM variant executes one book per matrix")
         if X.dim() != 2 or X.shape[1] != self.C or X.stride(1) != 1 or X.device != self.device:
             raise ValueError("X must be [T, C] with unit column stride on the matrix's device")
         T = X.shape[0]

@@ -89,8 +89,8 @@ class PackedLinear(torch.nn.Module):
         return self.dm.M == 1 and self.R >= L8_MIN_ROWS
 
     def use_gemm(self) -> bool:
-        """The fused tensor-core prefill kernel executes one column order and one book."""
-        return self.dm.M == 1 and self.dm.books == 1
+        """The fused tensor-core prefill kernel executes one column order (one or two books)."""
+        return self.dm.M == 1
 
     def gemv(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [C] (fp16 / bf16 / fp32, contiguous) -> y [R] in x's dtype (or `out`'s)."""
@@ -116,7 +116,7 @@ class PackedLinear(torch.nn.Module):
         elif self.use_gemm():
             self.l8.gemm(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
         else:
-            # column orders or two books: decode to 16 bit into the shared scratch, then a library GEMM
+            # several column orders: decode to 16 bit into the shared scratch, then a library GEMM
             dt = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
             w = self.dm.dequant(_Scratch.get(self.R * self.C, x2.device, dt))
             y.copy_(x2.to(dt) @ w.t())

@@ -7,8 +7,8 @@ that vLLM's LinearMethod.apply can stay `torch.ops.shapequant.linear(x, handle)`
 
 Dispatch on the number of tokens M: 1 -> batch-1 kernel per piece, <= bmax -> small-batch
 tensor-core kernel per piece, each writing its column slice of the stacked output; larger ->
-the fused decode + tcgen05 GEMM per piece into its slice (pieces with column orders or two books:
-decode to x's 16-bit dtype into a shared scratch followed by a library GEMM)."""
+the fused decode + tcgen05 GEMM per piece into its slice (pieces with several column orders: decode
+to x's 16-bit dtype into a shared scratch followed by a library GEMM)."""
 
 from __future__ import annotations
 
