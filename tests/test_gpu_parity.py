@@ -449,3 +449,37 @@ def test_peer_reduce_reports_a_missing_peer_instead_of_hanging():
     # the device is fine: an ordinary product right after
     y2 = l8.run(x, torch.empty(2048, device="cuda"))
     assert orc.max_rel_err(y2.cpu().numpy(), orc.linear_ref(x.float().cpu().numpy()[None], ref)[0]) < TOL
+
+
+@pytest.mark.parametrize("C", [5120, 27648])
+def test_qwen32b_shaped_rows_with_two_books_and_sixteen_column_orders(C):
+    """Row samples of the 32B-shaped matrices (hidden 5120, SwiGLU 27648): two summed books and 16 seeded
+    column orders per matrix: decode bit-exact, decode batches 1..64 and a 300-token prefill within tolerance."""
+    from quantexperiments_b200.kernels import L8Matrix, T16Matrix
+    from quantexperiments_b200.linear import PackedLinear
+    R = 320
+    m = orc.synth_matrix(R, C, seed=C, books=2, M=16)
+    dm, ref = _dm(m), orc.synth_decode(m)
+    assert torch.equal(dm.dequant(dtype=torch.float32).cpu(), _t(ref))
+    t16 = T16Matrix(dm)
+    g = torch.Generator().manual_seed(C)
+    for B in (1, 32, 64):
+        x = torch.randn(B, C, generator=g).bfloat16()
+        y = t16.run(x.cuda(), torch.empty(B, R, device="cuda"))
+        assert orc.max_rel_err(y.cpu().numpy(), orc.linear_ref(x.float().numpy(), ref)) < TOL
+    # one column order: the table-lookup and tensor-core prefill paths with two books
+    m1 = orc.synth_matrix(2304, C, seed=C + 1, books=2, M=1)
+    dm1, ref1 = _dm(m1), orc.synth_decode(m1)
+    l8 = L8Matrix(dm1)
+    x = torch.randn(300, C, generator=g).bfloat16()
+    yref = orc.linear_ref(x.float().numpy(), ref1)
+    y1 = l8.run(x[0].cuda(), torch.empty(2304, device="cuda"))
+    assert orc.max_rel_err(y1.cpu().numpy(), yref[0]) < TOL
+    Y = l8.gemm(x.cuda(), torch.empty(300, 2304, device="cuda"))
+    l8.status()
+    assert orc.max_rel_err(Y.cpu().numpy(), yref) < TOL
+    # the module dispatches 300 tokens of a 16-order matrix to decode + library GEMM
+    lin = PackedLinear(_t(m["words"][0]).cuda(), _t(m["table"][0]).cuda(), _t(m["row_scale"]).cuda(), None, _t(m["row_mask"]).cuda(),
+                       _t(m["perms"]).cuda(), 4096, 8, words2=_t(m["words"][1]).cuda(), table2=_t(m["table"][1]).cuda())
+    yl = lin(x.cuda())
+    assert orc.max_rel_err(yl.float().cpu().numpy(), orc.linear_ref(x.float().numpy(), ref)) < 1e-2
