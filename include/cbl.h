@@ -213,6 +213,56 @@ int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_
 int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
                     void* stage, void* workspace, cbl_stream s);
 
+/* ------------------------------------------------------------------------------------------------
+ * Decode-step operators between the packed linears (Qwen2-style blocks).  `dtype` is the model's
+ * 16-bit activation type (CBL_F16 or CBL_BF16) shared by every 16-bit pointer of a call; the residual
+ * stream `h` is fp32.  Arithmetic follows the reference's batch-1 engine: activations are rounded to
+ * the 16-bit type between operators, biases are added and silu * up is multiplied in that type, cos / sin
+ * are rounded to it.  All calls enqueue on `s`, allocate nothing and do not synchronise.
+ * replaces the CuPy kernels of shapequant/kernels/decode_e2e.py:63-309 (embed, addnorm_perm, rope_cache,
+ * attn / attn_rope, silu_mul_perm), DenseLin.run (:329-341) and torch.argmax in DecodeEngine.step (:715),
+ * and their batched forms in shapequant/kernels/qwen2_batch_kernels.py:37-88. */
+
+/* h[b, :] = float(embed[tok[b] mod rows, :]) for b < B. */
+int cbl_embed_rows(const void* embed, int dtype, int64_t rows, int32_t H, const int64_t* tok, int32_t B, float* h, cbl_stream s);
+
+/* h[b] += add[b] (add may be NULL; row stride ld_add elements); x[b] = round(h[b] * rsqrt(mean(h[b]^2) + eps) * w).
+ * x is [B, H] contiguous. */
+int cbl_add_rmsnorm(float* h, const void* add, int64_t ld_add, const void* w, int dtype, float eps, int32_t B, int32_t H, void* x,
+                    cbl_stream s);
+
+/* Rotary embedding + cache write.  qkv [rows, ld] holds q heads | k heads | v heads per row; bias (NULL or
+ * [(NH + 2 NKV) * HD]) is added first.  Row r belongs to sequence r at position pos[r] (decode, pos != NULL)
+ * or to sequence seq0 at position pos0 + r (prefill, pos == NULL).  Writes the rotated queries to
+ * q_out [rows, NH * HD] and the rotated keys / the values into the caches [seq][NKV][max_len][HD].
+ * Rotation pairs element i with i + HD/2 (the Hugging Face convention). */
+int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* bias, const int32_t* pos, int32_t pos0, int32_t seq0, int32_t rows,
+                int32_t NH, int32_t NKV, int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, cbl_stream s);
+
+/* Grouped-query attention of one new token per sequence over cache positions 0..pos[b] (the step's own
+ * key / value already written by cbl_rope_kv).  q, out: [B, NH * HD]; caches [B][NKV][max_len][HD]; HD = 128,
+ * NH / NKV <= 8.  The positions of a sequence are cut into `nsplit` slices that run in parallel
+ * (nsplit >= cbl_attn_decode_min_splits(max_len)); `workspace` holds the slices' partial results
+ * (cbl_attn_decode_workspace_bytes, zero before the first call; its last word is a status word that
+ * becomes nonzero if a slice exceeded the kernel's capacity). */
+size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit);
+int32_t cbl_attn_decode_min_splits(int32_t max_len);
+int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
+                    int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s);
+
+/* out[b, i] = round(round(silu(gate_up[b, i])) * gate_up[b, I + i]); gate_up [B, ld], out [B, I] contiguous. */
+int cbl_silu_mul(const void* gate_up, int dtype, int64_t ld, int32_t B, int32_t I, void* out, cbl_stream s);
+
+/* Dense 16-bit output head for small batches: logits[b, v] = <W[v, :], x[b, :]>, W [V, H] and x [B, H]
+ * contiguous in `dtype`, fp32 accumulation, logits in `ldtype` (CBL_F32 / F16 / BF16) with row stride ldl.
+ * B <= cbl_head_gemv_max_batch() (larger batches are a plain library GEMM), H a multiple of 8. */
+int32_t cbl_head_gemv_max_batch(void);
+int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype, int64_t ldl,
+                  cbl_stream s);
+
+/* tok[b] = index of the first largest logit of row b; pos[b] += 1 when pos != NULL. */
+int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ raises. Build it with `python -m quantexperiments_b200.build`."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libcbl.so"
@@ -74,6 +74,18 @@ SIGNATURES = {
     "cbl_gemv_l8_ar": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, POINTER(c_void_p), c_int32, c_int32, c_void_p]),
     "cbl_gemv_l8_ar_status": (c_int, [c_void_p, c_int32, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
+    "cbl_embed_rows": (c_int, [c_void_p, c_int, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p]),
+    "cbl_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_float, c_int32, c_int32, c_void_p, c_void_p]),
+    "cbl_rope_kv": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
+                            c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "cbl_attn_decode_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_attn_decode_min_splits": (c_int32, [c_int32]),
+    "cbl_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
+                                c_void_p, c_void_p, c_int32, c_void_p]),
+    "cbl_silu_mul": (c_int, [c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
+    "cbl_head_gemv_max_batch": (c_int32, []),
+    "cbl_head_gemv": (c_int, [c_void_p, c_void_p, c_int, c_int32, c_int32, c_int32, c_void_p, c_int, c_int64, c_void_p]),
+    "cbl_argmax": (c_int, [c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
 }
 
 

@@ -1,0 +1,544 @@
+// The kernels of a decode step that sit between the packed linears (Qwen2-style blocks): embedding rows,
+// residual add + RMSNorm, rotary embedding + KV-cache write, grouped-query decode attention over the cache
+// (position slices in parallel, then a merge), silu(gate) * up, the dense 16-bit output head for small
+// batches, and greedy argmax.  They follow the arithmetic of the reference's batch-1 engine
+// (shapequant/kernels/decode_e2e.py:63-309): fp32 residual stream, activations rounded to the model's
+// 16-bit type between operations, biases added and silu * up multiplied in that type, cos / sin rounded
+// to it.  Every kernel handles B sequences (grid dimension) so that the batched engine
+// (shapequant/runtime_batch.py) shares them.
+//
+// All launches use programmatic stream serialization: a kernel may become resident while its predecessor
+// drains and waits (griddepcontrol.wait) before it touches memory.
+#include "cbl_common.cuh"
+
+namespace {
+
+template <typename... KA, typename... A>
+int step_launch(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...));
+    return cbl_check_launch();
+}
+
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+
+// 8 values of a 16-byte vector of T as floats
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]);
+template <> __device__ __forceinline__ void unpack8<__half>(const uint4& w, float (&f)[8]) {
+    const __half2* p = (const __half2*)&w;
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float2 v = __half22float2(p[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& w, float (&f)[8]) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------- embedding rows
+template <typename T>
+__global__ void __launch_bounds__(256) k_embed(const T* __restrict__ E, const int64_t* __restrict__ tok, int64_t rows, int H,
+                                               float* __restrict__ h) {
+    pdl_enter();
+    const int b = blockIdx.y;
+    int64_t t = tok[b] % rows;
+    if (t < 0) t += rows;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) h[(int64_t)b * H + i] = to_f(E[t * H + i]);
+}
+
+// ---------------------------------------------------------------------------------------- add + RMSNorm
+// h[b] += add[b] (if add); x[b] = T(h[b] * rsqrt(mean(h[b]^2) + eps) * w).  One block per sequence.
+template <typename T>
+__global__ void __launch_bounds__(512) k_add_rmsnorm(float* __restrict__ h, const T* __restrict__ add, int64_t ld_add,
+                                                     const T* __restrict__ w, float eps, int H, T* __restrict__ x) {
+    pdl_enter();
+    __shared__ float red[16];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float* hb = h + (int64_t)b * H;
+    float ss = 0.f;
+    for (int i = tid; i < H; i += blockDim.x) {
+        float v = hb[i];
+        if (add) { v += to_f(add[(int64_t)b * ld_add + i]); hb[i] = v; }
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid < 32) {
+        float v = tid < (int)(blockDim.x >> 5) ? red[tid] : 0.f;
+        v = warp_sum(v);
+        if (tid == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float rstd = rsqrtf(red[0] / (float)H + eps);
+    for (int i = tid; i < H; i += blockDim.x) x[(int64_t)b * H + i] = cbl_cvt_out<T>(hb[i] * rstd * to_f(w[i]));
+}
+
+// ---------------------------------------------------------------------------------------- rotary + cache write
+// Row r of qkv ([rows, ld]: q heads | k heads | v heads) belongs to sequence seq(r) at position p(r):
+// decode (pos != null): seq = r, p = pos[r]; prefill (pos == null): seq = seq0, p = pos0 + r.
+// Blocks (head, row): heads 0..NH-1 rotate q into qo [rows, NH*HD]; heads NH..NH+NKV-1 rotate k and copy v
+// (+ bias) into the caches [seq][NKV][max_len][HD].
+template <typename T>
+__global__ void __launch_bounds__(128) k_rope_kv(const T* __restrict__ qkv, int64_t ld, const T* __restrict__ bias,
+                                                 const int32_t* __restrict__ pos, int pos0, int seq0, int NH, int NKV, int HD,
+                                                 float theta, int max_len, T* __restrict__ qo, T* __restrict__ kc, T* __restrict__ vc) {
+    pdl_enter();
+    const int hd = blockIdx.x, r = blockIdx.y, i = threadIdx.x, half = HD >> 1;
+    if (i >= half) return;
+    const int p = pos ? pos[r] : pos0 + r;
+    const int seq = pos ? r : seq0;
+    if (p < 0 || p >= max_len) return;
+    const float inv = 1.f / powf(theta, (2.f * (float)i) / (float)HD);
+    const float ang = (float)p * inv;
+    const float c = to_f(cbl_cvt_out<T>(cosf(ang))), s = to_f(cbl_cvt_out<T>(sinf(ang)));
+    const T* row = qkv + (int64_t)r * ld;
+    const int o = hd * HD;                                   // q | k share the column arithmetic up to NH + NKV heads
+    auto in = [&](int col) {
+        const T v = row[col];
+        return bias ? to_f(cbl_cvt_out<T>(to_f(v) + to_f(bias[col]))) : to_f(v);
+    };
+    const float x1 = in(o + i), x2 = in(o + i + half);
+    const T r1 = cbl_cvt_out<T>(x1 * c - x2 * s), r2 = cbl_cvt_out<T>(x2 * c + x1 * s);
+    if (hd < NH) {
+        T* q = qo + (int64_t)r * NH * HD + o;
+        q[i] = r1;
+        q[i + half] = r2;
+    } else {
+        const int kv = hd - NH;
+        const int64_t co = (((int64_t)seq * NKV + kv) * max_len + p) * HD;
+        kc[co + i] = r1;
+        kc[co + i + half] = r2;
+        const int ov = (NH + NKV + kv) * HD;
+        vc[co + i] = cbl_cvt_out<T>(in(ov + i));
+        vc[co + i + half] = cbl_cvt_out<T>(in(ov + i + half));
+    }
+}
+
+// ---------------------------------------------------------------------------------------- decode attention
+// One block per (position slice, kv head, sequence): the slice's K rows are read once for all REP query
+// heads of the group.  Scores: one thread per position, the whole K row with 16-byte loads, q broadcast from
+// shared memory.  Values: 16 threads per V row (8 dims each), 8 rows in flight per pass.  The block writes
+// the slice's running max, denominator and un-normalised output per head; k_attn_merge combines slices.
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_MAX_SLICE = 1024;        // positions per block (scores live in shared memory)
+constexpr int ATT_HD = 128;
+
+__host__ __device__ inline void att_slice(int L, int nsplit, int split, int& s0, int& s1) {
+    int per = (L + nsplit - 1) / nsplit;
+    per = (per + 31) / 32 * 32;
+    s0 = split * per;
+    s1 = s0 + per < L ? s0 + per : L;
+}
+
+template <typename T, int REP>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
+                                                            const int32_t* __restrict__ pos, int NKV, int max_len, float scale,
+                                                            float* __restrict__ part, unsigned int* __restrict__ status) {
+    pdl_enter();
+    constexpr int HD = ATT_HD;
+    __shared__ __align__(16) float s_q[REP][HD];
+    __shared__ __align__(16) float s_p[ATT_MAX_SLICE][8];            // scores, then probabilities, [position][head]
+    __shared__ float s_red[4][8];
+    __shared__ float s_m[8], s_l[8];
+    const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x, tid = threadIdx.x;
+    const int NH = NKV * REP;
+    const int L = pos[b] + 1;                                        // positions 0..pos[b] are in the cache (the step's own included)
+    int s0, s1;
+    att_slice(L, nsplit, split, s0, s1);
+    float* pout = part + (((int64_t)b * NH + kv * REP) * nsplit + split) * (HD + 2);   // per head: stride nsplit * (HD + 2)
+    const int64_t hstride = (int64_t)nsplit * (HD + 2);
+    if (s1 - s0 > ATT_MAX_SLICE) {
+        if (tid == 0) atomicExch(status, 2u);                        // the caller gave too few slices for this length
+        s1 = s0;
+    }
+    if (s0 >= s1) {
+        if (tid < REP) { pout[tid * hstride + HD] = -3.0e38f; pout[tid * hstride + HD + 1] = 0.f; }
+        return;
+    }
+    for (int i = tid; i < REP * HD; i += ATT_THREADS) s_q[i / HD][i % HD] = to_f(q[((int64_t)b * NH + kv * REP) * HD + i]) * scale;
+    __syncthreads();
+    const T* kbase = kc + ((int64_t)b * NKV + kv) * max_len * HD;
+    const T* vbase = vc + ((int64_t)b * NKV + kv) * max_len * HD;
+    float mx[REP];
+#pragma unroll
+    for (int h = 0; h < REP; h++) mx[h] = -3.0e38f;
+    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
+        const uint4* kr = (const uint4*)(kbase + (int64_t)t * HD);
+        uint4 w[HD / 8];
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) w[c] = cbl_ldg_stream(kr + c);
+        float d[REP];
+#pragma unroll
+        for (int h = 0; h < REP; h++) d[h] = 0.f;
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) {
+            float f[8];
+            unpack8<T>(w[c], f);
+#pragma unroll
+            for (int h = 0; h < REP; h++) {
+                const float4 qa = *(const float4*)&s_q[h][c * 8], qb = *(const float4*)&s_q[h][c * 8 + 4];
+                d[h] += f[0] * qa.x + f[1] * qa.y + f[2] * qa.z + f[3] * qa.w + f[4] * qb.x + f[5] * qb.y + f[6] * qb.z + f[7] * qb.w;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < REP; h++) { s_p[t - s0][h] = d[h]; mx[h] = fmaxf(mx[h], d[h]); }
+    }
+    // slice max per head
+#pragma unroll
+    for (int h = 0; h < REP; h++) {
+        const float v = warp_max(mx[h]);
+        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
+    }
+    __syncthreads();
+    if (tid < REP) s_m[tid] = fmaxf(fmaxf(s_red[0][tid], s_red[1][tid]), fmaxf(s_red[2][tid], s_red[3][tid]));
+    __syncthreads();
+    float sum[REP];
+#pragma unroll
+    for (int h = 0; h < REP; h++) sum[h] = 0.f;
+    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
+#pragma unroll
+        for (int h = 0; h < REP; h++) {
+            const float e = __expf(s_p[t - s0][h] - s_m[h]);
+            s_p[t - s0][h] = e;
+            sum[h] += e;
+        }
+    }
+    __syncthreads();                                                 // s_red is reused
+#pragma unroll
+    for (int h = 0; h < REP; h++) {
+        const float v = warp_sum(sum[h]);
+        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
+    }
+    __syncthreads();
+    if (tid < REP) s_l[tid] = s_red[0][tid] + s_red[1][tid] + s_red[2][tid] + s_red[3][tid];
+    // values: thread = (row group rg of 8, dim block db of 16)
+    const int rg = tid >> 4, db = tid & 15;
+    float acc[REP][8];
+#pragma unroll
+    for (int h = 0; h < REP; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
+    for (int t0 = s0; t0 < s1; t0 += 32) {
+        uint4 w[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * 8 + rg;
+            w[u] = t < s1 ? cbl_ldg_stream((const uint4*)(vbase + (int64_t)t * HD) + db) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int t = t0 + u * 8 + rg;
+            if (t < s1) {
+                float f[8];
+                unpack8<T>(w[u], f);
+                const float4 pa = *(const float4*)&s_p[t - s0][0], pb = *(const float4*)&s_p[t - s0][4];
+                const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                for (int h = 0; h < REP; h++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[h][j] += pv[h] * f[j];
+            }
+        }
+    }
+    __syncthreads();                                                 // every thread is done with s_p: reuse it for the reduction
+    float* s_acc = &s_p[0][0];                                       // [8 row groups][REP][HD]
+#pragma unroll
+    for (int h = 0; h < REP; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) s_acc[(rg * REP + h) * HD + db * 8 + j] = acc[h][j];
+    __syncthreads();
+    for (int i = tid; i < REP * HD; i += ATT_THREADS) {
+        float v = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; g++) v += s_acc[g * REP * HD + i];
+        pout[(i / HD) * hstride + (i % HD)] = v;
+    }
+    if (tid < REP) { pout[tid * hstride + HD] = s_m[tid]; pout[tid * hstride + HD + 1] = s_l[tid]; }
+}
+
+// out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s
+template <typename T>
+__global__ void __launch_bounds__(ATT_HD) k_attn_merge(const float* __restrict__ part, int nsplit, T* __restrict__ out) {
+    pdl_enter();
+    constexpr int HD = ATT_HD;
+    const int head = blockIdx.x, b = blockIdx.y, NH = gridDim.x, d = threadIdx.x;
+    const float* p = part + ((int64_t)b * NH + head) * nsplit * (HD + 2);
+    float m = -3.0e38f;
+    for (int s = 0; s < nsplit; s++) m = fmaxf(m, p[s * (HD + 2) + HD]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+        const float l = p[s * (HD + 2) + HD + 1];
+        if (l > 0.f) {
+            const float wgt = __expf(p[s * (HD + 2) + HD] - m);
+            num += wgt * p[s * (HD + 2) + d];
+            den += wgt * l;
+        }
+    }
+    out[((int64_t)b * NH + head) * HD + d] = cbl_cvt_out<T>(den > 0.f ? num / den : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------- silu(gate) * up
+template <typename T>
+__global__ void __launch_bounds__(256) k_silu_mul(const T* __restrict__ gu, int64_t ld, int I, T* __restrict__ out) {
+    pdl_enter();
+    const int b = blockIdx.y;
+    const T* row = gu + (int64_t)b * ld;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+        const float a = to_f(row[i]);
+        const float sl = to_f(cbl_cvt_out<T>(a / (1.f + __expf(-a))));       // silu and the product are rounded to the model type
+        out[(int64_t)b * I + i] = cbl_cvt_out<T>(sl * to_f(row[I + i]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------- dense 16-bit head, B <= 8
+// logits[b][v] = <W[v], x[b]>.  A warp per vocabulary row (persistent over rows), the row read with 16-byte
+// loads, the B activation vectors in shared memory.  Streaming, HBM-bound.
+constexpr int HEAD_BMAX = 8;
+template <typename T, int B>
+__global__ void __launch_bounds__(256) k_head(const T* __restrict__ W, const T* __restrict__ x, int V, int H, void* __restrict__ logits,
+                                              int ldtype, int64_t ldl) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    T* s_x = (T*)s_raw;                                              // [B][H]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < B * H / 8; i += 256) ((uint4*)s_x)[i] = ((const uint4*)x)[i];
+    __syncthreads();
+    const int nvec = H / 8;
+    for (int v = blockIdx.x * 8 + warp; v < V; v += gridDim.x * 8) {
+        const uint4* wr = (const uint4*)(W + (int64_t)v * H);
+        float acc[B];
+#pragma unroll
+        for (int b = 0; b < B; b++) acc[b] = 0.f;
+        for (int c0 = 0; c0 < nvec; c0 += 32 * 4) {
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = c0 + u * 32 + lane;
+                w[u] = c < nvec ? cbl_ldg_stream(wr + c) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = c0 + u * 32 + lane;
+                if (c < nvec) {
+                    float f[8];
+                    unpack8<T>(w[u], f);
+#pragma unroll
+                    for (int b = 0; b < B; b++) {
+                        float g[8];
+                        unpack8<T>(((const uint4*)(s_x + (int64_t)b * H))[c], g);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[b] += f[j] * g[j];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            const float s = warp_sum(acc[b]);
+            if (lane == 0) cbl_store_out(logits, ldtype, (int64_t)b * ldl + v, s);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------- greedy argmax
+// tok[b] = first index of the largest logit of row b; pos[b] += 1 when pos is given.
+__global__ void __launch_bounds__(1024) k_argmax(const void* __restrict__ logits, int ldtype, int64_t ldl, int V, int64_t* __restrict__ tok,
+                                                 int32_t* __restrict__ pos) {
+    pdl_enter();
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float v = cbl_load_in(logits, ldtype, (int64_t)b * ldl + i);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    auto better = [](float v, int i, float w, int j) { return w > v || (w == v && j < i); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, best, o);
+        const int j = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(best, bi, w, j)) { best = w; bi = j; }
+    }
+    if ((tid & 31) == 0) { s_v[tid >> 5] = best; s_i[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid < 32) {
+        best = tid < (int)(blockDim.x >> 5) ? s_v[tid] : -INFINITY;
+        bi = tid < (int)(blockDim.x >> 5) ? s_i[tid] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float w = __shfl_xor_sync(0xffffffffu, best, o);
+            const int j = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(best, bi, w, j)) { best = w; bi = j; }
+        }
+        if (tid == 0) {
+            tok[b] = bi == 0x7fffffff ? 0 : bi;
+            if (pos) pos[b] += 1;
+        }
+    }
+}
+
+bool is16(int dt) { return dt == CBL_F16 || dt == CBL_BF16; }
+
+}  // namespace
+
+#define CBL_BY_TYPE(dt, ...)                                          \
+    do {                                                              \
+        if ((dt) == CBL_F16) { using T = __half; __VA_ARGS__; }       \
+        else { using T = __nv_bfloat16; __VA_ARGS__; }                \
+    } while (0)
+
+extern "C" int cbl_embed_rows(const void* embed, int dtype, int64_t rows, int32_t H, const int64_t* tok, int32_t B, float* h, cbl_stream s) {
+    if (!embed || !tok || !h || !is16(dtype) || rows < 1 || H < 1 || B < 0) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    if (B > 65535) return CBL_EUNSUPPORTED;
+    const dim3 grid(cbl_ceil_div(H, 256) < 16 ? cbl_ceil_div(H, 256) : 16, B);
+    CBL_BY_TYPE(dtype, return step_launch(k_embed<T>, grid, dim3(256), 0, (cudaStream_t)s, (const T*)embed, tok, rows, (int)H, h));
+}
+
+extern "C" int cbl_add_rmsnorm(float* h, const void* add, int64_t ld_add, const void* w, int dtype, float eps, int32_t B, int32_t H, void* x,
+                               cbl_stream s) {
+    if (!h || !w || !x || !is16(dtype) || H < 1 || B < 0) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    CBL_BY_TYPE(dtype, return step_launch(k_add_rmsnorm<T>, dim3(B), dim3(512), 0, (cudaStream_t)s, h, (const T*)add, ld_add, (const T*)w, eps,
+                                          (int)H, (T*)x));
+}
+
+extern "C" int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* bias, const int32_t* pos, int32_t pos0, int32_t seq0,
+                           int32_t rows, int32_t NH, int32_t NKV, int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc,
+                           cbl_stream s) {
+    if (!qkv || !q_out || !kc || !vc || !is16(dtype) || rows < 0 || NH < 1 || NKV < 1 || max_len < 1) return CBL_EINVAL;
+    if (HD < 2 || HD > 256 || (HD & 1)) return CBL_EUNSUPPORTED;
+    if (rows == 0) return CBL_OK;
+    if (rows > 65535) return CBL_EUNSUPPORTED;
+    CBL_BY_TYPE(dtype, return step_launch(k_rope_kv<T>, dim3(NH + NKV, rows), dim3(128), 0, (cudaStream_t)s, (const T*)qkv, ld, (const T*)bias,
+                                          pos, (int)pos0, (int)seq0, (int)NH, (int)NKV, (int)HD, theta, (int)max_len, (T*)q_out, (T*)kc,
+                                          (T*)vc));
+}
+
+extern "C" size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit) {
+    if (B < 0 || NH < 0 || nsplit < 1) return 0;
+    return (size_t)B * NH * nsplit * (ATT_HD + 2) * 4 + 16;
+}
+
+extern "C" int32_t cbl_attn_decode_min_splits(int32_t max_len) { return max_len < 1 ? 1 : (max_len + ATT_MAX_SLICE - 1) / ATT_MAX_SLICE; }
+
+template <typename T, int REP>
+static int attn_launch(const void* q, const void* kc, const void* vc, const int32_t* pos, int B, int NKV, int max_len, float scale, void* out,
+                       float* part, unsigned int* status, int nsplit, cudaStream_t st) {
+    int rc = step_launch(k_attn_slice<T, REP>, dim3(nsplit, NKV, B), dim3(ATT_THREADS), 0, st, (const T*)q, (const T*)kc, (const T*)vc, pos,
+                         NKV, max_len, scale, part, status);
+    if (rc != CBL_OK) return rc;
+    return step_launch(k_attn_merge<T>, dim3(NKV * REP, B), dim3(ATT_HD), 0, st, (const float*)part, nsplit, (T*)out);
+}
+
+extern "C" int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
+                               int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s) {
+    if (!q || !kc || !vc || !pos || !out || !workspace || !is16(dtype) || B < 0 || NH < 1 || NKV < 1 || nsplit < 1) return CBL_EINVAL;
+    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > 65535) return CBL_EUNSUPPORTED;
+    if (nsplit < cbl_attn_decode_min_splits(max_len)) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    float* part = (float*)workspace;
+    unsigned int* status = (unsigned int*)((char*)workspace + (size_t)B * NH * nsplit * (ATT_HD + 2) * 4);
+    const cudaStream_t st = (cudaStream_t)s;
+#define CBL_ATT(R) case R: CBL_BY_TYPE(dtype, return (attn_launch<T, R>(q, kc, vc, pos, B, NKV, max_len, scale, out, part, status, nsplit, st)))
+    switch (NH / NKV) {
+        CBL_ATT(1);
+        CBL_ATT(2);
+        CBL_ATT(3);
+        CBL_ATT(4);
+        CBL_ATT(5);
+        CBL_ATT(6);
+        CBL_ATT(7);
+        default: CBL_ATT(8);
+    }
+#undef CBL_ATT
+    return CBL_EUNSUPPORTED;
+}
+
+extern "C" int cbl_silu_mul(const void* gate_up, int dtype, int64_t ld, int32_t B, int32_t I, void* out, cbl_stream s) {
+    if (!gate_up || !out || !is16(dtype) || B < 0 || I < 1) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    if (B > 65535) return CBL_EUNSUPPORTED;
+    int gx = cbl_ceil_div(I, 256);
+    const int cap = cbl_ceil_div(4 * cbl_sm_count(), B);
+    if (gx > cap) gx = cap < 1 ? 1 : cap;
+    CBL_BY_TYPE(dtype, return step_launch(k_silu_mul<T>, dim3(gx, B), dim3(256), 0, (cudaStream_t)s, (const T*)gate_up, ld, (int)I, (T*)out));
+}
+
+extern "C" int32_t cbl_head_gemv_max_batch(void) { return HEAD_BMAX; }
+
+template <typename T, int B>
+static int head_launch(const void* W, const void* x, int V, int H, void* logits, int ldtype, int64_t ldl, cudaStream_t st) {
+    const size_t smem = (size_t)B * H * sizeof(T);
+    if (smem > 200 * 1024) return CBL_EUNSUPPORTED;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_head<T, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set[dev] = true;
+    }
+    const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+    int grid = cbl_sm_count() * per_sm;
+    if (grid > cbl_ceil_div(V, 8)) grid = cbl_ceil_div(V, 8);
+    return step_launch(k_head<T, B>, dim3(grid), dim3(256), smem, st, (const T*)W, (const T*)x, V, H, logits, ldtype, ldl);
+}
+
+extern "C" int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype, int64_t ldl,
+                             cbl_stream s) {
+    if (!W || !x || !logits || !is16(dtype) || V < 1 || H < 1 || B < 0) return CBL_EINVAL;
+    if (ldtype != CBL_F32 && !is16(ldtype)) return CBL_EINVAL;
+    if (B > HEAD_BMAX || H % 8) return CBL_EUNSUPPORTED;
+    if (B == 0) return CBL_OK;
+    const cudaStream_t st = (cudaStream_t)s;
+#define CBL_HEAD(N) case N: CBL_BY_TYPE(dtype, return (head_launch<T, N>(W, x, V, H, logits, ldtype, ldl, st)))
+    switch (B) {
+        CBL_HEAD(1);
+        CBL_HEAD(2);
+        CBL_HEAD(3);
+        CBL_HEAD(4);
+        CBL_HEAD(5);
+        CBL_HEAD(6);
+        CBL_HEAD(7);
+        default: CBL_HEAD(8);
+    }
+#undef CBL_HEAD
+    return CBL_EUNSUPPORTED;
+}
+
+extern "C" int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s) {
+    if (!logits || !tok || V < 1 || B < 0 || (ldtype != CBL_F32 && !is16(ldtype))) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    return step_launch(k_argmax, dim3(B), dim3(1024), 0, (cudaStream_t)s, logits, ldtype, ldl, (int)V, tok, pos);
+}

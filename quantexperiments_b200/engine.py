@@ -1,0 +1,445 @@
+"""Decode engine for Qwen2-architecture models whose block linears are packed codebook matrices.
+
+Mirrors the reference's engine surface: `Cfg`, `DecodeEngine` (step / reset / capture / generate /
+time_tokens / weight_bytes; shapequant/kernels/decode_e2e.py:313-327, 507-768), `Qwen2BatchEngine`
+(B sequences per step sharing a batch-1 engine's weights, shapequant/runtime_batch.py:27-180),
+`random_engine` (decode_e2e.py:770-817), and `start` / `generate` / `bench` (shapequant/runtime.py:166-280).
+
+One step = embedding row, then per layer: add + RMSNorm, q|k|v, rotary + cache write, grouped-query
+attention over the cache, o, add + RMSNorm, gate|up, silu * up, down; final norm, output head, greedy
+argmax. The residual stream is fp32, activations are rounded to the model's 16-bit type between
+operators. Every operator is a libcbl kernel launched on the current stream into preallocated
+buffers, so a step is captured in one CUDA graph. Prompts run through `prefill`: the same operators
+over all prompt tokens at once, the linears on the tcgen05 GEMM, causal attention by torch's
+scaled_dot_product_attention (a library call: the only one on this path besides the batched head).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import lib
+from .kernels import L8Group, _dt, _stream
+from .linear import PackedLinear, RunsLin
+
+NAMES = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+@dataclass
+class Cfg:
+    hidden: int = 3584
+    n_heads: int = 28
+    n_kv: int = 4
+    head_dim: int = 128
+    inter: int = 18944
+    vocab: int = 152064
+    layers: int = 28
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    max_len: int = 512
+
+
+def _lin(obj) -> PackedLinear:
+    return obj.lin if isinstance(obj, RunsLin) else obj
+
+
+class DenseHead:
+    """16-bit weight [V, H]: run(x [B, H], logits [B, V] fp32). Up to 8 sequences stream the weight once
+    through the library's own kernel; larger batches are a plain library GEMM."""
+
+    def __init__(self, w: torch.Tensor):
+        if w.dtype not in (torch.float16, torch.bfloat16) or w.device.type != "cuda":
+            raise ValueError("the head weight must be a CUDA fp16 / bf16 tensor")
+        self.w = w.contiguous()
+        self.R, self.C = w.shape
+        self.perms = None
+
+    def run(self, x: torch.Tensor, logits: torch.Tensor) -> None:
+        B = x.shape[0]
+        if B <= lib.cbl_head_gemv_max_batch():
+            _lib.check("cbl_head_gemv", lib.cbl_head_gemv(self.w.data_ptr(), x.data_ptr(), _dt(self.w.dtype), B, self.R, self.C,
+                                                          logits.data_ptr(), _dt(logits.dtype), logits.stride(0), _stream()))
+        else:
+            logits.copy_(x @ self.w.t())
+
+    def nbytes(self) -> int:
+        return self.w.numel() * 2
+
+
+class _Stage:
+    """Linears that read the same input and write column slices of one [B, sum R] buffer (q|k|v, gate|up,
+    or a single matrix). One token and one column order: one grouped table-lookup launch."""
+
+    def __init__(self, lins: list, out: torch.Tensor):
+        self.lins = [_lin(l) for l in lins]
+        self.out, self.B = out, out.shape[0]
+        self.offs, o = [], 0
+        for l in self.lins:
+            self.offs.append(o)
+            o += l.R
+        assert o == out.shape[1]
+        self.group = None
+        if self.B == 1 and all(l.dm.M == 1 for l in self.lins) and len(self.lins) <= L8Group.MAX:
+            self.group = L8Group([l.l8 for l in self.lins])
+            self.ys = [out[0, o:o + l.R] for o, l in zip(self.offs, self.lins)]
+        else:
+            for l in self.lins:
+                l.t16.xp_buffer(self.B)
+
+    def run(self, x: torch.Tensor) -> None:
+        if self.group is not None:
+            self.group.run(x[0], self.ys)
+        else:
+            for o, l in zip(self.offs, self.lins):
+                l.forward_into(x, self.out[:, o:o + l.R])
+
+
+class DecodeEngine:
+    """layers: list of dicts with ln1, ln2 (16-bit [hidden]), q, k, v, o, gate, up, down (PackedLinear or
+    RunsLin), bq, bk, bv (16-bit bias or None). B sequences advance together, each with its own cache and
+    position. step() reads tok [B] at pos [B], writes logits [B, vocab] (fp32), tok (greedy next), pos += 1."""
+
+    def __init__(self, cfg: Cfg, embed: torch.Tensor, layers: list, final_norm: torch.Tensor, lm_head, dev="cuda", B: int = 1,
+                 attn_split: int | None = None):
+        if cfg.head_dim != 128 or cfg.n_heads % cfg.n_kv or cfg.n_heads // cfg.n_kv > 8:
+            raise ValueError("attention shape not supported: head_dim 128, at most 8 query heads per kv head")
+        if not 1 <= B <= 64:
+            raise ValueError(f"B = {B} outside 1..64")
+        dev = torch.device(dev)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.cfg, self.embed, self.layers, self.final_norm, self.lm_head, self.B, self.dev = cfg, embed, layers, final_norm, lm_head, B, dev
+        self.dtype = dt = embed.dtype
+        if dt not in (torch.float16, torch.bfloat16):
+            raise ValueError("the model's activation type is fp16 or bf16")
+        H, NH, NKV, HD, I = cfg.hidden, cfg.n_heads, cfg.n_kv, cfg.head_dim, cfg.inter
+        a = dict(dtype=dt, device=dev)
+        self.h = torch.zeros(B, H, dtype=torch.float32, device=dev)
+        self.x16 = torch.zeros(B, H, **a)
+        self.yqkv = torch.zeros(B, (NH + 2 * NKV) * HD, **a)
+        self.qr, self.ao = torch.zeros(B, NH * HD, **a), torch.zeros(B, NH * HD, **a)
+        self.yo, self.yd = torch.zeros(B, H, **a), torch.zeros(B, H, **a)
+        self.ygu, self.act = torch.zeros(B, 2 * I, **a), torch.zeros(B, I, **a)
+        self.logits = torch.zeros(B, lm_head.R, dtype=torch.float32, device=dev)
+        self.kc = torch.zeros(len(layers), B, NKV, cfg.max_len, HD, **a)
+        self.vc = torch.zeros_like(self.kc)
+        self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
+        # attention slices: about two blocks per SM, never fewer than the kernel's capacity needs
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        ns = attn_split if attn_split is not None else max(1, (2 * sms) // (NKV * B))
+        self.nsplit = max(min(ns, max(1, cfg.max_len // 32)), lib.cbl_attn_decode_min_splits(cfg.max_len))
+        self.att_ws = torch.zeros(lib.cbl_attn_decode_workspace_bytes(B, NH, self.nsplit), dtype=torch.uint8, device=dev)
+        self.biases = []
+        for L in layers:
+            bs = [L.get("bq"), L.get("bk"), L.get("bv")]
+            if all(b is None for b in bs):
+                self.biases.append(None)
+            else:
+                sizes = (NH * HD, NKV * HD, NKV * HD)
+                self.biases.append(torch.cat([b.to(**a) if b is not None else torch.zeros(n, **a) for b, n in zip(bs, sizes)]))
+        self.stages = []
+        for L in layers:
+            self.stages.append({"qkv": _Stage([L["q"], L["k"], L["v"]], self.yqkv), "o": _Stage([L["o"]], self.yo),
+                                "gu": _Stage([L["gate"], L["up"]], self.ygu), "down": _Stage([L["down"]], self.yd)})
+        self.graph = None
+        self.only_linears = False
+
+    # -- operators (thin wrappers over the C ABI; all on the current stream)
+    def _addnorm(self, h, add, w, x, rows: int) -> None:
+        _lib.check("cbl_add_rmsnorm", lib.cbl_add_rmsnorm(h.data_ptr(), None if add is None else add.data_ptr(),
+                                                          0 if add is None else add.stride(0), w.data_ptr(), _dt(self.dtype),
+                                                          self.cfg.eps, rows, self.cfg.hidden, x.data_ptr(), _stream()))
+
+    def _rope(self, yqkv, bias, pos, pos0: int, seq0: int, rows: int, qr, kc, vc) -> None:
+        c = self.cfg
+        _lib.check("cbl_rope_kv", lib.cbl_rope_kv(yqkv.data_ptr(), _dt(self.dtype), yqkv.stride(0), None if bias is None else bias.data_ptr(),
+                                                  None if pos is None else pos.data_ptr(), pos0, seq0, rows, c.n_heads, c.n_kv, c.head_dim,
+                                                  c.rope_theta, c.max_len, qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), _stream()))
+
+    def _silu(self, ygu, act, rows: int) -> None:
+        _lib.check("cbl_silu_mul", lib.cbl_silu_mul(ygu.data_ptr(), _dt(self.dtype), ygu.stride(0), rows, self.cfg.inter, act.data_ptr(),
+                                                    _stream()))
+
+    def step(self) -> None:
+        """One greedy decode step of all B sequences (graph-capturable)."""
+        c, B, dtc = self.cfg, self.B, _dt(self.dtype)
+        with torch.cuda.device(self.dev):
+            if self.only_linears:          # product-only timing: the same linears in the same order, nothing else
+                for S in self.stages:
+                    S["qkv"].run(self.x16)
+                    S["o"].run(self.ao)
+                    S["gu"].run(self.x16)
+                    S["down"].run(self.act)
+                return
+            s = _stream()
+            _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), dtc, self.embed.shape[0], c.hidden, self.tok.data_ptr(), B,
+                                                            self.h.data_ptr(), s))
+            add = None
+            for li, (L, S) in enumerate(zip(self.layers, self.stages)):
+                self._addnorm(self.h, add, L["ln1"], self.x16, B)
+                S["qkv"].run(self.x16)
+                self._rope(self.yqkv, self.biases[li], self.pos, 0, 0, B, self.qr, self.kc[li], self.vc[li])
+                _lib.check("cbl_attn_decode", lib.cbl_attn_decode(self.qr.data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(),
+                                                                  self.pos.data_ptr(), dtc, B, c.n_heads, c.n_kv, c.head_dim, c.max_len,
+                                                                  c.head_dim ** -0.5, self.ao.data_ptr(), self.att_ws.data_ptr(), self.nsplit, s))
+                S["o"].run(self.ao)
+                self._addnorm(self.h, self.yo, L["ln2"], self.x16, B)
+                S["gu"].run(self.x16)
+                self._silu(self.ygu, self.act, B)
+                S["down"].run(self.act)
+                add = self.yd
+            self._addnorm(self.h, add, self.final_norm, self.x16, B)
+            self.lm_head.run(self.x16, self.logits)
+            _lib.check("cbl_argmax", lib.cbl_argmax(self.logits.data_ptr(), _dt(self.logits.dtype), self.logits.stride(0), B, self.logits.shape[1],
+                                                    self.tok.data_ptr(), self.pos.data_ptr(), s))
+
+    @torch.no_grad()
+    def prefill(self, ids, seq: int = 0) -> torch.Tensor:
+        """Run a whole prompt of sequence `seq` from position 0: fills its cache, leaves pos[seq] = len(ids) and
+        tok[seq] = the greedy next token; returns the last position's logits [vocab] (fp32)."""
+        c = self.cfg
+        ids = torch.as_tensor(ids, dtype=torch.int64, device=self.dev).reshape(-1)
+        T = ids.numel()
+        if not 1 <= T <= c.max_len:
+            raise ValueError(f"prompt of {T} tokens outside 1..max_len {c.max_len}")
+        if T > 65535:
+            raise ValueError("prompts are prefilled in one pass of at most 65535 tokens")
+        H, NH, NKV, HD, I = c.hidden, c.n_heads, c.n_kv, c.head_dim, c.inter
+        a = dict(dtype=self.dtype, device=self.dev)
+        with torch.cuda.device(self.dev):
+            h = torch.empty(T, H, dtype=torch.float32, device=self.dev)
+            x = torch.empty(T, H, **a)
+            yqkv, qr = torch.empty(T, (NH + 2 * NKV) * HD, **a), torch.empty(T, NH * HD, **a)
+            yo, ygu, act, yd = torch.empty(T, H, **a), torch.empty(T, 2 * I, **a), torch.empty(T, I, **a), torch.empty(T, H, **a)
+            _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), _dt(self.dtype), self.embed.shape[0], H, ids.data_ptr(), T,
+                                                            h.data_ptr(), _stream()))
+            add = None
+            for li, L in enumerate(self.layers):
+                self._addnorm(h, add, L["ln1"], x, T)
+                o = 0
+                for n in ("q", "k", "v"):
+                    l = _lin(L[n])
+                    l.forward_into(x, yqkv[:, o:o + l.R])
+                    o += l.R
+                kc, vc = self.kc[li], self.vc[li]
+                self._rope(yqkv, self.biases[li], None, 0, seq, T, qr, kc, vc)
+                q4 = qr.view(T, NH, HD).transpose(0, 1)[None]
+                ao = torch.nn.functional.scaled_dot_product_attention(q4, kc[seq, :, :T][None], vc[seq, :, :T][None], is_causal=True,
+                                                                      enable_gqa=True)
+                ao = ao[0].transpose(0, 1).reshape(T, NH * HD)
+                _lin(L["o"]).forward_into(ao, yo)
+                self._addnorm(h, yo, L["ln2"], x, T)
+                o = 0
+                for n in ("gate", "up"):
+                    l = _lin(L[n])
+                    l.forward_into(x, ygu[:, o:o + l.R])
+                    o += l.R
+                self._silu(ygu, act, T)
+                _lin(L["down"]).forward_into(act, yd)
+                add = yd
+            hl, xl = h[T - 1:T].clone(), torch.empty(1, H, **a)
+            self._addnorm(hl, yd[T - 1:T], self.final_norm, xl, 1)
+            lg = self.logits[seq:seq + 1]
+            self.lm_head.run(xl, lg)
+            _lib.check("cbl_argmax", lib.cbl_argmax(lg.data_ptr(), _dt(lg.dtype), lg.stride(0), 1, lg.shape[1], self.tok[seq:].data_ptr(), None,
+                                                    _stream()))
+            self.pos[seq] = T
+        return lg[0].clone()
+
+    def reset(self, tok=0) -> None:
+        if isinstance(tok, int):
+            self.tok.fill_(tok)
+        else:
+            self.tok.copy_(torch.as_tensor(tok, dtype=torch.int64))
+        self.pos.zero_()
+
+    def capture(self):
+        """Capture one step as a CUDA graph (two eager steps first: they advance the state, reset afterwards)."""
+        st = torch.cuda.Stream(device=self.dev)
+        st.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(st):
+            for _ in range(2):
+                self.step()
+        torch.cuda.current_stream(self.dev).wait_stream(st)
+        torch.cuda.synchronize(self.dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=st):      # the warm-up stream: its work spaces exist already
+            self.step()
+        return self.graph
+
+    def check(self) -> None:
+        """Synchronises; raises if an attention launch met a slice beyond the kernel's capacity."""
+        torch.cuda.synchronize(self.dev)
+        if int(self.att_ws[-16:].view(torch.int32)[0]) != 0:
+            raise _lib.CblError("cbl_attn_decode", _lib.EINVAL, "a position slice exceeded the kernel's capacity")
+
+    @torch.no_grad()
+    def generate(self, n: int, tok=0) -> list:
+        """Greedy-decode n tokens from `tok` at position 0 (eager steps; for checks). B = 1: a list of ints,
+        else a list of B lists."""
+        self.reset(tok)
+        out = []
+        for _ in range(n):
+            self.step()
+            out.append(self.tok.tolist())
+        return [o[0] for o in out] if self.B == 1 else [list(s) for s in zip(*out)]
+
+    @torch.no_grad()
+    def time_tokens(self, n: int = 128, reps: int = 3, start: int = 0) -> float:
+        """Seconds per step, averaged over n graph replays from position `start` (median of reps). The cache
+        below `start` is used as it is (decode speed does not depend on its values)."""
+        assert start + n <= self.cfg.max_len
+        if self.graph is None:
+            self.capture()
+        ts = []
+        for _ in range(reps):
+            self.reset()
+            self.pos.fill_(start)
+            torch.cuda.synchronize(self.dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                self.graph.replay()
+            b.record()
+            torch.cuda.synchronize(self.dev)
+            ts.append(a.elapsed_time(b) / 1e3 / n)
+        return sorted(ts)[len(ts) // 2]
+
+    def weight_bytes(self) -> int:
+        """Stored bytes a step reads: the packed block linears (tags, books, scales) and the head."""
+        return sum(_lin(L[n]).stored_bytes() for L in self.layers for n in NAMES) + self.lm_head.nbytes()
+
+
+class Qwen2BatchEngine(DecodeEngine):
+    """B sequences per step on the weights of a batch-1 engine (its own caches, positions and buffers)."""
+
+    def __init__(self, eng: DecodeEngine, B: int, *, nsplit: int | None = None, **_ignored):
+        super().__init__(eng.cfg, eng.embed, eng.layers, eng.final_norm, eng.lm_head, dev=eng.dev, B=B, attn_split=nsplit)
+        self.eng = eng
+
+
+def random_engine(cfg: Cfg, *, seed: int = 0, dev="cuda", dtype=torch.bfloat16, B: int = 1, books: int = 1, M: int = 1,
+                  bias: bool = True) -> DecodeEngine:
+    """A random-init model of the given architecture with every block linear in the packed format (d = 8,
+    12-bit tags, one 4096-entry book per matrix; `books` = 2 adds a second summed book, M > 1 seeded column
+    orders). Stand-in for a real checkpoint: tags uniform, books ~N(0, 1), row scales ~0.02 / sqrt(books),
+    embedding and head ~N(0, 0.02), norm weights 1 +- 0.1, q/k/v biases ~N(0, 0.1)."""
+    dev = torch.device(dev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    H, NH, NKV, HD, I = cfg.hidden, cfg.n_heads, cfg.n_kv, cfg.head_dim, cfg.inter
+
+    def lin(R, C):
+        W = (C // 8 * 12 + 31) // 32
+        words = torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device=dev, generator=g)
+        table = torch.randn(4096, 8, device=dev, generator=g).half()
+        rs = ((torch.rand(R, device=dev, generator=g) * 0.5 + 0.75) / math.sqrt(C * books)).half()
+        kw = {}
+        if books == 2:
+            kw = dict(words2=torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device=dev, generator=g),
+                      table2=torch.randn(4096, 8, device=dev, generator=g).half())
+        if M > 1:
+            from .packed import seeded_perms
+            perms = seeded_perms(C, M, torch.Generator().manual_seed(seed + R + C)).to(dev)
+            mask = torch.randint(0, M, (R,), dtype=torch.int32, device=dev, generator=g)
+        else:
+            perms, mask = torch.arange(C, device=dev)[None], None
+        return PackedLinear(words, table, rs, None, mask, perms, 4096, 8, **kw)
+
+    def vec(n, s, base=0.0):
+        return (torch.randn(n, device=dev, generator=g) * s + base).to(dtype)
+
+    layers = []
+    for _ in range(cfg.layers):
+        L = {"ln1": vec(H, 0.1, 1.0), "ln2": vec(H, 0.1, 1.0), "q": lin(NH * HD, H), "k": lin(NKV * HD, H), "v": lin(NKV * HD, H),
+             "o": lin(H, NH * HD), "gate": lin(I, H), "up": lin(I, H), "down": lin(H, I)}
+        if bias:
+            L.update(bq=vec(NH * HD, 0.1), bk=vec(NKV * HD, 0.1), bv=vec(NKV * HD, 0.1))
+        layers.append(L)
+    embed = (torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype)
+    head = DenseHead((torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype))
+    return DecodeEngine(cfg, embed, layers, vec(H, 0.1, 1.0), head, dev=dev, B=B)
+
+
+# ------------------------------------------------------------------------------------------- runtime helpers
+@torch.no_grad()
+def start(eng: DecodeEngine, prompt, seq: int = 0) -> torch.Tensor:
+    """Fresh context for sequence `seq`: run `prompt` from position 0 (batched prefill). Returns the last
+    position's fp32 logits; afterwards tok[seq] = greedy next token, pos[seq] = len(prompt)."""
+    return eng.prefill(prompt, seq)
+
+
+def _sample(logits: torch.Tensor, temperature: float, top_p: float, top_k: int, gen) -> int:
+    z = logits.float() / max(temperature, 1e-6)
+    if top_k and top_k < z.numel():
+        z = torch.where(z < torch.topk(z, top_k).values[-1], torch.full_like(z, float("-inf")), z)
+    if top_p < 1.0:
+        sz, si = torch.sort(z, descending=True)
+        pr = torch.softmax(sz, -1)
+        sz[pr.cumsum(-1) - pr > top_p] = float("-inf")          # keep the smallest prefix reaching top_p
+        z = torch.full_like(z, float("-inf")).scatter(0, si, sz)
+    return int(torch.multinomial(torch.softmax(z, -1), 1, generator=gen))
+
+
+@torch.no_grad()
+def generate(eng: DecodeEngine, prompt, n: int, graph: bool = True, *, temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0,
+             seed: int | None = None, stop_ids=()) -> list:
+    """Continue `prompt` by up to n tokens on a batch-1 engine. temperature 0: greedy (the step's own argmax),
+    else sampled with top-k / top-p. Stops after a token in stop_ids (included)."""
+    if eng.B != 1:
+        raise ValueError("generate() drives a batch-1 engine")
+    if len(prompt) + n > eng.cfg.max_len:
+        raise ValueError("prompt + n exceeds max_len")
+    if graph and eng.graph is None:
+        eng.capture()
+    gen = None
+    if temperature > 0:
+        gen = torch.Generator(device=eng.dev)
+        gen.manual_seed(seed if seed is not None else torch.seed() % (2 ** 63))
+    stop_ids = set(stop_ids or ())
+    eng.reset(0)
+    logits = start(eng, prompt)
+    out = []
+    while True:
+        if temperature > 0:
+            t = _sample(logits, temperature, top_p, top_k, gen)
+            eng.tok.fill_(t)
+        else:
+            t = int(eng.tok[0])
+        out.append(t)
+        if len(out) >= n or t in stop_ids:
+            break
+        if graph:
+            eng.graph.replay()
+        else:
+            eng.step()
+        logits = eng.logits[0]
+    return out
+
+
+@torch.no_grad()
+def bench(eng: DecodeEngine, pp: int = 512, tg: int = 128, reps: int = 3) -> dict:
+    """Prompt tokens/s of one prefill of `pp` tokens and generated tokens/s over `tg` graph-replayed steps
+    that follow it (all B sequences; median of reps)."""
+    res = {}
+    if pp:
+        ids = torch.randint(0, eng.cfg.vocab, (pp,), device=eng.dev)
+        ts = []
+        for _ in range(reps + 1):
+            torch.cuda.synchronize(eng.dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.prefill(ids, 0)
+            b.record()
+            torch.cuda.synchronize(eng.dev)
+            ts.append(a.elapsed_time(b) / 1e3)
+        ts = sorted(ts[1:])
+        res.update(pp=pp, pp_tok_s=pp / ts[len(ts) // 2])
+    if tg:
+        res.update(tg=tg, tg_tok_s=eng.B / eng.time_tokens(tg, reps, start=pp))
+    return res
