@@ -260,6 +260,25 @@ int32_t cbl_head_gemv_max_batch(void);
 int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype, int64_t ldl,
                   cbl_stream s);
 
+/* Batch-1 products whose finish kernel also runs the step operator that follows them (one launch less,
+ * no round trip of the vector through memory).  Results equal the product followed by the separate
+ * operator: the product is rounded to `dtype` first.  `workspace` as for cbl_gemv_l8_multi (the
+ * matrices' padded rows x 4 bytes in order, plus 16 bytes; zero before the first call, left zero).
+ *   cbl_gemv_l8_silu_mul: gate_up[0..1] (equal row counts) -> out[i] = silu(gate.x)[i] * (up.x)[i]
+ *   cbl_gemv_l8_add_norm: h += W.x; xout = RMSNorm(h) * w   (R <= cbl_gemv_l8_add_norm_max_rows())
+ *   cbl_gemv_l8_rope_kv:  qkv[0..2] = q, k, v projections -> bias, rotary at position pos[0], rotated
+ *                         query to q_out [NH * HD], key / value into the caches of sequence 0
+ * replaces the epilogue modes of the reference's run kernel (shapequant/kernels/proto_runs.py:223-287:
+ * add + norm and silu * mul written by the last blocks) and its fused rope + attention prologue
+ * (decode_e2e.py:200-250). */
+int cbl_gemv_l8_silu_mul(const cbl_l8* gate_up, const void* x, int xdtype, void* out, int dtype, void* workspace, cbl_stream s);
+int32_t cbl_gemv_l8_add_norm_max_rows(void);
+int cbl_gemv_l8_add_norm(const cbl_l8* m, const void* x, int xdtype, float* h, const void* w, float eps, void* xout, int dtype,
+                         void* workspace, cbl_stream s);
+int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype, const void* bias, const int32_t* pos, int32_t NH, int32_t NKV,
+                        int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, int dtype, void* workspace,
+                        cbl_stream s);
+
 /* tok[b] = index of the first largest logit of row b; pos[b] += 1 when pos != NULL. */
 int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s);
 

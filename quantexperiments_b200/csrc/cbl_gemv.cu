@@ -726,14 +726,13 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, int ydtype, u
     return cbl_check_launch();
 }
 
-extern "C" int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
-                                 void* workspace, cbl_stream s) {
-    if (!mats || !ys || !x || !workspace || n < 1) return CBL_EINVAL;
+// Fills the launch descriptor of a group: accumulators carved from `workspace` in order, the status word after them.
+static int l8_group(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, void* workspace, L8Launch& P,
+                    unsigned int*& status) {
+    if (!mats || !x || !workspace || n < 1) return CBL_EINVAL;
     if (n > L8_MAX_GROUP) return CBL_EUNSUPPORTED;
     if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
-    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
     if ((uintptr_t)workspace % 16) return CBL_EINVAL;
-    L8Launch P;
     P.n = 0;
     P.tile0[0] = 0;
     size_t off = 0;
@@ -741,22 +740,36 @@ extern "C" int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, i
         int rc = check_l8(mats + i);
         if (rc) return rc;
         if (mats[i].C != mats[0].C) return CBL_EINVAL;          // one shared activation vector
-        if (!ys[i]) return CBL_EINVAL;
+        if (ys && !ys[i]) return CBL_EINVAL;
         if (mats[i].R == 0) continue;
         P.m[P.n] = mats[i];
         P.acc[P.n] = (float*)((char*)workspace + off);
-        P.y[P.n] = ys[i];
+        P.y[P.n] = ys ? ys[i] : nullptr;
         P.tile0[P.n + 1] = P.tile0[P.n] + mats[i].ntile;
         off += (size_t)mats[i].Rpad * 4;
         P.n++;
     }
     P.calls = nullptr;
     P.acc_stride = 0;
+    status = (unsigned int*)((char*)workspace + off);
+    return CBL_OK;
+}
+
+static int l8_launch_any(const L8Launch& P, const void* x, int xdtype, int ydtype, unsigned int* status, cudaStream_t st, bool finish) {
+    if (l8_threads() == 256) return launch_l8<256>(P, x, xdtype, ydtype, status, st, finish);
+    return launch_l8<512>(P, x, xdtype, ydtype, status, st, finish);
+}
+
+extern "C" int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
+                                 void* workspace, cbl_stream s) {
+    if (!ys) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    L8Launch P;
+    unsigned int* status = nullptr;
+    int rc = l8_group(mats, n, x, xdtype, ys, workspace, P, status);
+    if (rc) return rc;
     if (P.n == 0) return CBL_OK;
-    unsigned int* status = (unsigned int*)((char*)workspace + off);
-    cudaStream_t st = (cudaStream_t)s;
-    if (l8_threads() == 256) return launch_l8<256>(P, x, xdtype, ydtype, status, st);
-    return launch_l8<512>(P, x, xdtype, ydtype, status, st);
+    return l8_launch_any(P, x, xdtype, ydtype, status, (cudaStream_t)s, true);
 }
 
 extern "C" int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s) {
@@ -774,6 +787,223 @@ extern "C" int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s
     CBL_CUDA(cudaMemcpyAsync(&v, (const char*)workspace + Rpad * 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
     return v ? CBL_ETIMEOUT : CBL_OK;
+}
+
+// ------------------------------------------------------------------------------------ batch-1 products with a decode-step epilogue
+//
+// In a decode step most products are followed by a small operator on their output vector.  These entry
+// points run that operator inside the finish kernel (one launch less per product, no round trip of the
+// vector through memory); results are identical to the separate operators of the step library because
+// the product is rounded to the model's 16-bit type first, exactly as if it had been stored.
+//   gate|up  -> silu(gate) * up                      (cbl_silu_mul)
+//   o / down -> residual add + RMSNorm               (cbl_add_rmsnorm): the finish kernel's blocks form one
+//               cluster and exchange their sums of squares through distributed shared memory
+//   q|k|v    -> bias, rotary embedding, cache write  (cbl_rope_kv, decode form, sequence 0)
+template <typename T> __device__ __forceinline__ float l8_f(T v);
+template <> __device__ __forceinline__ float l8_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float l8_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ void l8_pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_l8_finish_silu(const __grid_constant__ L8Launch P, T* __restrict__ out) {
+    l8_pdl_enter();
+    const cbl_l8& mg = P.m[0];
+    const cbl_l8& mu = P.m[1];
+    const int gi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= (mg.Rpad >> 2)) return;
+    float4* ag = (float4*)P.acc[0];
+    float4* au = (float4*)P.acc[1];
+    const float4 g = __ldcg(ag + gi), u = __ldcg(au + gi);
+    __stcg(ag + gi, make_float4(0.f, 0.f, 0.f, 0.f));
+    __stcg(au + gi, make_float4(0.f, 0.f, 0.f, 0.f));
+    const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int r = gi * 4 + k;
+        if (r < mg.R) {
+            const float a = l8_f(cbl_cvt_out<T>(gv[k] * __half2float(((const __half*)mg.row_scale)[r])));
+            const float b = l8_f(cbl_cvt_out<T>(uv[k] * __half2float(((const __half*)mu.row_scale)[r])));
+            const float sl = l8_f(cbl_cvt_out<T>(a / (1.f + __expf(-a))));
+            out[r] = cbl_cvt_out<T>(sl * b);
+        }
+    }
+}
+
+constexpr int L8_NORM_MAX_CTAS = 8;          // portable cluster size: up to 8 x 1024 rows
+template <typename T>
+__global__ void __launch_bounds__(256) k_l8_finish_addnorm(const __grid_constant__ L8Launch P, float* __restrict__ h, const T* __restrict__ w,
+                                                           float eps, T* __restrict__ xout) {
+    l8_pdl_enter();
+    __shared__ float s_warp[8];
+    __shared__ float s_ss, s_tot;
+    const cbl_l8& mm = P.m[0];
+    const int tid = threadIdx.x, gi = blockIdx.x * blockDim.x + tid, nb = gridDim.x;
+    float hv[4] = {0.f, 0.f, 0.f, 0.f};
+    float ss = 0.f;
+    if (gi < (mm.Rpad >> 2)) {
+        float4* acc = (float4*)P.acc[0];
+        const float4 v = __ldcg(acc + gi);
+        __stcg(acc + gi, make_float4(0.f, 0.f, 0.f, 0.f));
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int r = gi * 4 + k;
+            if (r < mm.R) {
+                hv[k] = h[r] + l8_f(cbl_cvt_out<T>(vv[k] * __half2float(((const __half*)mm.row_scale)[r])));
+                h[r] = hv[k];
+                ss += hv[k] * hv[k];
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) s_warp[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) s_ss = ((s_warp[0] + s_warp[1]) + (s_warp[2] + s_warp[3])) + ((s_warp[4] + s_warp[5]) + (s_warp[6] + s_warp[7]));
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid < 32) {
+        float v = 0.f;
+        if (tid < nb) {
+            uint32_t a;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(cbl_smem_u32(&s_ss)), "r"(tid));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+        }
+        // fixed order of addition over the blocks: every block computes the same total
+        float tot = 0.f;
+        for (int k = 0; k < nb; k++) tot += __shfl_sync(0xffffffffu, v, k);
+        if (tid == 0) s_tot = tot;
+    }
+    __syncthreads();
+    const float rstd = rsqrtf(s_tot / (float)mm.R + eps);
+    if (gi < (mm.Rpad >> 2)) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int r = gi * 4 + k;
+            if (r < mm.R) xout[r] = cbl_cvt_out<T>(hv[k] * rstd * l8_f(w[r]));
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // no block leaves while another may still read its sum
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L8Launch P, const T* __restrict__ bias,
+                                                       const int32_t* __restrict__ pos, int NH, int NKV, int HD, float theta, int max_len,
+                                                       T* __restrict__ qo, T* __restrict__ kc, T* __restrict__ vc) {
+    l8_pdl_enter();
+    const int hd = blockIdx.x, i = threadIdx.x, half = HD >> 1;
+    if (i >= half) return;
+    const int p = pos[0];
+    const bool ok = p >= 0 && p < max_len;
+    const float inv = 1.f / powf(theta, (2.f * (float)i) / (float)HD);
+    const float ang = (float)p * inv;
+    const float c = l8_f(cbl_cvt_out<T>(cosf(ang))), sn = l8_f(cbl_cvt_out<T>(sinf(ang)));
+    // one output element of matrix mi: take the sum, clear it, scale, round, add the bias in the 16-bit type
+    auto take = [&](int mi, int r, int bcol) {
+        float* a = P.acc[mi] + r;
+        const float v = __ldcg(a);
+        __stcg(a, 0.f);
+        const float y = l8_f(cbl_cvt_out<T>(v * __half2float(((const __half*)P.m[mi].row_scale)[r])));
+        return bias ? l8_f(cbl_cvt_out<T>(y + l8_f(bias[bcol]))) : y;
+    };
+    const bool isq = hd < NH;
+    const int mi = isq ? 0 : 1, o = (isq ? hd : hd - NH) * HD, bo = hd * HD;
+    const float x1 = take(mi, o + i, bo + i), x2 = take(mi, o + i + half, bo + i + half);
+    const T r1 = cbl_cvt_out<T>(x1 * c - x2 * sn), r2 = cbl_cvt_out<T>(x2 * c + x1 * sn);
+    if (isq) {
+        if (ok) { qo[o + i] = r1; qo[o + i + half] = r2; }
+    } else {
+        const int kv = hd - NH, bv = (NH + NKV + kv) * HD;
+        const float v1 = take(2, o + i, bv + i), v2 = take(2, o + i + half, bv + i + half);
+        if (ok) {
+            const int64_t co = ((int64_t)kv * max_len + p) * HD;
+            kc[co + i] = r1;
+            kc[co + i + half] = r2;
+            vc[co + i] = cbl_cvt_out<T>(v1);
+            vc[co + i + half] = cbl_cvt_out<T>(v2);
+        }
+    }
+}
+
+template <typename... KA, typename... A>
+static int l8_finish_launch(void (*kern)(KA...), dim3 grid, dim3 block, int cluster_x, cudaStream_t st, A... args) {
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster_x;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = cluster_x > 1 ? 2 : 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...));
+    return cbl_check_launch();
+}
+
+extern "C" int cbl_gemv_l8_silu_mul(const cbl_l8* gate_up, const void* x, int xdtype, void* out, int dtype, void* workspace, cbl_stream s) {
+    if (!out || (dtype != CBL_F16 && dtype != CBL_BF16)) return CBL_EINVAL;
+    L8Launch P;
+    unsigned int* status = nullptr;
+    int rc = l8_group(gate_up, 2, x, xdtype, nullptr, workspace, P, status);
+    if (rc) return rc;
+    if (gate_up[0].R != gate_up[1].R) return CBL_EINVAL;
+    if (P.n == 0) return CBL_OK;
+    const cudaStream_t st = (cudaStream_t)s;
+    rc = l8_launch_any(P, x, xdtype, dtype, status, st, false);
+    if (rc) return rc;
+    const dim3 grid(cbl_ceil_div(P.m[0].Rpad >> 2, 256));
+    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_silu<__half>, grid, dim3(256), 1, st, P, (__half*)out);
+    return l8_finish_launch(k_l8_finish_silu<__nv_bfloat16>, grid, dim3(256), 1, st, P, (__nv_bfloat16*)out);
+}
+
+extern "C" int32_t cbl_gemv_l8_add_norm_max_rows(void) { return L8_NORM_MAX_CTAS * 1024; }
+
+extern "C" int cbl_gemv_l8_add_norm(const cbl_l8* m, const void* x, int xdtype, float* h, const void* w, float eps, void* xout, int dtype,
+                                    void* workspace, cbl_stream s) {
+    if (!h || !w || !xout || (dtype != CBL_F16 && dtype != CBL_BF16)) return CBL_EINVAL;
+    L8Launch P;
+    unsigned int* status = nullptr;
+    int rc = l8_group(m, 1, x, xdtype, nullptr, workspace, P, status);
+    if (rc) return rc;
+    if (m->R < 1) return CBL_EINVAL;
+    if (m->R > L8_NORM_MAX_CTAS * 1024) return CBL_EUNSUPPORTED;
+    const cudaStream_t st = (cudaStream_t)s;
+    rc = l8_launch_any(P, x, xdtype, dtype, status, st, false);
+    if (rc) return rc;
+    const int nb = cbl_ceil_div(P.m[0].Rpad >> 2, 256);
+    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_addnorm<__half>, dim3(nb), dim3(256), nb, st, P, h, (const __half*)w, eps, (__half*)xout);
+    return l8_finish_launch(k_l8_finish_addnorm<__nv_bfloat16>, dim3(nb), dim3(256), nb, st, P, h, (const __nv_bfloat16*)w, eps,
+                            (__nv_bfloat16*)xout);
+}
+
+extern "C" int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype, const void* bias, const int32_t* pos, int32_t NH, int32_t NKV,
+                                   int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, int dtype, void* workspace,
+                                   cbl_stream s) {
+    if (!pos || !q_out || !kc || !vc || (dtype != CBL_F16 && dtype != CBL_BF16) || NH < 1 || NKV < 1 || max_len < 1) return CBL_EINVAL;
+    if (HD < 2 || HD > 128 || (HD & 1)) return CBL_EUNSUPPORTED;
+    L8Launch P;
+    unsigned int* status = nullptr;
+    int rc = l8_group(qkv, 3, x, xdtype, nullptr, workspace, P, status);
+    if (rc) return rc;
+    if (qkv[0].R != NH * HD || qkv[1].R != NKV * HD || qkv[2].R != NKV * HD) return CBL_EINVAL;
+    const cudaStream_t st = (cudaStream_t)s;
+    rc = l8_launch_any(P, x, xdtype, dtype, status, st, false);
+    if (rc) return rc;
+    const dim3 grid(NH + NKV);
+    if (dtype == CBL_F16)
+        return l8_finish_launch(k_l8_finish_rope<__half>, grid, dim3(64), 1, st, P, (const __half*)bias, pos, (int)NH, (int)NKV, (int)HD, theta,
+                                (int)max_len, (__half*)q_out, (__half*)kc, (__half*)vc);
+    return l8_finish_launch(k_l8_finish_rope<__nv_bfloat16>, grid, dim3(64), 1, st, P, (const __nv_bfloat16*)bias, pos, (int)NH, (int)NKV, (int)HD,
+                            theta, (int)max_len, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc);
 }
 
 // ------------------------------------------------------------------------------------ row-split product + all-reduce over peer memory

@@ -13,15 +13,19 @@
 
 namespace {
 
-template <typename... KA, typename... A>
+template <int CLUSTER_X = 1, typename... KA, typename... A>
 int step_launch(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CLUSTER_X;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.stream = st;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = CLUSTER_X > 1 ? 2 : 1;
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
@@ -195,7 +199,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict_
         const uint4* kr = (const uint4*)(kbase + (int64_t)t * HD);
         uint4 w[HD / 8];
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) w[c] = cbl_ldg_stream(kr + c);
+        for (int c = 0; c < HD / 8; c++) w[c] = __ldg(kr + c);           // L1-allocating: a thread uses both halves of each sector
         float d[REP];
 #pragma unroll
         for (int h = 0; h < REP; h++) d[h] = 0.f;
@@ -247,15 +251,16 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict_
     for (int h = 0; h < REP; h++)
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
-    for (int t0 = s0; t0 < s1; t0 += 32) {
-        uint4 w[4];
+    constexpr int VU = 8;                                            // V rows in flight per thread
+    for (int t0 = s0; t0 < s1; t0 += 8 * VU) {
+        uint4 w[VU];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < VU; u++) {
             const int t = t0 + u * 8 + rg;
             w[u] = t < s1 ? cbl_ldg_stream((const uint4*)(vbase + (int64_t)t * HD) + db) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < VU; u++) {
             const int t = t0 + u * 8 + rg;
             if (t < s1) {
                 float f[8];
@@ -285,23 +290,39 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict_
     if (tid < REP) { pout[tid * hstride + HD] = s_m[tid]; pout[tid * hstride + HD + 1] = s_l[tid]; }
 }
 
-// out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s
+// out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s.  One block per (head, sequence): the
+// slices' weights are computed once (a thread per slice), then every thread sums its output dimension.
+constexpr int ATT_MAX_SPLITS = 512;
 template <typename T>
 __global__ void __launch_bounds__(ATT_HD) k_attn_merge(const float* __restrict__ part, int nsplit, T* __restrict__ out) {
     pdl_enter();
     constexpr int HD = ATT_HD;
+    __shared__ float s_w[ATT_MAX_SPLITS];
+    __shared__ float s_red[4];
     const int head = blockIdx.x, b = blockIdx.y, NH = gridDim.x, d = threadIdx.x;
     const float* p = part + ((int64_t)b * NH + head) * nsplit * (HD + 2);
     float m = -3.0e38f;
-    for (int s = 0; s < nsplit; s++) m = fmaxf(m, p[s * (HD + 2) + HD]);
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < nsplit; s++) {
+    for (int s = d; s < nsplit; s += HD) m = fmaxf(m, p[s * (HD + 2) + HD]);
+    m = warp_max(m);
+    if ((d & 31) == 0) s_red[d >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    __syncthreads();
+    float den = 0.f;
+    for (int s = d; s < nsplit; s += HD) {
         const float l = p[s * (HD + 2) + HD + 1];
-        if (l > 0.f) {
-            const float wgt = __expf(p[s * (HD + 2) + HD] - m);
-            num += wgt * p[s * (HD + 2) + d];
-            den += wgt * l;
-        }
+        const float w = l > 0.f ? __expf(p[s * (HD + 2) + HD] - m) : 0.f;
+        s_w[s] = w;
+        den += w * l;
+    }
+    den = warp_sum(den);
+    if ((d & 31) == 0) s_red[d >> 5] = den;
+    __syncthreads();
+    den = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float num = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < nsplit; s++) {
+        num += s_w[s] * p[s * (HD + 2) + d];          // an empty slice has weight 0 and finite (stale or zero) sums
     }
     out[((int64_t)b * NH + head) * HD + d] = cbl_cvt_out<T>(den > 0.f ? num / den : 0.f);
 }
@@ -370,16 +391,25 @@ __global__ void __launch_bounds__(256) k_head(const T* __restrict__ W, const T* 
 }
 
 // ---------------------------------------------------------------------------------------- greedy argmax
-// tok[b] = first index of the largest logit of row b; pos[b] += 1 when pos is given.
+// tok[b] = first index of the largest logit of row b; pos[b] += 1 when pos is given.  A cluster of ARGMAX_CTAS
+// thread blocks per row: every block reduces its share, block 0 collects the others' results through
+// distributed shared memory.
+constexpr int ARGMAX_CTAS = 8;
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __global__ void __launch_bounds__(1024) k_argmax(const void* __restrict__ logits, int ldtype, int64_t ldl, int V, int64_t* __restrict__ tok,
                                                  int32_t* __restrict__ pos) {
     pdl_enter();
     __shared__ float s_v[32];
     __shared__ int s_i[32];
-    const int b = blockIdx.x, tid = threadIdx.x;
+    __shared__ float s_bv;
+    __shared__ int s_bi;
+    const int b = blockIdx.y, tid = threadIdx.x, rank = blockIdx.x;             // the cluster spans blockIdx.x
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += blockDim.x) {
+    for (int i = rank * 1024 + tid; i < V; i += ARGMAX_CTAS * 1024) {
         const float v = cbl_load_in(logits, ldtype, (int64_t)b * ldl + i);
         if (v > best || (v == best && i < bi)) { best = v; bi = i; }
     }
@@ -393,8 +423,27 @@ __global__ void __launch_bounds__(1024) k_argmax(const void* __restrict__ logits
     if ((tid & 31) == 0) { s_v[tid >> 5] = best; s_i[tid >> 5] = bi; }
     __syncthreads();
     if (tid < 32) {
-        best = tid < (int)(blockDim.x >> 5) ? s_v[tid] : -INFINITY;
-        bi = tid < (int)(blockDim.x >> 5) ? s_i[tid] : 0x7fffffff;
+        best = s_v[tid];
+        bi = s_i[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float w = __shfl_xor_sync(0xffffffffu, best, o);
+            const int j = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(best, bi, w, j)) { best = w; bi = j; }
+        }
+        if (tid == 0) { s_bv = best; s_bi = bi; }
+    }
+    cluster_sync_all();                                              // every block's result is in its shared memory
+    if (rank == 0 && tid < 32) {
+        best = -INFINITY;
+        bi = 0x7fffffff;
+        if (tid < ARGMAX_CTAS) {
+            uint32_t av, ai;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(av) : "r"(cbl_smem_u32(&s_bv)), "r"(tid));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ai) : "r"(cbl_smem_u32(&s_bi)), "r"(tid));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(best) : "r"(av) : "memory");
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(bi) : "r"(ai) : "memory");
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float w = __shfl_xor_sync(0xffffffffu, best, o);
@@ -406,6 +455,7 @@ __global__ void __launch_bounds__(1024) k_argmax(const void* __restrict__ logits
             if (pos) pos[b] += 1;
         }
     }
+    cluster_sync_all();                                              // no block leaves while block 0 may still read it
 }
 
 bool is16(int dt) { return dt == CBL_F16 || dt == CBL_BF16; }
@@ -465,7 +515,7 @@ static int attn_launch(const void* q, const void* kc, const void* vc, const int3
 extern "C" int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
                                int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s) {
     if (!q || !kc || !vc || !pos || !out || !workspace || !is16(dtype) || B < 0 || NH < 1 || NKV < 1 || nsplit < 1) return CBL_EINVAL;
-    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > 65535) return CBL_EUNSUPPORTED;
+    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > ATT_MAX_SPLITS) return CBL_EUNSUPPORTED;
     if (nsplit < cbl_attn_decode_min_splits(max_len)) return CBL_EINVAL;
     if (B == 0) return CBL_OK;
     float* part = (float*)workspace;
@@ -540,5 +590,6 @@ extern "C" int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B,
 extern "C" int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s) {
     if (!logits || !tok || V < 1 || B < 0 || (ldtype != CBL_F32 && !is16(ldtype))) return CBL_EINVAL;
     if (B == 0) return CBL_OK;
-    return step_launch(k_argmax, dim3(B), dim3(1024), 0, (cudaStream_t)s, logits, ldtype, ldl, (int)V, tok, pos);
+    if (B > 65535) return CBL_EUNSUPPORTED;
+    return step_launch<ARGMAX_CTAS>(k_argmax, dim3(ARGMAX_CTAS, B), dim3(1024), 0, (cudaStream_t)s, logits, ldtype, ldl, (int)V, tok, pos);
 }

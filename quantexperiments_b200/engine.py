@@ -130,10 +130,10 @@ class DecodeEngine:
         self.vc = torch.zeros_like(self.kc)
         self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
-        # attention slices: about two blocks per SM, never fewer than the kernel's capacity needs
+        # attention slices: about four blocks per SM, never fewer than the kernel's capacity needs
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        ns = attn_split if attn_split is not None else max(1, (2 * sms) // (NKV * B))
-        self.nsplit = max(min(ns, max(1, cfg.max_len // 32)), lib.cbl_attn_decode_min_splits(cfg.max_len))
+        ns = attn_split if attn_split is not None else max(1, (4 * sms) // (NKV * B))
+        self.nsplit = max(min(ns, max(1, cfg.max_len // 32), 512), lib.cbl_attn_decode_min_splits(cfg.max_len))
         self.att_ws = torch.zeros(lib.cbl_attn_decode_workspace_bytes(B, NH, self.nsplit), dtype=torch.uint8, device=dev)
         self.biases = []
         for L in layers:
@@ -149,6 +149,8 @@ class DecodeEngine:
                                 "gu": _Stage([L["gate"], L["up"]], self.ygu), "down": _Stage([L["down"]], self.yd)})
         self.graph = None
         self.only_linears = False
+        # one token, one column order everywhere: the operators that follow a product run in its finish kernel
+        self.fused = all(st.group is not None for S in self.stages for st in S.values()) and H <= lib.cbl_gemv_l8_add_norm_max_rows()
 
     # -- operators (thin wrappers over the C ABI; all on the current stream)
     def _addnorm(self, h, add, w, x, rows: int) -> None:
@@ -180,6 +182,9 @@ class DecodeEngine:
             s = _stream()
             _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), dtc, self.embed.shape[0], c.hidden, self.tok.data_ptr(), B,
                                                             self.h.data_ptr(), s))
+            if self.fused:
+                self._step_fused(s)
+                return
             add = None
             for li, (L, S) in enumerate(zip(self.layers, self.stages)):
                 self._addnorm(self.h, add, L["ln1"], self.x16, B)
@@ -198,6 +203,32 @@ class DecodeEngine:
             self.lm_head.run(self.x16, self.logits)
             _lib.check("cbl_argmax", lib.cbl_argmax(self.logits.data_ptr(), _dt(self.logits.dtype), self.logits.stride(0), B, self.logits.shape[1],
                                                     self.tok.data_ptr(), self.pos.data_ptr(), s))
+
+    def _step_fused(self, s: int) -> None:
+        """Batch-1 layers with the step operators inside the products' finish kernels: q|k|v + rotary + cache
+        write, attention, o + add + norm, gate|up + silu * up, down + add + norm (of the next layer)."""
+        from .kernels import l8_workspace
+        c, dtc = self.cfg, _dt(self.dtype)
+        ws = l8_workspace(self.dev, 0, max(st.group.ws_bytes for S in self.stages for st in S.values())).data_ptr()
+        x, act, ao, h = self.x16.data_ptr(), self.act.data_ptr(), self.ao.data_ptr(), self.h.data_ptr()
+        self._addnorm(self.h, None, self.layers[0]["ln1"], self.x16, 1)
+        n = len(self.layers)
+        for li, (L, S) in enumerate(zip(self.layers, self.stages)):
+            bias = self.biases[li]
+            kc, vc = self.kc[li], self.vc[li]
+            _lib.check("cbl_gemv_l8_rope_kv", lib.cbl_gemv_l8_rope_kv(S["qkv"].group._structs, x, dtc, None if bias is None else bias.data_ptr(),
+                                                                      self.pos.data_ptr(), c.n_heads, c.n_kv, c.head_dim, c.rope_theta, c.max_len,
+                                                                      self.qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), dtc, ws, s))
+            _lib.check("cbl_attn_decode", lib.cbl_attn_decode(self.qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.pos.data_ptr(), dtc, 1,
+                                                              c.n_heads, c.n_kv, c.head_dim, c.max_len, c.head_dim ** -0.5, ao,
+                                                              self.att_ws.data_ptr(), self.nsplit, s))
+            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["o"].group._structs, ao, dtc, h, L["ln2"].data_ptr(), c.eps, x, dtc, ws, s))
+            _lib.check("cbl_gemv_l8_silu_mul", lib.cbl_gemv_l8_silu_mul(S["gu"].group._structs, x, dtc, act, dtc, ws, s))
+            w_next = self.layers[li + 1]["ln1"] if li + 1 < n else self.final_norm
+            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["down"].group._structs, act, dtc, h, w_next.data_ptr(), c.eps, x, dtc, ws, s))
+        self.lm_head.run(self.x16, self.logits)
+        _lib.check("cbl_argmax", lib.cbl_argmax(self.logits.data_ptr(), _dt(self.logits.dtype), self.logits.stride(0), 1, self.logits.shape[1],
+                                                self.tok.data_ptr(), self.pos.data_ptr(), s))
 
     @torch.no_grad()
     def prefill(self, ids, seq: int = 0) -> torch.Tensor:

@@ -198,6 +198,88 @@ def test_silu_mul_embed_head_and_argmax(dtype):
     assert pos.tolist() == [1, 11, 21, 31]
 
 
+def _rand_lin(R, C, g, books=1):
+    from quantexperiments_b200.linear import PackedLinear
+    W = (C // 8 * 12 + 31) // 32
+    mk = lambda: torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device="cuda", generator=g)      # noqa: E731
+    tb = lambda: torch.randn(4096, 8, device="cuda", generator=g).half()                                         # noqa: E731
+    rs = ((torch.rand(R, device="cuda", generator=g) * 0.5 + 0.75) / math.sqrt(C * books)).half()
+    kw = dict(words2=mk(), table2=tb()) if books == 2 else {}
+    return PackedLinear(mk(), tb(), rs, None, None, torch.arange(C, device="cuda")[None], 4096, 8, **kw)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("books", [1, 2])
+def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books):
+    """cbl_gemv_l8_silu_mul / _add_norm / _rope_kv against cbl_gemv_l8_multi + the separate operators."""
+    import ctypes
+    from quantexperiments_b200.kernels import L8Group, l8_workspace
+    L = _lib()
+    g = torch.Generator(device="cuda").manual_seed(21 + books)
+    dtc, s = _dt(dtype), _s()
+    ws = l8_workspace(torch.device("cuda", 0), 0, 1 << 20).data_ptr()
+    # gate | up -> silu * up   (row count not a multiple of 4: padded accumulator rows)
+    C, I = 520, 2050
+    gate, up = _rand_lin(I, C, g, books), _rand_lin(I, C, g, books)
+    x = torch.randn(C, device="cuda", generator=g).to(dtype)
+    grp = L8Group([gate.l8, up.l8])
+    ygu = torch.empty(2 * I, device="cuda", dtype=dtype)
+    grp.run(x, [ygu[:I], ygu[I:]])
+    ref = torch.empty(1, I, device="cuda", dtype=dtype)
+    L.check("cbl_silu_mul", L.lib.cbl_silu_mul(ygu.data_ptr(), dtc, 2 * I, 1, I, ref.data_ptr(), s))
+    out = torch.zeros(I, device="cuda", dtype=dtype)
+    # the product's partial sums meet in memory in any order, so two runs may differ in the last place of the
+    # 16-bit product; everything after it is the same arithmetic
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+
+    def close(a, b, n=4):
+        a, b = a.float(), b.float()
+        return bool(((a - b).abs() <= n * ulp * b.abs().max()).all()) and float((a - b).abs().mean()) <= 0.05 * ulp * float(b.abs().max())
+
+    for _ in range(2):          # the work space is left zero: a second call gives the same result
+        L.check("cbl_gemv_l8_silu_mul", L.lib.cbl_gemv_l8_silu_mul(grp._structs, x.data_ptr(), dtc, out.data_ptr(), dtc, ws, s))
+        assert close(out, ref[0])
+    # down -> add + norm   (R = 3584: four finish blocks in one cluster; and a single-block case)
+    for R, Cd in ((3584, 1032), (520, 264), (8192, 64)):
+        down = _rand_lin(R, Cd, g, books)
+        xd = torch.randn(Cd, device="cuda", generator=g).to(dtype)
+        h0 = torch.randn(1, R, device="cuda", generator=g) * 2
+        w = (torch.randn(R, device="cuda", generator=g) * 0.1 + 1).to(dtype)
+        y = down.l8.run(xd, torch.empty(R, device="cuda", dtype=dtype))
+        h_ref, x_ref = h0.clone(), torch.empty(1, R, device="cuda", dtype=dtype)
+        L.check("cbl_add_rmsnorm", L.lib.cbl_add_rmsnorm(h_ref.data_ptr(), y.data_ptr(), R, w.data_ptr(), dtc, 1e-6, 1, R, x_ref.data_ptr(), s))
+        h, xo = h0.clone(), torch.zeros(R, device="cuda", dtype=dtype)
+        st = (L.L8 * 1)(down.l8.struct())
+        L.check("cbl_gemv_l8_add_norm", L.lib.cbl_gemv_l8_add_norm(st, xd.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s))
+        assert close(h, h_ref[0]) and close(xo, x_ref[0])
+    assert L.lib.cbl_gemv_l8_add_norm_max_rows() == 8192
+    # q | k | v -> bias, rotary, cache write
+    NH, NKV, HD, max_len, Cq = 6, 2, 128, 24, 264
+    q, k, v = _rand_lin(NH * HD, Cq, g, books), _rand_lin(NKV * HD, Cq, g, books), _rand_lin(NKV * HD, Cq, g, books)
+    xq = torch.randn(Cq, device="cuda", generator=g).to(dtype)
+    bias = (torch.randn((NH + 2 * NKV) * HD, device="cuda", generator=g) * 0.1).to(dtype)
+    grp = L8Group([q.l8, k.l8, v.l8])
+    yqkv = torch.empty(1, (NH + 2 * NKV) * HD, device="cuda", dtype=dtype)
+    grp.run(xq, [yqkv[0, :NH * HD], yqkv[0, NH * HD:(NH + NKV) * HD], yqkv[0, (NH + NKV) * HD:]])
+    for with_bias in (True, False):
+        pos = torch.tensor([17], dtype=torch.int32, device="cuda")
+        bp = bias.data_ptr() if with_bias else None
+        q_ref, kc_ref, vc_ref = (torch.zeros(1, NH * HD, device="cuda", dtype=dtype), torch.zeros(1, NKV, max_len, HD, device="cuda", dtype=dtype),
+                                 torch.zeros(1, NKV, max_len, HD, device="cuda", dtype=dtype))
+        L.check("cbl_rope_kv", L.lib.cbl_rope_kv(yqkv.data_ptr(), dtc, yqkv.stride(0), bp, pos.data_ptr(), 0, 0, 1, NH, NKV, HD, 1e6, max_len,
+                                                 q_ref.data_ptr(), kc_ref.data_ptr(), vc_ref.data_ptr(), s))
+        qo, kc, vc = torch.zeros_like(q_ref), torch.zeros_like(kc_ref), torch.zeros_like(vc_ref)
+        L.check("cbl_gemv_l8_rope_kv", L.lib.cbl_gemv_l8_rope_kv(grp._structs, xq.data_ptr(), dtc, bp, pos.data_ptr(), NH, NKV, HD, 1e6, max_len,
+                                                                 qo.data_ptr(), kc.data_ptr(), vc.data_ptr(), dtc, ws, s))
+        assert close(qo, q_ref) and close(kc, kc_ref) and close(vc, vc_ref)
+        assert kc[0, :, 17].any() and vc[0, :, 17].any()
+    # shapes the fused forms refuse
+    assert L.lib.cbl_gemv_l8_rope_kv(grp._structs, xq.data_ptr(), dtc, None, pos.data_ptr(), NH + 1, NKV, HD, 1e6, max_len, qo.data_ptr(),
+                                     kc.data_ptr(), vc.data_ptr(), dtc, ws, s) == L.EINVAL
+    big = (L.L8 * 1)(L.L8(8196, 64, 1, 1, 8196, 16, 16, None, 16, None, None))
+    assert L.lib.cbl_gemv_l8_add_norm(big, xq.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s) == L.EUNSUPPORTED
+
+
 # ------------------------------------------------------------------------------------------- the engine
 class _RefModel:
     """One Qwen2 decode step in plain torch (fp32 math, 16-bit rounding where the engine rounds)."""
@@ -260,6 +342,16 @@ def test_engine_steps_match_the_torch_restatement(dtype, books, M):
         assert int(eng.pos[0]) == p + 1
         assert int(eng.tok[0]) == int(eng.logits[0].argmax())
     eng.check()
+    assert eng.fused == (M == 1)
+    if eng.fused:
+        # the same steps with every operator as its own kernel
+        lg = eng.logits.clone()
+        eng.fused = False
+        eng.reset(toks[0])
+        for t in toks:
+            eng.tok.fill_(t)
+            eng.step()
+        assert (eng.logits - lg).abs().max() / lg.abs().max() <= 2e-3
 
 
 def test_engine_graph_replay_prefill_and_batched_engine_agree():
