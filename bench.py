@@ -459,6 +459,78 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args, rank: int, world: int, local_rank: int) -> None:
+    """End-to-end decode of a random-init Qwen2.5-7B architecture with every block linear in the packed format:
+    prompt of --tokens random ids (batched prefill), then --steps generated tokens per sequence by CUDA-graph replay
+    of the decode step, --batch sequences at once. Metric: generated tokens/s. N > 1: independent replicas (the
+    engine is a single-GPU program), value = sum over ranks."""
+    import torch.distributed as dist
+    from quantexperiments_b200.engine import Cfg, Qwen2BatchEngine, generate, random_engine
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, T, K = args.batch, args.tokens, args.steps
+    cfg = Cfg(max_len=(T + 2 * K + 64 + 31) // 32 * 32)
+    eng = random_engine(cfg, seed=rank, dev=dev)
+    run_eng = eng if B == 1 else Qwen2BatchEngine(eng, B)
+    gcpu = torch.Generator().manual_seed(5 + rank)
+    prompts = [torch.randint(0, cfg.vocab, (T,), generator=gcpu) for _ in range(B)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    run_eng.capture()
+    run_eng.reset(0)
+    for b in range(B):
+        run_eng.prefill(prompts[b].to(dev), b)
+    for _ in range(max(args.warmup, 3)):
+        run_eng.graph.replay()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(K):
+        run_eng.graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    run_eng.check()
+    # end to end through generate(): host prompt in, every token read back by the host (batch 1 engine)
+    t0 = time.perf_counter()
+    out = generate(eng, prompts[0].tolist(), K, graph=True)
+    torch.cuda.synchronize(dev)
+    s_e2e = time.perf_counter() - t0
+    assert len(out) == K
+    tv = torch.tensor([ms, s_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+    ms, s_e2e = float(tv[0]), float(tv[1])
+    if rank != 0:
+        return
+    peak, src = measured_peak()
+    kv_bytes = 2 * cfg.layers * cfg.n_kv * cfg.head_dim * 2 * (T + K // 2) * B
+    step_bytes = eng.weight_bytes() + kv_bytes
+    achieved = step_bytes / (ms / K * 1e-3) / 1e9
+    launches = (10 * cfg.layers + 4) if B == 1 else (22 * cfg.layers + 5)
+    line = {"metric": "decode_tok_s", "value": B * K * world / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b architecture, random init, every block linear packed (d=8, K=4096, 12-bit tags); prompt {T}, "
+                                   f"generate {K}, batch {B}; bf16 embedding / head, bf16 KV cache",
+                       "parallelism": "replicas" if world > 1 else "single", "launch": "one CUDA graph per decode step",
+                       "l2": "inputs larger than L2 (2.3 GB of weights per step)"},
+            "clocks": clocks, "gpu_launches": launches * K * world,
+            "e2e": {"value": K * world / s_e2e, "unit": "tok/s", "h2d_bytes_per_step": T * 8 // K, "d2h_bytes_per_step": 8,
+                    "note": f"generate() at batch 1: prompt upload + prefill of {T} tokens + {K} steps with a host read per token"},
+            "roofline": {"bound": "hbm", "kernel": "decode step (all kernels)", "achieved": achieved, "peak": peak, "peak_source": src,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "algorithmic_bytes_per_step": step_bytes}}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline_sample() -> dict:
     """The reference's CPU path (oracle port) timed on this host's cores on a bounded sample."""
     from oracle import cbl_oracle as orc
@@ -488,8 +560,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill"],
-                    help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill", "decode"],
+                    help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens; "
+                         "decode: end-to-end generation (prompt --tokens, --steps generated tokens, --batch sequences)")
     ap.add_argument("--tokens", type=int, default=2048)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -506,6 +579,8 @@ def main() -> None:
     try:
         if args.workload == "prefill":
             run_prefill(args, rank, world, local_rank)
+        elif args.workload == "decode":
+            run_decode(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:
