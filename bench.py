@@ -372,17 +372,38 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     T = args.tokens
+    from quantexperiments_b200.kernels import DenseStack
+    from quantexperiments_b200.linear import DENSE_MIN_TOKENS
     lins, kinds, _ = build_set(dev, rank, world, 64)
     g = torch.Generator(device=dev).manual_seed(7)
     xs = {c: torch.randn(T, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
-    ys = {r: torch.empty(T, r, device=dev, dtype=torch.bfloat16) for r in {l.R for l in lins}}
     flops = sum(2.0 * T * l.R * l.C for l in lins)
+    # q|k|v and gate|up share their activations: one stacked product each, as the reference's gemm(x, [pieces]) does.
+    # From DENSE_MIN_TOKENS tokens on the stack is decoded once into a 16-bit scratch and multiplied by the TMA-fed
+    # tcgen05 GEMM; below, every piece runs the kernel that decodes weight tiles on the fly.
+    dense = T >= (args.dense_min if args.dense_min is not None else DENSE_MIN_TOKENS)
+    groups, launches = [], 0
+    for l0 in range(0, len(lins), len(SHAPES_7B)):
+        q, k, v, o, gate, up, down = lins[l0:l0 + len(SHAPES_7B)]
+        for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
+            y = torch.empty(T, sum(m.R for m in members), device=dev, dtype=torch.bfloat16)
+            groups.append((DenseStack([m.dm for m in members]) if dense else None, members, xs[members[0].C], y, kind))
+            launches += (len(members) + 2) if dense else 2 * len(members)
+
+    def run_group(stack, members, x, y, kind):
+        if stack is not None:
+            stack.gemm(x, y)
+        else:
+            off = 0
+            for m in members:
+                m.l8.gemm(x, y[:, off:off + m.R])
+                off += m.R
+        if world > 1 and kind == "row":
+            dist.all_reduce(y)
 
     def step():
-        for lin, kind in zip(lins, kinds):
-            lin.l8.gemm(xs[lin.C], ys[lin.R])
-            if world > 1 and kind == "row":
-                dist.all_reduce(ys[lin.R])
+        for grp in groups:
+            run_group(*grp)
 
     def barrier():
         if world > 1:
@@ -407,16 +428,13 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         clocks = sampler.stop()
         # end to end: the layer inputs come from pinned host memory, the last token's outputs go back
         hx = {c: torch.randn(T, c).bfloat16().pin_memory() for c in xs}
-        hy = {r: torch.empty(r, dtype=torch.bfloat16).pin_memory() for r in ys}
+        hyo = [torch.empty(grp[3].shape[1], dtype=torch.bfloat16).pin_memory() for grp in groups[:4]]
 
         def step_e2e():
-            for i, (lin, kind) in enumerate(zip(lins, kinds)):
-                if i % 7 in (0, 3, 4, 6):          # q, o, gate, down: a new activation tensor enters the layer
-                    xs[lin.C].copy_(hx[lin.C], non_blocking=True)
-                lin.l8.gemm(xs[lin.C], ys[lin.R])
-                if world > 1 and kind == "row":
-                    dist.all_reduce(ys[lin.R])
-                hy[lin.R].copy_(ys[lin.R][T - 1], non_blocking=True)
+            for gi, grp in enumerate(groups):
+                grp[2].copy_(hx[grp[2].shape[1]], non_blocking=True)      # every stack's activations come from the host
+                run_group(*grp)
+                hyo[gi % 4].copy_(grp[3][T - 1], non_blocking=True)
             stream.synchronize()
 
         step_e2e()
@@ -447,13 +465,15 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"qwen2.5-7b prefill dequant-GEMM set (196 codebook matrices), {T} tokens", "accumulate": "fp32",
+                       "path": "decode once into a 16-bit scratch + TMA-fed tcgen05 GEMM (q|k|v and gate|up stacked)" if dense
+                               else "weight tiles decoded on the fly inside the tcgen05 GEMM",
                        "activations": "bf16 in, fp16 on the tensor cores with a power-of-two scale per token", "output": "bf16",
                        "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 per step"},
-            "clocks": clocks, "gpu_launches": 2 * len(lins) * args.steps * world,
+            "clocks": clocks, "gpu_launches": launches * args.steps * world,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": sum(T * l.C * 2 for i, l in enumerate(lins) if i % 7 in (0, 3, 4, 6)) * world,
-                    "d2h_bytes_per_step": sum(l.R * 2 for l in lins) * world, "ms_per_step": ms_e2e},
-            "roofline": {"bound": "tensor", "kernel": "k_gemm_l8", "achieved": value / world, "peak": peak,
+                    "h2d_bytes_per_step": sum(T * grp[2].shape[1] * 2 for grp in groups) * world,
+                    "d2h_bytes_per_step": sum(grp[3].shape[1] * 2 for grp in groups) * world, "ms_per_step": ms_e2e},
+            "roofline": {"bound": "tensor", "kernel": "k_gemm_dense_2sm" if dense else "k_gemm_l8", "achieved": value / world, "peak": peak,
                          "peak_source": "measured (sustained)" if peaks else "fallback", "unit": "TFLOP/s", "frac": value / world / peak,
                          "frac_of_burst": value / world / float(peaks.get("bf16_tflops", 1590.0)), "traffic": None}}
     print(json.dumps(line), flush=True)
@@ -564,6 +584,7 @@ def main() -> None:
                     help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens; "
                          "decode: end-to-end generation (prompt --tokens, --steps generated tokens, --batch sequences)")
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--dense-min", type=int, default=None, help="prefill: token count from which the two-phase path runs (default: the library's)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -213,6 +213,21 @@ int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_
 int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
                     void* stage, void* workspace, cbl_stream s);
 
+/* Two-phase prefill for many tokens and for matrices with several column orders: decode the matrix ONCE
+ * into a 16-bit scratch, then multiply with a TMA-fed tcgen05 GEMM (both operands by TMA, accumulators in
+ * tensor memory).
+ *   cbl_decode_raw: out fp16 [R, ld], ld = C rounded up to 8, = cbl_dense_scratch_bytes(R, C) bytes:
+ *                   out[r, col] = fp16(A[tag]) or fp16(fp32(A[tag]) + fp32(B[tag2])), col the ORIGINAL column
+ *                   (column orders undone), without the row scale.  d = 8, 12-bit tags, G = 1.
+ *   cbl_gemm_dense: y[t, r] = round(row_scale[r] * sum_c out[r, c] * x[t, c]); x, y, stage, workspace as for
+ *                   cbl_gemm_l8.  256-token x 256-row tiles.
+ * replaces the dequant + cuBLAS large-M path of shapequant/vllm_ext/core.py:386-420 (_large) and the
+ *          multi-token branch of shapequant/kernels/gemv.py:164-170 (dense() + F.linear). */
+size_t cbl_dense_scratch_bytes(int32_t R, int32_t C);
+int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s);
+int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void* row_scale, const void* x, int xdtype, int32_t ntok, int64_t ldx,
+                   void* y, int ydtype, int64_t ldy, void* stage, void* workspace, cbl_stream s);
+
 /* ------------------------------------------------------------------------------------------------
  * Decode-step operators between the packed linears (Qwen2-style blocks).  `dtype` is the model's
  * 16-bit activation type (CBL_F16 or CBL_BF16) shared by every 16-bit pointer of a call; the residual

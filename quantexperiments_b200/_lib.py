@@ -74,6 +74,10 @@ SIGNATURES = {
     "cbl_gemv_l8_ar": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, POINTER(c_void_p), c_int32, c_int32, c_void_p]),
     "cbl_gemv_l8_ar_status": (c_int, [c_void_p, c_int32, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
+    "cbl_dense_scratch_bytes": (c_size_t, [c_int32, c_int32]),
+    "cbl_decode_raw": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
+    "cbl_gemm_dense": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p,
+                               c_void_p, c_void_p]),
     "cbl_embed_rows": (c_int, [c_void_p, c_int, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p]),
     "cbl_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_float, c_int32, c_int32, c_void_p, c_void_p]),
     "cbl_rope_kv": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,

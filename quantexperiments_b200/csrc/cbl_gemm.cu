@@ -482,6 +482,303 @@ k_gemm_l8_2sm(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* _
     }
 }
 
+// ------------------------------------------------------------------------------------ two-phase variant for many tokens
+//
+// The fused kernels above decode every weight tile once per 256 (or 512) tokens; their shared-memory pipe
+// carries the codeword gathers, the B-tile stores, the activation tiles and the tensor cores' operand
+// reads, and saturates before the tensor pipe does.  From about a thousand tokens on it is cheaper to
+// decode the matrix ONCE into a 16-bit scratch (k_decode_raw: raw codewords, or the sum of the two books'
+// codewords, column orders undone) and to run a plain TMA-fed tcgen05 GEMM over it (k_gemm_dense: both
+// operands arrive by TMA, nothing but the tensor cores reads shared memory).  Row scales and the tokens'
+// power-of-two scales are applied in the epilogue exactly as in the fused kernel.  The scratch also
+// serves matrices with several column orders, which the fused kernels do not execute.
+constexpr int GD_STAGES = 3;
+constexpr int GD_STAGE_BYTES = 2 * GM_A_BYTES + GM_B_BYTES;                 // 256 tokens + 256 rows of one k-block: 64 KB
+constexpr int GD_SMEM = GD_STAGES * GD_STAGE_BYTES + 1024;                  // + slack to align the ring to 1024 bytes
+constexpr int GD_EPI_WARPS = 8, GD_THREADS = (GD_EPI_WARPS + 2) * 32;
+
+__global__ void __launch_bounds__(GD_THREADS, 1)
+k_gemm_dense(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, cbl_l8 m, const float* __restrict__ xinv,
+             int ntok, void* __restrict__ y, int ydtype, int64_t ldy, int vec_ok, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * GD_STAGES + 1];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // token tiles vary fastest across the grid: blocks that run together share weight rows in L2
+    const int r0 = blockIdx.y * GM_BN, tok0 = blockIdx.x * GM_BM;
+    const int nkb = (m.C + GM_BK - 1) / GM_BK;
+    const uint32_t sbase = (cbl_smem_u32(smem_raw) + 1023u) & ~1023u, bar0 = cbl_smem_u32(s_bar);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (GD_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (2 * GD_STAGES);
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < GD_STAGES; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == GD_EPI_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == GD_EPI_WARPS) {
+        if (lane == 0) {                                      // TMA producer: activations (2 x 128 tokens) and weights (256 rows)
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % GD_STAGES;
+                if (!mbar_wait(empty(s), ((kb / GD_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+                mbar_expect_tx(full(s), GD_STAGE_BYTES);
+                const uint32_t dst = sbase + s * GD_STAGE_BYTES;
+                tma_load_2d(dst, &xmap, kb * GM_BK, tok0, full(s));
+                tma_load_2d(dst + GM_A_BYTES, &xmap, kb * GM_BK, tok0 + 128, full(s));
+                tma_load_2d(dst + 2 * GM_A_BYTES, &wmap, kb * GM_BK, r0, full(s));
+            }
+        }
+    } else if (warp == GD_EPI_WARPS + 1) {
+        if (lane == 0) {                                      // MMA issuer
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % GD_STAGES;
+                if (!mbar_wait(full(s), (kb / GD_STAGES) & 1)) { s_abort = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = sbase + s * GD_STAGE_BYTES, b_addr = a_addr + 2 * GM_A_BYTES;
+#pragma unroll
+                for (int tb = 0; tb < 2; tb++) {
+#pragma unroll
+                    for (int kk = 0; kk < GM_BK / 16; kk++) {
+                        const uint64_t da = umma_desc_sw128(a_addr + tb * GM_A_BYTES + kk * 32);
+                        const uint64_t db = umma_desc_sw128(b_addr + kk * 32);
+                        umma_f16(tmem + tb * GM_BN, da, db, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                }
+                umma_commit(empty(s));
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const bool ok = mbar_wait(tmem_full, 0);
+        if (!ok) s_abort = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3, tb = warp >> 2;
+        const int tok = tok0 + tb * 128 + q * 32 + lane;
+        const float tsc = (tok < ntok) ? xinv[tok] : 0.f;
+        if (ok) {
+            for (int c0 = 0; c0 < GM_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(tb * GM_BN + c0), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                gemm_store_row32(v, tok, ntok, r0 + c0, m, tsc, y, ydtype, ldy, vec_ok);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    if (warp == GD_EPI_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// The same GEMM on pairs of thread blocks, persistent, with the epilogue overlapped: a cluster of two blocks
+// computes 256-token x 256-row tiles with tcgen05.mma.cta_group::2 (each block holds 128 tokens of the
+// activations and 128 rows of the weights per k-block, so the traffic from L2 per MMA cycle is the one of a
+// 256 x 256 tile although a block only accumulates 128 x 256).  A block's accumulator takes 256 of the 512
+// tensor-memory columns: two buffers alternate, the epilogue warps drain one while the MMAs fill the other.
+// Barriers: "full" (leader block; TMA bytes of both blocks), "empty" and "accumulator full" (each block;
+// multicast commits from the leader), "accumulator empty" (leader; one arrival per epilogue warp of both blocks).
+constexpr int G3_STAGES = 4;              // 128 KB: leaves room for a decode block of the NEXT matrix on the same SM
+constexpr int G3_STAGE_BYTES = GM_A_BYTES + 128 * GM_BK * 2;                // 128 tokens + 128 rows of one k-block: 32 KB
+constexpr int G3_SMEM = G3_STAGES * G3_STAGE_BYTES + 1024;
+constexpr int G3_EPI_WARPS = 8, G3_THREADS = (G3_EPI_WARPS + 2) * 32;
+
+__global__ void __launch_bounds__(G3_THREADS, 1)
+k_gemm_dense_2sm(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, cbl_l8 m, const float* __restrict__ xinv,
+                 int ntok, void* __restrict__ y, int ydtype, int64_t ldy, int vec_ok, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * G3_STAGES + 4];   // full, empty per stage; acc_full[2], acc_empty[2]
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // a decode kernel of the next matrix (launched with programmatic serialization) may share the SMs with this GEMM
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int nkb = (m.C + GM_BK - 1) / GM_BK;
+    const int ntt = (ntok + 255) / 256, nrt = (m.R + GM_BN - 1) / GM_BN, ntiles = ntt * nrt;
+    const int cluster = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+    const uint32_t sbase = (cbl_smem_u32(smem_raw) + 1023u) & ~1023u, bar0 = cbl_smem_u32(s_bar);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (G3_STAGES + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * G3_STAGES + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * G3_STAGES + 2 + b); };
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < G3_STAGES; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 2 * G3_EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == G3_EPI_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                        // both blocks' barriers and tensor memory exist
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == G3_EPI_WARPS) {
+        if (lane == 0) {                                      // TMA producer: this block's 128 tokens and 128 weight rows
+            int it = 0;
+            for (int t = cluster; t < ntiles && !s_abort; t += nclusters) {
+                const int tok0 = (t % ntt) * 256 + (int)rank * 128, r0 = (t / ntt) * GM_BN + (int)rank * 128;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % G3_STAGES;
+                    if (!mbar_wait(empty(s), ((it / G3_STAGES) & 1) ^ 1)) { s_abort = 1; break; }
+                    if (rank == 0) mbar_expect_tx(full(s), 2 * G3_STAGE_BYTES);
+                    const uint32_t dst = sbase + s * G3_STAGE_BYTES;
+                    const uint32_t lead_bar = mapa_u32(full(s), 0);
+                    tma_load_2d_2sm(dst, &xmap, kb * GM_BK, tok0, lead_bar);
+                    tma_load_2d_2sm(dst + GM_A_BYTES, &wmap, kb * GM_BK, r0, lead_bar);
+                }
+            }
+        }
+    } else if (warp == G3_EPI_WARPS + 1) {
+        if (lane == 0 && rank == 0) {                         // MMA issuer (leader block)
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int it = 0, li = 0;
+            for (int t = cluster; t < ntiles && !s_abort; t += nclusters, li++) {
+                const int buf = li & 1;
+                if (!mbar_wait(acc_empty(buf), ((li >> 1) & 1) ^ 1)) { s_abort = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % G3_STAGES;
+                    if (!mbar_wait(full(s), (it / G3_STAGES) & 1)) { s_abort = 1; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = sbase + s * G3_STAGE_BYTES, b_addr = a_addr + GM_A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < GM_BK / 16; kk++)
+                        umma_f16_2sm(tmem + buf * GM_BN, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc,
+                                     (kb | kk) ? 1u : 0u);
+                    umma_commit_2sm(empty(s));
+                }
+                umma_commit_2sm(acc_full(buf));
+            }
+        }
+    } else {
+        // epilogue: warp w drains TMEM lanes 32 (w % 4).., columns 128 (w / 4).. of the tile's buffer
+        const int q = warp & 3, ch = warp >> 2;
+        int li = 0;
+        for (int t = cluster; t < ntiles; t += nclusters, li++) {
+            const int buf = li & 1;
+            if (!mbar_wait(acc_full(buf), (li >> 1) & 1)) { s_abort = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int tok = (t % ntt) * 256 + (int)rank * 128 + q * 32 + lane, r0 = (t / ntt) * GM_BN;
+            const float tsc = (tok < ntok) ? xinv[tok] : 0.f;
+            for (int c0 = ch * 128; c0 < ch * 128 + 128; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GM_BN + c0), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                gemm_store_row32(v, tok, ntok, r0 + c0, m, tsc, y, ydtype, ldy, vec_ok);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(acc_empty(buf), 0));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    cluster_sync_all();                                        // the peer no longer reads or signals this block's memory
+    if (warp == G3_EPI_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// Raw 16-bit decode of a packed matrix (d = 8, 12-bit tags): out[r, col] = fp16(A[a] (+ B[b])) without the row
+// scale, col = the original column (column orders undone).  A warp walks one row 256 chunks at a time, lane l
+// taking chunks l, l + 32, ...: the 16-byte codewords of a warp-wide store are contiguous.  The book(s) sit in
+// shared memory.  One block of 512 threads per SM; it is launched with programmatic serialization and waits
+// for its predecessors only at its END, so that it decodes the next matrix beside a running GEMM (which
+// leaves shared memory for it) while everything after it still sees the stream's order.
+constexpr int DR_THREADS = 512;            // x 56 registers: fits beside the GEMM's 320 threads x 104 registers
+template <int BOOKS, bool PERM>
+__global__ void __maxnreg__(56) k_decode_raw(cbl_packed m, __half* __restrict__ out, int64_t ld) {
+    extern __shared__ __align__(16) unsigned char dsm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    {
+        uint4* dst = (uint4*)dsm;
+        const uint4* t0 = (const uint4*)m.table;
+        for (int i = tid; i < 4096; i += DR_THREADS) dst[i] = __ldg(t0 + i);
+        if (BOOKS == 2) {
+            const uint4* t1 = (const uint4*)m.table2;
+            for (int i = tid; i < 4096; i += DR_THREADS) dst[4096 + i] = __ldg(t1 + i);
+        }
+    }
+    __syncthreads();
+    const uint32_t sb = cbl_smem_u32(dsm);
+    const int nch = m.C >> 3;
+    auto tag_of = [&](const int32_t* rw, int j) {
+        const uint32_t bit = 12u * (uint32_t)j, w = bit >> 5, sh = bit & 31u;
+        const uint32_t lo = (uint32_t)__ldg(rw + w);
+        const uint32_t hi = (sh > 20u && (int)(w + 1) < m.W) ? (uint32_t)__ldg(rw + w + 1) : 0u;
+        return (__funnelshift_r(lo, hi, sh) & 0xFFFu) << 4;
+    };
+    for (int r = blockIdx.x * (DR_THREADS / 32) + warp; r < m.R; r += gridDim.x * (DR_THREADS / 32)) {
+        const int32_t* rw = m.tags + (int64_t)r * m.W;
+        const int32_t* rw2 = BOOKS == 2 ? m.tags2 + (int64_t)r * m.W : nullptr;
+        const int32_t* perm = PERM ? m.perms + (int64_t)m.row_mask[r] * m.C : nullptr;
+        __half* orow = out + (int64_t)r * ld;
+        for (int j0 = 0; j0 < nch; j0 += 256) {
+            uint4 cw[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int j = j0 + 32 * i + lane;
+                cw[i] = make_uint4(0, 0, 0, 0);
+                if (j < nch) cw[i] = cbl_lds128(sb + tag_of(rw, j));
+            }
+            if (BOOKS == 2) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int j = j0 + 32 * i + lane;
+                    if (j < nch) {
+                        const uint4 o = cbl_lds128(sb + 65536u + tag_of(rw2, j));
+                        __half2* a = (__half2*)&cw[i];
+                        const __half2* b = (const __half2*)&o;
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float2 fa = __half22float2(a[e]), fb = __half22float2(b[e]);
+                            a[e] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int j = j0 + 32 * i + lane;
+                if (j < nch) {
+                    if (!PERM) {
+                        *(uint4*)(orow + j * 8) = cw[i];
+                    } else {
+                        const __half* hv = (const __half*)&cw[i];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) orow[__ldg(perm + j * 8 + e)] = hv[e];
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // later kernels that wait for this one also wait for its predecessors
+}
+
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -577,3 +874,137 @@ extern "C" int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32
                                void* stage, void* workspace, cbl_stream s) {
     return gemm_l8_impl(m, x, xdtype, ntok, ldx, y, ydtype, ldy, stage, workspace, s, 1);
 }
+
+// ---- two-phase variant: host side
+extern "C" size_t cbl_dense_scratch_bytes(int32_t R, int32_t C) {
+    if (R < 0 || C < 0) return 0;
+    return (size_t)R * ((size_t)(C + 7) / 8 * 8) * 2;
+}
+
+extern "C" int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s) {
+    if (!m || !m->tags || !m->table || !out || ((uintptr_t)out % 16) || ((uintptr_t)m->table % 16)) return CBL_EINVAL;
+    if (m->d != 8 || m->bits != 12 || m->G != 1) return CBL_EUNSUPPORTED;
+    if (m->R < 0 || m->C <= 0 || m->C % 8 || (int64_t)m->W * 32 < (int64_t)(m->C / 8) * 12) return CBL_EINVAL;
+    if (m->books != 1 && m->books != 2) return CBL_EINVAL;
+    if (m->books == 2 && (!m->tags2 || !m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
+    if (m->M > 1 && (!m->row_mask || !m->perms)) return CBL_EINVAL;
+    if (m->R == 0) return CBL_OK;
+    const int64_t ld = (m->C + 7) / 8 * 8;
+    const size_t smem = (size_t)65536 * m->books;
+    int grid = cbl_sm_count();
+    if (grid > cbl_ceil_div(m->R, DR_THREADS / 32)) grid = cbl_ceil_div(m->R, DR_THREADS / 32);
+    const cudaStream_t st = (cudaStream_t)s;
+    static bool attr_set[64][4] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(DR_THREADS);
+    cfg.dynamicSmemBytes = smem;
+#define CBL_RAW(BK, PM, SLOT)                                                                                              \
+    do {                                                                                                                   \
+        if (dev >= 0 && dev < 64 && !attr_set[dev][SLOT]) {                                                                \
+            CBL_CUDA(cudaFuncSetAttribute(k_decode_raw<BK, PM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * BK)); \
+            attr_set[dev][SLOT] = true;                                                                                    \
+        }                                                                                                                  \
+        CBL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_raw<BK, PM>, *m, (__half*)out, ld));                                    \
+    } while (0)
+    if (m->books == 1 && m->M == 1) CBL_RAW(1, false, 0);
+    else if (m->books == 1) CBL_RAW(1, true, 1);
+    else if (m->M == 1) CBL_RAW(2, false, 2);
+    else CBL_RAW(2, true, 3);
+#undef CBL_RAW
+    return cbl_check_launch();
+}
+
+extern "C" int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void* row_scale, const void* x, int xdtype, int32_t ntok,
+                              int64_t ldx, void* y, int ydtype, int64_t ldy, void* stage, void* workspace, cbl_stream s) {
+    if (!w16 || !row_scale || !x || !y || !stage || !workspace) return CBL_EINVAL;
+    if (R <= 0 || C <= 0 || C % 8 || ntok <= 0 || ldx < C || ldy < R) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (((uintptr_t)stage % 16) || ((uintptr_t)w16 % 16) || ((uintptr_t)workspace % 4)) return CBL_EINVAL;
+    const cudaStream_t st = (cudaStream_t)s;
+    int rc = cbl_prep_x(x, xdtype, ntok, C, ldx, nullptr, 1, stage, s);
+    if (rc) return rc;
+    const int Mpad = (ntok + 7) / 8 * 8, Cpad = (C + 511) / 512 * 512;
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return CBL_ECUDA;
+    CUtensorMap xmap, wmap;
+    const cuuint32_t estr[2] = {1, 1};
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)Cpad, (cuuint64_t)Mpad};
+        const cuuint64_t strides[1] = {(cuuint64_t)Cpad * 2};
+        const cuuint32_t box[2] = {GM_BK, 128};
+        CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, stage, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) { g_cbl_last_cuda_error = (int)cr; return CBL_ECUDA; }
+    }
+    {
+        // columns beyond C and rows beyond R are outside the map: TMA fills them with zeros
+        const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)R};
+        const cuuint64_t strides[1] = {(cuuint64_t)((C + 7) / 8 * 8) * 2};
+        const cuuint32_t box[2] = {GM_BK, GM_BN};
+        CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)w16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) { g_cbl_last_cuda_error = (int)cr; return CBL_ECUDA; }
+    }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_gemm_dense, cudaFuncAttributeMaxDynamicSharedMemorySize, GD_SMEM));
+        attr_set[dev] = true;
+    }
+    cbl_l8 m = {};
+    m.R = R;
+    m.C = C;
+    m.row_scale = row_scale;
+    const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
+    const int esz = ydtype == CBL_F32 ? 4 : 2;
+    const int vec_ok = ((uintptr_t)y % 16 == 0) && ((ldy * esz) % 16 == 0) && ((uintptr_t)row_scale % 16 == 0);
+    static int variant = -1;                                  // CBL_DENSE_1SM=1 selects the one-block kernel (for comparisons)
+    if (variant < 0) { const char* e = getenv("CBL_DENSE_1SM"); variant = (e && atoi(e) == 1) ? 1 : 2; }
+    if (variant == 2) {
+        // box of the pair kernel: 128 tokens / 128 weight rows per block
+        {
+            const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)R};
+            const cuuint64_t strides[1] = {(cuuint64_t)((C + 7) / 8 * 8) * 2};
+            const cuuint32_t box[2] = {GM_BK, 128};
+            CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)w16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) { g_cbl_last_cuda_error = (int)cr; return CBL_ECUDA; }
+        }
+        static bool attr3_set[64] = {};
+        if (dev >= 0 && dev < 64 && !attr3_set[dev]) {
+            CBL_CUDA(cudaFuncSetAttribute(k_gemm_dense_2sm, cudaFuncAttributeMaxDynamicSharedMemorySize, G3_SMEM));
+            attr3_set[dev] = true;
+        }
+        const int ntiles = cbl_ceil_div(R, GM_BN) * cbl_ceil_div(ntok, 256);
+        int nclusters = cbl_sm_count() / 2;
+        if (nclusters > ntiles) nclusters = ntiles;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * nclusters);
+        cfg.blockDim = dim3(G3_THREADS);
+        cfg.dynamicSmemBytes = G3_SMEM;
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_dense_2sm, xmap, wmap, m, xinv, (int)ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace));
+        return cbl_check_launch();
+    }
+    dim3 grid(cbl_ceil_div(ntok, GM_BM), cbl_ceil_div(R, GM_BN));
+    k_gemm_dense<<<grid, GD_THREADS, GD_SMEM, st>>>(xmap, wmap, m, xinv, ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace);
+    return cbl_check_launch();
+}
+

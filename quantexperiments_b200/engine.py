@@ -24,8 +24,8 @@ import torch
 
 from . import _lib
 from ._lib import lib
-from .kernels import L8Group, _dt, _stream
-from .linear import PackedLinear, RunsLin
+from .kernels import DenseStack, L8Group, _dt, _stream
+from .linear import DENSE_MIN_TOKENS, PackedLinear, RunsLin
 
 NAMES = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -147,6 +147,9 @@ class DecodeEngine:
         for L in layers:
             self.stages.append({"qkv": _Stage([L["q"], L["k"], L["v"]], self.yqkv), "o": _Stage([L["o"]], self.yo),
                                 "gu": _Stage([L["gate"], L["up"]], self.ygu), "down": _Stage([L["down"]], self.yd)})
+        # prompts: q|k|v and gate|up as stacked two-phase GEMMs (decode once, one launch over the stacked rows)
+        self.stacks = [{"qkv": DenseStack([_lin(L[n]).dm for n in ("q", "k", "v")]), "gu": DenseStack([_lin(L[n]).dm for n in ("gate", "up")])}
+                       for L in layers]
         self.graph = None
         self.only_linears = False
         # one token, one column order everywhere: the operators that follow a product run in its finish kernel
@@ -204,6 +207,19 @@ class DecodeEngine:
             _lib.check("cbl_argmax", lib.cbl_argmax(self.logits.data_ptr(), _dt(self.logits.dtype), self.logits.stride(0), B, self.logits.shape[1],
                                                     self.tok.data_ptr(), self.pos.data_ptr(), s))
 
+    def _pieces(self, li: int, stack: str, names, x, y) -> None:
+        """Prompt tokens through stacked linears: one stacked two-phase GEMM for long prompts (or several column
+        orders), else piece by piece into column slices of y."""
+        L = self.layers[li]
+        if x.shape[0] >= DENSE_MIN_TOKENS or (x.shape[0] > 64 and any(_lin(L[n]).dm.M > 1 for n in names)):
+            self.stacks[li][stack].gemm(x, y)
+            return
+        o = 0
+        for n in names:
+            l = _lin(L[n])
+            l.forward_into(x, y[:, o:o + l.R])
+            o += l.R
+
     def _step_fused(self, s: int) -> None:
         """Batch-1 layers with the step operators inside the products' finish kernels: q|k|v + rotary + cache
         write, attention, o + add + norm, gate|up + silu * up, down + add + norm (of the next layer)."""
@@ -253,11 +269,7 @@ class DecodeEngine:
             add = None
             for li, L in enumerate(self.layers):
                 self._addnorm(h, add, L["ln1"], x, T)
-                o = 0
-                for n in ("q", "k", "v"):
-                    l = _lin(L[n])
-                    l.forward_into(x, yqkv[:, o:o + l.R])
-                    o += l.R
+                self._pieces(li, "qkv", ("q", "k", "v"), x, yqkv)
                 kc, vc = self.kc[li], self.vc[li]
                 self._rope(yqkv, self.biases[li], None, 0, seq, T, qr, kc, vc)
                 q4 = qr.view(T, NH, HD).transpose(0, 1)[None]
@@ -266,11 +278,7 @@ class DecodeEngine:
                 ao = ao[0].transpose(0, 1).reshape(T, NH * HD)
                 _lin(L["o"]).forward_into(ao, yo)
                 self._addnorm(h, yo, L["ln2"], x, T)
-                o = 0
-                for n in ("gate", "up"):
-                    l = _lin(L[n])
-                    l.forward_into(x, ygu[:, o:o + l.R])
-                    o += l.R
+                self._pieces(li, "gu", ("gate", "up"), x, ygu)
                 self._silu(ygu, act, T)
                 _lin(L["down"]).forward_into(act, yd)
                 add = yd

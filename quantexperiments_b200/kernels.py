@@ -110,6 +110,10 @@ class DeviceMatrix:
                                                       self.C, r0, r1, _stream()))
         return res
 
+    def gemm_dense(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
+        """Y [T, R] = X [T, C] . W^T through the two-phase path (see DenseStack)."""
+        return DenseStack([self]).gemm(X, Y)
+
     def unpack(self, plane: int = 0) -> torch.Tensor:
         out = torch.empty(self.R, self.nch, dtype=torch.int32, device=self.device)
         with torch.cuda.device(self.device):
@@ -203,6 +207,69 @@ class T16Matrix:
             _lib.check("cbl_gemv_t16", lib.cbl_gemv_t16(ctypes.byref(self.struct()), xp.data_ptr(), B, Y.data_ptr(), _dt(Y.dtype),
                                                         ldy, s))
         return Y
+
+
+class DenseStack:
+    """Matrices that multiply the same activations (q|k|v, gate|up, or a single matrix), for many tokens or
+    for matrices with several column orders: every matrix is decoded ONCE into a 16-bit scratch shared by
+    all stacks of the device and stream (rows stacked in order), then one TMA-fed tensor-core GEMM writes
+    Y [T, sum R]. d = 8, 12-bit tags, G = 1; one or two books; any number of column orders."""
+
+    _scratch: dict = {}
+    _stage: dict = {}
+
+    def __init__(self, dms: list):
+        for dm in dms:
+            _need_fast(dm)
+        if len({dm.C for dm in dms}) != 1 or len({dm.device for dm in dms}) != 1:
+            raise ValueError("stacked matrices share the input size and the device")
+        self.dms, self.C, self.device = dms, dms[0].C, dms[0].device
+        self.R = sum(dm.R for dm in dms)
+        self.row_scale = dms[0].row_scale if len(dms) == 1 else torch.cat([dm.row_scale for dm in dms])
+        self.ld = (self.C + 7) // 8 * 8
+
+    def gemm(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
+        if X.dim() != 2 or X.shape[1] != self.C or X.stride(1) != 1 or X.device != self.device:
+            raise ValueError("X must be [T, C] with unit column stride on the matrices' device")
+        T = X.shape[0]
+        if Y is None:
+            Y = torch.empty(T, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape != (T, self.R) or Y.stride(1) != 1:
+            raise ValueError("Y must be [T, sum R] with unit column stride")
+        if T == 0 or self.R == 0:
+            return Y
+        key = (self.device.index, _stream())
+        need = lib.cbl_dense_scratch_bytes(self.R, self.C)
+        # two scratch buffers alternate: the decode of this stack may run beside the GEMM of the previous one
+        pair = DenseStack._scratch.setdefault(key, [None, None, 0])
+        pair[2] ^= 1
+        sc = pair[pair[2]]
+        if sc is None or sc.numel() < need:
+            sc = pair[pair[2]] = torch.empty(need, dtype=torch.uint8, device=self.device)
+        need = lib.cbl_gemm_stage_bytes(T, self.C) + 16
+        st = DenseStack._stage.get(key)
+        if st is None or st.numel() < need:
+            st = DenseStack._stage[key] = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            s, row = _stream(), 0
+            for dm in self.dms:
+                _lib.check("cbl_decode_raw", lib.cbl_decode_raw(ctypes.byref(dm.struct()), sc.data_ptr() + row * self.ld * 2, s))
+                row += dm.R
+            _lib.check("cbl_gemm_dense", lib.cbl_gemm_dense(sc.data_ptr(), self.R, self.C, self.row_scale.data_ptr(), X.data_ptr(), _dt(X.dtype),
+                                                            T, X.stride(0), Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
+                                                            st.data_ptr() + st.numel() - 16, s))
+        return Y
+
+    @classmethod
+    def status(cls, device) -> None:
+        """Synchronises and raises CblError if a bounded device-side wait of an earlier gemm() expired."""
+        device = torch.device(device)
+        key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+        st = cls._stage.get(key)
+        if st is not None:
+            torch.cuda.synchronize(device)
+            if int(st[-16:].view(torch.int32)[0]) != 0:
+                raise _lib.CblError("cbl_gemm_dense", _lib.ETIMEOUT, "a bounded device-side wait expired")
 
 
 _WORKSPACES: dict[tuple, torch.Tensor] = {}

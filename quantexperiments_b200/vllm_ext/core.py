@@ -16,8 +16,8 @@ import re
 
 import torch
 
-from ..kernels import L8Group, T16Matrix
-from ..linear import L8_MIN_ROWS, PackedLinear, _Scratch
+from ..kernels import DenseStack, L8Group, T16Matrix
+from ..linear import DENSE_MIN_TOKENS, L8_MIN_ROWS, PackedLinear
 
 BMAX = T16Matrix.BMAX
 
@@ -65,7 +65,7 @@ class PackedShards:
                 lin.l8
             for b in range(1, bmax + 1, 8):
                 lin.t16.xp_buffer(b)
-        _Scratch.get(max(self.Rs) * self.C, self.device, torch.bfloat16)
+        self.stack = DenseStack([lin.dm for lin in lins])     # many tokens / several column orders: decode once, one GEMM
         # one token: all pieces in one launch when they share a column order and the stack is tall enough
         self.group = None
         if all(lin.dm.M == 1 for lin in lins) and self.R >= L8_MIN_ROWS and len(lins) <= L8Group.MAX:
@@ -115,14 +115,11 @@ class PackedShards:
         return y
 
     def _large(self, x: torch.Tensor) -> torch.Tensor:
-        scratch = _Scratch.get(max(self.Rs) * self.C, x.device, x.dtype)
         y = torch.empty(x.shape[0], self.R, dtype=x.dtype, device=x.device)
+        if x.shape[0] >= DENSE_MIN_TOKENS or not all(lin.use_gemm() for lin in self.lins):
+            return self.stack.gemm(x, y)                  # all pieces decoded once, one TMA-fed tcgen05 GEMM over the stacked rows
         for lin, off, R in zip(self.lins, self.offs, self.Rs):
-            if lin.use_gemm():
-                lin.l8.gemm(x, y[:, off:off + R])         # fused decode + tcgen05 GEMM straight into the column slice
-            else:
-                w = lin.dm.dequant(scratch)
-                torch.mm(x, w.t(), out=y[:, off:off + R])  # the GEMM finishes before the scratch is reused (one stream)
+            lin.l8.gemm(x, y[:, off:off + R])             # fused decode + tcgen05 GEMM straight into the column slice
         return y
 
 

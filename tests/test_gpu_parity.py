@@ -483,3 +483,67 @@ def test_qwen32b_shaped_rows_with_two_books_and_sixteen_column_orders(C):
                        _t(m["perms"]).cuda(), 4096, 8, words2=_t(m["words"][1]).cuda(), table2=_t(m["table"][1]).cuda())
     yl = lin(x.cuda())
     assert orc.max_rel_err(yl.float().cpu().numpy(), orc.linear_ref(x.float().numpy(), ref)) < 1e-2
+
+
+# ------------------------------------------------------------------------------------------ two-phase prefill
+@pytest.mark.parametrize("R,C,T,books,M", [(300, 264, 70, 1, 1), (1000, 520, 300, 2, 1), (520, 1032, 257, 1, 4), (260, 264, 65, 2, 3),
+                                            (777, 3584, 1100, 1, 1), (2, 8, 1, 1, 1)])
+def test_two_phase_prefill_matches_fp32_matmul(R, C, T, books, M):
+    """cbl_decode_raw + cbl_gemm_dense (decode once into a 16-bit scratch, TMA-fed tcgen05 GEMM) for one or two
+    books and for several column orders, fp32 and 16-bit outputs."""
+    from quantexperiments_b200.kernels import DenseStack
+    m = orc.synth_matrix(R, C, seed=R + C + T, books=books, M=M)
+    dm = _dm(m)
+    w = torch.from_numpy(orc.synth_decode(m)).cuda()
+    g = torch.Generator(device="cuda").manual_seed(T)
+    for xdt in (torch.bfloat16, torch.float16, torch.float32):
+        X = torch.randn(T, C, device="cuda", generator=g).to(xdt)
+        ref = X.float() @ w.t()
+        for ydt in (torch.float32, torch.bfloat16):
+            Y = dm.gemm_dense(X, torch.full((T, R), 7.0, device="cuda", dtype=ydt))
+            err = (Y.float() - ref).abs().max() / ref.abs().max()
+            assert err <= _out_tol(ydt), (xdt, ydt, float(err))
+    DenseStack.status("cuda")
+
+
+def test_two_phase_prefill_stacks_pieces_writes_a_column_slice_and_survives_outliers():
+    from quantexperiments_b200.kernels import DenseStack
+    C, T = 520, 200
+    ms = [orc.synth_matrix(R, C, seed=40 + i, books=1 + (i == 1), M=1 + 2 * (i == 2)) for i, R in enumerate((300, 129, 260))]
+    dms = [_dm(m) for m in ms]
+    w = torch.cat([torch.from_numpy(orc.synth_decode(m)) for m in ms]).cuda()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    X = torch.randn(T, C, device="cuda", generator=g)
+    X[5, 17] = 3.0e4                      # an outlier token: its own power-of-two scale keeps the others exact
+    X[9] *= 1e-6
+    X = X.bfloat16()
+    ref = X.float() @ w.t()
+    wide = torch.full((T, 689 + 16), 5.0, device="cuda", dtype=torch.bfloat16)
+    st = DenseStack(dms)
+    assert st.R == 689
+    st.gemm(X, wide[:, 8:8 + 689])
+    assert (wide[:, :8] == 5.0).all() and (wide[:, 8 + 689:] == 5.0).all()
+    got = wide[:, 8:8 + 689].float()
+    for t in (0, 5, 9, 199):              # per token: every token is scaled by its own power of two
+        assert (got[t] - ref[t]).abs().max() / ref[t].abs().max() <= _out_tol(torch.bfloat16), t
+    # twice in a row (the two scratch buffers alternate) and from a non-contiguous activation view
+    Xw = torch.randn(T, C + 24, device="cuda", generator=g).bfloat16()
+    y1 = st.gemm(Xw[:, 8:8 + C])
+    y2 = st.gemm(Xw[:, 8:8 + C])
+    assert torch.equal(y1, y2)
+    assert (y1.float() - Xw[:, 8:8 + C].float() @ w.t()).abs().max() / ref.abs().max() <= _out_tol(torch.bfloat16)
+    DenseStack.status("cuda")
+
+
+def test_two_phase_prefill_rejects_unsupported_arguments():
+    from quantexperiments_b200 import _lib
+    import ctypes
+    m = orc.synth_matrix(64, 64, seed=1, d=4, bits=10)
+    dm = _dm(m)
+    t = torch.zeros(64 * 64, device="cuda", dtype=torch.float16)
+    s = torch.cuda.current_stream().cuda_stream
+    assert _lib.lib.cbl_decode_raw(ctypes.byref(dm.struct()), t.data_ptr(), s) == _lib.EUNSUPPORTED
+    assert _lib.lib.cbl_decode_raw(None, t.data_ptr(), s) == _lib.EINVAL
+    assert _lib.lib.cbl_gemm_dense(t.data_ptr(), 64, 60, t.data_ptr(), t.data_ptr(), 1, 4, 64, t.data_ptr(), 1, 64, t.data_ptr(), t.data_ptr(), s) == _lib.EINVAL
+    assert _lib.lib.cbl_gemm_dense(t.data_ptr(), 64, 64, t.data_ptr(), t.data_ptr(), 1, 4, 64, t.data_ptr(), 1, 32, t.data_ptr(), t.data_ptr(), s) == _lib.EINVAL
+    assert _lib.lib.cbl_dense_scratch_bytes(3, 12) == 3 * 16 * 2
