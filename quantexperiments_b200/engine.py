@@ -90,10 +90,19 @@ class _Stage:
         else:
             for l in self.lins:
                 l.t16.xp_buffer(self.B)
+            # one staging pass of the activations serves every matrix of the stage when they share the column orders
+            p0 = self.lins[0].dm.perms
+            self.share = all(l.dm.M == self.lins[0].dm.M and (l.dm.perms is p0 or (p0 is not None and l.dm.perms is not None
+                                                                                     and torch.equal(l.dm.perms, p0)))
+                             for l in self.lins)
 
     def run(self, x: torch.Tensor) -> None:
         if self.group is not None:
             self.group.run(x[0], self.ys)
+        elif self.share:
+            xp = self.lins[0].t16.prep(x, self.B)
+            for o, l in zip(self.offs, self.lins):
+                l.t16.run_prepped(xp, self.out[:, o:o + l.R], self.B)
         else:
             for o, l in zip(self.offs, self.lins):
                 l.forward_into(x, self.out[:, o:o + l.R])

@@ -208,6 +208,22 @@ class T16Matrix:
                                                         ldy, s))
         return Y
 
+    def prep(self, X: torch.Tensor, B: int) -> torch.Tensor:
+        """Stage a batch of activations once for several matrices that share it and its column orders
+        (q|k|v, gate|up): returns the staging buffer to pass to run_prepped()."""
+        xp = self.xp_buffer(B)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_prep_x", lib.cbl_prep_x(X.data_ptr(), _dt(X.dtype), B, self.C, X.stride(0), _ptr(self.dm.perms), self.M,
+                                                    xp.data_ptr(), _stream()))
+        return xp
+
+    def run_prepped(self, xp: torch.Tensor, Y: torch.Tensor, B: int) -> torch.Tensor:
+        """The product alone, on activations staged by prep() of a matrix with the same input size and column orders."""
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_t16", lib.cbl_gemv_t16(ctypes.byref(self.struct()), xp.data_ptr(), B, Y.data_ptr(), _dt(Y.dtype),
+                                                        Y.stride(0) if Y.dim() == 2 else self.R, _stream()))
+        return Y
+
 
 class DenseStack:
     """Matrices that multiply the same activations (q|k|v, gate|up, or a single matrix), for many tokens or
