@@ -213,15 +213,29 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         # row-parallel products sum their partial outputs through peer memory inside the finish kernel
         from quantexperiments_b200.tp import PeerArena, PeerReduceGemv
         arena = PeerArena(8 << 20)
-    if B == 1:
-        for l0 in range(0, len(lins), per_layer):
-            q, k, v, o, gate, up, down = lins[l0:l0 + per_layer]
-            for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
-                outs = [torch.empty(m.R, device=dev, dtype=torch.bfloat16) for m in members]
+    # every product reads its own slice of one input arena and writes its own slice of one output arena, so that the
+    # end-to-end leg moves a step's inputs and results with ONE copy each way
+    n_in = sum(B * l.C for i, l in enumerate(lins) if i % per_layer in (0, 3, 4, 6))
+    xarena = torch.randn(n_in, device=dev, generator=g).bfloat16()
+    yarena = torch.empty(sum(B * l.R for l in lins), device=dev, dtype=torch.bfloat16)
+    xoff = yoff = 0
+    items = []                     # batch > 1: (lin, x [B, C], y [B, R], kind)
+    for l0 in range(0, len(lins), per_layer):
+        q, k, v, o, gate, up, down = lins[l0:l0 + per_layer]
+        for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
+            C = members[0].C
+            x = xarena[xoff:xoff + B * C].view(B, C)
+            xoff += B * C
+            outs = []
+            for m in members:
+                outs.append(yarena[yoff:yoff + B * m.R].view(B, m.R))
+                yoff += B * m.R
+                items.append((m, x, outs[-1], kind))
+            if B == 1:
                 if arena is not None and kind == "row":
-                    groups.append((PeerReduceGemv(members[0].l8, arena), xs[members[0].C][0], outs, "fused"))
+                    groups.append((PeerReduceGemv(members[0].l8, arena), x[0], [outs[0][0]], "fused"))
                 else:
-                    groups.append((L8Group([m.l8 for m in members]), xs[members[0].C][0], outs, kind))
+                    groups.append((L8Group([m.l8 for m in members]), x[0], [o_[0] for o_ in outs], kind))
 
     def step_kernels():
         if B == 1:
@@ -231,13 +245,15 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                 else:
                     grp.run(x, outs)
             return
-        for lin, kind in zip(lins, kinds):
-            y = ys[lin.R]
-            launch(lin, xs[lin.C], y)
+        staged = (None, None)             # matrices that share their input share one staging pass of it
+        for lin, x, y, kind in items:
+            if staged[0] is not x:
+                staged = (x, lin.t16.prep(x, B))
+            lin.t16.run_prepped(staged[1], y, B)
             if world > 1 and kind == "row":
                 dist.all_reduce(y)
 
-    launches_per_step = 2 * len(groups) if B == 1 else 2 * len(lins)
+    launches_per_step = 2 * len(groups) if B == 1 else len(lins) + 4 * (len(lins) // per_layer)
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         step_kernels()
@@ -295,33 +311,26 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                     "traffic": alg * NCU_TRAFFIC_GATE[0] / NCU_TRAFFIC_GATE[1], "algorithmic_bytes_per_launch": alg,
                     "us_per_launch": per_launch_s * 1e6, "launches_timed": args.steps * len(big)}
 
-        # end to end through the public call with HOST buffers: pinned x -> device, products, y -> host
-        hx = {c: torch.randn(B, c).bfloat16().pin_memory() for c in xs}
-        hy = {r: torch.empty(B, r, dtype=torch.bfloat16).pin_memory() for r in ys}
-        h2d = sum(x.numel() * 2 for _, x, _, _ in groups) if B == 1 else sum(B * lin.C * 2 for lin in lins)
-        d2h = sum(B * lin.R * 2 for lin in lins)
+        # end to end with HOST buffers: the step's inputs come from pinned host memory (one copy into the input arena),
+        # the products run, the step's results go back to pinned host memory (one copy of the output arena); copies and
+        # kernels of a step form one CUDA graph and the host waits for every step's results
+        hx = torch.randn(xarena.numel()).bfloat16().pin_memory()
+        hy = torch.empty(yarena.numel(), dtype=torch.bfloat16).pin_memory()
+        h2d, d2h = xarena.numel() * 2, yarena.numel() * 2
 
-        hys = [[torch.empty(o.numel(), dtype=torch.bfloat16).pin_memory() for o in outs] for _, _, outs, _ in groups[:4]]
+        def e2e_body():
+            xarena.copy_(hx, non_blocking=True)
+            step_kernels()
+            hy.copy_(yarena, non_blocking=True)
+
+        e2e_body()
+        stream.synchronize()
+        ge = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ge, stream=stream):
+            e2e_body()
 
         def step_e2e():
-            if B == 1:
-                for gi, (grp, x, outs, kind) in enumerate(groups):
-                    x.copy_(hx[x.numel()][0], non_blocking=True)
-                    if kind == "fused":
-                        grp.run(x, outs[0])
-                    else:
-                        grp.run(x, outs)
-                    for o, h in zip(outs, hys[gi % 4]):
-                        h.copy_(o, non_blocking=True)
-                stream.synchronize()
-                return
-            for lin, kind in zip(lins, kinds):
-                x, y = xs[lin.C], ys[lin.R]
-                x.copy_(hx[lin.C], non_blocking=True)
-                launch(lin, x, y)
-                if world > 1 and kind == "row":
-                    dist.all_reduce(y)
-                hy[lin.R].copy_(y, non_blocking=True)
+            ge.replay()
             stream.synchronize()
 
         for _ in range(2):
@@ -354,7 +363,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"qwen2.5-7b decode GEMV set (196 codebook matrices, d=8, K=4096, 12-bit tags), batch {B}",
                        "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 (1.24 GB of packed weights per step)",
-                       "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step (q|k|v and gate|up grouped)" + ("" if world == 1 else "; o/down summed over ranks through peer memory in the finish kernel")},
+                       "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step (q|k|v and gate|up grouped)" + ("" if world == 1 else "; o/down summed over ranks through peer memory in the finish kernel"),
+                       "e2e": "a step's inputs from pinned host memory and its results back to pinned host memory (one copy each way), copies and kernels in one CUDA graph, host synchronises every step"},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps * world,
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                     "ms_per_step": ms_e2e / args.steps}}
