@@ -86,6 +86,16 @@ extern "C" int cbl_prep_x(const void* x, int xdtype, int32_t B, int32_t C, int64
     return cbl_check_launch();
 }
 
+#ifdef CBL_TRACE
+// Debug builds only: per-block phase timestamps (ns) for offline inspection.
+__device__ unsigned long long g_cbl_trace[1024 * 16];
+__device__ __forceinline__ unsigned long long cbl_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define CBL_MARK(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) g_cbl_trace[blockIdx.x * 16 + (i)] = cbl_now(); } while (0)
+extern "C" int cbl_trace_read(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_cbl_trace, sizeof(g_cbl_trace)); }
+#else
+#define CBL_MARK(i) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------------ t16 product
 // Byte offset (tag * 16) of tag i of a lane's 384-bit stream held in w[0..11].
 template <int I>
@@ -96,31 +106,53 @@ __device__ __forceinline__ uint32_t t16_tag_off(const uint32_t (&w)[12]) {
     else return (w[wi] << (4 - sh)) & 0xFFF0u;
 }
 
+// One step = 4 chunks of each of the tile's 16 rows (two codeword reads per lane and book, two MMAs per batch
+// block).  The codewords and activations of step S + 1 are requested before the MMAs of step S are issued, and
+// the two MMAs of a step accumulate into separate registers (two shorter dependency chains), summed at the end.
+template <int BOOKS, int NB>
+struct T16Operands {
+    uint4 c[BOOKS][2];
+    uint4 x[NB];
+};
+
 template <int BOOKS, int NB, int S>
-__device__ __forceinline__ void t16_step(float (&acc)[NB][4], const uint32_t (&w)[BOOKS][12], uint32_t tbl,
-                                         const uint4* __restrict__ xrow, int64_t xstride8, int rows_left) {
+__device__ __forceinline__ void t16_fetch(T16Operands<BOOKS, NB>& o, const uint32_t (&w)[BOOKS][12], uint32_t tbl,
+                                          const uint4* __restrict__ xrow, int64_t xstride8, int rows_left) {
     // xrow points at chunk (ss*16)*4 + t of batch row g; step S adds 4 chunks.  Lanes whose batch row does not
     // exist (padding up to a multiple of 8) feed zeros without touching memory.
-    uint4 xv[NB];
 #pragma unroll
-    for (int nb = 0; nb < NB; nb++) xv[nb] = (nb * 8 < rows_left) ? __ldg(xrow + S * 4 + nb * xstride8) : make_uint4(0, 0, 0, 0);
+    for (int nb = 0; nb < NB; nb++) o.x[nb] = (nb * 8 < rows_left) ? __ldg(xrow + S * 4 + nb * xstride8) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int bk = 0; bk < BOOKS; bk++) {
-        uint4 c0 = cbl_lds128(tbl + bk * 65536u + t16_tag_off<2 * S>(w[bk]));
-        uint4 c1 = cbl_lds128(tbl + bk * 65536u + t16_tag_off<2 * S + 1>(w[bk]));
-#pragma unroll
-        for (int nb = 0; nb < NB; nb++) {
-            cbl_mma16816(acc[nb], c0.x, c1.x, c0.y, c1.y, xv[nb].x, xv[nb].y);
-            cbl_mma16816(acc[nb], c0.z, c1.z, c0.w, c1.w, xv[nb].z, xv[nb].w);
-        }
+        o.c[bk][0] = cbl_lds128(tbl + bk * 65536u + t16_tag_off<2 * S>(w[bk]));
+        o.c[bk][1] = cbl_lds128(tbl + bk * 65536u + t16_tag_off<2 * S + 1>(w[bk]));
     }
 }
 
+template <int BOOKS, int NB, int S>
+__device__ __forceinline__ void t16_step(float (&acc)[2][NB][4], T16Operands<BOOKS, NB>& cur, const uint32_t (&w)[BOOKS][12], uint32_t tbl,
+                                         const uint4* __restrict__ xrow, int64_t xstride8, int rows_left) {
+    T16Operands<BOOKS, NB> nxt;
+    if constexpr (S + 1 < 16) t16_fetch<BOOKS, NB, S + 1>(nxt, w, tbl, xrow, xstride8, rows_left);
+#pragma unroll
+    for (int bk = 0; bk < BOOKS; bk++) {
+        const uint4 c0 = cur.c[bk][0], c1 = cur.c[bk][1];
+#pragma unroll
+        for (int nb = 0; nb < NB; nb++) {
+            cbl_mma16816(acc[0][nb], c0.x, c1.x, c0.y, c1.y, cur.x[nb].x, cur.x[nb].y);
+            cbl_mma16816(acc[1][nb], c0.z, c1.z, c0.w, c1.w, cur.x[nb].z, cur.x[nb].w);
+        }
+    }
+    if constexpr (S + 1 < 16) cur = nxt;
+}
+
 template <int BOOKS, int NB, int... S>
-__device__ __forceinline__ void t16_steps(float (&acc)[NB][4], const uint32_t (&w)[BOOKS][12], uint32_t tbl,
+__device__ __forceinline__ void t16_steps(float (&acc)[2][NB][4], const uint32_t (&w)[BOOKS][12], uint32_t tbl,
                                           const uint4* __restrict__ xrow, int64_t xstride8, int rows_left,
                                           std::integer_sequence<int, S...>) {
-    (t16_step<BOOKS, NB, S>(acc, w, tbl, xrow, xstride8, rows_left), ...);
+    T16Operands<BOOKS, NB> cur;
+    t16_fetch<BOOKS, NB, 0>(cur, w, tbl, xrow, xstride8, rows_left);
+    (t16_step<BOOKS, NB, S>(acc, cur, w, tbl, xrow, xstride8, rows_left), ...);
 }
 
 constexpr int T16_WARPS = 8;
@@ -133,6 +165,7 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
     float* s_red = (float*)(smem + BOOKS * 65536);                  // [warps][NB][32][4]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    CBL_MARK(0);
     {
         const uint4* t0 = (const uint4*)m.table;
         for (int i = tid; i < 4096; i += T16_WARPS * 32) s_table[i] = __ldg(t0 + i);
@@ -144,6 +177,8 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");          // the staged activations come from the kernel before
     __syncthreads();
+    CBL_MARK(1);
+    int trace_it = 0;
     const uint32_t tbl = cbl_smem_u32(s_table);
     const uint4* words = (const uint4*)m.words;
     const int64_t book_stride = (int64_t)m.ntile * m.nsuper * 96;   // uint4 per book
@@ -153,11 +188,11 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
         const int mk = m.tile_mask ? m.tile_mask[tile] : 0;
         const float* xinv = (const float*)(xp + (int64_t)m.M * Bpad * Cpad);
         const uint4* xbase = (const uint4*)(xp + ((int64_t)mk * Bpad + g) * Cpad) + t;
-        float acc[NB][4];
+        float acc[2][NB][4];
 #pragma unroll
         for (int nb = 0; nb < NB; nb++)
 #pragma unroll
-            for (int k = 0; k < 4; k++) acc[nb][k] = 0.f;
+            for (int k = 0; k < 4; k++) acc[0][nb][k] = acc[1][nb][k] = 0.f;
         uint32_t w[BOOKS][12];
         int ss = warp;
         if (ss < m.nsuper) {
@@ -194,11 +229,14 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
             }
             ss = sn;
         }
+        if (trace_it < 4) CBL_MARK(2 + 3 * trace_it);
         // cross-warp sum in a fixed order (deterministic), row scale, output rounding
 #pragma unroll
         for (int nb = 0; nb < NB; nb++)
-            *(float4*)(s_red + ((warp * NB + nb) * 32 + lane) * 4) = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+            *(float4*)(s_red + ((warp * NB + nb) * 32 + lane) * 4) = make_float4(acc[0][nb][0] + acc[1][nb][0], acc[0][nb][1] + acc[1][nb][1],
+                                                                                 acc[0][nb][2] + acc[1][nb][2], acc[0][nb][3] + acc[1][nb][3]);
         __syncthreads();
+        if (trace_it < 4) CBL_MARK(3 + 3 * trace_it);
         for (int e = tid; e < 128 * NB; e += T16_WARPS * 32) {
             int nb = e >> 7, ln = (e & 127) >> 2, k = e & 3;
             float sum = 0.f;
@@ -213,7 +251,10 @@ __global__ void __launch_bounds__(T16_WARPS * 32) k_gemv_t16(cbl_t16 m, const __
             }
         }
         __syncthreads();
+        if (trace_it < 4) CBL_MARK(4 + 3 * trace_it);
+        trace_it++;
     }
+    CBL_MARK(15);
 }
 
 template <int BOOKS, int NB>
@@ -338,15 +379,6 @@ __device__ __forceinline__ bool l8_mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-#ifdef CBL_TRACE
-// Debug builds only: per-block phase timestamps (ns) for offline inspection.
-__device__ unsigned long long g_cbl_trace[1024 * 16];
-__device__ __forceinline__ unsigned long long cbl_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define CBL_MARK(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) g_cbl_trace[blockIdx.x * 16 + (i)] = cbl_now(); } while (0)
-extern "C" int cbl_trace_read(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_cbl_trace, sizeof(g_cbl_trace)); }
-#else
-#define CBL_MARK(i) do { } while (0)
-#endif
 
 // Up to L8_MAX_GROUP matrices that share one activation vector (q|k|v, gate|up) run as ONE launch:
 // their tiles form one list, the work split and the tag ring run across matrix boundaries.
