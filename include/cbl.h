@@ -213,6 +213,20 @@ int cbl_gemm_l8(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_
 int cbl_gemm_l8_2sm(const cbl_l8* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
                     void* stage, void* workspace, cbl_stream s);
 
+/* Up to cbl_gemm_rows_max_tokens() (32) tokens on the tensor cores with the WEIGHT ROWS as the M side of
+ * tcgen05.mma: every block decodes 128 rows x its share of k into the swizzled A tile (each weight is
+ * decoded once whatever the token count), the tokens are the N side (TMA).  Up to four matrices that share
+ * the activations (q|k|v, gate|up; same C and book count) run as one launch; ys[i] receives
+ * y_i[t * ldy + r].  Products with few row tiles are split along k, summed in `workspace`
+ * (cbl_gemm_rows_workspace_bytes(sum of the matrices' padded rows) bytes, zero before the first call, left
+ * zero; its last 16 bytes hold the status word) and finished by a second kernel.  x, stage as for cbl_gemm_l8.
+ * One column order only (M = 1); one or two books.
+ * replaces shapequant/kernels/batched_runs.py:745-771 (RunsBatch.run) for batches of 9..32 tokens. */
+int32_t cbl_gemm_rows_max_tokens(void);
+size_t cbl_gemm_rows_workspace_bytes(int32_t sum_rows_padded);
+int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* const* ys, int ydtype,
+                        int64_t ldy, void* stage, void* workspace, cbl_stream s);
+
 /* Two-phase prefill for many tokens and for matrices with several column orders: decode the matrix ONCE
  * into a 16-bit scratch, then multiply with a TMA-fed tcgen05 GEMM (both operands by TMA, accumulators in
  * tensor memory).

@@ -74,6 +74,10 @@ SIGNATURES = {
     "cbl_gemv_l8_ar": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, POINTER(c_void_p), c_int32, c_int32, c_void_p]),
     "cbl_gemv_l8_ar_status": (c_int, [c_void_p, c_int32, c_void_p]),
     "cbl_gemv_l8_status": (c_int, [c_void_p, c_int32, c_void_p]),
+    "cbl_gemm_rows_max_tokens": (c_int32, []),
+    "cbl_gemm_rows_workspace_bytes": (c_size_t, [c_int32]),
+    "cbl_gemm_rows_multi": (c_int, [POINTER(L8), c_int32, c_void_p, c_int, c_int32, c_int64, POINTER(c_void_p), c_int, c_int64, c_void_p,
+                                    c_void_p, c_void_p]),
     "cbl_dense_scratch_bytes": (c_size_t, [c_int32, c_int32]),
     "cbl_decode_raw": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
     "cbl_gemm_dense": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p,

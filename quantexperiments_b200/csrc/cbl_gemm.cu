@@ -482,6 +482,235 @@ k_gemm_l8_2sm(const __grid_constant__ CUtensorMap xmap, cbl_l8 m, const float* _
     }
 }
 
+// ------------------------------------------------------------------------------------ up to 32 tokens: weight rows as M
+//
+// For a handful of tokens the product is bound by decoding alone, so the tile is turned around: 128 weight rows
+// are the M side of tcgen05.mma (decoded into the K-major swizzled A tile), the tokens the N side (16 or 32,
+// brought in by TMA).  Every weight is decoded exactly once whatever the token count, the MMAs are negligible,
+// and there are no per-step activation fragments to fetch as in the mma.sync kernel.  512 decode threads = 128
+// rows x 4 k-blocks per hand-off (64 KB of A per stage, two stages).  Blocks = (row tile, k part): products with
+// few row tiles are split along k and summed with fp32 reductions into a work space, finished by a second
+// kernel.  Up to four matrices that share the activations run as one launch (each block stages its own
+// matrix's book).
+constexpr int GR_ROWS = 128;
+constexpr int GR_KBS = 4;                                  // k-blocks per stage
+constexpr int GR_STAGES = 2;
+constexpr int GR_NMAX = 32;                                // tokens per launch
+constexpr int GR_A_KB = GR_ROWS * 128;                     // one k-block of A: 16 KB
+constexpr int GR_X_KB = GR_NMAX * 128;                     // one k-block of the activations: 4 KB
+constexpr int GR_A_STAGE = GR_KBS * GR_A_KB, GR_X_STAGE = GR_KBS * GR_X_KB;
+constexpr int GR_SMEM = 65536 + GR_STAGES * (GR_A_STAGE + GR_X_STAGE);   // 224 KB
+constexpr int GR_DECODE_WARPS = 16, GR_THREADS = (GR_DECODE_WARPS + 2) * 32;
+constexpr int GR_MAX_GROUP = 4;
+
+struct GRLaunch {
+    int n;                            // matrices
+    int tile0[GR_MAX_GROUP + 1];      // prefix sums of their row-tile counts
+    cbl_l8 m[GR_MAX_GROUP];
+    float* acc[GR_MAX_GROUP];         // fp32 [npad][Rpad] partial sums (k-split launches)
+    void* y[GR_MAX_GROUP];
+    int ksplit, npad;
+};
+
+__global__ void __launch_bounds__(GR_THREADS, 1)
+k_gemm_rows(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ GRLaunch P, const float* __restrict__ xinv, int ntok, int ydtype,
+            int64_t ldy, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_bar[3 * GR_STAGES + 1];    // full_a, full_x, empty per stage; tmem_full
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int mi = 0;
+    while (mi + 1 < P.n && (int)blockIdx.x >= P.tile0[mi + 1]) mi++;
+    const cbl_l8& m = P.m[mi];
+    const int r0 = ((int)blockIdx.x - P.tile0[mi]) * GR_ROWS;
+    const int nkb = m.ntile, nkb1 = m.ntile / m.books;
+    // this block's k-blocks: part blockIdx.y of ksplit equal parts
+    const int kb_lo = (int)(((int64_t)nkb * blockIdx.y) / P.ksplit), kb_hi = (int)(((int64_t)nkb * (blockIdx.y + 1)) / P.ksplit);
+    const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
+    auto full_a = [&](int s) { return bar0 + 8u * s; };
+    auto full_x = [&](int s) { return bar0 + 8u * (GR_STAGES + s); };
+    auto empty = [&](int s) { return bar0 + 8u * (2 * GR_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (3 * GR_STAGES);
+    const uint32_t a_base = sbase + 65536, x_base = a_base + GR_STAGES * GR_A_STAGE;
+    // stages never straddle the two books: segment 0 = this part's k-blocks of the first book, segment 1 = of the second
+    const int seg_lo[2] = {kb_lo < nkb1 ? kb_lo : nkb1, kb_lo > nkb1 ? kb_lo : nkb1};
+    const int seg_hi[2] = {kb_hi < nkb1 ? kb_hi : nkb1, kb_hi > nkb1 ? kb_hi : nkb1};
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < GR_STAGES; s++) { mbar_init(full_a(s), GR_DECODE_WARPS); mbar_init(full_x(s), 1); mbar_init(empty(s), 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == GR_DECODE_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(32u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp < GR_DECODE_WARPS) {                              // the book of the first segment that has work
+        const uint4* t0 = (const uint4*)((seg_lo[0] < seg_hi[0]) ? m.table : m.table2);
+        uint4* dst = (uint4*)smem;
+        for (int i = tid; i < 4096; i += GR_DECODE_WARPS * 32) dst[i] = __ldg(t0 + i);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // the staged activations (and zeroed sums) come from earlier kernels
+    // A wait that expires marks the block aborted; every thread then keeps the shape of its loops (the decode
+    // warps meet at a named barrier when the book changes) but waits for nothing more.
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        if (*(volatile int*)&s_abort) return;
+        if (!mbar_wait(bar, parity)) s_abort = 1;
+    };
+
+    if (warp == GR_DECODE_WARPS) {
+        if (lane == 0) {                                      // TMA producer of the activations
+            int it = 0;
+            for (int sg = 0; sg < 2; sg++) {
+                for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                    const int s = it % GR_STAGES, nv = min(GR_KBS, seg_hi[sg] - kb);
+                    wait(empty(s), ((it / GR_STAGES) & 1) ^ 1);
+                    if (*(volatile int*)&s_abort) break;              // no copies after an abort: nothing would wait for them
+                    mbar_expect_tx(full_x(s), (uint32_t)nv * (uint32_t)P.npad * 128u);
+                    for (int j = 0; j < nv; j++)
+                        tma_load_2d(x_base + s * GR_X_STAGE + j * GR_X_KB, &xmap, (kb + j - sg * nkb1) * GM_BK, 0, full_x(s));
+                }
+            }
+        }
+    } else if (warp == GR_DECODE_WARPS + 1) {
+        if (lane == 0) {                                      // MMA issuer
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(P.npad >> 3) << 17) | ((uint32_t)(GR_ROWS >> 4) << 24);
+            int it = 0;
+            uint32_t accumulate = 0;
+            for (int sg = 0; sg < 2; sg++) {
+                for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                    const int s = it % GR_STAGES, nv = min(GR_KBS, seg_hi[sg] - kb);
+                    const uint32_t par = (it / GR_STAGES) & 1;
+                    wait(full_x(s), par);
+                    wait(full_a(s), par);
+                    if (*(volatile int*)&s_abort) break;              // no MMAs on tiles that never arrived
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int j = 0; j < nv; j++) {
+#pragma unroll
+                        for (int kk = 0; kk < GM_BK / 16; kk++) {
+                            umma_f16(tmem, umma_desc_sw128(a_base + s * GR_A_STAGE + j * GR_A_KB + kk * 32),
+                                     umma_desc_sw128(x_base + s * GR_X_STAGE + j * GR_X_KB + kk * 32), idesc, accumulate);
+                            accumulate = 1;
+                        }
+                    }
+                    umma_commit(empty(s));
+                }
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        // ---------------- decode: thread = (W row r0 + (tid & 127), k-block tid >> 7 of the stage)
+        const int rl = tid & 127, kbs = tid >> 7, row = r0 + rl;
+        const bool live = row < m.Rpad;
+        const uint32_t* wp = (const uint32_t*)m.words + row;
+        const uint32_t sw = (uint32_t)(rl & 7);
+        const uint32_t rowoff = (uint32_t)kbs * GR_A_KB + (uint32_t)(rl >> 3) * 1024u + sw * 128u;
+        int it = 0;
+        for (int sg = 0; sg < 2; sg++) {
+            if (seg_lo[sg] >= seg_hi[sg]) continue;
+            if (sg == 1 && seg_lo[0] < seg_hi[0]) {
+                // switch books: every decode thread is done with the first one (barrier among the decode warps only)
+                asm volatile("bar.sync 1, %0;" ::"n"(GR_DECODE_WARPS * 32) : "memory");
+                const uint4* t1 = (const uint4*)m.table2;
+                uint4* dst = (uint4*)smem;
+                for (int i = tid; i < 4096; i += GR_DECODE_WARPS * 32) dst[i] = __ldg(t1 + i);
+                asm volatile("bar.sync 1, %0;" ::"n"(GR_DECODE_WARPS * 32) : "memory");
+            }
+            uint32_t wa = 0, wb = 0, wc = 0, na = 0, nb = 0, nc = 0;
+            auto load_tags = [&](int kb, uint32_t& a, uint32_t& b, uint32_t& c) {
+                a = b = c = 0;
+                if (live && kb < seg_hi[sg]) {
+                    const uint32_t* p = wp + (int64_t)kb * 3 * m.Rpad;
+                    a = __ldg(p); b = __ldg(p + m.Rpad); c = __ldg(p + 2 * (int64_t)m.Rpad);
+                }
+            };
+            load_tags(seg_lo[sg] + kbs, wa, wb, wc);
+            for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                const int s = it % GR_STAGES;
+                load_tags(kb + GR_KBS + kbs, na, nb, nc);
+                wait(empty(s), ((it / GR_STAGES) & 1) ^ 1);
+                if (kb + kbs < seg_hi[sg]) {
+                    const uint32_t dst = a_base + s * GR_A_STAGE + rowoff;
+                    uint32_t off[8];
+                    off[0] = (wa << 4) & 0xFFF0u;
+                    off[1] = (wa >> 8) & 0xFFF0u;
+                    off[2] = __funnelshift_r(wa, wb, 20) & 0xFFF0u;
+                    off[3] = wb & 0xFFF0u;
+                    off[4] = (wb >> 12) & 0xFFF0u;
+                    off[5] = __funnelshift_r(wb, wc, 24) & 0xFFF0u;
+                    off[6] = (wc >> 4) & 0xFFF0u;
+                    off[7] = (wc >> 16) & 0xFFF0u;
+                    uint4 cw[8];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) cw[c] = cbl_lds128(sbase + off[c]);
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((uint32_t)c ^ sw) << 4)), "r"(cw[c].x), "r"(cw[c].y),
+                                     "r"(cw[c].z), "r"(cw[c].w)
+                                     : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
+                wa = na; wb = nb; wc = nc;
+            }
+        }
+        // ---------------- epilogue: decode warps 0..3 read TMEM lanes (= W rows) 32 w ..; columns = tokens
+        if (warp < 4) {
+            wait(tmem_full, 0);
+            const bool ok = *(volatile int*)&s_abort == 0;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int r = r0 + warp * 32 + lane;
+            if (ok) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < m.R) {
+                    if (P.ksplit == 1) {
+                        const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
+#pragma unroll 4
+                        for (int n = 0; n < GR_NMAX; n++)
+                            if (n < ntok) cbl_store_out(P.y[mi], ydtype, (int64_t)n * ldy + r, __uint_as_float(v[n]) * xinv[n] * rs);
+                    } else {
+                        float* acc = P.acc[mi] + r;
+#pragma unroll 4
+                        for (int n = 0; n < GR_NMAX; n++)
+                            if (n < ntok) atomicAdd(acc + (int64_t)n * m.Rpad, __uint_as_float(v[n]));
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    if (warp == GR_DECODE_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
+    }
+}
+
+// k-split launches: y[n][r] = round(sum * token scale * row scale); the sums are left zero.  blockIdx.y = token,
+// blockIdx.z = matrix of the group.
+__global__ void __launch_bounds__(256) k_rows_finish(const __grid_constant__ GRLaunch P, const float* __restrict__ xinv, int ydtype, int64_t ldy) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const cbl_l8& m = P.m[blockIdx.z];
+    const int r = blockIdx.x * blockDim.x + threadIdx.x, n = blockIdx.y;
+    if (r >= m.R) return;
+    float* a = P.acc[blockIdx.z] + (int64_t)n * m.Rpad + r;
+    const float v = __ldcg(a);
+    __stcg(a, 0.f);
+    cbl_store_out(P.y[blockIdx.z], ydtype, (int64_t)n * ldy + r, v * xinv[n] * __half2float(((const __half*)m.row_scale)[r]));
+}
+
 // ------------------------------------------------------------------------------------ two-phase variant for many tokens
 //
 // The fused kernels above decode every weight tile once per 256 (or 512) tokens; their shared-memory pipe
@@ -1005,6 +1234,98 @@ extern "C" int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void*
     }
     dim3 grid(cbl_ceil_div(ntok, GM_BM), cbl_ceil_div(R, GM_BN));
     k_gemm_dense<<<grid, GD_THREADS, GD_SMEM, st>>>(xmap, wmap, m, xinv, ntok, y, ydtype, ldy, vec_ok, (unsigned int*)workspace);
+    return cbl_check_launch();
+}
+
+// ---- up to 32 tokens: host side
+extern "C" int32_t cbl_gemm_rows_max_tokens(void) { return GR_NMAX; }
+
+extern "C" size_t cbl_gemm_rows_workspace_bytes(int32_t sum_rows_padded) {
+    if (sum_rows_padded < 0) return 0;
+    return (size_t)GR_NMAX * (size_t)sum_rows_padded * 4 + 16;
+}
+
+extern "C" int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* const* ys, int ydtype,
+                                   int64_t ldy, void* stage, void* workspace, cbl_stream s) {
+    if (!mats || !ys || !x || !stage || !workspace || n < 1) return CBL_EINVAL;
+    if (n > GR_MAX_GROUP || ntok > GR_NMAX) return CBL_EUNSUPPORTED;
+    if (ntok < 1) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (((uintptr_t)stage % 16) || ((uintptr_t)workspace % 16)) return CBL_EINVAL;
+    GRLaunch P;
+    P.n = 0;
+    P.tile0[0] = 0;
+    size_t off = 0;
+    for (int i = 0; i < n; i++) {
+        const cbl_l8* m = mats + i;
+        if (!m->words || !m->table || !m->row_scale || !ys[i]) return CBL_EINVAL;
+        if (m->books != 1 && m->books != 2) return CBL_EINVAL;
+        if (m->books == 2 && (!m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
+        if (m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+        if (m->C != mats[0].C || m->books != mats[0].books || ldx < m->C || ldy < m->R || ((uintptr_t)m->table % 16)) return CBL_EINVAL;
+        if (m->R == 0) continue;
+        P.m[P.n] = *m;
+        P.acc[P.n] = (float*)((char*)workspace + off);
+        P.y[P.n] = ys[i];
+        P.tile0[P.n + 1] = P.tile0[P.n] + cbl_ceil_div(m->R, GR_ROWS);
+        off += (size_t)GR_NMAX * m->Rpad * 4;
+        P.n++;
+    }
+    if (P.n == 0) return CBL_OK;
+    unsigned int* status = (unsigned int*)((char*)workspace + off);
+    const int C = mats[0].C, nkb = mats[0].ntile;
+    const cudaStream_t st = (cudaStream_t)s;
+    int rc = cbl_prep_x(x, xdtype, ntok, C, ldx, nullptr, 1, stage, s);
+    if (rc) return rc;
+    const int Mpad = (ntok + 7) / 8 * 8, Cpad = (C + 511) / 512 * 512;
+    P.npad = ntok <= 16 ? 16 : 32;
+    // few row tiles: split along k so that about every SM gets a block, at least two stages of k-blocks per part
+    const int tiles = P.tile0[P.n];
+    int ksplit = 1;
+    if (tiles * 2 <= cbl_sm_count()) {
+        ksplit = cbl_sm_count() / tiles;
+        const int most = nkb / (2 * GR_KBS);
+        if (ksplit > most) ksplit = most;
+        if (ksplit < 1) ksplit = 1;
+    }
+    P.ksplit = ksplit;
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return CBL_ECUDA;
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)Cpad, (cuuint64_t)Mpad};
+    const cuuint64_t strides[1] = {(cuuint64_t)Cpad * 2};
+    const cuuint32_t box[2] = {GM_BK, (cuuint32_t)P.npad};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, stage, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) { g_cbl_last_cuda_error = (int)cr; return CBL_ECUDA; }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_gemm_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, GR_SMEM));
+        attr_set[dev] = true;
+    }
+    const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(tiles, ksplit);
+    cfg.blockDim = dim3(GR_THREADS);
+    cfg.dynamicSmemBytes = GR_SMEM;
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_rows, xmap, P, xinv, (int)ntok, ydtype, ldy, status));
+    if (ksplit > 1) {
+        int maxR = 0;
+        for (int i = 0; i < P.n; i++) maxR = maxR > P.m[i].R ? maxR : P.m[i].R;
+        cfg.gridDim = dim3(cbl_ceil_div(maxR, 256), ntok, P.n);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        CBL_CUDA(cudaLaunchKernelEx(&cfg, k_rows_finish, P, xinv, ydtype, ldy));
+    }
     return cbl_check_launch();
 }
 

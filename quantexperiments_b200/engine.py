@@ -25,7 +25,7 @@ import torch
 from . import _lib
 from ._lib import lib
 from .kernels import DenseStack, L8Group, _dt, _stream
-from .linear import DENSE_MIN_TOKENS, PackedLinear, RunsLin
+from .linear import DENSE_MIN_TOKENS, ROWS_MIN_TOKENS, PackedLinear, RunsLin
 
 NAMES = ("q", "k", "v", "o", "gate", "up", "down")
 
@@ -83,10 +83,15 @@ class _Stage:
             self.offs.append(o)
             o += l.R
         assert o == out.shape[1]
-        self.group = None
-        if self.B == 1 and all(l.dm.M == 1 for l in self.lins) and len(self.lins) <= L8Group.MAX:
+        self.group = self.rows = None
+        one_order = all(l.dm.M == 1 for l in self.lins) and len(self.lins) <= L8Group.MAX and len({l.dm.books for l in self.lins}) == 1
+        if self.B == 1 and one_order:
             self.group = L8Group([l.l8 for l in self.lins])
             self.ys = [out[0, o:o + l.R] for o, l in zip(self.offs, self.lins)]
+        elif self.B >= ROWS_MIN_TOKENS and one_order:
+            # a few dozen sequences: the tensor-core kernel with the weight rows as the M side, all matrices in one launch
+            self.rows = L8Group([l.l8 for l in self.lins])
+            self.ys = [out[:, o:o + l.R] for o, l in zip(self.offs, self.lins)]
         else:
             for l in self.lins:
                 l.t16.xp_buffer(self.B)
@@ -99,6 +104,8 @@ class _Stage:
     def run(self, x: torch.Tensor) -> None:
         if self.group is not None:
             self.group.run(x[0], self.ys)
+        elif self.rows is not None:
+            self.rows.gemm_rows(x, self.ys)
         elif self.share:
             xp = self.lins[0].t16.prep(x, self.B)
             for o, l in zip(self.offs, self.lins):
@@ -162,7 +169,7 @@ class DecodeEngine:
         self.graph = None
         self.only_linears = False
         # one token, one column order everywhere: the operators that follow a product run in its finish kernel
-        self.fused = all(st.group is not None for S in self.stages for st in S.values()) and H <= lib.cbl_gemv_l8_add_norm_max_rows()
+        self.fused = B == 1 and all(st.group is not None for S in self.stages for st in S.values()) and H <= lib.cbl_gemv_l8_add_norm_max_rows()
 
     # -- operators (thin wrappers over the C ABI; all on the current stream)
     def _addnorm(self, h, add, w, x, rows: int) -> None:

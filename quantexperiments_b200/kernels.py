@@ -412,6 +412,38 @@ class L8Group:
         self._structs = (_lib.L8 * len(mats))(*[m.struct() for m in mats])
         self._ys = (ctypes.c_void_p * len(mats))()
         self.ws_bytes = sum(lib.cbl_gemv_l8_workspace_bytes(m.R) for m in mats)
+        self.rows_ws_bytes = lib.cbl_gemm_rows_workspace_bytes(sum(m.Rpad for m in mats))
+        self._rows_stage: dict = {}
+
+    def gemm_rows(self, X: torch.Tensor, ys: list[torch.Tensor]) -> list[torch.Tensor]:
+        """A few dozen tokens on the tensor cores with the weight rows as the M side: ys[i] [B, R_i] = X [B, C] . W_i^T.
+        The outputs share one row stride (column slices of one stacked buffer, or equal-width tensors). More than
+        32 tokens run as several launches of up to 32."""
+        B = X.shape[0]
+        nmax = lib.cbl_gemm_rows_max_tokens()
+        if B > nmax:
+            for b0 in range(0, B, nmax):
+                self.gemm_rows(X[b0:b0 + nmax], [y[b0:b0 + nmax] for y in ys])
+            return ys
+        if X.dim() != 2 or X.shape[1] != self.C or X.stride(1) != 1 or X.device != self.device or B < 1:
+            raise ValueError("X must be [B, C] with unit column stride on the matrices' device")
+        if len(ys) != len(self.mats) or len({y.dtype for y in ys}) != 1:
+            raise ValueError("one output per matrix, one dtype")
+        ldy = ys[0].stride(0) if B > 1 else max(m.R for m in self.mats)
+        for i, (y, R) in enumerate(zip(ys, self.Rs)):
+            if y.shape != (B, R) or y.stride(1) != 1 or (B > 1 and y.stride(0) != ldy):
+                raise ValueError("outputs must be [B, R_i] with unit column stride and a common row stride")
+            self._ys[i] = y.data_ptr()
+        key = _stream()
+        st = self._rows_stage.get(key)
+        if st is None:
+            st = self._rows_stage[key] = torch.empty(lib.cbl_gemm_stage_bytes(lib.cbl_gemm_rows_max_tokens(), self.C), dtype=torch.uint8,
+                                                     device=self.device)
+        ws = l8_workspace(self.device, 0, self.rows_ws_bytes)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemm_rows_multi", lib.cbl_gemm_rows_multi(self._structs, len(self.mats), X.data_ptr(), _dt(X.dtype), B, X.stride(0),
+                                                                      self._ys, _dt(ys[0].dtype), ldy, st.data_ptr(), ws.data_ptr(), _stream()))
+        return ys
 
     def run(self, x: torch.Tensor, ys: list[torch.Tensor]) -> list[torch.Tensor]:
         x = x.reshape(-1)

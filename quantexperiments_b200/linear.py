@@ -27,6 +27,10 @@ L8_MIN_ROWS = 2048
 # GEMM). Measured on B200 it beats the kernel that decodes weight tiles on the fly at every token count above the
 # small-batch kernel's 64 (12.1 vs 20.6 ms for the 196 Qwen2.5-7B matrices at 128 tokens, 30 vs 36 ms at 2048).
 DENSE_MIN_TOKENS = 65
+# tokens from which (up to 64) matrices with one column order run on the tensor-core kernel that takes the weight
+# rows as the M side (its cost does not grow with the token count; the mma.sync kernel wins below: 18944 x 3584 pair
+# 66 us at any count against 49 / 63 / 132 us at 8 / 16 / 32 tokens)
+ROWS_MIN_TOKENS = 16
 
 
 def _is_capturing() -> bool:
@@ -76,6 +80,13 @@ class PackedLinear(torch.nn.Module):
             self._l8 = L8Matrix(self.dm)
         return self._l8
 
+    @property
+    def rows_group(self):
+        if getattr(self, "_rows_group", None) is None:
+            from .kernels import L8Group
+            self._rows_group = L8Group([self.l8])
+        return self._rows_group
+
     def use_l8(self) -> bool:
         return self.dm.M == 1 and self.R >= L8_MIN_ROWS
 
@@ -103,8 +114,10 @@ class PackedLinear(torch.nn.Module):
             return y
         if n == 1 and self.use_l8() and y.is_contiguous():
             self.l8.run(x2[0].contiguous(), y[0])
-        elif n <= T16Matrix.BMAX:
+        elif n <= T16Matrix.BMAX and (n < ROWS_MIN_TOKENS or self.dm.M > 1):
             self.t16.run(x2.contiguous(), y, n)
+        elif n <= T16Matrix.BMAX:
+            self.rows_group.gemm_rows(x2 if x2.stride(1) == 1 else x2.contiguous(), [y])
         elif self.use_gemm() and n < DENSE_MIN_TOKENS:
             self.l8.gemm(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
         else:

@@ -17,7 +17,7 @@ import re
 import torch
 
 from ..kernels import DenseStack, L8Group, T16Matrix
-from ..linear import DENSE_MIN_TOKENS, L8_MIN_ROWS, PackedLinear
+from ..linear import DENSE_MIN_TOKENS, L8_MIN_ROWS, ROWS_MIN_TOKENS, PackedLinear
 
 BMAX = T16Matrix.BMAX
 
@@ -67,9 +67,12 @@ class PackedShards:
                 lin.t16.xp_buffer(b)
         self.stack = DenseStack([lin.dm for lin in lins])     # many tokens / several column orders: decode once, one GEMM
         # one token: all pieces in one launch when they share a column order and the stack is tall enough
-        self.group = None
-        if all(lin.dm.M == 1 for lin in lins) and self.R >= L8_MIN_ROWS and len(lins) <= L8Group.MAX:
-            self.group = L8Group([lin.l8 for lin in lins])
+        self.group = self.rows = None
+        if all(lin.dm.M == 1 for lin in lins) and len(lins) <= L8Group.MAX:
+            if self.R >= L8_MIN_ROWS:
+                self.group = L8Group([lin.l8 for lin in lins])
+            if len({lin.dm.books for lin in lins}) == 1:
+                self.rows = self.group if self.group is not None else L8Group([lin.l8 for lin in lins])
 
     @classmethod
     def from_packed(cls, pf, names: list[str], dev="cuda", **kw) -> "PackedShards":
@@ -106,6 +109,9 @@ class PackedShards:
         y = torch.empty(M, self.R, dtype=x.dtype, device=x.device)
         if M == 1 and self.group is not None:
             self.group.run(x[0], [y[0, off:off + R] for off, R in zip(self.offs, self.Rs)])
+            return y
+        if M >= ROWS_MIN_TOKENS and self.rows is not None:
+            self.rows.gemm_rows(x, [y[:, off:off + R] for off, R in zip(self.offs, self.Rs)])
             return y
         for lin, off, R in zip(self.lins, self.offs, self.Rs):
             if M == 1 and lin.use_l8():

@@ -391,6 +391,16 @@ def test_engine_graph_replay_prefill_and_batched_engine_agree():
     for b in range(B):
         assert (beng.logits[b] - eng.logits[0]).abs().max() / eng.logits[0].abs().max() <= 2e-2
     assert beng.pos.tolist() == [12] * B
+    # twenty sequences: the products run on the tensor-core kernel with the weight rows as the M side
+    b20 = Qwen2BatchEngine(eng, 20)
+    assert b20.stages[0]["qkv"].rows is not None
+    b20.reset(prompt[0])
+    for t in prompt[:12]:
+        b20.tok.fill_(t)
+        b20.step()
+    for b in (0, 7, 19):
+        assert (b20.logits[b] - eng.logits[0]).abs().max() / eng.logits[0].abs().max() <= 2e-2
+    b20.check()
     # sequences at different positions: prefill two prompts of different lengths, then step both
     beng.reset(0)
     beng.prefill(prompt[:40], 0)

@@ -547,3 +547,53 @@ def test_two_phase_prefill_rejects_unsupported_arguments():
     assert _lib.lib.cbl_gemm_dense(t.data_ptr(), 64, 60, t.data_ptr(), t.data_ptr(), 1, 4, 64, t.data_ptr(), 1, 64, t.data_ptr(), t.data_ptr(), s) == _lib.EINVAL
     assert _lib.lib.cbl_gemm_dense(t.data_ptr(), 64, 64, t.data_ptr(), t.data_ptr(), 1, 4, 64, t.data_ptr(), 1, 32, t.data_ptr(), t.data_ptr(), s) == _lib.EINVAL
     assert _lib.lib.cbl_dense_scratch_bytes(3, 12) == 3 * 16 * 2
+
+
+# ------------------------------------------------------------------------------------------ a few dozen tokens, weight rows as M
+@pytest.mark.parametrize("Rs,C,B,books", [((300,), 264, 5, 1), ((1000, 129), 520, 32, 1), ((260, 130, 130), 1032, 17, 2),
+                                         ((3584, 512, 512), 3584, 32, 1), ((130,), 64, 1, 1), ((520, 520), 4104, 40, 1)])
+def test_rows_as_m_product_matches_fp32_matmul(Rs, C, B, books):
+    """cbl_gemm_rows_multi: grouped matrices, k-split launches (few row tiles) and whole-k launches, one and two
+    books, ragged row counts, more than 32 tokens as several launches; outputs are column slices of one buffer."""
+    from quantexperiments_b200.kernels import L8Group, L8Matrix
+    ms = [orc.synth_matrix(R, C, seed=R + C + B + i, books=books) for i, R in enumerate(Rs)]
+    l8s = [L8Matrix(_dm(m)) for m in ms]
+    w = torch.cat([torch.from_numpy(orc.synth_decode(m)) for m in ms]).cuda()
+    g = torch.Generator(device="cuda").manual_seed(B)
+    X = torch.randn(B, C, device="cuda", generator=g)
+    X[0, 3] = 2.0e4
+    X = X.bfloat16()
+    ref = X.float() @ w.t()
+    grp = L8Group(l8s)
+    for ydt in (torch.float32, torch.bfloat16, torch.float16):
+        Y = torch.full((B, sum(Rs) + 8), 3.0, device="cuda", dtype=ydt)
+        ys, o = [], 0
+        for R in Rs:
+            ys.append(Y[:, o:o + R])
+            o += R
+        for _ in range(2):              # the work space is left zero: a second call gives the same result
+            grp.gemm_rows(X, ys)
+            got = Y[:, :sum(Rs)].float()
+            for t in range(B):
+                assert (got[t] - ref[t]).abs().max() / ref[t].abs().max() <= _out_tol(ydt), (ydt, t)
+            assert (Y[:, sum(Rs):] == 3.0).all()
+    l8s[0].status()
+
+
+def test_rows_as_m_product_rejects_unsupported_arguments():
+    from quantexperiments_b200 import _lib
+    from quantexperiments_b200.kernels import L8Matrix
+    import ctypes
+    l8 = L8Matrix(_dm(orc.synth_matrix(64, 64, seed=2)))
+    st = (_lib.L8 * 1)(l8.struct())
+    t = torch.zeros(1 << 16, device="cuda", dtype=torch.float16)
+    ys = (ctypes.c_void_p * 1)(t.data_ptr())
+    s = torch.cuda.current_stream().cuda_stream
+    call = lambda n, ntok, ldy: _lib.lib.cbl_gemm_rows_multi(st, n, t.data_ptr(), 1, ntok, 64, ys, 1, ldy, t.data_ptr(), t.data_ptr(), s)   # noqa: E731
+    assert call(1, 33, 64) == _lib.EUNSUPPORTED
+    assert call(5, 4, 64) == _lib.EUNSUPPORTED
+    assert call(1, 0, 64) == _lib.EINVAL
+    assert call(1, 4, 32) == _lib.EINVAL
+    assert _lib.lib.cbl_gemm_rows_max_tokens() == 32
+    assert _lib.lib.cbl_gemm_rows_workspace_bytes(128) == 32 * 128 * 4 + 16
+
