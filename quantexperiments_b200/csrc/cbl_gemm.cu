@@ -15,6 +15,16 @@
 #include <cuda.h>
 #include "cbl_common.cuh"
 
+#ifdef CBL_TRACE
+// Debug builds only: per-block phase timestamps (ns) for offline inspection.
+__device__ unsigned long long g_cbl_trace_gemm[1024 * 16];
+__device__ __forceinline__ unsigned long long cbl_now_gemm() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define CBL_GMARK(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024 && blockIdx.y == 0) g_cbl_trace_gemm[blockIdx.x * 16 + (i)] = cbl_now_gemm(); } while (0)
+extern "C" int cbl_trace_read_gemm(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_cbl_trace_gemm, sizeof(g_cbl_trace_gemm)); }
+#else
+#define CBL_GMARK(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int GM_BM = 256;                 // tokens per tile (2 accumulators of 128)
@@ -697,6 +707,223 @@ k_gemm_rows(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ GR
     }
 }
 
+// Variant with the decoded A tile in TENSOR memory: a decode thread writes its row's codewords straight from
+// registers into its TMEM lane (tcgen05.st) and the MMA takes A from TMEM, so neither the store of the A tile nor
+// the tensor cores' read of it touch shared memory - only the codeword gathers do.  TMEM columns: 0..31 the
+// accumulator, then GT_STAGES stages of 4 k-blocks x 32 columns (a k-block = 64 fp16 per row = 32 columns).
+// What bounds it now is the tensor pipe itself: an MMA of 128 rows x 16 k takes about 170 cycles however few the
+// tokens (independent accumulators and a software-pipelined decode loop changed nothing), i.e. 1.4 us per stage.
+constexpr int GT_STAGES = 3;
+constexpr int GT_A_COL0 = 32, GT_A_STAGE_COLS = GR_KBS * 32;
+constexpr int GT_SMEM = 65536 + GT_STAGES * GR_X_STAGE;
+
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&c)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(c[0].x), "r"(c[0].y), "r"(c[0].z), "r"(c[0].w), "r"(c[1].x), "r"(c[1].y), "r"(c[1].z), "r"(c[1].w), "r"(c[2].x),
+          "r"(c[2].y), "r"(c[2].z), "r"(c[2].w), "r"(c[3].x), "r"(c[3].y), "r"(c[3].z), "r"(c[3].w), "r"(c[4].x), "r"(c[4].y), "r"(c[4].z),
+          "r"(c[4].w), "r"(c[5].x), "r"(c[5].y), "r"(c[5].z), "r"(c[5].w), "r"(c[6].x), "r"(c[6].y), "r"(c[6].z), "r"(c[6].w), "r"(c[7].x),
+          "r"(c[7].y), "r"(c[7].z), "r"(c[7].w)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(GR_THREADS, 1)
+k_gemm_rows_ta(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ GRLaunch P, const float* __restrict__ xinv, int ntok, int ydtype,
+            int64_t ldy, unsigned int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_bar[3 * GT_STAGES + 1];    // full_a, full_x, empty per stage; tmem_full
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    CBL_GMARK(0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int mi = 0;
+    while (mi + 1 < P.n && (int)blockIdx.x >= P.tile0[mi + 1]) mi++;
+    const cbl_l8& m = P.m[mi];
+    const int r0 = ((int)blockIdx.x - P.tile0[mi]) * GR_ROWS;
+    const int nkb = m.ntile, nkb1 = m.ntile / m.books;
+    // this block's k-blocks: part blockIdx.y of ksplit equal parts
+    const int kb_lo = (int)(((int64_t)nkb * blockIdx.y) / P.ksplit), kb_hi = (int)(((int64_t)nkb * (blockIdx.y + 1)) / P.ksplit);
+    const uint32_t sbase = cbl_smem_u32(smem), bar0 = cbl_smem_u32(s_bar);
+    auto full_a = [&](int s) { return bar0 + 8u * s; };
+    auto full_x = [&](int s) { return bar0 + 8u * (GT_STAGES + s); };
+    auto empty = [&](int s) { return bar0 + 8u * (2 * GT_STAGES + s); };
+    const uint32_t tmem_full = bar0 + 8u * (3 * GT_STAGES);
+    const uint32_t x_base = sbase + 65536;
+    // stages never straddle the two books: segment 0 = this part's k-blocks of the first book, segment 1 = of the second
+    const int seg_lo[2] = {kb_lo < nkb1 ? kb_lo : nkb1, kb_lo > nkb1 ? kb_lo : nkb1};
+    const int seg_hi[2] = {kb_hi < nkb1 ? kb_hi : nkb1, kb_hi > nkb1 ? kb_hi : nkb1};
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < GT_STAGES; s++) { mbar_init(full_a(s), GR_DECODE_WARPS); mbar_init(full_x(s), 1); mbar_init(empty(s), 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == GR_DECODE_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbl_smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp < GR_DECODE_WARPS) {                              // the book of the first segment that has work
+        const uint4* t0 = (const uint4*)((seg_lo[0] < seg_hi[0]) ? m.table : m.table2);
+        uint4* dst = (uint4*)smem;
+        for (int i = tid; i < 4096; i += GR_DECODE_WARPS * 32) dst[i] = __ldg(t0 + i);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    CBL_GMARK(1);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    CBL_GMARK(2);          // the staged activations (and zeroed sums) come from earlier kernels
+    // A wait that expires marks the block aborted; every thread then keeps the shape of its loops (the decode
+    // warps meet at a named barrier when the book changes) but waits for nothing more.
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        if (*(volatile int*)&s_abort) return;
+        if (!mbar_wait(bar, parity)) s_abort = 1;
+    };
+
+    if (warp == GR_DECODE_WARPS) {
+        if (lane == 0) {                                      // TMA producer of the activations
+            int it = 0;
+            for (int sg = 0; sg < 2; sg++) {
+                for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                    const int s = it % GT_STAGES, nv = min(GR_KBS, seg_hi[sg] - kb);
+                    wait(empty(s), ((it / GT_STAGES) & 1) ^ 1);
+                    if (*(volatile int*)&s_abort) break;              // no copies after an abort: nothing would wait for them
+                    mbar_expect_tx(full_x(s), (uint32_t)nv * (uint32_t)P.npad * 128u);
+                    for (int j = 0; j < nv; j++)
+                        tma_load_2d(x_base + s * GR_X_STAGE + j * GR_X_KB, &xmap, (kb + j - sg * nkb1) * GM_BK, 0, full_x(s));
+                }
+            }
+        }
+    } else if (warp == GR_DECODE_WARPS + 1) {
+        if (lane == 0) {                                      // MMA issuer
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(P.npad >> 3) << 17) | ((uint32_t)(GR_ROWS >> 4) << 24);
+            int it = 0;
+            uint32_t accumulate = 0;
+            for (int sg = 0; sg < 2; sg++) {
+                for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                    const int s = it % GT_STAGES, nv = min(GR_KBS, seg_hi[sg] - kb);
+                    const uint32_t par = (it / GT_STAGES) & 1;
+                    wait(full_x(s), par);
+                    wait(full_a(s), par);
+                    if (*(volatile int*)&s_abort) break;              // no MMAs on tiles that never arrived
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int j = 0; j < nv; j++) {
+#pragma unroll
+                        for (int kk = 0; kk < GM_BK / 16; kk++) {
+                            umma_f16_ta(tmem, tmem + GT_A_COL0 + s * GT_A_STAGE_COLS + j * 32 + kk * 8,
+                                        umma_desc_sw128(x_base + s * GR_X_STAGE + j * GR_X_KB + kk * 32), idesc, accumulate);
+                            accumulate = 1;
+                        }
+                    }
+                    umma_commit(empty(s));
+                }
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        // ---------------- decode: thread = (W row r0 + (tid & 127), k-block tid >> 7 of the stage)
+        const int rl = tid & 127, kbs = tid >> 7, row = r0 + rl;
+        const bool live = row < m.Rpad;
+        const uint32_t* wp = (const uint32_t*)m.words + row;
+        int it = 0;
+        for (int sg = 0; sg < 2; sg++) {
+            if (seg_lo[sg] >= seg_hi[sg]) continue;
+            if (sg == 1 && seg_lo[0] < seg_hi[0]) {
+                // switch books: every decode thread is done with the first one (barrier among the decode warps only)
+                asm volatile("bar.sync 1, %0;" ::"n"(GR_DECODE_WARPS * 32) : "memory");
+                const uint4* t1 = (const uint4*)m.table2;
+                uint4* dst = (uint4*)smem;
+                for (int i = tid; i < 4096; i += GR_DECODE_WARPS * 32) dst[i] = __ldg(t1 + i);
+                asm volatile("bar.sync 1, %0;" ::"n"(GR_DECODE_WARPS * 32) : "memory");
+            }
+            uint32_t wa = 0, wb = 0, wc = 0, na = 0, nb = 0, nc = 0;
+            auto load_tags = [&](int kb, uint32_t& a, uint32_t& b, uint32_t& c) {
+                a = b = c = 0;
+                if (live && kb < seg_hi[sg]) {
+                    const uint32_t* p = wp + (int64_t)kb * 3 * m.Rpad;
+                    a = __ldg(p); b = __ldg(p + m.Rpad); c = __ldg(p + 2 * (int64_t)m.Rpad);
+                }
+            };
+            load_tags(seg_lo[sg] + kbs, wa, wb, wc);
+            for (int kb = seg_lo[sg]; kb < seg_hi[sg]; kb += GR_KBS, it++) {
+                const int s = it % GT_STAGES;
+                load_tags(kb + GR_KBS + kbs, na, nb, nc);
+                wait(empty(s), ((it / GT_STAGES) & 1) ^ 1);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");      // the MMAs that read this TMEM stage are complete
+                if (kb + kbs < seg_hi[sg]) {
+                    uint32_t off[8];
+                    off[0] = (wa << 4) & 0xFFF0u;
+                    off[1] = (wa >> 8) & 0xFFF0u;
+                    off[2] = __funnelshift_r(wa, wb, 20) & 0xFFF0u;
+                    off[3] = wb & 0xFFF0u;
+                    off[4] = (wb >> 12) & 0xFFF0u;
+                    off[5] = __funnelshift_r(wb, wc, 24) & 0xFFF0u;
+                    off[6] = (wc >> 4) & 0xFFF0u;
+                    off[7] = (wc >> 16) & 0xFFF0u;
+                    uint4 cw[8];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) cw[c] = cbl_lds128(sbase + off[c]);
+                    // the row's 64 values of this k-block = 32 consecutive 32-bit columns of its TMEM lane
+                    tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(GT_A_COL0 + s * GT_A_STAGE_COLS + kbs * 32), cw);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
+                if (it < 8) CBL_GMARK(3 + it);
+                wa = na; wb = nb; wc = nc;
+            }
+        }
+        // ---------------- epilogue: decode warps 0..3 read TMEM lanes (= W rows) 32 w ..; columns = tokens
+        CBL_GMARK(11);
+        if (warp < 4) {
+            wait(tmem_full, 0);
+            CBL_GMARK(12);
+            const bool ok = *(volatile int*)&s_abort == 0;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int r = r0 + warp * 32 + lane;
+            if (ok) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < m.R) {
+                    if (P.ksplit == 1) {
+                        const float rs = __half2float(__ldg((const __half*)m.row_scale + r));
+#pragma unroll 4
+                        for (int n = 0; n < GR_NMAX; n++)
+                            if (n < ntok) cbl_store_out(P.y[mi], ydtype, (int64_t)n * ldy + r, __uint_as_float(v[n]) * xinv[n] * rs);
+                    } else {
+                        float* acc = P.acc[mi] + r;
+#pragma unroll 4
+                        for (int n = 0; n < GR_NMAX; n++)
+                            if (n < ntok) atomicAdd(acc + (int64_t)n * m.Rpad, __uint_as_float(v[n]));
+                    }
+                }
+            }
+        }
+    }
+    CBL_GMARK(13);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    CBL_GMARK(14);
+    if (s_abort && tid == 0) atomicExch(status, 1u);
+    if (warp == GR_DECODE_WARPS) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // k-split launches: y[n][r] = round(sum * token scale * row scale); the sums are left zero.  blockIdx.y = token,
 // blockIdx.z = matrix of the group.
 __global__ void __launch_bounds__(256) k_rows_finish(const __grid_constant__ GRLaunch P, const float* __restrict__ xinv, int ydtype, int64_t ldy) {
@@ -1304,8 +1531,11 @@ extern "C" int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x,
     CBL_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         CBL_CUDA(cudaFuncSetAttribute(k_gemm_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, GR_SMEM));
+        CBL_CUDA(cudaFuncSetAttribute(k_gemm_rows_ta, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM));
         attr_set[dev] = true;
     }
+    static int ta = -1;                                        // CBL_ROWS_SMEM_A=1: the A tile through shared memory (comparisons)
+    if (ta < 0) { const char* e = getenv("CBL_ROWS_SMEM_A"); ta = (e && atoi(e) == 1) ? 0 : 1; }
     const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1316,8 +1546,9 @@ extern "C" int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x,
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(tiles, ksplit);
     cfg.blockDim = dim3(GR_THREADS);
-    cfg.dynamicSmemBytes = GR_SMEM;
-    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_rows, xmap, P, xinv, (int)ntok, ydtype, ldy, status));
+    cfg.dynamicSmemBytes = ta ? GT_SMEM : GR_SMEM;
+    if (ta) CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_rows_ta, xmap, P, xinv, (int)ntok, ydtype, ldy, status));
+    else CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_rows, xmap, P, xinv, (int)ntok, ydtype, ldy, status));
     if (ksplit > 1) {
         int maxR = 0;
         for (int i = 0; i < P.n; i++) maxR = maxR > P.m[i].R ? maxR : P.m[i].R;

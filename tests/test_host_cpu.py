@@ -96,3 +96,23 @@ def test_device_matrix_refuses_cpu():
     from quantexperiments_b200.kernels import DeviceMatrix
     with pytest.raises(ValueError):
         DeviceMatrix(torch.zeros(2, 3, dtype=torch.int32), torch.zeros(4096, 8), torch.ones(2), K=4096, d=8, device="cpu")
+
+
+def test_engine_sampling_helper_and_config_defaults():
+    """Host logic of the decode engine that needs no GPU: the config defaults are the Qwen2.5-7B shape of the
+    reference's Cfg (shapequant/kernels/decode_e2e.py:313-327) and the sampler keeps the reference's top-k / top-p
+    rules (shapequant/runtime.py:202-214)."""
+    import torch
+    from quantexperiments_b200.engine import Cfg, _sample
+    c = Cfg()
+    assert (c.hidden, c.n_heads, c.n_kv, c.head_dim, c.inter, c.vocab, c.layers) == (3584, 28, 4, 128, 18944, 152064, 28)
+    logits = torch.tensor([0.1, 2.0, -1.0, 1.9, 0.0])
+    g = torch.Generator().manual_seed(0)
+    assert _sample(logits, 1.0, 1.0, 1, g) == 1                     # top-k 1 = argmax
+    assert _sample(logits, 1e-4, 1.0, 0, g) == 1                    # vanishing temperature = argmax
+    assert _sample(logits, 1.0, 0.01, 0, g) == 1                    # a tiny nucleus keeps only the best token
+    picks = {_sample(logits, 1.0, 1.0, 2, g) for _ in range(64)}
+    assert picks == {1, 3}                                          # top-k 2: only the two best are ever drawn
+    a = [_sample(logits, 1.0, 0.9, 0, torch.Generator().manual_seed(5)) for _ in range(3)]
+    b = [_sample(logits, 1.0, 0.9, 0, torch.Generator().manual_seed(5)) for _ in range(3)]
+    assert a == b                                                   # seeded draws repeat
