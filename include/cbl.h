@@ -270,11 +270,12 @@ int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* bias, const 
 
 /* Grouped-query attention of one new token per sequence over cache positions 0..pos[b] (the step's own
  * key / value already written by cbl_rope_kv).  q, out: [B, NH * HD]; caches [B][NKV][max_len][HD]; HD = 128,
- * NH / NKV <= 8.  The positions of a sequence are cut into `nsplit` slices (1..cbl_attn_decode_max_splits())
- * that run in parallel, four warps per slice; `workspace` holds their partial results
- * (cbl_attn_decode_workspace_bytes bytes; no initial contents required). */
+ * NH / NKV <= 8.  The positions of a sequence are cut into `nsplit` slices that run in parallel
+ * (nsplit >= cbl_attn_decode_min_splits(max_len)); `workspace` holds the slices' partial results
+ * (cbl_attn_decode_workspace_bytes, zero before the first call; its last word is a status word that
+ * becomes nonzero if a slice exceeded the kernel's capacity). */
 size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit);
-int32_t cbl_attn_decode_max_splits(void);
+int32_t cbl_attn_decode_min_splits(int32_t max_len);
 int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
                     int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s);
 

@@ -148,14 +148,12 @@ __global__ void __launch_bounds__(128) k_rope_kv(const T* __restrict__ qkv, int6
 }
 
 // ---------------------------------------------------------------------------------------- decode attention
-// One block per (position slice, kv head, sequence); its four warps walk the slice independently, 32 positions
-// at a time (chunks interleaved over the warps), with an online softmax per warp: there is no block-wide
-// barrier after the queries are staged.  Scores: one lane per position, the whole K row with 16-byte loads
-// (read once for all REP query heads of the group), q broadcast from shared memory.  Values: the chunk's
-// probabilities go through a 1 KB per-warp shared-memory tile; a lane owns 4 of the 128 output dimensions, so a
-// warp-wide 8-byte load is one V row.  Every warp writes its running max, denominator and un-normalised output
-// per head; k_attn_merge combines the 4 * nsplit partial results.
-constexpr int ATT_WARPS = 4, ATT_THREADS = ATT_WARPS * 32;
+// One block per (position slice, kv head, sequence): the slice's K rows are read once for all REP query
+// heads of the group.  Scores: one thread per position, the whole K row with 16-byte loads, q broadcast from
+// shared memory.  Values: 16 threads per V row (8 dims each), 8 rows in flight per pass.  The block writes
+// the slice's running max, denominator and un-normalised output per head; k_attn_merge combines slices.
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_MAX_SLICE = 1024;        // positions per block (scores live in shared memory)
 constexpr int ATT_HD = 128;
 
 __host__ __device__ inline void att_slice(int L, int nsplit, int split, int& s0, int& s1) {
@@ -165,124 +163,131 @@ __host__ __device__ inline void att_slice(int L, int nsplit, int split, int& s0,
     s1 = s0 + per < L ? s0 + per : L;
 }
 
-template <typename T> __device__ __forceinline__ void unpack4(const uint2& w, float (&f)[4]);
-template <> __device__ __forceinline__ void unpack4<__half>(const uint2& w, float (&f)[4]) {
-    const float2 a = __half22float2(*(const __half2*)&w.x), c = __half22float2(*(const __half2*)&w.y);
-    f[0] = a.x; f[1] = a.y; f[2] = c.x; f[3] = c.y;
-}
-template <> __device__ __forceinline__ void unpack4<__nv_bfloat16>(const uint2& w, float (&f)[4]) {
-    f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
-    f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
-}
-
 template <typename T, int REP>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
                                                             const int32_t* __restrict__ pos, int NKV, int max_len, float scale,
-                                                            float* __restrict__ part) {
+                                                            float* __restrict__ part, unsigned int* __restrict__ status) {
     pdl_enter();
     constexpr int HD = ATT_HD;
     __shared__ __align__(16) float s_q[REP][HD];
-    __shared__ __align__(16) float s_p[ATT_WARPS][32][8];            // a chunk's probabilities, [position][head]
+    __shared__ __align__(16) float s_p[ATT_MAX_SLICE][8];            // scores, then probabilities, [position][head]
+    __shared__ float s_red[4][8];
+    __shared__ float s_m[8], s_l[8];
     const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x, tid = threadIdx.x;
-    const int lane = tid & 31, warp = tid >> 5;
     const int NH = NKV * REP;
     const int L = pos[b] + 1;                                        // positions 0..pos[b] are in the cache (the step's own included)
     int s0, s1;
     att_slice(L, nsplit, split, s0, s1);
-    // partial results of this warp: per head [HD sums | max | denominator]
-    const int nparts = nsplit * ATT_WARPS;
-    float* pout = part + (((int64_t)b * NH + kv * REP) * nparts + split * ATT_WARPS + warp) * (HD + 2);
-    const int64_t hstride = (int64_t)nparts * (HD + 2);
-    if (s0 + 32 * warp >= s1) {                                      // nothing for this warp (block-uniform when the slice is empty)
-        if (lane < REP) { pout[lane * hstride + HD] = -3.0e38f; pout[lane * hstride + HD + 1] = 0.f; }
-        if (s0 >= s1) return;
+    float* pout = part + (((int64_t)b * NH + kv * REP) * nsplit + split) * (HD + 2);   // per head: stride nsplit * (HD + 2)
+    const int64_t hstride = (int64_t)nsplit * (HD + 2);
+    if (s1 - s0 > ATT_MAX_SLICE) {
+        if (tid == 0) atomicExch(status, 2u);                        // the caller gave too few slices for this length
+        s1 = s0;
+    }
+    if (s0 >= s1) {
+        if (tid < REP) { pout[tid * hstride + HD] = -3.0e38f; pout[tid * hstride + HD + 1] = 0.f; }
+        return;
     }
     for (int i = tid; i < REP * HD; i += ATT_THREADS) s_q[i / HD][i % HD] = to_f(q[((int64_t)b * NH + kv * REP) * HD + i]) * scale;
     __syncthreads();
-    if (s0 + 32 * warp >= s1) return;
     const T* kbase = kc + ((int64_t)b * NKV + kv) * max_len * HD;
-    const T* vbase = vc + ((int64_t)b * NKV + kv) * max_len * HD + 4 * lane;
-    float m[REP], l[REP], acc[REP][4];
+    const T* vbase = vc + ((int64_t)b * NKV + kv) * max_len * HD;
+    float mx[REP];
 #pragma unroll
-    for (int h = 0; h < REP; h++) {
-        m[h] = -3.0e38f;
-        l[h] = 0.f;
+    for (int h = 0; h < REP; h++) mx[h] = -3.0e38f;
+    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
+        const uint4* kr = (const uint4*)(kbase + (int64_t)t * HD);
+        uint4 w[HD / 8];
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[h][j] = 0.f;
-    }
-    for (int base = s0 + 32 * warp; base < s1; base += 32 * ATT_WARPS) {
-        const int t = base + lane, n = min(32, s1 - base);
-        // the first V rows of the chunk are requested before the scores are computed
-        constexpr int VU = 8;
-        uint2 vw[VU];
-#pragma unroll
-        for (int u = 0; u < VU; u++) vw[u] = u < n ? __ldg((const uint2*)(vbase + (int64_t)(base + u) * HD)) : make_uint2(0, 0);
+        for (int c = 0; c < HD / 8; c++) w[c] = __ldg(kr + c);           // L1-allocating: a thread uses both halves of each sector
         float d[REP];
 #pragma unroll
-        for (int h = 0; h < REP; h++) d[h] = -3.0e38f;
-        if (t < s1) {
-            const uint4* kr = (const uint4*)(kbase + (int64_t)t * HD);
-            uint4 w[HD / 8];
+        for (int h = 0; h < REP; h++) d[h] = 0.f;
 #pragma unroll
-            for (int c = 0; c < HD / 8; c++) w[c] = __ldg(kr + c);       // L1-allocating: a lane uses both halves of each sector
+        for (int c = 0; c < HD / 8; c++) {
+            float f[8];
+            unpack8<T>(w[c], f);
 #pragma unroll
-            for (int h = 0; h < REP; h++) d[h] = 0.f;
-#pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
-                float f[8];
-                unpack8<T>(w[c], f);
-#pragma unroll
-                for (int h = 0; h < REP; h++) {
-                    const float4 qa = *(const float4*)&s_q[h][c * 8], qb = *(const float4*)&s_q[h][c * 8 + 4];
-                    d[h] += f[0] * qa.x + f[1] * qa.y + f[2] * qa.z + f[3] * qa.w + f[4] * qb.x + f[5] * qb.y + f[6] * qb.z + f[7] * qb.w;
-                }
+            for (int h = 0; h < REP; h++) {
+                const float4 qa = *(const float4*)&s_q[h][c * 8], qb = *(const float4*)&s_q[h][c * 8 + 4];
+                d[h] += f[0] * qa.x + f[1] * qa.y + f[2] * qa.z + f[3] * qa.w + f[4] * qb.x + f[5] * qb.y + f[6] * qb.z + f[7] * qb.w;
             }
         }
-        // online softmax: new running max per head, rescale what has been accumulated, this chunk's probabilities
-        float pr[8];
 #pragma unroll
-        for (int h = 0; h < 8; h++) pr[h] = 0.f;
-#pragma unroll
-        for (int h = 0; h < REP; h++) {
-            const float mn = fmaxf(m[h], warp_max(d[h]));
-            const float sc = __expf(m[h] - mn);
-            m[h] = mn;
-            pr[h] = t < s1 ? __expf(d[h] - mn) : 0.f;
-            l[h] = l[h] * sc + pr[h];                                  // per-lane share of the denominator, summed at the end
-#pragma unroll
-            for (int j = 0; j < 4; j++) acc[h][j] *= sc;
-        }
-        __syncwarp();                                                  // the previous chunk's tile has been read by every lane
-        *(float4*)&s_p[warp][lane][0] = make_float4(pr[0], pr[1], pr[2], pr[3]);
-        *(float4*)&s_p[warp][lane][4] = make_float4(pr[4], pr[5], pr[6], pr[7]);
-        __syncwarp();
-        for (int i0 = 0; i0 < n; i0 += VU) {
-            uint2 vn[VU];
-#pragma unroll
-            for (int u = 0; u < VU; u++) vn[u] = (i0 + VU + u) < n ? __ldg((const uint2*)(vbase + (int64_t)(base + i0 + VU + u) * HD)) : make_uint2(0, 0);
-#pragma unroll
-            for (int u = 0; u < VU; u++) {
-                if (i0 + u < n) {
-                    float f[4];
-                    unpack4<T>(vw[u], f);
-                    const float4 pa = *(const float4*)&s_p[warp][i0 + u][0], pb = *(const float4*)&s_p[warp][i0 + u][4];
-                    const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-#pragma unroll
-                    for (int h = 0; h < REP; h++)
-#pragma unroll
-                        for (int j = 0; j < 4; j++) acc[h][j] += pv[h] * f[j];
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < VU; u++) vw[u] = vn[u];
-        }
+        for (int h = 0; h < REP; h++) { s_p[t - s0][h] = d[h]; mx[h] = fmaxf(mx[h], d[h]); }
     }
+    // slice max per head
 #pragma unroll
     for (int h = 0; h < REP; h++) {
-        const float ls = warp_sum(l[h]);
-        *(float4*)(pout + h * hstride + 4 * lane) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
-        if (lane == 0) { pout[h * hstride + HD] = m[h]; pout[h * hstride + HD + 1] = ls; }
+        const float v = warp_max(mx[h]);
+        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
     }
+    __syncthreads();
+    if (tid < REP) s_m[tid] = fmaxf(fmaxf(s_red[0][tid], s_red[1][tid]), fmaxf(s_red[2][tid], s_red[3][tid]));
+    __syncthreads();
+    float sum[REP];
+#pragma unroll
+    for (int h = 0; h < REP; h++) sum[h] = 0.f;
+    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
+#pragma unroll
+        for (int h = 0; h < REP; h++) {
+            const float e = __expf(s_p[t - s0][h] - s_m[h]);
+            s_p[t - s0][h] = e;
+            sum[h] += e;
+        }
+    }
+    __syncthreads();                                                 // s_red is reused
+#pragma unroll
+    for (int h = 0; h < REP; h++) {
+        const float v = warp_sum(sum[h]);
+        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
+    }
+    __syncthreads();
+    if (tid < REP) s_l[tid] = s_red[0][tid] + s_red[1][tid] + s_red[2][tid] + s_red[3][tid];
+    // values: thread = (row group rg of 8, dim block db of 16)
+    const int rg = tid >> 4, db = tid & 15;
+    float acc[REP][8];
+#pragma unroll
+    for (int h = 0; h < REP; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
+    constexpr int VU = 8;                                            // V rows in flight per thread
+    for (int t0 = s0; t0 < s1; t0 += 8 * VU) {
+        uint4 w[VU];
+#pragma unroll
+        for (int u = 0; u < VU; u++) {
+            const int t = t0 + u * 8 + rg;
+            w[u] = t < s1 ? cbl_ldg_stream((const uint4*)(vbase + (int64_t)t * HD) + db) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < VU; u++) {
+            const int t = t0 + u * 8 + rg;
+            if (t < s1) {
+                float f[8];
+                unpack8<T>(w[u], f);
+                const float4 pa = *(const float4*)&s_p[t - s0][0], pb = *(const float4*)&s_p[t - s0][4];
+                const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                for (int h = 0; h < REP; h++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[h][j] += pv[h] * f[j];
+            }
+        }
+    }
+    __syncthreads();                                                 // every thread is done with s_p: reuse it for the reduction
+    float* s_acc = &s_p[0][0];                                       // [8 row groups][REP][HD]
+#pragma unroll
+    for (int h = 0; h < REP; h++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) s_acc[(rg * REP + h) * HD + db * 8 + j] = acc[h][j];
+    __syncthreads();
+    for (int i = tid; i < REP * HD; i += ATT_THREADS) {
+        float v = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; g++) v += s_acc[g * REP * HD + i];
+        pout[(i / HD) * hstride + (i % HD)] = v;
+    }
+    if (tid < REP) { pout[tid * hstride + HD] = s_m[tid]; pout[tid * hstride + HD + 1] = s_l[tid]; }
 }
 
 // out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s.  One block per (head, sequence): the
@@ -317,7 +322,7 @@ __global__ void __launch_bounds__(ATT_HD) k_attn_merge(const float* __restrict__
     float num = 0.f;
 #pragma unroll 8
     for (int s = 0; s < nsplit; s++) {
-        if (s_w[s] != 0.f) num += s_w[s] * p[s * (HD + 2) + d];      // a part without positions wrote no sums
+        num += s_w[s] * p[s * (HD + 2) + d];          // an empty slice has weight 0 and finite (stale or zero) sums
     }
     out[((int64_t)b * NH + head) * HD + d] = cbl_cvt_out<T>(den > 0.f ? num / den : 0.f);
 }
@@ -493,28 +498,30 @@ extern "C" int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* b
 
 extern "C" size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit) {
     if (B < 0 || NH < 0 || nsplit < 1) return 0;
-    return (size_t)B * NH * nsplit * ATT_WARPS * (ATT_HD + 2) * 4 + 16;
+    return (size_t)B * NH * nsplit * (ATT_HD + 2) * 4 + 16;
 }
 
-extern "C" int32_t cbl_attn_decode_max_splits(void) { return ATT_MAX_SPLITS / ATT_WARPS; }
+extern "C" int32_t cbl_attn_decode_min_splits(int32_t max_len) { return max_len < 1 ? 1 : (max_len + ATT_MAX_SLICE - 1) / ATT_MAX_SLICE; }
 
 template <typename T, int REP>
 static int attn_launch(const void* q, const void* kc, const void* vc, const int32_t* pos, int B, int NKV, int max_len, float scale, void* out,
-                       float* part, int nsplit, cudaStream_t st) {
+                       float* part, unsigned int* status, int nsplit, cudaStream_t st) {
     int rc = step_launch(k_attn_slice<T, REP>, dim3(nsplit, NKV, B), dim3(ATT_THREADS), 0, st, (const T*)q, (const T*)kc, (const T*)vc, pos,
-                         NKV, max_len, scale, part);
+                         NKV, max_len, scale, part, status);
     if (rc != CBL_OK) return rc;
-    return step_launch(k_attn_merge<T>, dim3(NKV * REP, B), dim3(ATT_HD), 0, st, (const float*)part, nsplit * ATT_WARPS, (T*)out);
+    return step_launch(k_attn_merge<T>, dim3(NKV * REP, B), dim3(ATT_HD), 0, st, (const float*)part, nsplit, (T*)out);
 }
 
 extern "C" int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
                                int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s) {
     if (!q || !kc || !vc || !pos || !out || !workspace || !is16(dtype) || B < 0 || NH < 1 || NKV < 1 || nsplit < 1) return CBL_EINVAL;
-    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > ATT_MAX_SPLITS / ATT_WARPS) return CBL_EUNSUPPORTED;
+    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > ATT_MAX_SPLITS) return CBL_EUNSUPPORTED;
+    if (nsplit < cbl_attn_decode_min_splits(max_len)) return CBL_EINVAL;
     if (B == 0) return CBL_OK;
     float* part = (float*)workspace;
+    unsigned int* status = (unsigned int*)((char*)workspace + (size_t)B * NH * nsplit * (ATT_HD + 2) * 4);
     const cudaStream_t st = (cudaStream_t)s;
-#define CBL_ATT(R) case R: CBL_BY_TYPE(dtype, return (attn_launch<T, R>(q, kc, vc, pos, B, NKV, max_len, scale, out, part, nsplit, st)))
+#define CBL_ATT(R) case R: CBL_BY_TYPE(dtype, return (attn_launch<T, R>(q, kc, vc, pos, B, NKV, max_len, scale, out, part, status, nsplit, st)))
     switch (NH / NKV) {
         CBL_ATT(1);
         CBL_ATT(2);

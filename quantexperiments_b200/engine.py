@@ -146,10 +146,10 @@ class DecodeEngine:
         self.vc = torch.zeros_like(self.kc)
         self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
-        # attention slices: about four blocks (of four warps) per SM, at least 128 positions per slice at full length
+        # attention slices: about four blocks per SM, never fewer than the kernel's capacity needs
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         ns = attn_split if attn_split is not None else max(1, (4 * sms) // (NKV * B))
-        self.nsplit = max(1, min(ns, max(1, cfg.max_len // 128), lib.cbl_attn_decode_max_splits()))
+        self.nsplit = max(min(ns, max(1, cfg.max_len // 32), 512), lib.cbl_attn_decode_min_splits(cfg.max_len))
         self.att_ws = torch.zeros(lib.cbl_attn_decode_workspace_bytes(B, NH, self.nsplit), dtype=torch.uint8, device=dev)
         self.biases = []
         for L in layers:
@@ -329,9 +329,10 @@ class DecodeEngine:
         return self.graph
 
     def check(self) -> None:
-        """Synchronises; raises if a bounded device-side wait of a prompt product expired during the calls so far."""
+        """Synchronises; raises if an attention launch met a slice beyond the kernel's capacity."""
         torch.cuda.synchronize(self.dev)
-        DenseStack.status(self.dev)
+        if int(self.att_ws[-16:].view(torch.int32)[0]) != 0:
+            raise _lib.CblError("cbl_attn_decode", _lib.EINVAL, "a position slice exceeded the kernel's capacity")
 
     @torch.no_grad()
     def generate(self, n: int, tok=0) -> list:

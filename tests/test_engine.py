@@ -127,12 +127,13 @@ def test_decode_attention_matches_softmax_attention(dtype, NH, NKV, B, max_len, 
     vc = torch.randn(B, NKV, max_len, HD, device="cuda", generator=g).to(dtype)
     pos = torch.tensor(poss, dtype=torch.int32, device="cuda")
     out = torch.zeros(B, NH * HD, device="cuda", dtype=dtype)
-    ws = torch.full((L.lib.cbl_attn_decode_workspace_bytes(B, NH, nsplit),), 0xFF, dtype=torch.uint8, device="cuda")      # NaN patterns: nothing stale is read
-    assert nsplit <= L.lib.cbl_attn_decode_max_splits()
+    ws = torch.zeros(L.lib.cbl_attn_decode_workspace_bytes(B, NH, nsplit), dtype=torch.uint8, device="cuda")
+    assert nsplit >= L.lib.cbl_attn_decode_min_splits(max_len)
     for _ in range(2):          # the work space is reusable as it is left
         L.check("cbl_attn_decode", L.lib.cbl_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), _dt(dtype), B, NH, NKV, HD,
                                                          max_len, HD ** -0.5, out.data_ptr(), ws.data_ptr(), nsplit, _s()))
     torch.cuda.synchronize()
+    assert int(ws[-16:].view(torch.int32)[0]) == 0
     rep = NH // NKV
     for b in range(B):
         n = poss[b] + 1
@@ -144,12 +145,12 @@ def test_decode_attention_matches_softmax_attention(dtype, NH, NKV, B, max_len, 
         assert err <= (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4, (b, float(err))
 
 
-def test_decode_attention_rejects_too_many_slices_and_odd_shapes():
+def test_decode_attention_rejects_too_few_slices_and_odd_shapes():
     L = _lib()
     t = torch.zeros(16, device="cuda")
     args = lambda NH, NKV, HD, max_len, ns: (t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 2, 1, NH, NKV, HD, max_len, 1.0,  # noqa: E731
                                              t.data_ptr(), t.data_ptr(), ns, _s())
-    assert L.lib.cbl_attn_decode(*args(4, 2, 128, 4096, 129)) == L.EUNSUPPORTED  # at most 128 slices
+    assert L.lib.cbl_attn_decode(*args(4, 2, 128, 4096, 1)) == L.EINVAL          # 4096 positions need at least 4 slices
     assert L.lib.cbl_attn_decode(*args(4, 2, 64, 128, 1)) == L.EUNSUPPORTED
     assert L.lib.cbl_attn_decode(*args(18, 2, 128, 128, 1)) == L.EUNSUPPORTED    # 9 query heads per kv head
     assert L.lib.cbl_attn_decode(*args(5, 2, 128, 128, 1)) == L.EUNSUPPORTED
