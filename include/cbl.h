@@ -263,19 +263,20 @@ int cbl_add_rmsnorm(float* h, const void* add, int64_t ld_add, const void* w, in
 /* Rotary embedding + cache write.  qkv [rows, ld] holds q heads | k heads | v heads per row; bias (NULL or
  * [(NH + 2 NKV) * HD]) is added first.  Row r belongs to sequence r at position pos[r] (decode, pos != NULL)
  * or to sequence seq0 at position pos0 + r (prefill, pos == NULL).  Writes the rotated queries to
- * q_out [rows, NH * HD] and the rotated keys / the values into the caches [seq][NKV][max_len][HD].
+ * q_out [rows, NH * HD], the rotated keys into the key cache [seq][NKV][max_len][HD] and the values into the
+ * dimension-major value cache [seq][NKV][HD][max_len].
  * Rotation pairs element i with i + HD/2 (the Hugging Face convention). */
 int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* bias, const int32_t* pos, int32_t pos0, int32_t seq0, int32_t rows,
                 int32_t NH, int32_t NKV, int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, cbl_stream s);
 
 /* Grouped-query attention of one new token per sequence over cache positions 0..pos[b] (the step's own
- * key / value already written by cbl_rope_kv).  q, out: [B, NH * HD]; caches [B][NKV][max_len][HD]; HD = 128,
- * NH / NKV <= 8.  The positions of a sequence are cut into `nsplit` slices that run in parallel
- * (nsplit >= cbl_attn_decode_min_splits(max_len)); `workspace` holds the slices' partial results
- * (cbl_attn_decode_workspace_bytes, zero before the first call; its last word is a status word that
- * becomes nonzero if a slice exceeded the kernel's capacity). */
+ * key / value already written by cbl_rope_kv), flash-decoding on tensor cores.  q, out: [B, NH * HD]; key cache
+ * [B][NKV][max_len][HD], value cache dimension-major [B][NKV][HD][max_len]; HD = 128, NH / NKV <= 8, max_len a
+ * multiple of 32, both caches zero (or finite) where nothing has been written yet.  The positions of a sequence
+ * are cut into `nsplit` slices (1..cbl_attn_decode_max_splits()) that run in parallel, four warps per slice;
+ * `workspace` holds their partial results (cbl_attn_decode_workspace_bytes bytes; no initial contents required). */
 size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit);
-int32_t cbl_attn_decode_min_splits(int32_t max_len);
+int32_t cbl_attn_decode_max_splits(void);
 int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
                     int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s);
 

@@ -87,7 +87,7 @@ SIGNATURES = {
     "cbl_rope_kv": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
                             c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cbl_attn_decode_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
-    "cbl_attn_decode_min_splits": (c_int32, [c_int32]),
+    "cbl_attn_decode_max_splits": (c_int32, []),
     "cbl_attn_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
                                 c_void_p, c_void_p, c_int32, c_void_p]),
     "cbl_silu_mul": (c_int, [c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p, c_void_p]),

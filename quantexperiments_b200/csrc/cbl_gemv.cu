@@ -956,8 +956,9 @@ __global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L
             const int64_t co = ((int64_t)kv * max_len + p) * HD;
             kc[co + i] = r1;
             kc[co + i + half] = r2;
-            vc[co + i] = cbl_cvt_out<T>(v1);
-            vc[co + i + half] = cbl_cvt_out<T>(v2);
+            const int64_t vo = (int64_t)kv * HD * max_len + p;      // values dimension-major: [kv][HD][max_len]
+            vc[vo + (int64_t)i * max_len] = cbl_cvt_out<T>(v1);
+            vc[vo + (int64_t)(i + half) * max_len] = cbl_cvt_out<T>(v2);
         }
     }
 }

@@ -110,7 +110,8 @@ __global__ void __launch_bounds__(512) k_add_rmsnorm(float* __restrict__ h, cons
 // Row r of qkv ([rows, ld]: q heads | k heads | v heads) belongs to sequence seq(r) at position p(r):
 // decode (pos != null): seq = r, p = pos[r]; prefill (pos == null): seq = seq0, p = pos0 + r.
 // Blocks (head, row): heads 0..NH-1 rotate q into qo [rows, NH*HD]; heads NH..NH+NKV-1 rotate k and copy v
-// (+ bias) into the caches [seq][NKV][max_len][HD].
+// (+ bias) into the caches: keys [seq][NKV][max_len][HD], values dimension-major [seq][NKV][HD][max_len] (the layout
+// the attention kernel's tensor-core value product reads without a transpose).
 template <typename T>
 __global__ void __launch_bounds__(128) k_rope_kv(const T* __restrict__ qkv, int64_t ld, const T* __restrict__ bias,
                                                  const int32_t* __restrict__ pos, int pos0, int seq0, int NH, int NKV, int HD,
@@ -142,19 +143,26 @@ __global__ void __launch_bounds__(128) k_rope_kv(const T* __restrict__ qkv, int6
         kc[co + i] = r1;
         kc[co + i + half] = r2;
         const int ov = (NH + NKV + kv) * HD;
-        vc[co + i] = cbl_cvt_out<T>(in(ov + i));
-        vc[co + i + half] = cbl_cvt_out<T>(in(ov + i + half));
+        const int64_t vo = ((int64_t)seq * NKV + kv) * HD * max_len + p;      // values are cached dimension-major: [seq][kv][HD][max_len]
+        vc[vo + (int64_t)i * max_len] = cbl_cvt_out<T>(in(ov + i));
+        vc[vo + (int64_t)(i + half) * max_len] = cbl_cvt_out<T>(in(ov + i + half));
     }
 }
 
 // ---------------------------------------------------------------------------------------- decode attention
-// One block per (position slice, kv head, sequence): the slice's K rows are read once for all REP query
-// heads of the group.  Scores: one thread per position, the whole K row with 16-byte loads, q broadcast from
-// shared memory.  Values: 16 threads per V row (8 dims each), 8 rows in flight per pass.  The block writes
-// the slice's running max, denominator and un-normalised output per head; k_attn_merge combines slices.
-constexpr int ATT_THREADS = 128;
-constexpr int ATT_MAX_SLICE = 1024;        // positions per block (scores live in shared memory)
+// Flash-decoding on mma.sync tensor cores.  One block per (position slice, kv head, sequence); its four warps walk
+// the slice independently, 32 positions at a time, each with its own online softmax.  Per 32 positions:
+//   scores  S^T[head][pos] = Q[head][dim] . K^T: the group's REP (<= 8) query heads are the M side (rows 8..15 of the
+//           16-row MMA are zero), 4 tiles of 8 positions the N side; a lane loads the K row of "its" position with four
+//           16-byte loads (the dimension order inside an MMA is permuted the same way for Q and K, so no shuffles);
+//   values  O[head][dim] += P[head][pos] . V[pos][dim]: the score accumulators ARE the A fragments of this product
+//           (the positions of a score tile are chosen so that they line up), and because the value cache is stored
+//           dimension-major a lane's B fragment is 16 contiguous bytes of a V^T row (8 positions of one dimension).
+// K and V are read once for all heads of the group; nothing is staged in shared memory.  Every warp writes its running
+// max, denominator and un-normalised output per head; k_attn_merge combines the 4 * nsplit partial results.
+constexpr int ATT_WARPS = 4, ATT_THREADS = ATT_WARPS * 32;
 constexpr int ATT_HD = 128;
+constexpr int ATT_PART = ATT_HD + 4;       // floats per partial result: HD sums, max, denominator, 2 of padding (16-byte rows)
 
 __host__ __device__ inline void att_slice(int L, int nsplit, int split, int& s0, int& s1) {
     int per = (L + nsplit - 1) / nsplit;
@@ -163,168 +171,178 @@ __host__ __device__ inline void att_slice(int L, int nsplit, int split, int& s0,
     s1 = s0 + per < L ? s0 + per : L;
 }
 
+template <typename T> __device__ __forceinline__ void att_mma(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void att_mma<__half>(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void att_mma<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t att_pack(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t att_pack<__half>(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *(const uint32_t*)&h;
+}
+template <> __device__ __forceinline__ uint32_t att_pack<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *(const uint32_t*)&h;
+}
+
 template <typename T, int REP>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc,
                                                             const int32_t* __restrict__ pos, int NKV, int max_len, float scale,
-                                                            float* __restrict__ part, unsigned int* __restrict__ status) {
+                                                            float* __restrict__ part) {
     pdl_enter();
     constexpr int HD = ATT_HD;
-    __shared__ __align__(16) float s_q[REP][HD];
-    __shared__ __align__(16) float s_p[ATT_MAX_SLICE][8];            // scores, then probabilities, [position][head]
-    __shared__ float s_red[4][8];
-    __shared__ float s_m[8], s_l[8];
-    const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x, tid = threadIdx.x;
+    const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int NH = NKV * REP;
     const int L = pos[b] + 1;                                        // positions 0..pos[b] are in the cache (the step's own included)
     int s0, s1;
     att_slice(L, nsplit, split, s0, s1);
-    float* pout = part + (((int64_t)b * NH + kv * REP) * nsplit + split) * (HD + 2);   // per head: stride nsplit * (HD + 2)
-    const int64_t hstride = (int64_t)nsplit * (HD + 2);
-    if (s1 - s0 > ATT_MAX_SLICE) {
-        if (tid == 0) atomicExch(status, 2u);                        // the caller gave too few slices for this length
-        s1 = s0;
-    }
-    if (s0 >= s1) {
-        if (tid < REP) { pout[tid * hstride + HD] = -3.0e38f; pout[tid * hstride + HD + 1] = 0.f; }
+    // partial result of (this warp, head g): [HD sums | max | denominator]
+    const int nparts = nsplit * ATT_WARPS;
+    float* pout = part + ((((int64_t)b * NH + kv * REP + g) * nparts) + split * ATT_WARPS + warp) * ATT_PART;
+    const bool head_ok = g < REP;
+    if (s0 + 32 * warp >= s1) {                                      // nothing for this warp
+        if (head_ok && t == 0) { pout[HD] = -3.0e38f; pout[HD + 1] = 0.f; }
         return;
     }
-    for (int i = tid; i < REP * HD; i += ATT_THREADS) s_q[i / HD][i % HD] = to_f(q[((int64_t)b * NH + kv * REP) * HD + i]) * scale;
-    __syncthreads();
-    const T* kbase = kc + ((int64_t)b * NKV + kv) * max_len * HD;
-    const T* vbase = vc + ((int64_t)b * NKV + kv) * max_len * HD;
-    float mx[REP];
+    // Q fragments of head g: k16-step s covers, for lane t, dimensions 32t + 8(s/2) + 4(s%2) + {0,1 | 2,3}
+    uint32_t qa[8][2];
+    {
+        const uint32_t* qrow = (const uint32_t*)(q + ((int64_t)b * NH + kv * REP + (head_ok ? g : 0)) * HD);
 #pragma unroll
-    for (int h = 0; h < REP; h++) mx[h] = -3.0e38f;
-    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
-        const uint4* kr = (const uint4*)(kbase + (int64_t)t * HD);
-        uint4 w[HD / 8];
+        for (int s = 0; s < 8; s++) {
+            const int d0 = 32 * t + 8 * (s >> 1) + 4 * (s & 1);
+            qa[s][0] = head_ok ? __ldg(qrow + (d0 >> 1)) : 0u;
+            qa[s][1] = head_ok ? __ldg(qrow + (d0 >> 1) + 1) : 0u;
+        }
+    }
+    const T* kbase = kc + ((int64_t)b * NKV + kv) * max_len * HD + 32 * t;                  // + position * HD
+    const T* vbase = vc + (((int64_t)b * NKV + kv) * HD + g) * max_len + 8 * t;             // + 8 j * max_len + p0
+    float m = -3.0e38f, l = 0.f;
+    float o[16][4];
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) w[c] = __ldg(kr + c);           // L1-allocating: a thread uses both halves of each sector
-        float d[REP];
+    for (int j = 0; j < 16; j++)
 #pragma unroll
-        for (int h = 0; h < REP; h++) d[h] = 0.f;
+        for (int k = 0; k < 4; k++) o[j][k] = 0.f;
+    for (int p0 = s0 + 32 * warp; p0 < s1; p0 += 32 * ATT_WARPS) {
+        // ---- scores: tile u, column n <-> position p0 + 8 (n / 2) + 2 u + n % 2; this lane supplies column g and receives columns 2t, 2t + 1
+        float sc[4][2];
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) {
-            float f[8];
-            unpack8<T>(w[c], f);
+        for (int u = 0; u < 4; u++) {
+            const int pk = p0 + 8 * (g >> 1) + 2 * u + (g & 1);
+            uint4 kw[4];
 #pragma unroll
-            for (int h = 0; h < REP; h++) {
-                const float4 qa = *(const float4*)&s_q[h][c * 8], qb = *(const float4*)&s_q[h][c * 8 + 4];
-                d[h] += f[0] * qa.x + f[1] * qa.y + f[2] * qa.z + f[3] * qa.w + f[4] * qb.x + f[5] * qb.y + f[6] * qb.z + f[7] * qb.w;
+            for (int c = 0; c < 4; c++) kw[c] = pk < s1 ? __ldg((const uint4*)(kbase + (int64_t)pk * HD) + c) : make_uint4(0, 0, 0, 0);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                const uint4 w = kw[s >> 1];
+                att_mma<T>(acc, qa[s][0], qa[s][1], (s & 1) ? w.z : w.x, (s & 1) ? w.w : w.y);
             }
+            const int pc = p0 + 8 * t + 2 * u;                       // position of column 2t of tile u
+            sc[u][0] = pc < s1 ? acc[0] * scale : -3.0e38f;
+            sc[u][1] = pc + 1 < s1 ? acc[1] * scale : -3.0e38f;
         }
+        // ---- online softmax of head g over the chunk (its 32 positions live in the four lanes t of this g)
+        float cm = fmaxf(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])), fmaxf(fmaxf(sc[2][0], sc[2][1]), fmaxf(sc[3][0], sc[3][1])));
+        cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 1));
+        cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 2));
+        const float mn = fmaxf(m, cm);
+        const float rescale = __expf(m - mn);
+        m = mn;
+        float ps = 0.f;
 #pragma unroll
-        for (int h = 0; h < REP; h++) { s_p[t - s0][h] = d[h]; mx[h] = fmaxf(mx[h], d[h]); }
-    }
-    // slice max per head
+        for (int u = 0; u < 4; u++)
 #pragma unroll
-    for (int h = 0; h < REP; h++) {
-        const float v = warp_max(mx[h]);
-        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
-    }
-    __syncthreads();
-    if (tid < REP) s_m[tid] = fmaxf(fmaxf(s_red[0][tid], s_red[1][tid]), fmaxf(s_red[2][tid], s_red[3][tid]));
-    __syncthreads();
-    float sum[REP];
+            for (int e = 0; e < 2; e++) {
+                sc[u][e] = sc[u][e] > -1.0e38f ? __expf(sc[u][e] - mn) : 0.f;
+                ps += sc[u][e];
+            }
+        l = l * rescale + ps;
+        // the probabilities of positions 8t..8t+3 / 8t+4..8t+7 are the A fragments of the two value MMAs
+        const uint32_t pa0 = att_pack<T>(sc[0][0], sc[0][1]), pa2 = att_pack<T>(sc[1][0], sc[1][1]);
+        const uint32_t pb0 = att_pack<T>(sc[2][0], sc[2][1]), pb2 = att_pack<T>(sc[3][0], sc[3][1]);
+        // ---- values: dimension tile j = dimensions 8j..8j+7; this lane supplies dimension 8j + g, positions p0 + 8t..8t+7
 #pragma unroll
-    for (int h = 0; h < REP; h++) sum[h] = 0.f;
-    for (int t = s0 + tid; t < s1; t += ATT_THREADS) {
+        for (int j0 = 0; j0 < 16; j0 += 4) {
+            uint4 vw[4];
 #pragma unroll
-        for (int h = 0; h < REP; h++) {
-            const float e = __expf(s_p[t - s0][h] - s_m[h]);
-            s_p[t - s0][h] = e;
-            sum[h] += e;
-        }
-    }
-    __syncthreads();                                                 // s_red is reused
+            for (int j = 0; j < 4; j++) vw[j] = __ldg((const uint4*)(vbase + (int64_t)(8 * (j0 + j)) * max_len + p0));
 #pragma unroll
-    for (int h = 0; h < REP; h++) {
-        const float v = warp_sum(sum[h]);
-        if ((tid & 31) == 0) s_red[tid >> 5][h] = v;
-    }
-    __syncthreads();
-    if (tid < REP) s_l[tid] = s_red[0][tid] + s_red[1][tid] + s_red[2][tid] + s_red[3][tid];
-    // values: thread = (row group rg of 8, dim block db of 16)
-    const int rg = tid >> 4, db = tid & 15;
-    float acc[REP][8];
+            for (int j = 0; j < 4; j++) {
 #pragma unroll
-    for (int h = 0; h < REP; h++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
-    constexpr int VU = 8;                                            // V rows in flight per thread
-    for (int t0 = s0; t0 < s1; t0 += 8 * VU) {
-        uint4 w[VU];
-#pragma unroll
-        for (int u = 0; u < VU; u++) {
-            const int t = t0 + u * 8 + rg;
-            w[u] = t < s1 ? cbl_ldg_stream((const uint4*)(vbase + (int64_t)t * HD) + db) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < VU; u++) {
-            const int t = t0 + u * 8 + rg;
-            if (t < s1) {
-                float f[8];
-                unpack8<T>(w[u], f);
-                const float4 pa = *(const float4*)&s_p[t - s0][0], pb = *(const float4*)&s_p[t - s0][4];
-                const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-#pragma unroll
-                for (int h = 0; h < REP; h++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) acc[h][j] += pv[h] * f[j];
+                for (int k = 0; k < 4; k++) o[j0 + j][k] *= rescale;
+                att_mma<T>(o[j0 + j], pa0, pa2, vw[j].x, vw[j].y);
+                att_mma<T>(o[j0 + j], pb0, pb2, vw[j].z, vw[j].w);
             }
         }
     }
-    __syncthreads();                                                 // every thread is done with s_p: reuse it for the reduction
-    float* s_acc = &s_p[0][0];                                       // [8 row groups][REP][HD]
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (head_ok) {
 #pragma unroll
-    for (int h = 0; h < REP; h++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) s_acc[(rg * REP + h) * HD + db * 8 + j] = acc[h][j];
-    __syncthreads();
-    for (int i = tid; i < REP * HD; i += ATT_THREADS) {
-        float v = 0.f;
-#pragma unroll
-        for (int g = 0; g < 8; g++) v += s_acc[g * REP * HD + i];
-        pout[(i / HD) * hstride + (i % HD)] = v;
+        for (int j = 0; j < 16; j++) *(float2*)(pout + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+        if (t == 0) { pout[HD] = m; pout[HD + 1] = l; }
     }
-    if (tid < REP) { pout[tid * hstride + HD] = s_m[tid]; pout[tid * hstride + HD + 1] = s_l[tid]; }
 }
 
-// out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s.  One block per (head, sequence): the
-// slices' weights are computed once (a thread per slice), then every thread sums its output dimension.
+// out[b][head][:] = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s.  One block per (head, sequence): the parts'
+// weights are computed once (a thread per part), then every thread sums its output dimension; with many parts (few
+// sequences: few blocks, pure latency) four groups of 128 threads each take every fourth part and their sums are
+// added through shared memory.
 constexpr int ATT_MAX_SPLITS = 512;
-template <typename T>
-__global__ void __launch_bounds__(ATT_HD) k_attn_merge(const float* __restrict__ part, int nsplit, T* __restrict__ out) {
+constexpr int ATT_MERGE_GROUPS = 4;
+template <typename T, int G>
+__global__ void __launch_bounds__(ATT_HD * G) k_attn_merge(const float* __restrict__ part, int nsplit, T* __restrict__ out) {
     pdl_enter();
-    constexpr int HD = ATT_HD;
+    constexpr int HD = ATT_HD, NT = ATT_HD * G;                      // G groups of 128 threads
     __shared__ float s_w[ATT_MAX_SPLITS];
-    __shared__ float s_red[4];
-    const int head = blockIdx.x, b = blockIdx.y, NH = gridDim.x, d = threadIdx.x;
-    const float* p = part + ((int64_t)b * NH + head) * nsplit * (HD + 2);
+    __shared__ float s_red[NT / 32];
+    __shared__ float s_num[G][HD];
+    const int head = blockIdx.x, b = blockIdx.y, NH = gridDim.x, tid = threadIdx.x, d = tid & (HD - 1), grp = tid >> 7;
+    const float* p = part + ((int64_t)b * NH + head) * nsplit * ATT_PART;
     float m = -3.0e38f;
-    for (int s = d; s < nsplit; s += HD) m = fmaxf(m, p[s * (HD + 2) + HD]);
+    for (int s = tid; s < nsplit; s += NT) m = fmaxf(m, p[s * ATT_PART + HD]);
     m = warp_max(m);
-    if ((d & 31) == 0) s_red[d >> 5] = m;
+    if ((tid & 31) == 0) s_red[tid >> 5] = m;
     __syncthreads();
-    m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    m = s_red[0];
+#pragma unroll
+    for (int w = 1; w < NT / 32; w++) m = fmaxf(m, s_red[w]);
     __syncthreads();
     float den = 0.f;
-    for (int s = d; s < nsplit; s += HD) {
-        const float l = p[s * (HD + 2) + HD + 1];
-        const float w = l > 0.f ? __expf(p[s * (HD + 2) + HD] - m) : 0.f;
+    for (int s = tid; s < nsplit; s += NT) {
+        const float l = p[s * ATT_PART + HD + 1];
+        const float w = l > 0.f ? __expf(p[s * ATT_PART + HD] - m) : 0.f;
         s_w[s] = w;
         den += w * l;
     }
     den = warp_sum(den);
-    if ((d & 31) == 0) s_red[d >> 5] = den;
+    if ((tid & 31) == 0) s_red[tid >> 5] = den;
     __syncthreads();
-    den = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    den = 0.f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; w++) den += s_red[w];
     float num = 0.f;
 #pragma unroll 8
-    for (int s = 0; s < nsplit; s++) {
-        num += s_w[s] * p[s * (HD + 2) + d];          // an empty slice has weight 0 and finite (stale or zero) sums
+    for (int s = grp; s < nsplit; s += G) {
+        const float v = p[s * ATT_PART + d];
+        num += s_w[s] != 0.f ? s_w[s] * v : 0.f;                  // a part without positions wrote no sums (whatever is there is ignored)
     }
-    out[((int64_t)b * NH + head) * HD + d] = cbl_cvt_out<T>(den > 0.f ? num / den : 0.f);
+    s_num[grp][d] = num;
+    __syncthreads();
+    if (grp == 0) {
+#pragma unroll
+        for (int q = 1; q < G; q++) num += s_num[q][d];
+        out[((int64_t)b * NH + head) * HD + d] = cbl_cvt_out<T>(den > 0.f ? num / den : 0.f);
+    }
 }
 
 // ---------------------------------------------------------------------------------------- silu(gate) * up
@@ -498,30 +516,32 @@ extern "C" int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* b
 
 extern "C" size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit) {
     if (B < 0 || NH < 0 || nsplit < 1) return 0;
-    return (size_t)B * NH * nsplit * (ATT_HD + 2) * 4 + 16;
+    return (size_t)B * NH * nsplit * ATT_WARPS * ATT_PART * 4 + 16;
 }
 
-extern "C" int32_t cbl_attn_decode_min_splits(int32_t max_len) { return max_len < 1 ? 1 : (max_len + ATT_MAX_SLICE - 1) / ATT_MAX_SLICE; }
+extern "C" int32_t cbl_attn_decode_max_splits(void) { return ATT_MAX_SPLITS / ATT_WARPS; }
 
 template <typename T, int REP>
 static int attn_launch(const void* q, const void* kc, const void* vc, const int32_t* pos, int B, int NKV, int max_len, float scale, void* out,
-                       float* part, unsigned int* status, int nsplit, cudaStream_t st) {
+                       float* part, int nsplit, cudaStream_t st) {
     int rc = step_launch(k_attn_slice<T, REP>, dim3(nsplit, NKV, B), dim3(ATT_THREADS), 0, st, (const T*)q, (const T*)kc, (const T*)vc, pos,
-                         NKV, max_len, scale, part, status);
+                         NKV, max_len, scale, part);
     if (rc != CBL_OK) return rc;
-    return step_launch(k_attn_merge<T>, dim3(NKV * REP, B), dim3(ATT_HD), 0, st, (const float*)part, nsplit, (T*)out);
+    if (nsplit * ATT_WARPS > 32)
+        return step_launch(k_attn_merge<T, ATT_MERGE_GROUPS>, dim3(NKV * REP, B), dim3(ATT_HD * ATT_MERGE_GROUPS), 0, st, (const float*)part,
+                           nsplit * ATT_WARPS, (T*)out);
+    return step_launch(k_attn_merge<T, 1>, dim3(NKV * REP, B), dim3(ATT_HD), 0, st, (const float*)part, nsplit * ATT_WARPS, (T*)out);
 }
 
 extern "C" int cbl_attn_decode(const void* q, const void* kc, const void* vc, const int32_t* pos, int dtype, int32_t B, int32_t NH, int32_t NKV,
                                int32_t HD, int32_t max_len, float scale, void* out, void* workspace, int32_t nsplit, cbl_stream s) {
     if (!q || !kc || !vc || !pos || !out || !workspace || !is16(dtype) || B < 0 || NH < 1 || NKV < 1 || nsplit < 1) return CBL_EINVAL;
-    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > ATT_MAX_SPLITS) return CBL_EUNSUPPORTED;
-    if (nsplit < cbl_attn_decode_min_splits(max_len)) return CBL_EINVAL;
+    if (HD != ATT_HD || NH % NKV || NH / NKV > 8 || B > 65535 || nsplit > ATT_MAX_SPLITS / ATT_WARPS) return CBL_EUNSUPPORTED;
+    if (max_len % 32) return CBL_EINVAL;                       // the value cache's rows are read 32 positions at a time
     if (B == 0) return CBL_OK;
     float* part = (float*)workspace;
-    unsigned int* status = (unsigned int*)((char*)workspace + (size_t)B * NH * nsplit * (ATT_HD + 2) * 4);
     const cudaStream_t st = (cudaStream_t)s;
-#define CBL_ATT(R) case R: CBL_BY_TYPE(dtype, return (attn_launch<T, R>(q, kc, vc, pos, B, NKV, max_len, scale, out, part, status, nsplit, st)))
+#define CBL_ATT(R) case R: CBL_BY_TYPE(dtype, return (attn_launch<T, R>(q, kc, vc, pos, B, NKV, max_len, scale, out, part, nsplit, st)))
     switch (NH / NKV) {
         CBL_ATT(1);
         CBL_ATT(2);

@@ -142,14 +142,17 @@ class DecodeEngine:
         self.yo, self.yd = torch.zeros(B, H, **a), torch.zeros(B, H, **a)
         self.ygu, self.act = torch.zeros(B, 2 * I, **a), torch.zeros(B, I, **a)
         self.logits = torch.zeros(B, lm_head.R, dtype=torch.float32, device=dev)
-        self.kc = torch.zeros(len(layers), B, NKV, cfg.max_len, HD, **a)
-        self.vc = torch.zeros_like(self.kc)
+        # caches: keys [layer][seq][kv][position][dim], values dimension-major [layer][seq][kv][dim][position] (what the
+        # attention kernel's tensor-core value product reads directly); positions padded to a multiple of 32
+        self.cache_len = (cfg.max_len + 31) // 32 * 32
+        self.kc = torch.zeros(len(layers), B, NKV, self.cache_len, HD, **a)
+        self.vc = torch.zeros(len(layers), B, NKV, HD, self.cache_len, **a)
         self.tok = torch.zeros(B, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(B, dtype=torch.int32, device=dev)
-        # attention slices: about four blocks per SM, never fewer than the kernel's capacity needs
+        # attention slices: about four blocks (of four warps) per SM, at least 128 positions per slice at full length
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         ns = attn_split if attn_split is not None else max(1, (4 * sms) // (NKV * B))
-        self.nsplit = max(min(ns, max(1, cfg.max_len // 32), 512), lib.cbl_attn_decode_min_splits(cfg.max_len))
+        self.nsplit = max(1, min(ns, max(1, self.cache_len // 128), lib.cbl_attn_decode_max_splits()))
         self.att_ws = torch.zeros(lib.cbl_attn_decode_workspace_bytes(B, NH, self.nsplit), dtype=torch.uint8, device=dev)
         self.biases = []
         for L in layers:
@@ -181,7 +184,7 @@ class DecodeEngine:
         c = self.cfg
         _lib.check("cbl_rope_kv", lib.cbl_rope_kv(yqkv.data_ptr(), _dt(self.dtype), yqkv.stride(0), None if bias is None else bias.data_ptr(),
                                                   None if pos is None else pos.data_ptr(), pos0, seq0, rows, c.n_heads, c.n_kv, c.head_dim,
-                                                  c.rope_theta, c.max_len, qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), _stream()))
+                                                  c.rope_theta, self.cache_len, qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), _stream()))
 
     def _silu(self, ygu, act, rows: int) -> None:
         _lib.check("cbl_silu_mul", lib.cbl_silu_mul(ygu.data_ptr(), _dt(self.dtype), ygu.stride(0), rows, self.cfg.inter, act.data_ptr(),
@@ -210,7 +213,7 @@ class DecodeEngine:
                 S["qkv"].run(self.x16)
                 self._rope(self.yqkv, self.biases[li], self.pos, 0, 0, B, self.qr, self.kc[li], self.vc[li])
                 _lib.check("cbl_attn_decode", lib.cbl_attn_decode(self.qr.data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(),
-                                                                  self.pos.data_ptr(), dtc, B, c.n_heads, c.n_kv, c.head_dim, c.max_len,
+                                                                  self.pos.data_ptr(), dtc, B, c.n_heads, c.n_kv, c.head_dim, self.cache_len,
                                                                   c.head_dim ** -0.5, self.ao.data_ptr(), self.att_ws.data_ptr(), self.nsplit, s))
                 S["o"].run(self.ao)
                 self._addnorm(self.h, self.yo, L["ln2"], self.x16, B)
@@ -249,10 +252,10 @@ class DecodeEngine:
             bias = self.biases[li]
             kc, vc = self.kc[li], self.vc[li]
             _lib.check("cbl_gemv_l8_rope_kv", lib.cbl_gemv_l8_rope_kv(S["qkv"].group._structs, x, dtc, None if bias is None else bias.data_ptr(),
-                                                                      self.pos.data_ptr(), c.n_heads, c.n_kv, c.head_dim, c.rope_theta, c.max_len,
+                                                                      self.pos.data_ptr(), c.n_heads, c.n_kv, c.head_dim, c.rope_theta, self.cache_len,
                                                                       self.qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), dtc, ws, s))
             _lib.check("cbl_attn_decode", lib.cbl_attn_decode(self.qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.pos.data_ptr(), dtc, 1,
-                                                              c.n_heads, c.n_kv, c.head_dim, c.max_len, c.head_dim ** -0.5, ao,
+                                                              c.n_heads, c.n_kv, c.head_dim, self.cache_len, c.head_dim ** -0.5, ao,
                                                               self.att_ws.data_ptr(), self.nsplit, s))
             _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["o"].group._structs, ao, dtc, h, L["ln2"].data_ptr(), c.eps, x, dtc, ws, s))
             _lib.check("cbl_gemv_l8_silu_mul", lib.cbl_gemv_l8_silu_mul(S["gu"].group._structs, x, dtc, act, dtc, ws, s))
@@ -289,8 +292,10 @@ class DecodeEngine:
                 kc, vc = self.kc[li], self.vc[li]
                 self._rope(yqkv, self.biases[li], None, 0, seq, T, qr, kc, vc)
                 q4 = qr.view(T, NH, HD).transpose(0, 1)[None]
-                ao = torch.nn.functional.scaled_dot_product_attention(q4, kc[seq, :, :T][None], vc[seq, :, :T][None], is_causal=True,
-                                                                      enable_gqa=True)
+                v4 = yqkv[:, (NH + NKV) * HD:].view(T, NKV, HD).transpose(0, 1)[None]         # the values as projected (+ bias below)
+                if self.biases[li] is not None:
+                    v4 = (v4 + self.biases[li][(NH + NKV) * HD:].view(1, NKV, 1, HD)).to(self.dtype)
+                ao = torch.nn.functional.scaled_dot_product_attention(q4, kc[seq, :, :T][None], v4, is_causal=True, enable_gqa=True)
                 ao = ao[0].transpose(0, 1).reshape(T, NH * HD)
                 _lin(L["o"]).forward_into(ao, yo)
                 self._addnorm(h, yo, L["ln2"], x, T)
@@ -329,10 +334,9 @@ class DecodeEngine:
         return self.graph
 
     def check(self) -> None:
-        """Synchronises; raises if an attention launch met a slice beyond the kernel's capacity."""
+        """Synchronises; raises if a bounded device-side wait of a prompt product expired during the calls so far."""
         torch.cuda.synchronize(self.dev)
-        if int(self.att_ws[-16:].view(torch.int32)[0]) != 0:
-            raise _lib.CblError("cbl_attn_decode", _lib.EINVAL, "a position slice exceeded the kernel's capacity")
+        DenseStack.status(self.dev)
 
     @torch.no_grad()
     def generate(self, n: int, tok=0) -> list:

@@ -87,7 +87,7 @@ def test_rope_and_cache_write_decode_and_prefill_forms(dtype):
     pos = torch.tensor([0, 7, 39], dtype=torch.int32, device="cuda")
     qo = torch.zeros(B, NH * HD, device="cuda", dtype=dtype)
     kc = torch.zeros(B, NKV, max_len, HD, device="cuda", dtype=dtype)
-    vc = torch.zeros_like(kc)
+    vc = torch.zeros(B, NKV, HD, max_len, device="cuda", dtype=dtype)          # values are cached dimension-major
     L.check("cbl_rope_kv", L.lib.cbl_rope_kv(qkv.data_ptr(), _dt(dtype), qkv.stride(0), bias.data_ptr(), pos.data_ptr(), 0, 0, B, NH, NKV, HD, 1e6,
                                              max_len, qo.data_ptr(), kc.data_ptr(), vc.data_ptr(), _s()))
     xb = (qkv[:, :(NH + 2 * NKV) * HD].float() + bias.float()).to(dtype).float()
@@ -99,10 +99,10 @@ def test_rope_and_cache_write_decode_and_prefill_forms(dtype):
         v = xb[b, (NH + NKV) * HD:].view(NKV, HD)
         torch.testing.assert_close(qo[b].float().view(NH, HD), q, **tol)
         torch.testing.assert_close(kc[b, :, p].float(), k, **tol)
-        assert torch.equal(vc[b, :, p].float(), v)
+        assert torch.equal(vc[b, :, :, p].float(), v)
         untouched = torch.ones(max_len, dtype=torch.bool, device="cuda")
         untouched[p] = False
-        assert not kc[b][:, untouched].any() and not vc[b][:, untouched].any()
+        assert not kc[b][:, untouched].any() and not vc[b][:, :, untouched].any()
     # prefill form: rows are consecutive positions of one sequence
     kc.zero_(), vc.zero_()
     L.check("cbl_rope_kv", L.lib.cbl_rope_kv(qkv.data_ptr(), _dt(dtype), qkv.stride(0), None, None, 4, 1, B, NH, NKV, HD, 1e6, max_len,
@@ -116,7 +116,7 @@ def test_rope_and_cache_write_decode_and_prefill_forms(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("NH,NKV,B,max_len,nsplit,poss", [
-    (28, 4, 1, 2304, 74, [2047]), (28, 4, 3, 300, 9, [0, 1, 299]), (8, 8, 2, 64, 1, [31, 63]), (40, 8, 2, 4096, 4, [4095, 100]),
+    (28, 4, 1, 2304, 74, [2047]), (28, 4, 3, 320, 9, [0, 1, 299]), (8, 8, 2, 64, 1, [31, 63]), (40, 8, 2, 4096, 4, [4095, 100]),
     (4, 2, 4, 128, 7, [5, 64, 127, 33])])
 def test_decode_attention_matches_softmax_attention(dtype, NH, NKV, B, max_len, nsplit, poss):
     L = _lib()
@@ -124,33 +124,34 @@ def test_decode_attention_matches_softmax_attention(dtype, NH, NKV, B, max_len, 
     g = torch.Generator(device="cuda").manual_seed(NH * B + max_len)
     q = torch.randn(B, NH * HD, device="cuda", generator=g).to(dtype)
     kc = torch.randn(B, NKV, max_len, HD, device="cuda", generator=g).to(dtype)
-    vc = torch.randn(B, NKV, max_len, HD, device="cuda", generator=g).to(dtype)
+    vc = torch.randn(B, NKV, HD, max_len, device="cuda", generator=g).to(dtype)          # dimension-major value cache
     pos = torch.tensor(poss, dtype=torch.int32, device="cuda")
     out = torch.zeros(B, NH * HD, device="cuda", dtype=dtype)
-    ws = torch.zeros(L.lib.cbl_attn_decode_workspace_bytes(B, NH, nsplit), dtype=torch.uint8, device="cuda")
-    assert nsplit >= L.lib.cbl_attn_decode_min_splits(max_len)
+    ws = torch.full((L.lib.cbl_attn_decode_workspace_bytes(B, NH, nsplit),), 0xFF, dtype=torch.uint8, device="cuda")      # NaN patterns: nothing stale is read
+    assert nsplit <= L.lib.cbl_attn_decode_max_splits()
     for _ in range(2):          # the work space is reusable as it is left
         L.check("cbl_attn_decode", L.lib.cbl_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), _dt(dtype), B, NH, NKV, HD,
                                                          max_len, HD ** -0.5, out.data_ptr(), ws.data_ptr(), nsplit, _s()))
     torch.cuda.synchronize()
-    assert int(ws[-16:].view(torch.int32)[0]) == 0
     rep = NH // NKV
     for b in range(B):
         n = poss[b] + 1
         k = kc[b, :, :n].float().repeat_interleave(rep, 0)          # [NH, n, HD]
-        v = vc[b, :, :n].float().repeat_interleave(rep, 0)
+        v = vc[b, :, :, :n].float().transpose(1, 2).repeat_interleave(rep, 0)
         sc = torch.einsum("hd,hnd->hn", q[b].float().view(NH, HD), k) * HD ** -0.5
         ref = torch.einsum("hn,hnd->hd", torch.softmax(sc, -1), v)
         err = (out[b].float().view(NH, HD) - ref).abs().max() / ref.abs().max()
-        assert err <= (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4, (b, float(err))
+        # the probabilities enter the tensor-core value product rounded to the 16-bit type, the output is rounded once more
+        assert err <= 2 * (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4, (b, float(err))
 
 
-def test_decode_attention_rejects_too_few_slices_and_odd_shapes():
+def test_decode_attention_rejects_too_many_slices_and_odd_shapes():
     L = _lib()
     t = torch.zeros(16, device="cuda")
     args = lambda NH, NKV, HD, max_len, ns: (t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 2, 1, NH, NKV, HD, max_len, 1.0,  # noqa: E731
                                              t.data_ptr(), t.data_ptr(), ns, _s())
-    assert L.lib.cbl_attn_decode(*args(4, 2, 128, 4096, 1)) == L.EINVAL          # 4096 positions need at least 4 slices
+    assert L.lib.cbl_attn_decode(*args(4, 2, 128, 4096, 129)) == L.EUNSUPPORTED  # at most 128 slices
+    assert L.lib.cbl_attn_decode(*args(4, 2, 128, 100, 1)) == L.EINVAL           # cache length not a multiple of 32
     assert L.lib.cbl_attn_decode(*args(4, 2, 64, 128, 1)) == L.EUNSUPPORTED
     assert L.lib.cbl_attn_decode(*args(18, 2, 128, 128, 1)) == L.EUNSUPPORTED    # 9 query heads per kv head
     assert L.lib.cbl_attn_decode(*args(5, 2, 128, 128, 1)) == L.EUNSUPPORTED
@@ -265,14 +266,14 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
         pos = torch.tensor([17], dtype=torch.int32, device="cuda")
         bp = bias.data_ptr() if with_bias else None
         q_ref, kc_ref, vc_ref = (torch.zeros(1, NH * HD, device="cuda", dtype=dtype), torch.zeros(1, NKV, max_len, HD, device="cuda", dtype=dtype),
-                                 torch.zeros(1, NKV, max_len, HD, device="cuda", dtype=dtype))
+                                 torch.zeros(1, NKV, HD, max_len, device="cuda", dtype=dtype))
         L.check("cbl_rope_kv", L.lib.cbl_rope_kv(yqkv.data_ptr(), dtc, yqkv.stride(0), bp, pos.data_ptr(), 0, 0, 1, NH, NKV, HD, 1e6, max_len,
                                                  q_ref.data_ptr(), kc_ref.data_ptr(), vc_ref.data_ptr(), s))
         qo, kc, vc = torch.zeros_like(q_ref), torch.zeros_like(kc_ref), torch.zeros_like(vc_ref)
         L.check("cbl_gemv_l8_rope_kv", L.lib.cbl_gemv_l8_rope_kv(grp._structs, xq.data_ptr(), dtc, bp, pos.data_ptr(), NH, NKV, HD, 1e6, max_len,
                                                                  qo.data_ptr(), kc.data_ptr(), vc.data_ptr(), dtc, ws, s))
         assert close(qo, q_ref) and close(kc, kc_ref) and close(vc, vc_ref)
-        assert kc[0, :, 17].any() and vc[0, :, 17].any()
+        assert kc[0, :, 17].any() and vc[0, :, :, 17].any()
     # shapes the fused forms refuse
     assert L.lib.cbl_gemv_l8_rope_kv(grp._structs, xq.data_ptr(), dtc, None, pos.data_ptr(), NH + 1, NKV, HD, 1e6, max_len, qo.data_ptr(),
                                      kc.data_ptr(), vc.data_ptr(), dtc, ws, s) == L.EINVAL
