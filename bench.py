@@ -500,7 +500,7 @@ def run_decode(args, rank: int, world: int, local_rank: int) -> None:
     torch.cuda.set_device(dev)
     B, T, K = args.batch, args.tokens, args.steps
     cfg = Cfg(max_len=(T + 2 * K + 64 + 31) // 32 * 32)
-    eng = random_engine(cfg, seed=rank, dev=dev)
+    eng = random_engine(cfg, seed=rank, dev=dev, head=args.head, embed=args.embed)
     run_eng = eng if B == 1 else Qwen2BatchEngine(eng, B)
     gcpu = torch.Generator().manual_seed(5 + rank)
     prompts = [torch.randint(0, cfg.vocab, (T,), generator=gcpu) for _ in range(B)]
@@ -550,7 +550,9 @@ def run_decode(args, rank: int, world: int, local_rank: int) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"qwen2.5-7b architecture, random init, every block linear packed (d=8, K=4096, 12-bit tags); prompt {T}, "
-                                   f"generate {K}, batch {B}; bf16 embedding / head, bf16 KV cache",
+                                   f"generate {K}, batch {B}; "
+                                   + ("bf16" if args.embed == "16" else "4-bit block-32") + " embedding, " + ("bf16" if args.head == "16" else "8-bit block-32")
+                                   + " head, bf16 KV cache",
                        "parallelism": "replicas" if world > 1 else "single", "launch": "one CUDA graph per decode step",
                        "l2": "inputs larger than L2 (2.3 GB of weights per step)"},
             "clocks": clocks, "gpu_launches": launches * K * world,
@@ -594,6 +596,8 @@ def main() -> None:
                     help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens; "
                          "decode: end-to-end generation (prompt --tokens, --steps generated tokens, --batch sequences)")
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--head", default="16", choices=["16", "q8"], help="decode workload: output head in bf16 (the named config) or the reference's 8-bit block-32 format")
+    ap.add_argument("--embed", default="16", choices=["16", "q4"], help="decode workload: embedding in bf16 or the reference's 4-bit block-32 format")
     ap.add_argument("--dense-min", type=int, default=None, help="prefill: token count from which the two-phase path runs (default: the library's)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

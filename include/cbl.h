@@ -309,6 +309,22 @@ int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype, const void
                         int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, int dtype, void* workspace,
                         cbl_stream s);
 
+/* The reference's block-32 formats of the embedding and the output head (aux section of a packed file,
+ * shapequant/packed.py:33-41):
+ *   cbl_embed_rows_q4: 4-bit embedding, q uint8 [rows, H/2] (even column in the low nibble), scale fp16 [rows, H/32]:
+ *                      h[b, i] = (nibble - 8) * scale[tok[b] mod rows, i / 32] (exact in fp32); H a multiple of 32.
+ *                      replaces embed_q4 (shapequant/kernels/decode_e2e.py:74-85) and packed.q4_embed_rows (:151-155).
+ *   cbl_head_gemv_q8:  8-bit head (Q8_0-like), q int8 [V, H], scale fp16 [V, H/32]:
+ *                      logits[b, v] = sum over blocks of scale * <q, x[b]>, fp32 accumulation; x [B, H] contiguous in
+ *                      `dtype`, B <= cbl_head_gemv_q8_max_batch(), `scratch` = cbl_head_q8_scratch_bytes(B, H) bytes.
+ *                      replaces gemv_q8 (shapequant/kernels/proto_formats.py:413-462) behind Q8Lin.run
+ *                      (decode_e2e.py:385-402). */
+int cbl_embed_rows_q4(const void* q, const void* scale, int64_t rows, int32_t H, const int64_t* tok, int32_t B, float* h, cbl_stream s);
+size_t cbl_head_q8_scratch_bytes(int32_t B, int32_t H);
+int32_t cbl_head_gemv_q8_max_batch(void);
+int cbl_head_gemv_q8(const void* q, const void* scale, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype,
+                     int64_t ldl, void* scratch, cbl_stream s);
+
 /* tok[b] = index of the first largest logit of row b; pos[b] += 1 when pos != NULL. */
 int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s);
 

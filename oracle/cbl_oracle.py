@@ -196,6 +196,47 @@ def cpu_linear_torch(words_t: torch.Tensor, table_t: torch.Tensor, rs_t: torch.T
     return x_t.float() @ u.T
 
 
+# --------------------------------------------------------------------------- block-32 embedding / head formats
+
+def q4_embed_pack(w: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """4-bit block-32 embedding (shapequant/packed.py:134-148): per block of 32 columns s = fp16(max|w| / 7)
+    (clamped below at 1e-8 before the division; an fp16 zero becomes 1), n = clamp(round(w / s), -8, 7) + 8, two
+    nibbles per byte with the even column in the low nibble. Returns (q uint8 [V, C/2], scale fp16 [V, C/32])."""
+    w = np.asarray(w, dtype=np.float32)
+    V, C = w.shape
+    b = w.reshape(V, C // 32, 32)
+    k = (np.maximum(np.abs(b).max(-1), np.float32(1e-8)) / np.float32(7.0)).astype(np.float16).astype(np.float32)
+    k = np.where(k == 0, np.float32(1.0), k)
+    n = (np.clip(np.rint(b / k[..., None]), -8, 7) + 8).astype(np.uint8).reshape(V, C // 2, 2)
+    return (n[..., 0] | (n[..., 1] << 4)).astype(np.uint8), k.astype(np.float16)
+
+
+def q4_embed_rows(q: np.ndarray, sc: np.ndarray, ids: np.ndarray) -> np.ndarray:
+    """fp32 rows of a 4-bit block-32 embedding (shapequant/packed.py:151-155): (nibble - 8) * scale."""
+    b = np.asarray(q)[np.asarray(ids)]
+    n = np.stack([b & 15, b >> 4], -1).reshape(b.shape[0], -1).astype(np.float32) - 8
+    return (n.reshape(b.shape[0], -1, 32) * np.asarray(sc)[np.asarray(ids)].astype(np.float32)[..., None]).reshape(b.shape[0], -1)
+
+
+def q8_pack(w: np.ndarray) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """8-bit block-32 head (shapequant/kernels/proto_formats.py:464-471): s = fp16(max|w| / 127) per block of 32 (same
+    clamps as the 4-bit format), n = clamp(round(w / s), -127, 127). Returns (q int8 [R, C], scale fp16 [R, C/32],
+    dequantized fp32 [R, C])."""
+    w = np.asarray(w, dtype=np.float32)
+    R, C = w.shape
+    b = w.reshape(R, C // 32, 32)
+    k = (np.maximum(np.abs(b).max(-1), np.float32(1e-8)) / np.float32(127.0)).astype(np.float16).astype(np.float32)
+    k = np.where(k == 0, np.float32(1.0), k)
+    n = np.clip(np.rint(b / k[..., None]), -127, 127)
+    return n.reshape(R, C).astype(np.int8), k.astype(np.float16), (n * k[..., None]).reshape(R, C).astype(np.float32)
+
+
+def q8_rows(q: np.ndarray, sc: np.ndarray, s: int = 0, e: int | None = None) -> np.ndarray:
+    """fp32 rows s:e of an 8-bit block-32 matrix (shapequant/packed.py:158-160)."""
+    b = np.asarray(q)[s:e]
+    return (b.astype(np.float32).reshape(b.shape[0], -1, 32) * np.asarray(sc)[s:e].astype(np.float32)[..., None]).reshape(b.shape[0], -1)
+
+
 def synth_matrix(R: int, C: int, seed: int, *, d: int = 8, bits: int = 12, books: int = 1, M: int = 1):
     """Seeded synthetic matrix in the benchmark's format (random tags, N(0,1) fp16 book(s),
     positive fp16 row scales), generated like the reference tests' `_lin` helpers

@@ -98,6 +98,10 @@ SIGNATURES = {
     "cbl_gemv_l8_add_norm": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p]),
     "cbl_gemv_l8_rope_kv": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_float, c_int32, c_void_p,
                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "cbl_embed_rows_q4": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p]),
+    "cbl_head_q8_scratch_bytes": (c_size_t, [c_int32, c_int32]),
+    "cbl_head_gemv_q8_max_batch": (c_int32, []),
+    "cbl_head_gemv_q8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int32, c_int32, c_int32, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "cbl_argmax": (c_int, [c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
 }
 

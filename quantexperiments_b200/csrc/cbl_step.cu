@@ -408,6 +408,119 @@ __global__ void __launch_bounds__(256) k_head(const T* __restrict__ W, const T* 
     }
 }
 
+// ---------------------------------------------------------------------------------------- block-32 embedding and head
+// 4-bit block-32 embedding rows (shapequant/packed.py:33-36): h[b][i] = (nibble - 8) * scale[t][i / 32], even column in
+// the low nibble.  Exact in fp32.
+__global__ void __launch_bounds__(256) k_embed_q4(const uint8_t* __restrict__ Q, const __half* __restrict__ S, const int64_t* __restrict__ tok,
+                                                  int64_t rows, int H, float* __restrict__ h) {
+    pdl_enter();
+    const int b = blockIdx.y;
+    int64_t t = tok[b] % rows;
+    if (t < 0) t += rows;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
+        const uint8_t by = Q[t * (H >> 1) + (i >> 1)];
+        const int n = (i & 1) ? (by >> 4) : (by & 15);
+        h[(int64_t)b * H + i] = (float)(n - 8) * __half2float(S[t * (H >> 5) + (i >> 5)]);
+    }
+}
+
+// 8-bit block-32 head (Q8_0-like, shapequant/packed.py:38-39): logits[b][v] = sum over blocks of scale * <q, x[b]>, on
+// mma.sync tensor cores.  A warp owns 16 vocabulary rows; per block of 32 columns a lane loads 8 bytes of rows g and
+// g + 8, turns the int8 weights into fp16 exactly (byte permute + magic-number subtract) and issues two m16n8k16 MMAs
+// against the fp16 activations of up to 8 sequences (staged by cbl_prep_x: one power-of-two scale per sequence; in
+// shared memory with a padded row stride), then adds scale * block sum to its fp32 accumulators.  Streaming, HBM-bound
+// (8.5 bits per weight); the order of the columns inside an MMA is permuted identically for weights and activations.
+constexpr int HQ_BMAX = 8;
+__device__ __forceinline__ void hq_s8x4_to_h2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    // bytes b0..b3 (signed) -> half2 {b0, b1}, {b2, b3}: fp16(1024 + (b ^ 0x80)) - 1152 = b exactly
+    const uint32_t x = w ^ 0x80808080u;
+    uint32_t p0, p1;
+    asm("prmt.b32 %0, %1, %2, 0x7150;" : "=r"(p0) : "r"(x), "r"(0x64646464u));      // {x.b0, 0x64, x.b1, 0x64}
+    asm("prmt.b32 %0, %1, %2, 0x7352;" : "=r"(p1) : "r"(x), "r"(0x64646464u));      // {x.b2, 0x64, x.b3, 0x64}
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));   // 1152
+    const __half2 a = __hsub2(*(const __half2*)&p0, bias), c = __hsub2(*(const __half2*)&p1, bias);
+    lo = *(const uint32_t*)&a;
+    hi = *(const uint32_t*)&c;
+}
+
+__global__ void __launch_bounds__(256, 3) k_head_q8(const int8_t* __restrict__ Q, const __half* __restrict__ S, const __half* __restrict__ xp,
+                                                 const float* __restrict__ xinv, int B, int V, int H, int Cpad, void* __restrict__ logits,
+                                                 int ldtype, int64_t ldl) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    __half* s_x = (__half*)s_raw;                                    // [B + 1][H + 8] fp16; the last row is zero (sequences beyond B)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int xs = H + 8;                                            // padded row stride: the 8 rows of a fragment load hit different banks
+    for (int i = tid; i < (B + 1) * (H / 8); i += 256) {
+        const int r = i / (H / 8), c = i - r * (H / 8);
+        *(uint4*)(s_x + r * xs + c * 8) = r < B ? *(const uint4*)(xp + (int64_t)r * Cpad + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    const int nblk = H >> 5;
+    const bool vec_scales = (nblk % 8 == 0) && (((uintptr_t)S & 15) == 0);
+    const uint4* xrow = (const uint4*)(s_x + (g < B ? g : B) * xs + 8 * t);       // + 4 * blk (uint4 units): columns 32 blk + 8 t .. + 8 of sequence g
+    for (int v0 = (blockIdx.x * 8 + warp) * 16; v0 < V; v0 += gridDim.x * 128) {
+        const int ra = min(v0 + g, V - 1), rb = min(v0 + g + 8, V - 1);
+        const uint2* qa = (const uint2*)(Q + (int64_t)ra * H) + t;  // + 4 * blk (uint2 units)
+        const uint2* qb = (const uint2*)(Q + (int64_t)rb * H) + t;
+        const __half* sa = S + (int64_t)ra * nblk;
+        const __half* sb = S + (int64_t)rb * nblk;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        constexpr int HU = 8;                                        // blocks in flight per lane: 16 eight-byte loads + their scales
+        for (int k0 = 0; k0 < nblk; k0 += HU) {
+            uint2 wa[HU], wb[HU];
+            float fa[HU], fb[HU];
+#pragma unroll
+            for (int u = 0; u < HU; u++) {
+                const bool ok = k0 + u < nblk;
+                wa[u] = ok ? __ldg(qa + 4 * (k0 + u)) : make_uint2(0, 0);
+                wb[u] = ok ? __ldg(qb + 4 * (k0 + u)) : make_uint2(0, 0);
+            }
+            if (vec_scales) {                                        // the 8 scales of a row = one 16-byte load (the same for the 4 lanes of a row)
+                union { uint4 u; __half h[8]; } va, vb;
+                va.u = __ldg((const uint4*)(sa + k0));
+                vb.u = __ldg((const uint4*)(sb + k0));
+#pragma unroll
+                for (int u = 0; u < HU; u++) { fa[u] = __half2float(va.h[u]); fb[u] = __half2float(vb.h[u]); }
+            } else {
+#pragma unroll
+                for (int u = 0; u < HU; u++) {
+                    const bool ok = k0 + u < nblk;
+                    fa[u] = ok ? __half2float(__ldg(sa + k0 + u)) : 0.f;
+                    fb[u] = ok ? __half2float(__ldg(sb + k0 + u)) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < HU; u++) {
+                if (k0 + u < nblk) {
+                    const uint4 xv = xrow[4 * (k0 + u)];
+                    uint32_t a0, a2, a1, a3, c0, c2, c1, c3;
+                    hq_s8x4_to_h2x2(wa[u].x, a0, a2);                // row g,     columns 8t + {0,1 | 2,3}
+                    hq_s8x4_to_h2x2(wb[u].x, a1, a3);                // row g + 8
+                    hq_s8x4_to_h2x2(wa[u].y, c0, c2);                // columns 8t + {4,5 | 6,7}
+                    hq_s8x4_to_h2x2(wb[u].y, c1, c3);
+                    float d[4] = {0.f, 0.f, 0.f, 0.f};
+                    cbl_mma16816(d, a0, a1, a2, a3, xv.x, xv.y);
+                    cbl_mma16816(d, c0, c1, c2, c3, xv.z, xv.w);
+                    acc[0] += fa[u] * d[0];
+                    acc[1] += fa[u] * d[1];
+                    acc[2] += fb[u] * d[2];
+                    acc[3] += fb[u] * d[3];
+                }
+            }
+        }
+        // d[0], d[1]: row g, sequences 2t, 2t + 1; d[2], d[3]: row g + 8
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int n = 2 * t + e;
+            if (n < B) {
+                if (v0 + g < V) cbl_store_out(logits, ldtype, (int64_t)n * ldl + v0 + g, acc[e] * xinv[n]);
+                if (v0 + g + 8 < V) cbl_store_out(logits, ldtype, (int64_t)n * ldl + v0 + g + 8, acc[2 + e] * xinv[n]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------- greedy argmax
 // tok[b] = first index of the largest logit of row b; pos[b] += 1 when pos is given.  A cluster of ARGMAX_CTAS
 // thread blocks per row: every block reduces its share, block 0 collects the others' results through
@@ -605,6 +718,45 @@ extern "C" int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B,
     }
 #undef CBL_HEAD
     return CBL_EUNSUPPORTED;
+}
+
+extern "C" int cbl_embed_rows_q4(const void* q, const void* scale, int64_t rows, int32_t H, const int64_t* tok, int32_t B, float* h, cbl_stream s) {
+    if (!q || !scale || !tok || !h || rows < 1 || H < 32 || H % 32 || B < 0) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    if (B > 65535) return CBL_EUNSUPPORTED;
+    const dim3 grid(cbl_ceil_div(H, 256) < 16 ? cbl_ceil_div(H, 256) : 16, B);
+    return step_launch(k_embed_q4, grid, dim3(256), 0, (cudaStream_t)s, (const uint8_t*)q, (const __half*)scale, tok, rows, (int)H, h);
+}
+
+extern "C" size_t cbl_head_q8_scratch_bytes(int32_t B, int32_t H) { return cbl_prep_x_bytes(B, H, 1); }
+
+extern "C" int32_t cbl_head_gemv_q8_max_batch(void) { return HQ_BMAX; }
+
+extern "C" int cbl_head_gemv_q8(const void* q, const void* scale, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype,
+                                int64_t ldl, void* scratch, cbl_stream s) {
+    if (!q || !scale || !x || !logits || !scratch || !is16(dtype) || V < 1 || H < 32 || B < 0) return CBL_EINVAL;
+    if (ldtype != CBL_F32 && !is16(ldtype)) return CBL_EINVAL;
+    if (B > HQ_BMAX || H % 32) return CBL_EUNSUPPORTED;
+    if (((uintptr_t)q % 16) || ((uintptr_t)scratch % 16)) return CBL_EINVAL;
+    if (B == 0) return CBL_OK;
+    const size_t smem = (size_t)(B + 1) * (H + 8) * 2;
+    if (smem > 200 * 1024) return CBL_EUNSUPPORTED;
+    const cudaStream_t st = (cudaStream_t)s;
+    int rc = cbl_prep_x(x, dtype, B, H, H, nullptr, 1, scratch, s);          // fp16 [8][Cpad] + one power-of-two scale per sequence
+    if (rc != CBL_OK) return rc;
+    const int Cpad = (H + 511) / 512 * 512;
+    const float* xinv = (const float*)((const __half*)scratch + (int64_t)8 * Cpad);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_head_q8, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set[dev] = true;
+    }
+    int grid = cbl_sm_count() * 4;
+    if (grid > cbl_ceil_div(V, 128)) grid = cbl_ceil_div(V, 128);
+    return step_launch(k_head_q8, dim3(grid), dim3(256), smem, st, (const int8_t*)q, (const __half*)scale, (const __half*)scratch, xinv, (int)B, (int)V,
+                       (int)H, Cpad, logits, ldtype, ldl);
 }
 
 extern "C" int cbl_argmax(const void* logits, int ldtype, int64_t ldl, int32_t B, int32_t V, int64_t* tok, int32_t* pos, cbl_stream s) {

@@ -71,6 +71,61 @@ class DenseHead:
         return self.w.numel() * 2
 
 
+class Q8Head:
+    """The reference's 8-bit block-32 head (Q8Lin, shapequant/kernels/decode_e2e.py:385-402): q int8 [V, H], scale fp16
+    [V, H/32]; run(x [B, H], logits [B, V] fp32). Up to 8 sequences per pass over the weights (more run as several passes)."""
+
+    def __init__(self, q: torch.Tensor, sc: torch.Tensor):
+        if q.dtype != torch.int8 or sc.dtype != torch.float16 or q.device.type != "cuda" or q.shape[1] % 32:
+            raise ValueError("the 8-bit head is int8 [V, H] + fp16 [V, H/32] on a CUDA device, H a multiple of 32")
+        self.q, self.sc = q.contiguous(), sc.contiguous()
+        self.R, self.C = q.shape
+        self.perms = None
+        self._scratch = torch.empty(lib.cbl_head_q8_scratch_bytes(lib.cbl_head_gemv_q8_max_batch(), self.C), dtype=torch.uint8, device=q.device)
+
+    @classmethod
+    def from_weight(cls, w: torch.Tensor, dev="cuda") -> "Q8Head":
+        from .packed import q8_pack
+        q, sc = q8_pack(w.to(dev))
+        return cls(q, sc)
+
+    def run(self, x: torch.Tensor, logits: torch.Tensor) -> None:
+        nmax = lib.cbl_head_gemv_q8_max_batch()
+        for b0 in range(0, x.shape[0], nmax):
+            xb, lb = x[b0:b0 + nmax], logits[b0:b0 + nmax]
+            _lib.check("cbl_head_gemv_q8", lib.cbl_head_gemv_q8(self.q.data_ptr(), self.sc.data_ptr(), xb.data_ptr(), _dt(x.dtype), xb.shape[0],
+                                                                self.R, self.C, lb.data_ptr(), _dt(logits.dtype), logits.stride(0),
+                                                                self._scratch.data_ptr(), _stream()))
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.sc.numel() * 2
+
+
+class Q4Embed:
+    """The reference's 4-bit block-32 token embedding (Q4Embed, shapequant/kernels/decode_e2e.py:370-382): q uint8
+    [V, H/2], scale fp16 [V, H/32]. `dtype` names the model's activation type (the rows themselves decode to fp32)."""
+
+    def __init__(self, q: torch.Tensor, sc: torch.Tensor, dtype=torch.bfloat16):
+        if q.dtype != torch.uint8 or sc.dtype != torch.float16 or q.device.type != "cuda":
+            raise ValueError("the 4-bit embedding is uint8 [V, H/2] + fp16 [V, H/32] on a CUDA device")
+        self.q, self.sc, self.dtype = q.contiguous(), sc.contiguous(), dtype
+        self.shape = (q.shape[0], q.shape[1] * 2)
+        self.device = q.device
+
+    @classmethod
+    def from_weight(cls, w: torch.Tensor, dev="cuda", dtype=None) -> "Q4Embed":
+        from .packed import q4_embed_pack
+        q, sc = q4_embed_pack(w.to(dev))
+        return cls(q, sc, dtype if dtype is not None else (w.dtype if w.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16))
+
+    def rows(self, ids: torch.Tensor) -> torch.Tensor:
+        from .packed import q4_embed_rows
+        return q4_embed_rows(self.q, self.sc, ids)
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.sc.numel() * 2
+
+
 class _Stage:
     """Linears that read the same input and write column slices of one [B, sum R] buffer (q|k|v, gate|up,
     or a single matrix). One token and one column order: one grouped table-lookup launch."""
@@ -131,6 +186,7 @@ class DecodeEngine:
             dev = torch.device("cuda", torch.cuda.current_device())
         self.cfg, self.embed, self.layers, self.final_norm, self.lm_head, self.B, self.dev = cfg, embed, layers, final_norm, lm_head, B, dev
         self.dtype = dt = embed.dtype
+        self.vocab_rows = embed.shape[0]
         if dt not in (torch.float16, torch.bfloat16):
             raise ValueError("the model's activation type is fp16 or bf16")
         H, NH, NKV, HD, I = cfg.hidden, cfg.n_heads, cfg.n_kv, cfg.head_dim, cfg.inter
@@ -175,6 +231,14 @@ class DecodeEngine:
         self.fused = B == 1 and all(st.group is not None for S in self.stages for st in S.values()) and H <= lib.cbl_gemv_l8_add_norm_max_rows()
 
     # -- operators (thin wrappers over the C ABI; all on the current stream)
+    def _embed(self, tok, rows: int, h) -> None:
+        if isinstance(self.embed, Q4Embed):
+            _lib.check("cbl_embed_rows_q4", lib.cbl_embed_rows_q4(self.embed.q.data_ptr(), self.embed.sc.data_ptr(), self.vocab_rows, self.cfg.hidden,
+                                                                  tok.data_ptr(), rows, h.data_ptr(), _stream()))
+        else:
+            _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), _dt(self.dtype), self.vocab_rows, self.cfg.hidden, tok.data_ptr(),
+                                                            rows, h.data_ptr(), _stream()))
+
     def _addnorm(self, h, add, w, x, rows: int) -> None:
         _lib.check("cbl_add_rmsnorm", lib.cbl_add_rmsnorm(h.data_ptr(), None if add is None else add.data_ptr(),
                                                           0 if add is None else add.stride(0), w.data_ptr(), _dt(self.dtype),
@@ -202,8 +266,7 @@ class DecodeEngine:
                     S["down"].run(self.act)
                 return
             s = _stream()
-            _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), dtc, self.embed.shape[0], c.hidden, self.tok.data_ptr(), B,
-                                                            self.h.data_ptr(), s))
+            self._embed(self.tok, B, self.h)
             if self.fused:
                 self._step_fused(s)
                 return
@@ -283,8 +346,7 @@ class DecodeEngine:
             x = torch.empty(T, H, **a)
             yqkv, qr = torch.empty(T, (NH + 2 * NKV) * HD, **a), torch.empty(T, NH * HD, **a)
             yo, ygu, act, yd = torch.empty(T, H, **a), torch.empty(T, 2 * I, **a), torch.empty(T, I, **a), torch.empty(T, H, **a)
-            _lib.check("cbl_embed_rows", lib.cbl_embed_rows(self.embed.data_ptr(), _dt(self.dtype), self.embed.shape[0], H, ids.data_ptr(), T,
-                                                            h.data_ptr(), _stream()))
+            self._embed(ids, T, h)
             add = None
             for li, L in enumerate(self.layers):
                 self._addnorm(h, add, L["ln1"], x, T)
@@ -384,11 +446,12 @@ class Qwen2BatchEngine(DecodeEngine):
 
 
 def random_engine(cfg: Cfg, *, seed: int = 0, dev="cuda", dtype=torch.bfloat16, B: int = 1, books: int = 1, M: int = 1,
-                  bias: bool = True) -> DecodeEngine:
+                  bias: bool = True, head: str = "16", embed: str = "16") -> DecodeEngine:
     """A random-init model of the given architecture with every block linear in the packed format (d = 8,
     12-bit tags, one 4096-entry book per matrix; `books` = 2 adds a second summed book, M > 1 seeded column
     orders). Stand-in for a real checkpoint: tags uniform, books ~N(0, 1), row scales ~0.02 / sqrt(books),
-    embedding and head ~N(0, 0.02), norm weights 1 +- 0.1, q/k/v biases ~N(0, 0.1)."""
+    embedding and head ~N(0, 0.02), norm weights 1 +- 0.1, q/k/v biases ~N(0, 0.1). head = "16" (the model's 16-bit
+    type) or "q8" (the reference's 8-bit block-32 head), embed = "16" or "q4" (its 4-bit block-32 embedding)."""
     dev = torch.device(dev)
     g = torch.Generator(device=dev).manual_seed(seed)
     H, NH, NKV, HD, I = cfg.hidden, cfg.n_heads, cfg.n_kv, cfg.head_dim, cfg.inter
@@ -420,9 +483,13 @@ def random_engine(cfg: Cfg, *, seed: int = 0, dev="cuda", dtype=torch.bfloat16, 
         if bias:
             L.update(bq=vec(NH * HD, 0.1), bk=vec(NKV * HD, 0.1), bv=vec(NKV * HD, 0.1))
         layers.append(L)
-    embed = (torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype)
-    head = DenseHead((torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype))
-    return DecodeEngine(cfg, embed, layers, vec(H, 0.1, 1.0), head, dev=dev, B=B)
+    we = (torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype)
+    wh = (torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).to(dtype)
+    if head not in ("16", "q8") or embed not in ("16", "q4"):
+        raise ValueError("head is '16' or 'q8', embed is '16' or 'q4'")
+    emb = Q4Embed.from_weight(we, dev, dtype) if embed == "q4" else we
+    hd = Q8Head.from_weight(wh, dev) if head == "q8" else DenseHead(wh)
+    return DecodeEngine(cfg, emb, layers, vec(H, 0.1, 1.0), hd, dev=dev, B=B)
 
 
 # ------------------------------------------------------------------------------------------- runtime helpers

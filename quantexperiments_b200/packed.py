@@ -156,6 +156,52 @@ class PackedFile:
         return self.matrix(name, device).dequant(dtype=torch.float32)
 
 
+def q4_embed_pack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """w [V, C] -> (q uint8 [V, C/2], scale fp16 [V, C/32]): the reference's 4-bit block-32 embedding
+    (shapequant/packed.py:134-148): s = fp16(max|w| / 7) per 32 columns, n = clamp(round(w / s), -8, 7) + 8, even column
+    in the low nibble. Runs on the tensor's device."""
+    V, C = w.shape
+    q = torch.empty(V, C // 2, dtype=torch.uint8, device=w.device)
+    sc = torch.empty(V, C // 32, dtype=torch.float16, device=w.device)
+    for s in range(0, V, 8192):
+        b = w[s:s + 8192].float().view(-1, C // 32, 32)
+        k = (b.abs().amax(-1).clamp_min(1e-8) / 7.0).half().float()
+        k = torch.where(k == 0, torch.ones_like(k), k)
+        n = ((b / k[..., None]).round().clamp(-8, 7) + 8).to(torch.uint8).view(-1, C // 2, 2)
+        q[s:s + 8192] = n[..., 0] | (n[..., 1] << 4)
+        sc[s:s + 8192] = k.half()
+    return q, sc
+
+
+def q4_embed_rows(q: torch.Tensor, sc: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """fp32 [len(ids), C] rows of a 4-bit block-32 embedding (shapequant/packed.py:151-155); on a CUDA device the
+    engine uses cbl_embed_rows_q4 instead."""
+    b = q[ids]
+    n = torch.stack([b & 15, b >> 4], -1).view(b.shape[0], -1).float() - 8
+    return (n.view(b.shape[0], -1, 32) * sc[ids].float()[..., None]).view(b.shape[0], -1)
+
+
+def q8_pack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """w [R, C] -> (q int8 [R, C], scale fp16 [R, C/32]): the reference's 8-bit block-32 head
+    (shapequant/kernels/proto_formats.py:464-471; aux.lm_head of shapequant/packed.py:38-39)."""
+    R, C = w.shape
+    q = torch.empty(R, C, dtype=torch.int8, device=w.device)
+    sc = torch.empty(R, C // 32, dtype=torch.float16, device=w.device)
+    for s in range(0, R, 8192):
+        b = w[s:s + 8192].float().view(-1, C // 32, 32)
+        k = (b.abs().amax(-1).clamp_min(1e-8) / 127.0).half().float()
+        k = torch.where(k == 0, torch.ones_like(k), k)
+        q[s:s + 8192] = (b / k[..., None]).round().clamp(-127, 127).to(torch.int8).view(-1, C)
+        sc[s:s + 8192] = k.half()
+    return q, sc
+
+
+def q8_rows(q: torch.Tensor, sc: torch.Tensor, s: int = 0, e: int | None = None) -> torch.Tensor:
+    """fp32 rows s:e of an 8-bit block-32 matrix (shapequant/packed.py:158-160)."""
+    b = q[s:e]
+    return (b.float().view(b.shape[0], -1, 32) * sc[s:e].float()[..., None]).view(b.shape[0], -1)
+
+
 def decode_tensors(local_tags, table, row_scale, row_book, row_mask, perms, K: int) -> torch.Tensor:
     """Decode from unpacked parts on the GPU (argument order of shapequant/packed.py:259-270):
     local_tags [R, nch], table [G*K, d] fp16, row_scale [R], row_book / row_mask [R] or None,

@@ -142,6 +142,22 @@ def main() -> None:
                x=x.float().numpy(), y=y.numpy(), dense_sum=np.array([dense.double().sum().item()]),
                stored_bytes=np.array([lin.stored_bytes()], dtype=np.int64))
     np.savez_compressed(HERE / "linear.npz", **out)
+
+    # 8. block-32 formats of the embedding and the head (packed.py:33-41, 134-160; kernels/proto_formats.py:464-471):
+    #    4-bit embedding pack + row decode, 8-bit head pack + row decode, incl. an all-zero block and an outlier block
+    from shapequant.kernels import proto_formats as pfm
+    out = {}
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(24, 128, generator=g) * 0.02
+    w[3, 32:64] = 0.0
+    w[5, 7] = 1.5
+    w = w.bfloat16().float()
+    q4, s4 = packed.q4_embed_pack(w)
+    ids = torch.tensor([0, 3, 5, 23, 3])
+    q8, s8, deq8 = pfm.q8_pack(w)
+    out.update(w=w.numpy(), q4=q4.numpy(), s4=s4.numpy(), ids=ids.numpy(), rows4=packed.q4_embed_rows(q4, s4, ids).numpy(),
+               q8=q8.numpy(), s8=s8.numpy(), deq8=deq8.numpy(), rows8=packed.q8_rows(q8, s8, 2, 9).numpy())
+    np.savez_compressed(HERE / "blockq.npz", **out)
     print("golden fixtures written to", HERE)
 
 

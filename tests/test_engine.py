@@ -281,6 +281,48 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
     assert L.lib.cbl_gemv_l8_add_norm(big, xq.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s) == L.EUNSUPPORTED
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_block32_embedding_rows_and_head_match_the_oracle(dtype):
+    """cbl_embed_rows_q4 (exact) and cbl_head_gemv_q8 (fp32 matmul on the oracle's dequantized weights)."""
+    from quantexperiments_b200.engine import Q4Embed, Q8Head
+    L = _lib()
+    g = torch.Generator().manual_seed(4)
+    V, H = 777, 1056
+    w = (torch.randn(V, H, generator=g) * 0.02).to(dtype).float()
+    w[5, 64:96] = 0.0
+    w[9, 3] = 2.0
+    q4, s4 = orc.q4_embed_pack(w.numpy())
+    emb = Q4Embed(torch.from_numpy(q4).cuda(), torch.from_numpy(s4).cuda(), dtype)
+    tok = torch.tensor([5, 776, 777 + 9, 0], dtype=torch.int64, device="cuda")
+    h = torch.empty(4, H, device="cuda")
+    L.check("cbl_embed_rows_q4", L.lib.cbl_embed_rows_q4(emb.q.data_ptr(), emb.sc.data_ptr(), V, H, tok.data_ptr(), 4, h.data_ptr(), _s()))
+    ref = orc.q4_embed_rows(q4, s4, np.array([5, 776, 9, 0]))
+    assert np.array_equal(h.cpu().numpy(), ref)
+    assert np.array_equal(emb.rows(torch.tensor([5, 776, 9, 0], device="cuda")).cpu().numpy(), ref)
+    q8, s8, deq = orc.q8_pack(w.numpy())
+    head = Q8Head(torch.from_numpy(q8).cuda(), torch.from_numpy(s8).cuda())
+    assert head.nbytes() == V * H + V * H // 32 * 2
+    wd = torch.from_numpy(deq).cuda()
+    for B in (1, 3, 8, 11):             # more than 8 sequences: several passes
+        x = torch.randn(B, H, generator=g).to(dtype).cuda()
+        lgv = torch.zeros(B, V, device="cuda")
+        head.run(x, lgv)
+        r = x.float() @ wd.t()
+        assert (lgv - r).abs().max() / r.abs().max() <= 1e-5          # int8 weights and 16-bit activations are exact in the fp16 MMAs
+    # a 16-bit logits buffer with a wider row stride, through the C ABI
+    x = torch.randn(2, H, generator=g).to(dtype).cuda()
+    lg = torch.zeros(2, V + 3, device="cuda", dtype=dtype)
+    sc = torch.empty(L.lib.cbl_head_q8_scratch_bytes(2, H), dtype=torch.uint8, device="cuda")
+    L.check("cbl_head_gemv_q8", L.lib.cbl_head_gemv_q8(head.q.data_ptr(), head.sc.data_ptr(), x.data_ptr(), _dt(dtype), 2, V, H, lg.data_ptr(),
+                                                       _dt(dtype), lg.stride(0), sc.data_ptr(), _s()))
+    r = x.float() @ wd.t()
+    assert (lg[:, :V].float() - r).abs().max() / r.abs().max() <= (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-5
+    assert not lg[:, V:].any()
+    assert L.lib.cbl_head_gemv_q8(head.q.data_ptr(), head.sc.data_ptr(), x.data_ptr(), _dt(dtype), 9, V, H, lg.data_ptr(), _dt(dtype), lg.stride(0),
+                                  sc.data_ptr(), _s()) == L.EUNSUPPORTED
+    assert L.lib.cbl_embed_rows_q4(emb.q.data_ptr(), emb.sc.data_ptr(), V, 40, tok.data_ptr(), 4, h.data_ptr(), _s()) == L.EINVAL
+
+
 # ------------------------------------------------------------------------------------------- the engine
 class _RefModel:
     """One Qwen2 decode step in plain torch (fp32 math, 16-bit rounding where the engine rounds)."""
@@ -300,7 +342,9 @@ class _RefModel:
     def step(self, tok: int, p: int) -> torch.Tensor:
         e, c = self.e, self.c
         NH, NKV, HD = c.n_heads, c.n_kv, c.head_dim
-        h = e.embed[tok].float()
+        from quantexperiments_b200.engine import Q4Embed, Q8Head
+        from quantexperiments_b200.packed import q8_rows
+        h = e.embed.rows(torch.tensor([tok], device="cuda"))[0] if isinstance(e.embed, Q4Embed) else e.embed[tok].float()
         for li, (L, W) in enumerate(zip(e.layers, self.W)):
             x = self.norm(h, L["ln1"])
             q, k, v = self.r(W["q"] @ x), self.r(W["k"] @ x), self.r(W["v"] @ x)
@@ -319,7 +363,8 @@ class _RefModel:
             act = self.r(self.r(g * torch.sigmoid(g)) * u)
             h = h + self.r(W["down"] @ act)
         x = self.norm(h, e.final_norm)
-        return e.lm_head.w.float() @ x
+        wh = q8_rows(e.lm_head.q, e.lm_head.sc) if isinstance(e.lm_head, Q8Head) else e.lm_head.w.float()
+        return wh @ x
 
 
 def _small_cfg(max_len=96):
@@ -414,6 +459,33 @@ def test_engine_graph_replay_prefill_and_batched_engine_agree():
     eng.step()
     assert (beng.logits[1] - eng.logits[0]).abs().max() / eng.logits[0].abs().max() <= 2e-2
     beng.check()
+
+
+def test_engine_with_the_8bit_head_and_the_4bit_embedding():
+    from quantexperiments_b200.engine import Q4Embed, Q8Head, Qwen2BatchEngine, random_engine
+    eng = random_engine(_small_cfg(), seed=6, head="q8", embed="q4")
+    assert isinstance(eng.embed, Q4Embed) and isinstance(eng.lm_head, Q8Head)
+    ref = _RefModel(eng)
+    toks = [3, 999, 17, 256]
+    eng.reset(toks[0])
+    for p, t in enumerate(toks):
+        eng.tok.fill_(t)
+        eng.step()
+        lr = ref.step(t, p)
+        assert (eng.logits[0] - lr).abs().max() / lr.abs().max() <= 2e-2, p
+    lg1 = eng.logits[0].clone()
+    # prompt path and batched engine on the same formats
+    eng.reset(0)
+    lgp = eng.prefill(toks)
+    assert (lgp - lg1).abs().max() / lg1.abs().max() <= 2e-2
+    b6 = Qwen2BatchEngine(eng, 6)
+    b6.reset(toks[0])
+    for t in toks:
+        b6.tok.fill_(t)
+        b6.step()
+    for b in range(6):
+        assert (b6.logits[b] - lg1).abs().max() / lg1.abs().max() <= 2e-2
+    assert eng.weight_bytes() < random_engine(_small_cfg(), seed=6).weight_bytes()
 
 
 def test_engine_rejects_unsupported_shapes():

@@ -105,3 +105,25 @@ def test_synth_matrix_round_trip():
                              t.ones(1, 128), 12, 8).numpy()
     m1 = orc.synth_matrix(20, 128, seed=3, M=1)
     assert np.allclose(y[0], orc.synth_decode(m1).sum(1), rtol=1e-5, atol=1e-6)
+
+
+def test_block32_embedding_and_head_formats_match_the_reference_fixture():
+    """4-bit embedding / 8-bit head pack + row decode (incl. an all-zero block and an outlier) against arrays written
+    by the reference's q4_embed_pack / q4_embed_rows / q8_pack / q8_rows; the host packers agree with the oracle."""
+    import torch
+    from quantexperiments_b200 import packed
+    f = np.load(G / "blockq.npz")
+    q4, s4 = orc.q4_embed_pack(f["w"])
+    assert np.array_equal(q4, f["q4"]) and np.array_equal(s4, f["s4"])
+    assert np.array_equal(orc.q4_embed_rows(f["q4"], f["s4"], f["ids"]), f["rows4"])
+    q8, s8, deq8 = orc.q8_pack(f["w"])
+    assert np.array_equal(q8, f["q8"]) and np.array_equal(s8, f["s8"]) and np.array_equal(deq8, f["deq8"])
+    assert np.array_equal(orc.q8_rows(f["q8"], f["s8"], 2, 9), f["rows8"])
+    w = torch.from_numpy(f["w"])
+    hq4, hs4 = packed.q4_embed_pack(w)
+    hq8, hs8 = packed.q8_pack(w)
+    assert np.array_equal(hq4.numpy(), f["q4"]) and np.array_equal(hs4.numpy(), f["s4"])
+    assert np.array_equal(hq8.numpy(), f["q8"]) and np.array_equal(hs8.numpy(), f["s8"])
+    assert np.array_equal(packed.q4_embed_rows(hq4, hs4, torch.from_numpy(f["ids"])).numpy(), f["rows4"])
+    assert np.array_equal(packed.q8_rows(hq8, hs8, 2, 9).numpy(), f["rows8"])
+
