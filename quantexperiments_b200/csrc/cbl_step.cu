@@ -521,6 +521,70 @@ __global__ void __launch_bounds__(256, 3) k_head_q8(const int8_t* __restrict__ Q
     }
 }
 
+// The 16-bit head for 2..8 sequences on mma.sync (the FMA kernel above is at the HBM roofline for one sequence but its
+// arithmetic grows with the batch): a warp owns 16 vocabulary rows, per block of 32 columns a lane loads 16 bytes of
+// rows g and g + 8 straight into the A fragments of two m16n8k16 MMAs (same column permutation for the activations,
+// which sit in shared memory with a padded row stride; sequences beyond B read a zero row).
+template <typename T> __device__ __forceinline__ void head_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void head_mma<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    cbl_mma16816(c, a0, a1, a2, a3, b0, b1);
+}
+template <> __device__ __forceinline__ void head_mma<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                                    uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256, 3) k_head_mma(const T* __restrict__ W, const T* __restrict__ x, int B, int V, int H, void* __restrict__ logits,
+                                                     int ldtype, int64_t ldl) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    T* s_x = (T*)s_raw;                                              // [B + 1][H + 8]; the last row is zero
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int xs = H + 8;
+    for (int i = tid; i < (B + 1) * (H / 8); i += 256) {
+        const int r = i / (H / 8), c = i - r * (H / 8);
+        *(uint4*)(s_x + r * xs + c * 8) = r < B ? *(const uint4*)(x + (int64_t)r * H + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    const int nblk = H >> 5;
+    const uint4* xrow = (const uint4*)(s_x + (g < B ? g : B) * xs + 8 * t);
+    for (int v0 = (blockIdx.x * 8 + warp) * 16; v0 < V; v0 += gridDim.x * 128) {
+        const int ra = min(v0 + g, V - 1), rb = min(v0 + g + 8, V - 1);
+        const uint4* qa = (const uint4*)(W + (int64_t)ra * H) + t;  // + 4 * blk: columns 32 blk + 8 t .. + 8
+        const uint4* qb = (const uint4*)(W + (int64_t)rb * H) + t;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        constexpr int HU = 4;
+        for (int k0 = 0; k0 < nblk; k0 += HU) {
+            uint4 wa[HU], wb[HU];
+#pragma unroll
+            for (int u = 0; u < HU; u++) {
+                const bool ok = k0 + u < nblk;
+                wa[u] = ok ? cbl_ldg_stream(qa + 4 * (k0 + u)) : make_uint4(0, 0, 0, 0);
+                wb[u] = ok ? cbl_ldg_stream(qb + 4 * (k0 + u)) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < HU; u++) {
+                if (k0 + u < nblk) {
+                    const uint4 xv = xrow[4 * (k0 + u)];
+                    head_mma<T>(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+                    head_mma<T>(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int n = 2 * t + e;
+            if (n < B) {
+                if (v0 + g < V) cbl_store_out(logits, ldtype, (int64_t)n * ldl + v0 + g, acc[e]);
+                if (v0 + g + 8 < V) cbl_store_out(logits, ldtype, (int64_t)n * ldl + v0 + g + 8, acc[2 + e]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------- greedy argmax
 // tok[b] = first index of the largest logit of row b; pos[b] += 1 when pos is given.  A cluster of ARGMAX_CTAS
 // thread blocks per row: every block reduces its share, block 0 collects the others' results through
@@ -705,6 +769,21 @@ extern "C" int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B,
     if (B > HEAD_BMAX || H % 8) return CBL_EUNSUPPORTED;
     if (B == 0) return CBL_OK;
     const cudaStream_t st = (cudaStream_t)s;
+    if (B >= 2 && H % 32 == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)x % 16) == 0 && (size_t)(B + 1) * (H + 8) * 2 <= 200 * 1024) {
+        const size_t smem = (size_t)(B + 1) * (H + 8) * 2;
+        static bool attr_mma[64] = {};
+        int dev = 0;
+        CBL_CUDA(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !attr_mma[dev]) {
+            CBL_CUDA(cudaFuncSetAttribute(k_head_mma<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            CBL_CUDA(cudaFuncSetAttribute(k_head_mma<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr_mma[dev] = true;
+        }
+        int grid = cbl_sm_count() * 4;
+        if (grid > cbl_ceil_div(V, 128)) grid = cbl_ceil_div(V, 128);
+        CBL_BY_TYPE(dtype, return step_launch(k_head_mma<T>, dim3(grid), dim3(256), smem, st, (const T*)W, (const T*)x, (int)B, (int)V, (int)H, logits,
+                                              ldtype, ldl));
+    }
 #define CBL_HEAD(N) case N: CBL_BY_TYPE(dtype, return (head_launch<T, N>(W, x, V, H, logits, ldtype, ldl, st)))
     switch (B) {
         CBL_HEAD(1);
