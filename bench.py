@@ -179,7 +179,7 @@ def build_set(dev, rank: int, world: int, batch: int):
             rs = (torch.rand(r, device=dev, generator=g) * 0.02 + 0.01).half()
             perms = torch.arange(c, device=dev)[None]
             lin = PackedLinear(words, table, rs, None, None, perms, 4096, 8)
-            lin.l8 if (batch == 1 and lin.use_l8()) else lin.t16.xp_buffer(batch)
+            lin.l8 if (batch == 1 and lin.use_l8()) else lin.small_batch(batch).xp_buffer(batch)
             lins.append(lin)
             kinds.append(kind)
             total_bytes += algorithmic_bytes(r, c, batch)
@@ -201,7 +201,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         if B == 1:
             lin.gemv(x[0], y[0])
         else:
-            lin.t16.run(x, y, B)
+            lin.small_batch(B).run(x, y, B)
 
     # batch 1: q|k|v and gate|up share their input and run as one grouped launch each, as the reference merges
     # them (7 matrices per layer -> 4 launches + 4 finish kernels)
@@ -248,8 +248,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         staged = (None, None)             # matrices that share their input share one staging pass of it
         for lin, x, y, kind in items:
             if staged[0] is not x:
-                staged = (x, lin.t16.prep(x, B))
-            lin.t16.run_prepped(staged[1], y, B)
+                staged = (x, lin.small_batch(B).prep(x, B))
+            lin.small_batch(B).run_prepped(staged[1], y, B)
             if world > 1 and kind == "row":
                 dist.all_reduce(y)
 

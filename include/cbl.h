@@ -78,6 +78,20 @@ typedef struct cbl_packed {
  *          shapequant/kernels/batched_runs.py:935-961 (dequant_tile, fp16 / bf16 output). */
 int cbl_dequant(const cbl_packed* m, void* out, int dtype, int64_t ld, int32_t r0, int32_t r1, cbl_stream s);
 
+/* Encoder side ("snap"): index of the nearest codeword of every chunk and its squared error,
+ *   idx[i] = argmin_k (|c_k|^2 - 2 x_i . c_k)   (first k on ties),   err[i] = max(min + |x_i|^2, 0),
+ * all in fp32 (8 FMAs per codeword from |c_k|^2, no reduced-precision contraction).  wt (optional, same shape as x):
+ * per-element weights, argmin_k sum_j wt_j (x_j - c_kj)^2 and err = that minimum.
+ * x, wt fp32 [n, d]; book f16 / bf16 / f32 [K, d]; d = 8, K <= cbl_assign_max_codewords().
+ * replaces shapequant/codebook.py:40-71 (_assign_batch, assign). */
+int cbl_assign_max_codewords(void);
+int cbl_assign(const float* x, const float* wt, int64_t n, int32_t d, const void* book, int bdtype, int32_t K, int64_t* idx, float* err,
+               cbl_stream s);
+
+/* [R, n] tags (low `bits` bits of each int64) -> [R, ceil(n * bits / 32)] int32, a little-endian bit stream per row.
+ * replaces shapequant/packed.py:60-77 (pack_bits). */
+int cbl_pack_tags(const int64_t* vals, int64_t R, int32_t n, int32_t bits, int32_t* words, cbl_stream s);
+
 /* Unpacked tags of plane `plane` (0 or 1) as int32 [R, C/d].
  * replaces shapequant/packed.py:80-90 (unpack_bits) / :246-248 (PackedFile.local_tags). */
 int cbl_unpack_tags(const cbl_packed* m, int plane, int32_t* out, cbl_stream s);
@@ -226,6 +240,32 @@ int32_t cbl_gemm_rows_max_tokens(void);
 size_t cbl_gemm_rows_workspace_bytes(int32_t sum_rows_padded);
 int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* const* ys, int ydtype,
                         int64_t ldy, void* stage, void* workspace, cbl_stream s);
+
+/* ------------------------------------------------------------------------------------------
+ * Activation-stationary layout ("x16") for 16..32 tokens on mma.sync: a warp keeps the activations of its
+ * 128 input columns in registers (A fragments, tokens = M) and walks over the weight rows, 8 at a time
+ * (N = 8): per 8 rows x 128 columns four 16-byte codeword reads per lane feed 8 (16 tokens) or 16 (32
+ * tokens) MMAs, nothing else touches shared memory except the partial sums that the 16 warps of a block
+ * (16 column ranges) add into a 64-row x 32-token tile.  Tags are stored per (column range, block of 64
+ * rows) so that a lane reads its 32 tags (8 row tiles x 4 chunks) with three coalesced 16-byte loads.
+ * d = 8, bits = 12, G = 1, M = 1; books = 2 stored as a second run.
+ * replaces shapequant/kernels/batched_runs.py:745-771 (RunsBatch.run) for batches of 16..32 tokens.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct cbl_x16 {
+    int32_t R, C, books, nkr, nrb;     /* nkr = ceil(C / 128) column ranges, nrb = ceil(R / 64) row blocks */
+    const void* words;                 /* uint4 [books][nkr][nrb][3][32] */
+    const void* table;                 /* fp16 [4096, 8] */
+    const void* table2;                /* fp16 [4096, 8] when books == 2 */
+    const void* row_scale;             /* fp16 [R] */
+} cbl_x16;
+
+size_t cbl_x16_bytes(int32_t R, int32_t C, int32_t books);
+int cbl_repack_x16(const cbl_packed* m, void* out, cbl_stream s);
+/* y[t * ldy + r] = round(row_scale[r] * sum_c W[r, c] x[t, c]) for t < B <= 32.  xp: the activations staged by
+ * cbl_prep_x (M = 1).  workspace: cbl_gemv_x16_workspace_bytes(R) bytes, zero before the first call, left zero
+ * (fp32 sums of products whose columns are split over several blocks). */
+size_t cbl_gemv_x16_workspace_bytes(int32_t R);
+int cbl_gemv_x16(const cbl_x16* m, const void* xp, int32_t B, void* y, int ydtype, int64_t ldy, void* workspace, cbl_stream s);
 
 /* Two-phase prefill for many tokens and for matrices with several column orders: decode the matrix ONCE
  * into a 16-bit scratch, then multiply with a TMA-fed tcgen05 GEMM (both operands by TMA, accumulators in

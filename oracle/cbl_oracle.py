@@ -145,15 +145,62 @@ def round_to(w: np.ndarray, dtype: str) -> np.ndarray:
 
 # --------------------------------------------------------------------------- assign (format definition)
 
-def assign(x: np.ndarray, codebook: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
-    """Nearest codeword per chunk by squared Euclidean distance, argmin of c_sq - 2 x.c
-    (shapequant/codebook.py:40-71, unweighted branch). Returns (idx int64 [n], err fp32 [n])."""
+def assign(x: np.ndarray, codebook: np.ndarray, wt: np.ndarray | None = None) -> tuple[np.ndarray, np.ndarray]:
+    """Nearest codeword per chunk: argmin of c_sq - 2 x.c, or with per-element weights argmin of
+    [-2 w x, w] . [c, c^2] (shapequant/codebook.py:40-71, both branches). Returns (idx int64 [n], err fp32 [n])."""
     xt = torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32))
     c = torch.from_numpy(np.asarray(codebook, dtype=np.float16).astype(np.float32))
-    c_sq = (c * c).sum(1)
-    d2 = torch.addmm(c_sq[None, :], xt, c.T, alpha=-2.0)
-    m, i = d2.min(dim=1)
-    return i.numpy(), (m + (xt * xt).sum(1)).clamp_min(0).numpy()
+    if wt is None:
+        c_sq = (c * c).sum(1)
+        d2 = torch.addmm(c_sq[None, :], xt, c.T, alpha=-2.0)
+        m, i = d2.min(dim=1)
+        return i.numpy(), (m + (xt * xt).sum(1)).clamp_min(0).numpy()
+    w = torch.from_numpy(np.ascontiguousarray(wt, dtype=np.float32))
+    a = torch.cat([-2.0 * w * xt, w], dim=1)
+    b = torch.cat([c, c * c], dim=1)
+    m, i = (a @ b.T).min(dim=1)
+    return i.numpy(), (m + (w * xt * xt).sum(1)).clamp_min(0).numpy()
+
+
+def assign_margin(x: np.ndarray, codebook: np.ndarray, idx: np.ndarray, wt: np.ndarray | None = None) -> np.ndarray:
+    """In float64: (weighted) squared distance to codeword idx[i] minus the smallest distance to any codeword, per
+    chunk. Zero where idx is the exact nearest; a few fp32 ulps of the distances where two codewords all but tie."""
+    x64 = np.asarray(x, dtype=np.float64)
+    c64 = np.asarray(codebook, dtype=np.float16).astype(np.float64)
+    w64 = np.ones_like(x64) if wt is None else np.asarray(wt, dtype=np.float64)
+    out = np.empty(x64.shape[0])
+    for s in range(0, x64.shape[0], 4096):
+        df = x64[s:s + 4096, None, :] - c64[None, :, :]
+        d2 = (w64[s:s + 4096, None, :] * df * df).sum(-1)
+        out[s:s + 4096] = d2[np.arange(d2.shape[0]), np.asarray(idx[s:s + 4096], dtype=np.int64)] - d2.min(1)
+    return out
+
+
+def snap(w: np.ndarray, codebook: np.ndarray, d: int = 8, perm: np.ndarray | None = None, col_weight: np.ndarray | None = None,
+         row_weighted: bool = False) -> dict:
+    """compress() after the codebook fit (shapequant/codebook.py:237-274): permute, row-normalise by the fp16 rms,
+    chunk with zero padding, weights h_c (* row_scale^2) normalised to mean 1 with padding weight 0, assign."""
+    wt_ = torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32))
+    rows, cols = wt_.shape
+    if perm is not None:
+        wt_ = wt_[:, torch.from_numpy(np.asarray(perm, dtype=np.int64))]
+    rms = wt_.pow(2).mean(dim=1).sqrt()
+    row_scale = torch.where(rms == 0, torch.ones_like(rms), rms).to(torch.float16)
+    wn = wt_ / row_scale.to(torch.float32)[:, None]
+    pad = (-cols) % d
+    chunks = torch.nn.functional.pad(wn, (0, pad)).reshape(-1, d)
+    wts = None
+    if col_weight is not None or row_weighted:
+        h = torch.ones(cols) if col_weight is None else torch.from_numpy(np.asarray(col_weight, dtype=np.float32))
+        if perm is not None and col_weight is not None:
+            h = h[torch.from_numpy(np.asarray(perm, dtype=np.int64))]
+        full = h[None, :].expand(rows, cols)
+        if row_weighted:
+            full = full * row_scale.to(torch.float32).pow(2)[:, None]
+        full = full / full.mean()
+        wts = torch.nn.functional.pad(full.contiguous(), (0, pad)).reshape(-1, d).numpy()
+    idx, err = assign(chunks.numpy(), codebook, wts)
+    return {"idx": idx.reshape(rows, -1), "row_scale": row_scale.numpy(), "err": err, "chunks": chunks.numpy(), "wt": wts}
 
 
 # --------------------------------------------------------------------------- linear

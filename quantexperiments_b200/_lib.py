@@ -38,6 +38,12 @@ class T16(Structure):
                 ("table", c_void_p), ("table2", c_void_p), ("row_scale", c_void_p)]
 
 
+class X16(Structure):
+    """struct cbl_x16: activation-stationary layout for 16..32 tokens."""
+    _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("nkr", c_int32), ("nrb", c_int32),
+                ("words", c_void_p), ("table", c_void_p), ("table2", c_void_p), ("row_scale", c_void_p)]
+
+
 class L8(Structure):
     """struct cbl_l8: column-tile layout for the batch-1 product."""
     _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("ntile", c_int32), ("Rpad", c_int32),
@@ -53,11 +59,18 @@ SIGNATURES = {
     "cbl_last_cuda_error": (c_int, []),
     "cbl_dequant": (c_int, [POINTER(Packed), c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p]),
     "cbl_unpack_tags": (c_int, [POINTER(Packed), c_int, c_void_p, c_void_p]),
+    "cbl_assign_max_codewords": (c_int, []),
+    "cbl_assign": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int, c_int32, c_void_p, c_void_p, c_void_p]),
+    "cbl_pack_tags": (c_int, [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
     "cbl_t16_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "cbl_repack_t16": (c_int, [POINTER(Packed), c_void_p, c_int32, c_void_p, c_void_p]),
     "cbl_prep_x_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "cbl_prep_x": (c_int, [c_void_p, c_int, c_int32, c_int32, c_int64, c_void_p, c_int32, c_void_p, c_void_p]),
     "cbl_gemv_t16": (c_int, [POINTER(T16), c_void_p, c_int32, c_void_p, c_int, c_int64, c_void_p]),
+    "cbl_x16_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_repack_x16": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
+    "cbl_gemv_x16_workspace_bytes": (c_size_t, [c_int32]),
+    "cbl_gemv_x16": (c_int, [POINTER(X16), c_void_p, c_int32, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "cbl_l8_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "cbl_repack_l8": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
     "cbl_book_frag_bytes": (c_size_t, []),

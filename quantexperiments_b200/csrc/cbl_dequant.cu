@@ -214,6 +214,59 @@ extern "C" int cbl_repack_t16(const cbl_packed* m, const int32_t* tile_rows, int
     return cbl_check_launch();
 }
 
+// ------------------------------------------------------------------------------------ x16 layout
+//
+// Column range kr = chunks 16 kr .. 16 kr + 15, row block rb = rows 64 rb .. 64 rb + 63.  Lane (g, t) of a warp owns,
+// for each of the block's 8 row tiles rt, the 4 chunks 16 kr + 4 j + t (j = 0..3) of row 64 rb + 8 rt + g: 32 tags,
+// tag index 4 rt + j, packed as a 384-bit little-endian stream = three uint4 at [book][kr][rb][3][32 lanes].
+extern "C" size_t cbl_x16_bytes(int32_t R, int32_t C, int32_t books) {
+    if (R < 0 || C <= 0 || books < 1) return 0;
+    return (size_t)books * cbl_ceil_div(C / 8, 16) * cbl_ceil_div(R, 64) * 96 * 16;
+}
+
+__global__ void __launch_bounds__(128) k_repack_x16(cbl_packed m, int nkr, int nrb, uint4* __restrict__ out, int64_t nthreads) {
+    int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gi >= nthreads) return;
+    const int lane = (int)(gi & 31);
+    int64_t rest = gi >> 5;
+    const int rb = (int)(rest % nrb);
+    rest /= nrb;
+    const int kr = (int)(rest % nkr);
+    const int book = (int)(rest / nkr);
+    const int g = lane >> 2, t = lane & 3;
+    const int nch = m.C / 8;
+    const int32_t* words = book ? m.tags2 : m.tags;
+    uint32_t w[13];
+#pragma unroll
+    for (int i = 0; i < 13; i++) w[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        const int rt = i >> 2, j = i & 3;
+        const int row = rb * 64 + rt * 8 + g, chunk = kr * 16 + 4 * j + t;
+        uint32_t tag = 0;
+        if (row < m.R && chunk < nch) tag = cbl_read_tag(words + (int64_t)row * m.W, m.W, chunk, 12);
+        const int bit = 12 * i;
+        w[bit >> 5] |= tag << (bit & 31);
+        if ((bit & 31) > 20) w[(bit >> 5) + 1] |= tag >> (32 - (bit & 31));
+    }
+    uint4* o = out + (((int64_t)book * nkr + kr) * nrb + rb) * 96 + lane;
+    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[32] = make_uint4(w[4], w[5], w[6], w[7]);
+    o[64] = make_uint4(w[8], w[9], w[10], w[11]);
+}
+
+extern "C" int cbl_repack_x16(const cbl_packed* m, void* out, cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (m->d != 8 || m->bits != 12 || m->G != 1 || m->M != 1) return CBL_EUNSUPPORTED;
+    if (!out || ((uintptr_t)out % 16)) return CBL_EINVAL;
+    const int nkr = cbl_ceil_div(m->C / 8, 16), nrb = cbl_ceil_div(m->R, 64);
+    const int64_t n = (int64_t)m->books * nkr * nrb * 32;
+    if (n == 0) return CBL_OK;
+    k_repack_x16<<<(unsigned)((n + 127) / 128), 128, 0, (cudaStream_t)s>>>(*m, nkr, nrb, (uint4*)out, n);
+    return cbl_check_launch();
+}
+
 // ------------------------------------------------------------------------------------ l8 layout
 //
 // Tile v covers chunk columns 8*(v % ntile1) .. +7 of book v / ntile1.  Row r's 8 tags of the tile

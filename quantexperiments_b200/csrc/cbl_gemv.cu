@@ -326,6 +326,229 @@ extern "C" int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y
 #undef CBL_T16_CASE
 }
 
+// ------------------------------------------------------------------------------------ x16 product
+//
+// Activation-stationary product for up to 32 tokens.  A block owns a run of 64-row blocks (at most X16_NR at a time,
+// their 64 x 32 fp32 sums live in shared memory) and a run of column blocks (8 column ranges of 128 columns, one per
+// warp); two blocks share an SM, so that one block's table load and output overlap the other's products.  For each column block a warp loads its activations once as MMA A fragments (tokens = M) and then walks over
+// the block's rows: per 8 rows x 128 columns four 16-byte codeword reads per lane feed 8 MT MMAs (N = 8 weight
+// rows), and the 8 x 16 MT results are added into the shared sums.  When the columns of a row block are split over
+// several blocks (few rows, many columns) the sums go to a global fp32 accumulator and the last block to arrive
+// writes the output.
+constexpr int X16_WARPS = 8, X16_NR = 5, X16_ASTRIDE = 36, X16_ATILE = 64 * X16_ASTRIDE, X16_TQ = X16_WARPS * 32 / 64;
+
+template <int MT, int RT>
+__device__ __forceinline__ void x16_tile(const uint32_t (&w)[12], const uint4 (&xa)[MT][4][2], uint32_t tbl, float* __restrict__ sa, int g, int t) {
+    uint4 cw[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) cw[j] = j == 0 ? cbl_lds128(tbl + t16_tag_off<4 * RT>(w)) : j == 1 ? cbl_lds128(tbl + t16_tag_off<4 * RT + 1>(w))
+                                      : j == 2 ? cbl_lds128(tbl + t16_tag_off<4 * RT + 2>(w)) : cbl_lds128(tbl + t16_tag_off<4 * RT + 3>(w));
+    float d[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) d[mt][0] = d[mt][1] = d[mt][2] = d[mt][3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            cbl_mma16816(d[mt], xa[mt][j][0].x, xa[mt][j][1].x, xa[mt][j][0].y, xa[mt][j][1].y, cw[j].x, cw[j].y);
+            cbl_mma16816(d[mt], xa[mt][j][0].z, xa[mt][j][1].z, xa[mt][j][0].w, xa[mt][j][1].w, cw[j].z, cw[j].w);
+        }
+    float* o = sa + (RT * 8 + 2 * t) * X16_ASTRIDE + g;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        atomicAdd(o + mt * 16, d[mt][0]);
+        atomicAdd(o + X16_ASTRIDE + mt * 16, d[mt][1]);
+        atomicAdd(o + mt * 16 + 8, d[mt][2]);
+        atomicAdd(o + X16_ASTRIDE + mt * 16 + 8, d[mt][3]);
+    }
+}
+
+template <int MT, int... RT>
+__device__ __forceinline__ void x16_tiles(const uint32_t (&w)[12], const uint4 (&xa)[MT][4][2], uint32_t tbl, float* __restrict__ sa, int g, int t,
+                                          std::integer_sequence<int, RT...>) {
+    (x16_tile<MT, RT>(w, xa, tbl, sa, g, t), ...);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(X16_WARPS * 32, 2)
+k_gemv_x16(cbl_x16 m, const __half* __restrict__ xp, int B, int Bpad, int Cpad, void* __restrict__ y, int ydtype, int64_t ldy,
+           float* __restrict__ acc_g, unsigned int* __restrict__ counters, int Rpad, int PR, int KS) {
+    extern __shared__ __align__(16) unsigned char x16_smem[];
+    uint4* s_table = (uint4*)x16_smem;
+    float* s_acc = (float*)(x16_smem + 65536);
+    __shared__ unsigned int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int pr = blockIdx.x % PR, ks = blockIdx.x / PR;
+    const int rb_lo = (int)((int64_t)pr * m.nrb / PR), rb_hi = (int)((int64_t)(pr + 1) * m.nrb / PR);
+    const int KB = (m.nkr + X16_WARPS - 1) / X16_WARPS;
+    const int kb_lo = (int)((int64_t)ks * KB / KS), kb_hi = (int)((int64_t)(ks + 1) * KB / KS);
+    const uint32_t tbl = cbl_smem_u32(s_table);
+    const uint4* words = (const uint4*)m.words;
+    const float* xinv = (const float*)(xp + (int64_t)Bpad * Cpad);
+    bool waited = false;
+
+    for (int rb0 = rb_lo; rb0 < rb_hi; rb0 += X16_NR) {
+        const int nr = min(X16_NR, rb_hi - rb0);
+        for (int i = tid; i < nr * X16_ATILE; i += X16_WARPS * 32) s_acc[i] = 0.f;
+        for (int book = 0; book < m.books; book++) {
+            __syncthreads();                                   // previous readers of the table, the zeroed sums
+            const uint4* tb = (const uint4*)(book ? m.table2 : m.table);
+            for (int i = tid; i < 4096; i += X16_WARPS * 32) s_table[i] = __ldg(tb + i);
+            if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+            __syncthreads();
+            for (int kb = kb_lo; kb < kb_hi; kb++) {
+                const int kr = kb * X16_WARPS + warp;
+                if (kr >= m.nkr) continue;
+                uint4 xa[MT][4][2];
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int tok = mt * 16 + h * 8 + g;
+                        const uint4* xr = (const uint4*)(xp + (int64_t)tok * Cpad) + kr * 16 + t;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) xa[mt][j][h] = tok < Bpad ? __ldg(xr + 4 * j) : make_uint4(0, 0, 0, 0);
+                    }
+                const uint4* wp = words + (((int64_t)book * m.nkr + kr) * m.nrb + rb0) * 96 + lane;
+                // warps start at different row blocks so that their additions land in different sums
+                int ri = warp % nr;
+                uint32_t w[12];
+                {
+                    const uint4* p = wp + (int64_t)ri * 96;
+#pragma unroll
+                    for (int q = 0; q < 3; q++) { uint4 v = cbl_ldg_stream(p + 32 * q); w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w; }
+                }
+                for (int it = 0; it < nr; it++) {
+                    const int rn = ri + 1 == nr ? 0 : ri + 1;
+                    uint32_t wn[12];
+                    if (it + 1 < nr) {
+                        const uint4* p = wp + (int64_t)rn * 96;
+#pragma unroll
+                        for (int q = 0; q < 3; q++) { uint4 v = cbl_ldg_stream(p + 32 * q); wn[4 * q] = v.x; wn[4 * q + 1] = v.y; wn[4 * q + 2] = v.z; wn[4 * q + 3] = v.w; }
+                    }
+                    x16_tiles<MT>(w, xa, tbl, s_acc + ri * X16_ATILE, g, t, std::make_integer_sequence<int, 8>{});
+                    if (it + 1 < nr) {
+#pragma unroll
+                        for (int k = 0; k < 12; k++) w[k] = wn[k];
+                    }
+                    ri = rn;
+                }
+            }
+        }
+        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+        __syncthreads();
+        const int row = tid & 63, tq = tid >> 6;
+        if (KS == 1) {
+            for (int i = 0; i < nr; i++) {
+                const int r = (rb0 + i) * 64 + row;
+                if (r >= m.R) continue;
+                const float rs = __half2float(((const __half*)m.row_scale)[r]);
+#pragma unroll
+                for (int q = 0; q < 16 * MT / X16_TQ; q++) {
+                    const int tok = tq + X16_TQ * q;
+                    if (tok < B) cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, s_acc[i * X16_ATILE + row * X16_ASTRIDE + tok] * xinv[tok] * rs);
+                }
+            }
+        } else {
+            for (int i = 0; i < nr; i++) {
+                const int r = (rb0 + i) * 64 + row;
+#pragma unroll
+                for (int q = 0; q < 16 * MT / X16_TQ; q++) {
+                    const int tok = tq + X16_TQ * q;
+                    if (tok < B) atomicAdd(acc_g + (int64_t)tok * Rpad + r, s_acc[i * X16_ATILE + row * X16_ASTRIDE + tok]);
+                }
+            }
+            __threadfence();
+            __syncthreads();
+            for (int i = 0; i < nr; i++) {
+                if (tid == 0) s_last = atomicAdd(counters + rb0 + i, 1u) == (unsigned)(KS - 1);
+                __syncthreads();
+                const bool last = s_last != 0;
+                __syncthreads();
+                if (!last) continue;
+                __threadfence();
+                const int r = (rb0 + i) * 64 + row;
+                const float rs = r < m.R ? __half2float(((const __half*)m.row_scale)[r]) : 0.f;
+#pragma unroll
+                for (int q = 0; q < 16 * MT / X16_TQ; q++) {
+                    const int tok = tq + X16_TQ * q;
+                    if (tok < B) {
+                        float* a = acc_g + (int64_t)tok * Rpad + r;
+                        const float v = __ldcg(a);
+                        *a = 0.f;
+                        if (r < m.R) cbl_store_out(y, ydtype, (int64_t)tok * ldy + r, v * xinv[tok] * rs);
+                    }
+                }
+                if (tid == 0) counters[rb0 + i] = 0;
+            }
+        }
+        __syncthreads();
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+extern "C" size_t cbl_gemv_x16_workspace_bytes(int32_t R) {
+    if (R <= 0) return 16;
+    size_t nrb = ((size_t)R + 63) / 64;
+    return 32 * nrb * 64 * 4 + nrb * 4;
+}
+
+// Row parts x column splits of a launch: the fewest block iterations on the longest block, the fewest splits among equals.
+static void x16_shape(int nrb, int KB, int sms, int& PR, int& KS) {
+    long best = -1;
+    PR = 1; KS = 1;
+    for (int ks = 1; ks <= KB && ks <= sms; ks++) {
+        int pr = sms / ks;
+        if (pr > nrb) pr = nrb;
+        if (pr < 1) pr = 1;
+        long cost = (long)cbl_ceil_div(nrb, pr) * cbl_ceil_div(KB, ks);
+        if (best < 0 || cost < best) { best = cost; PR = pr; KS = ks; }
+    }
+}
+
+template <int MT>
+static int launch_x16(const cbl_x16* m, const void* xp, int B, void* y, int ydtype, int64_t ldy, void* workspace, cudaStream_t st) {
+    const size_t smem = 65536 + (size_t)X16_NR * X16_ATILE * sizeof(float);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_gemv_x16<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    int PR, KS;
+    x16_shape(m->nrb, cbl_ceil_div(m->nkr, X16_WARPS), 2 * cbl_sm_count(), PR, KS);   // two blocks per SM
+    const int Bpad = (B + 7) / 8 * 8, Cpad = (m->C + 511) / 512 * 512, Rpad = m->nrb * 64;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(PR * KS);
+    cfg.blockDim = dim3(X16_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    float* acc = (float*)workspace;
+    unsigned int* counters = (unsigned int*)(acc + (size_t)32 * Rpad);
+    CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_x16<MT>, *m, (const __half*)xp, B, Bpad, Cpad, y, ydtype, ldy, acc, counters, Rpad, PR, KS));
+    return cbl_check_launch();
+}
+
+extern "C" int cbl_gemv_x16(const cbl_x16* m, const void* xp, int32_t B, void* y, int ydtype, int64_t ldy, void* workspace, cbl_stream s) {
+    if (!m || !m->words || !m->table || !m->row_scale || !xp || !y || !workspace) return CBL_EINVAL;
+    if (m->books != 1 && m->books != 2) return CBL_EINVAL;
+    if (m->books == 2 && !m->table2) return CBL_EINVAL;
+    if (B < 1 || ldy < m->R || m->C % 8 || m->nkr != cbl_ceil_div(m->C / 8, 16) || m->nrb != cbl_ceil_div(m->R, 64)) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (B > 32) return CBL_EUNSUPPORTED;
+    if (((uintptr_t)m->words % 16) || ((uintptr_t)m->table % 16) || ((uintptr_t)xp % 16) || ((uintptr_t)workspace % 16)) return CBL_EINVAL;
+    if (m->R == 0) return CBL_OK;
+    if (B <= 16) return launch_x16<1>(m, xp, B, y, ydtype, ldy, workspace, (cudaStream_t)s);
+    return launch_x16<2>(m, xp, B, y, ydtype, ldy, workspace, (cudaStream_t)s);
+}
+
 // ------------------------------------------------------------------------------------ l8 product
 //
 // Work decomposition: the (tile, row group) pairs of a matrix, tile-major, are cut into gridDim.x equal

@@ -149,7 +149,7 @@ class _Stage:
             self.ys = [out[:, o:o + l.R] for o, l in zip(self.offs, self.lins)]
         else:
             for l in self.lins:
-                l.t16.xp_buffer(self.B)
+                l.small_batch(self.B).xp_buffer(self.B)
             # one staging pass of the activations serves every matrix of the stage when they share the column orders
             p0 = self.lins[0].dm.perms
             self.share = all(l.dm.M == self.lins[0].dm.M and (l.dm.perms is p0 or (p0 is not None and l.dm.perms is not None
@@ -162,9 +162,9 @@ class _Stage:
         elif self.rows is not None:
             self.rows.gemm_rows(x, self.ys)
         elif self.share:
-            xp = self.lins[0].t16.prep(x, self.B)
+            xp = self.lins[0].small_batch(self.B).prep(x, self.B)
             for o, l in zip(self.offs, self.lins):
-                l.t16.run_prepped(xp, self.out[:, o:o + l.R], self.B)
+                l.small_batch(self.B).run_prepped(xp, self.out[:, o:o + l.R], self.B)
         else:
             for o, l in zip(self.offs, self.lins):
                 l.forward_into(x, self.out[:, o:o + l.R])

@@ -225,6 +225,69 @@ class T16Matrix:
         return Y
 
 
+class X16Matrix:
+    """Activation-stationary layout for 16..32 tokens (one column order): a warp keeps its 128 columns of the
+    batch in registers and walks over the weight rows on mma.sync.  d = 8, 12-bit tags, G = 1, M = 1."""
+
+    BMAX = 32
+
+    def __init__(self, dm: DeviceMatrix):
+        _need_fast(dm)
+        if dm.M != 1:
+            raise ValueError("the x16 layout needs a single column order")
+        self.dm, self.R, self.C, self.books, self.device = dm, dm.R, dm.C, dm.books, dm.device
+        self.nkr, self.nrb = -(-dm.nch // 16), -(-dm.R // 64)
+        nbytes = lib.cbl_x16_bytes(dm.R, dm.C, dm.books)
+        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        self.ws = torch.zeros(max(lib.cbl_gemv_x16_workspace_bytes(dm.R), 16) // 4, dtype=torch.int32, device=dm.device)
+        with torch.cuda.device(dm.device):
+            _lib.check("cbl_repack_x16", lib.cbl_repack_x16(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
+        self._xp: dict[int, torch.Tensor] = {}
+
+    def struct(self) -> _lib.X16:
+        dm = self.dm
+        return _lib.X16(self.R, self.C, self.books, self.nkr, self.nrb, _ptr(self.words), _ptr(dm.table), _ptr(dm.table2),
+                        _ptr(dm.row_scale))
+
+    def nbytes(self) -> int:
+        return self.words.numel() * 4
+
+    def xp_buffer(self, B: int) -> torch.Tensor:
+        nb = -(-B // 8)
+        buf = self._xp.get(nb)
+        if buf is None:
+            buf = self._xp[nb] = torch.empty(lib.cbl_prep_x_bytes(B, self.C, 1) // 2, dtype=torch.float16, device=self.device)
+        return buf
+
+    def prep(self, X: torch.Tensor, B: int) -> torch.Tensor:
+        """Stage a batch once for several matrices with the same input size (q|k|v, gate|up)."""
+        xp = self.xp_buffer(B)
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_prep_x", lib.cbl_prep_x(X.data_ptr(), _dt(X.dtype), B, self.C, X.stride(0), None, 1, xp.data_ptr(), _stream()))
+        return xp
+
+    def run_prepped(self, xp: torch.Tensor, Y: torch.Tensor, B: int) -> torch.Tensor:
+        if B < 1 or B > self.BMAX:
+            raise ValueError(f"batch {B} outside 1..{self.BMAX}")
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_x16", lib.cbl_gemv_x16(ctypes.byref(self.struct()), xp.data_ptr(), B, Y.data_ptr(), _dt(Y.dtype),
+                                                        Y.stride(0) if Y.dim() == 2 else self.R, self.ws.data_ptr(), _stream()))
+        return Y
+
+    def run(self, X: torch.Tensor, Y: torch.Tensor | None = None, B: int | None = None) -> torch.Tensor:
+        """Y [B, R] = X [B, C] . W^T for B <= 32; X and Y with unit column stride."""
+        if X.dim() == 1:
+            X = X[None]
+        B = X.shape[0] if B is None else B
+        if X.shape[-1] != self.C or X.stride(-1) != 1 or X.device != self.device:
+            raise ValueError("X must be [B, C] with unit column stride on the matrix's device")
+        if Y is None:
+            Y = torch.empty(B, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape[-1] != self.R or Y.stride(-1) != 1:
+            raise ValueError("Y must be [B, R] with unit column stride")
+        return self.run_prepped(self.prep(X, B), Y, B)
+
+
 class DenseStack:
     """Matrices that multiply the same activations (q|k|v, gate|up, or a single matrix), for many tokens or
     for matrices with several column orders: every matrix is decoded ONCE into a 16-bit scratch shared by

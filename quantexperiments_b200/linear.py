@@ -30,7 +30,10 @@ DENSE_MIN_TOKENS = 65
 # tokens from which (up to 64) matrices with one column order run on the tensor-core kernel that takes the weight
 # rows as the M side (its cost does not grow with the token count; the mma.sync kernel wins below: 18944 x 3584 pair
 # 66 us at any count against 49 / 63 / 132 us at 8 / 16 / 32 tokens)
-ROWS_MIN_TOKENS = 16
+ROWS_MIN_TOKENS = 17
+# 2..16 tokens, one column order: the activation-stationary mma.sync kernel (18944 x 3584 pair 45 us at 8..16 tokens
+# against 57 / 75 us for the row-tile kernel at 8 / 16 and 64 us for the rows-as-M kernel)
+X16_MIN_TOKENS, X16_MAX_TOKENS = 2, 16
 
 
 def _is_capturing() -> bool:
@@ -81,6 +84,18 @@ class PackedLinear(torch.nn.Module):
         return self._l8
 
     @property
+    def x16(self):
+        if getattr(self, "_x16", None) is None:
+            from .kernels import X16Matrix
+            self._x16 = X16Matrix(self.dm)
+        return self._x16
+
+    def small_batch(self, n: int):
+        """The kernel layout that multiplies n <= 64 tokens by this matrix (prep / run_prepped / run / xp_buffer): the
+        activation-stationary one for 2..16 tokens and one column order, else the row-tile one."""
+        return self.x16 if (self.dm.M == 1 and X16_MIN_TOKENS <= n <= X16_MAX_TOKENS) else self.t16
+
+    @property
     def rows_group(self):
         if getattr(self, "_rows_group", None) is None:
             from .kernels import L8Group
@@ -114,6 +129,8 @@ class PackedLinear(torch.nn.Module):
             return y
         if n == 1 and self.use_l8() and y.is_contiguous():
             self.l8.run(x2[0].contiguous(), y[0])
+        elif X16_MIN_TOKENS <= n <= X16_MAX_TOKENS and self.dm.M == 1:
+            self.x16.run(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
         elif n <= T16Matrix.BMAX and (n < ROWS_MIN_TOKENS or self.dm.M > 1):
             self.t16.run(x2.contiguous(), y, n)
         elif n <= T16Matrix.BMAX:
@@ -179,9 +196,8 @@ class RunsBatch:
         if bmax > T16Matrix.BMAX:
             raise ValueError(f"bmax {bmax} over {T16Matrix.BMAX}")
         self.R, self.C, self.bmax = self.lin.R, self.lin.C, bmax
-        self.t16 = self.lin.t16
-        for b in range(1, bmax + 1, 8):
-            self.t16.xp_buffer(b)
+        for b in range(1, bmax + 1):
+            self.lin.small_batch(b).xp_buffer(b)
 
     def run(self, X: torch.Tensor, Y: torch.Tensor, B: int | None = None) -> torch.Tensor:
         B = X.shape[0] if B is None else B
@@ -190,4 +206,4 @@ class RunsBatch:
             raise ValueError("RunsBatch.run: B <= bmax, X contiguous, X and Y fp16 or bf16")
         if Y.stride(-1) != 1 or Y.shape[-1] != self.R:
             raise ValueError("RunsBatch.run: Y must be [B, R] with unit column stride")
-        return self.t16.run(X, Y, B)
+        return self.lin.small_batch(B).run(X, Y, B)

@@ -63,8 +63,8 @@ class PackedShards:
         for lin in lins:                       # build kernel layouts and staging buffers up front
             if lin.use_l8() or lin.use_gemm():
                 lin.l8
-            for b in range(1, bmax + 1, 8):
-                lin.t16.xp_buffer(b)
+            for b in range(1, bmax + 1):
+                lin.small_batch(b).xp_buffer(b)
         self.stack = DenseStack([lin.dm for lin in lins])     # many tokens / several column orders: decode once, one GEMM
         # one token: all pieces in one launch when they share a column order and the stack is tall enough
         self.group = self.rows = None
@@ -83,6 +83,7 @@ class PackedShards:
         for lin in self.lins:
             n += lin.stored_bytes()
             n += lin._t16.nbytes() if lin._t16 is not None else 0
+            n += lin._x16.nbytes() if getattr(lin, "_x16", None) is not None else 0
             n += lin._l8.nbytes() if lin._l8 is not None else 0
         return n
 
@@ -117,7 +118,7 @@ class PackedShards:
             if M == 1 and lin.use_l8():
                 lin.l8.run(x[0], y[0, off:off + R])
             else:
-                lin.t16.run(x, y[:, off:off + R], M)
+                lin.small_batch(M).run(x, y[:, off:off + R], M)
         return y
 
     def _large(self, x: torch.Tensor) -> torch.Tensor:

@@ -158,6 +158,27 @@ def main() -> None:
     out.update(w=w.numpy(), q4=q4.numpy(), s4=s4.numpy(), ids=ids.numpy(), rows4=packed.q4_embed_rows(q4, s4, ids).numpy(),
                q8=q8.numpy(), s8=s8.numpy(), deq8=deq8.numpy(), rows8=packed.q8_rows(q8, s8, 2, 9).numpy())
     np.savez_compressed(HERE / "blockq.npz", **out)
+
+    # 9. the snap of compress() (shapequant/codebook.py:237-274) with and without weights, and the weighted branch of
+    #    assign (codebook.py:52-55): matrix, weights and the fitted codebook in, tags / row scales / errors out
+    out = {}
+    g = torch.Generator().manual_seed(9)
+    w = torch.randn(48, 200, generator=g) * (torch.rand(48, 1, generator=g) + 0.1)
+    h = torch.rand(200, generator=g) + 0.05
+    perm = torch.randperm(200, generator=torch.Generator().manual_seed(1))
+    for tag, kw in (("plain", {}), ("weighted", dict(col_weight=h, row_weighted=True, perm=perm))):
+        cm, stats = cb.compress(w, 8, 256, iters=3, max_fit_chunks=10_000, seed=4, **kw)
+        out.update({f"{tag}_idx": cm.idx.numpy().astype(np.int32), f"{tag}_codebook": cm.codebook.numpy(),
+                    f"{tag}_row_scale": cm.row_scale.numpy(), f"{tag}_mse": np.array([stats["normalized_chunk_mse"]], dtype=np.float64)})
+    x = torch.randn(500, 8, generator=g)
+    wt = torch.rand(500, 8, generator=g) * 2
+    wt[7] = 0.0
+    book = torch.randn(4096, 8, generator=g).half()
+    i, e = cb.assign(x, book, wt=wt)
+    i0, e0 = cb.assign(x, book)
+    out.update(w=w.numpy(), h=h.numpy(), perm=perm.numpy().astype(np.int32), x=x.numpy(), wt=wt.numpy(), book=book.numpy(),
+               widx=i.numpy().astype(np.int32), werr=e.numpy(), idx=i0.numpy().astype(np.int32), err=e0.numpy())
+    np.savez_compressed(HERE / "snap.npz", **out)
     print("golden fixtures written to", HERE)
 
 

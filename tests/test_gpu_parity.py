@@ -597,3 +597,47 @@ def test_rows_as_m_product_rejects_unsupported_arguments():
     assert _lib.lib.cbl_gemm_rows_max_tokens() == 32
     assert _lib.lib.cbl_gemm_rows_workspace_bytes(128) == 32 * 128 * 4 + 16
 
+
+
+# ------------------------------------------------------------------------------------------ 16..32 tokens, activations stationary
+@pytest.mark.parametrize("R,C,books", [(300, 264, 1), (2304, 896, 1), (129, 8200, 1), (640, 4104, 2), (1100, 3584, 1), (64, 128, 2)])
+def test_activation_stationary_product_matches_fp32_matmul(R, C, books):
+    """cbl_gemv_x16: ragged rows and columns, one and two books, whole-k launches and launches whose columns are
+    split over several blocks (few rows, many columns); the output is a column slice; the work space is left zero."""
+    from quantexperiments_b200.kernels import X16Matrix
+    m = orc.synth_matrix(R, C, seed=R + C + books, books=books)
+    xm = X16Matrix(_dm(m))
+    w = torch.from_numpy(orc.synth_decode(m)).cuda()
+    g = torch.Generator(device="cuda").manual_seed(R)
+    for B in (1, 16, 17, 32):
+        X = torch.randn(B, C, device="cuda", generator=g)
+        X[0, 3] = 2.0e4
+        X = X.bfloat16()
+        ref = X.float() @ w.t()
+        for ydt in (torch.float32, torch.bfloat16):
+            Y = torch.full((B, R + 8), 3.0, device="cuda", dtype=ydt)
+            for _ in range(2):
+                xm.run(X, Y[:, :R])
+                got = Y[:, :R].float()
+                for t in range(B):
+                    assert (got[t] - ref[t]).abs().max() / ref[t].abs().max() <= _out_tol(ydt), (B, ydt, t)
+                assert (Y[:, R:] == 3.0).all()
+    assert (xm.ws == 0).all()
+
+
+def test_activation_stationary_product_rejects_unsupported_arguments():
+    from quantexperiments_b200 import _lib
+    from quantexperiments_b200.kernels import X16Matrix
+    import ctypes
+    xm = X16Matrix(_dm(orc.synth_matrix(64, 64, seed=2)))
+    st = xm.struct()
+    t = torch.zeros(1 << 16, device="cuda", dtype=torch.float16)
+    s = torch.cuda.current_stream().cuda_stream
+    call = lambda B, ldy: _lib.lib.cbl_gemv_x16(ctypes.byref(st), t.data_ptr(), B, t.data_ptr(), 1, ldy, xm.ws.data_ptr(), s)   # noqa: E731
+    assert call(33, 64) == _lib.EUNSUPPORTED
+    assert call(0, 64) == _lib.EINVAL
+    assert call(4, 32) == _lib.EINVAL
+    assert _lib.lib.cbl_gemv_x16_workspace_bytes(100) == 32 * 128 * 4 + 2 * 4
+    assert _lib.lib.cbl_x16_bytes(100, 264, 2) == 2 * 3 * 2 * 96 * 16
+    with pytest.raises(ValueError):
+        X16Matrix(_dm(orc.synth_matrix(64, 64, seed=2, M=4)))

@@ -77,6 +77,23 @@ def test_assign_matches_reference():
     assert np.allclose(err, z["assign_err"], rtol=1e-5, atol=1e-6)
 
 
+def test_weighted_assign_and_snap_match_reference():
+    """Both branches of assign on a 4096-word book, and the snap of compress() (row scales, chunking with padding,
+    weight normalisation, permutation) against what the reference produced from the same matrix and codebook."""
+    z = np.load(G / "snap.npz")
+    idx, err = orc.assign(z["x"], z["book"])
+    assert np.array_equal(idx, z["idx"]) and np.allclose(err, z["err"], rtol=1e-5, atol=1e-6)
+    idx, err = orc.assign(z["x"], z["book"], z["wt"])
+    assert np.array_equal(idx, z["widx"]) and np.allclose(err, z["werr"], rtol=1e-5, atol=1e-6)
+    assert np.all(orc.assign_margin(z["x"], z["book"], z["widx"], z["wt"]) < 1e-4)
+    s = orc.snap(z["w"], z["plain_codebook"])
+    assert np.array_equal(s["row_scale"], z["plain_row_scale"]) and np.array_equal(s["idx"], z["plain_idx"])
+    assert abs(float(s["err"].mean()) - float(z["plain_mse"][0])) < 1e-6
+    s = orc.snap(z["w"], z["weighted_codebook"], perm=z["perm"], col_weight=z["h"], row_weighted=True)
+    assert np.array_equal(s["row_scale"], z["weighted_row_scale"]) and np.array_equal(s["idx"], z["weighted_idx"])
+    assert abs(float(s["err"].mean()) - float(z["weighted_mse"][0])) < 1e-6
+
+
 def test_additive_two_book_decode_is_bit_exact():
     z = np.load(G / "additive.npz")
     w = orc.additive_decode(z["A"], z["B"], z["ta"], z["tb"], z["rs"])
