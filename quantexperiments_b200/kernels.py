@@ -127,12 +127,19 @@ def _need_fast(dm: DeviceMatrix) -> None:
                          f"(got d={dm.d}, bits={dm.bits}, G={dm.G})")
 
 
+def _alloc_i32(n: int, device, alloc=None) -> torch.Tensor:
+    """n int32 elements on `device`: from `alloc` (a loader's arena: alloc(nbytes) -> uint8 view) or the caching allocator."""
+    if alloc is None:
+        return torch.empty(n, dtype=torch.int32, device=device)
+    return alloc(n * 4).view(torch.int32)
+
+
 class T16Matrix:
     """Row-tile layout: rows grouped by column order into tiles of 16; run() multiplies a batch."""
 
     BMAX = 64
 
-    def __init__(self, dm: DeviceMatrix):
+    def __init__(self, dm: DeviceMatrix, alloc=None):
         _need_fast(dm)
         self.dm, self.R, self.C, self.M, self.books, self.device = dm, dm.R, dm.C, dm.M, dm.books, dm.device
         # tiles: rows of one column order, padded with -1 to whole tiles (the reference groups rows
@@ -157,7 +164,7 @@ class T16Matrix:
         self.ntile = self.tile_rows.numel() // 16
         self.nsuper = -(-dm.nch // 64)
         nbytes = lib.cbl_t16_bytes(self.ntile, dm.C, dm.books)
-        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        self.words = _alloc_i32(max(nbytes, 16) // 4, dm.device, alloc)
         with torch.cuda.device(dm.device):
             _lib.check("cbl_repack_t16", lib.cbl_repack_t16(ctypes.byref(dm.struct()), self.tile_rows.data_ptr(), self.ntile,
                                                             self.words.data_ptr(), _stream()))
@@ -231,14 +238,14 @@ class X16Matrix:
 
     BMAX = 32
 
-    def __init__(self, dm: DeviceMatrix):
+    def __init__(self, dm: DeviceMatrix, alloc=None):
         _need_fast(dm)
         if dm.M != 1:
             raise ValueError("the x16 layout needs a single column order")
         self.dm, self.R, self.C, self.books, self.device = dm, dm.R, dm.C, dm.books, dm.device
         self.nkr, self.nrb = -(-dm.nch // 16), -(-dm.R // 64)
         nbytes = lib.cbl_x16_bytes(dm.R, dm.C, dm.books)
-        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
+        self.words = _alloc_i32(max(nbytes, 16) // 4, dm.device, alloc)
         self.ws = torch.zeros(max(lib.cbl_gemv_x16_workspace_bytes(dm.R), 16) // 4, dtype=torch.int32, device=dm.device)
         with torch.cuda.device(dm.device):
             _lib.check("cbl_repack_x16", lib.cbl_repack_x16(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
@@ -368,7 +375,7 @@ def l8_workspace(device: torch.device, R: int, nbytes: int = 0) -> torch.Tensor:
 class L8Matrix:
     """Column-tile layout for the batch-1 product by activation-side tables (one column order)."""
 
-    def __init__(self, dm: DeviceMatrix):
+    def __init__(self, dm: DeviceMatrix, alloc=None):
         _need_fast(dm)
         if dm.M != 1:
             raise ValueError("the table-lookup product supports one column order (M = 1)")
@@ -376,9 +383,9 @@ class L8Matrix:
         self.Rpad = (dm.R + 3) // 4 * 4
         self.ntile = dm.books * (-(-dm.nch // 8))
         nbytes = lib.cbl_l8_bytes(dm.R, dm.C, dm.books)
-        self.words = torch.empty(max(nbytes, 16) // 4, dtype=torch.int32, device=dm.device)
-        self.frag = torch.empty(lib.cbl_book_frag_bytes() // 4, dtype=torch.int32, device=dm.device)
-        self.frag2 = torch.empty_like(self.frag) if dm.books == 2 else None
+        self.words = _alloc_i32(max(nbytes, 16) // 4, dm.device, alloc)
+        self.frag = _alloc_i32(lib.cbl_book_frag_bytes() // 4, dm.device, alloc)
+        self.frag2 = _alloc_i32(lib.cbl_book_frag_bytes() // 4, dm.device, alloc) if dm.books == 2 else None
         with torch.cuda.device(dm.device):
             _lib.check("cbl_repack_l8", lib.cbl_repack_l8(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
             _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table.data_ptr(), self.frag.data_ptr(), _stream()))

@@ -31,9 +31,10 @@ DENSE_MIN_TOKENS = 65
 # rows as the M side (its cost does not grow with the token count; the mma.sync kernel wins below: 18944 x 3584 pair
 # 66 us at any count against 49 / 63 / 132 us at 8 / 16 / 32 tokens)
 ROWS_MIN_TOKENS = 17
-# 2..16 tokens, one column order: the activation-stationary mma.sync kernel (18944 x 3584 pair 45 us at 8..16 tokens
-# against 57 / 75 us for the row-tile kernel at 8 / 16 and 64 us for the rows-as-M kernel)
-X16_MIN_TOKENS, X16_MAX_TOKENS = 2, 16
+# 9..16 tokens, one column order: the activation-stationary mma.sync kernel (18944 x 3584 pair 45 us at any count up to
+# 16, against 72-75 us for the row-tile kernel at 12 / 16 tokens and 64 us for the rows-as-M kernel; up to 8 tokens the
+# row-tile kernel is as fast inside a step: 3.26 / 3.60 ms for the 196-matrix set at 4 / 8 tokens against 3.40 / 3.61)
+X16_MIN_TOKENS, X16_MAX_TOKENS = 9, 16
 
 
 def _is_capturing() -> bool:
