@@ -3,15 +3,22 @@
 //
 // k_assign     each thread keeps CH chunks in registers and scans the whole book from shared memory (fp32, read as
 //              warp-wide broadcasts): 8 fp32 FMAs per (chunk, codeword) starting from |c|^2, i.e. c_sq - 2 x.c in fp32
-//              exactly as the reference states it.  The minimum is tracked per group of four codewords (two min
-//              instructions and one compare per group instead of a compare and two selects per codeword); the winning
+//              exactly as the reference states it.  The minimum is tracked per group of eight codewords (one min per
+//              codeword and one compare per group instead of a compare and two selects per codeword); the winning
 //              group is evaluated once more at the end to name the first codeword that reaches the minimum.
 //              Bound by the fp32 FMA rate, not by memory: 65 kflop per 44 bytes of traffic.
 // k_pack_tags  one thread per 32-bit word of the stream.
 #include "cbl_common.cuh"
 #include <cmath>
 
-constexpr int AS_THREADS = 512;
+constexpr int AS_THREADS = 256, AS_GROUP = 8;
+
+// Three-input minimum (one instruction on sm_100).
+__device__ __forceinline__ float as_min3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 
 template <int CH, bool WT>
 __global__ void __launch_bounds__(AS_THREADS, 1)
@@ -74,20 +81,21 @@ k_assign(const float* __restrict__ x, const float* __restrict__ wt, int64_t n, c
             }
             return d;
         };
-        for (int k4 = 0; k4 < Kpad; k4 += 4) {
-            float d[CH][4];
+        for (int k0 = 0; k0 < Kpad; k0 += AS_GROUP) {
+            float gm[CH];
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const float4 c0 = s_book[2 * (k4 + q)], c1 = s_book[2 * (k4 + q) + 1];
-                const float init = s_init[k4 + q];
+            for (int j = 0; j < CH; j++) gm[j] = INFINITY;
 #pragma unroll
-                for (int j = 0; j < CH; j++) d[j][q] = dist(j, c0, c1, init);
+            for (int q = 0; q < AS_GROUP; q += 2) {
+                const float4 c0 = s_book[2 * (k0 + q)], c1 = s_book[2 * (k0 + q) + 1];
+                const float4 e0 = s_book[2 * (k0 + q) + 2], e1 = s_book[2 * (k0 + q) + 3];
+                const float2 init = *(const float2*)(s_init + k0 + q);
+#pragma unroll
+                for (int j = 0; j < CH; j++) gm[j] = as_min3(gm[j], dist(j, c0, c1, init.x), dist(j, e0, e1, init.y));
             }
 #pragma unroll
-            for (int j = 0; j < CH; j++) {
-                const float m = fminf(fminf(d[j][0], d[j][1]), fminf(d[j][2], d[j][3]));
-                if (m < best[j]) { best[j] = m; bg[j] = k4; }
-            }
+            for (int j = 0; j < CH; j++)
+                if (gm[j] < best[j]) { best[j] = gm[j]; bg[j] = k0; }
         }
 #pragma unroll
         for (int j = 0; j < CH; j++) {
@@ -96,7 +104,7 @@ k_assign(const float* __restrict__ x, const float* __restrict__ wt, int64_t n, c
             int bi = bg[j];
             float bd = INFINITY;
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
+            for (int q = 0; q < AS_GROUP; q++) {
                 const int k = bg[j] + q;
                 const float dq = dist(j, s_book[2 * k], s_book[2 * k + 1], s_init[k]);
                 if (dq < bd) { bd = dq; bi = k; }
@@ -116,23 +124,23 @@ extern "C" int cbl_assign(const float* x, const float* wt, int64_t n, int32_t d,
     if (d != 8 || K > 4096) return CBL_EUNSUPPORTED;
     if (((uintptr_t)x % 16) || (wt && ((uintptr_t)wt % 16))) return CBL_EINVAL;
     if (n == 0) return CBL_OK;
-    const int Kpad = (K + 3) / 4 * 4;
+    const int Kpad = (K + AS_GROUP - 1) / AS_GROUP * AS_GROUP;
     const size_t smem = (size_t)Kpad * 36;
     static bool attr_set[64][2] = {};
     int dev = 0;
     CBL_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev][wt ? 1 : 0]) {
-        if (wt) CBL_CUDA(cudaFuncSetAttribute(k_assign<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 36));
-        else CBL_CUDA(cudaFuncSetAttribute(k_assign<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 36));
+        if (wt) CBL_CUDA(cudaFuncSetAttribute(k_assign<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 36));
+        else CBL_CUDA(cudaFuncSetAttribute(k_assign<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 36));
         attr_set[dev][wt ? 1 : 0] = true;
     }
-    const int ch = wt ? 2 : 4;
+    const int ch = wt ? 4 : 8;
     int64_t blocks = (n + (int64_t)AS_THREADS * ch - 1) / ((int64_t)AS_THREADS * ch);
     const int sms = cbl_sm_count();
     // whole waves: every block scans the same number of chunk batches (the last may be short)
     if (blocks > sms) blocks = sms;
-    if (wt) k_assign<2, true><<<(unsigned)blocks, AS_THREADS, smem, (cudaStream_t)s>>>(x, wt, n, book, bdtype, K, Kpad, idx, err);
-    else k_assign<4, false><<<(unsigned)blocks, AS_THREADS, smem, (cudaStream_t)s>>>(x, wt, n, book, bdtype, K, Kpad, idx, err);
+    if (wt) k_assign<4, true><<<(unsigned)blocks, AS_THREADS, smem, (cudaStream_t)s>>>(x, wt, n, book, bdtype, K, Kpad, idx, err);
+    else k_assign<8, false><<<(unsigned)blocks, AS_THREADS, smem, (cudaStream_t)s>>>(x, wt, n, book, bdtype, K, Kpad, idx, err);
     return cbl_check_launch();
 }
 
