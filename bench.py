@@ -563,6 +563,152 @@ def run_decode(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_snap(args, rank: int, world: int, local_rank: int) -> None:
+    """Encoder side: snap one 18944 x 3584 matrix (8,486,912 chunks, the 7B gate shape) against a 4096-word book and pack
+    the 12-bit tags. A step = assign + pack_bits of the whole matrix. Metric: million chunks per second. The kernel is
+    bound by fp32 FMAs (16 flop per chunk and codeword), so the roofline is the fp32 rate, not HBM. N > 1: replicas."""
+    import torch.distributed as dist
+    from quantexperiments_b200 import codebook as cb
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    R, C, K = 18944, 3584, 4096
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    x = torch.randn(R * C // 8, 8, device=dev, generator=g)
+    book = torch.randn(K, 8, device=dev, generator=g).half()
+    n = x.shape[0]
+
+    def step():
+        idx, err = cb.assign(x, book)
+        return cb.pack_bits(idx.view(R, C // 8), 12), err
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        words, err = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+    # end to end: fp32 chunks from pinned host memory in, packed tags out to the host
+    hx = x.cpu().pin_memory()
+    hw = torch.empty(words.shape, dtype=torch.int32).pin_memory()
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        x.copy_(hx, non_blocking=True)
+        words, err = step()
+        hw.copy_(words, non_blocking=True)
+        torch.cuda.synchronize(dev)
+    s_e2e = (time.perf_counter() - t0) / 3
+    tv = torch.tensor([ms, s_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+    ms, s_e2e = float(tv[0]), float(tv[1])
+    if rank != 0:
+        return
+    # the reference's CPU path (torch addmm + min in batches of 65,536, shapequant/codebook.py:58-71) on a bounded sample
+    from oracle import cbl_oracle as orc
+    ns = 1 << 20
+    xs, bk = x[:ns].cpu().numpy(), book.cpu().numpy()
+    t0 = time.perf_counter()
+    for s0 in range(0, ns, 65536):
+        orc.assign(xs[s0:s0 + 65536], bk)
+    cpu_s = time.perf_counter() - t0
+    flops = n * K * 16.0
+    sm_clock = (clocks.get("sm_mhz") or 1900) * 1e6
+    peak = 148 * 128 * 2 * sm_clock / 1e12
+    line = {"metric": "snap_mchunks_s", "value": n * world / (ms * 1e-3) / 1e6, "unit": "Mchunks/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"snap of one {R} x {C} matrix: {n} chunks of 8 against a {K}-word fp16 book (exact fp32 argmin) + 12-bit packing",
+                       "parallelism": "replicas" if world > 1 else "single", "l2": "inputs larger than L2 (272 MB of chunks per step)"},
+            "clocks": clocks, "gpu_launches": 2 * args.steps * world,
+            "e2e": {"value": n * world / s_e2e / 1e6, "unit": "Mchunks/s", "h2d_bytes_per_step": n * 32, "d2h_bytes_per_step": int(hw.numel()) * 4},
+            "roofline": {"bound": "fp32", "kernel": "k_assign<8,false>", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak,
+                         "peak_source": "148 SMs x 128 FMA x 2 x the SM clock sampled during the run", "unit": "TFLOP/s",
+                         "frac": flops / (ms * 1e-3) / 1e12 / peak, "traffic": None},
+            "cpu_baseline": {"value": ns / cpu_s / 1e6, "unit": "Mchunks/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"{ns} chunks through the oracle's assign (torch addmm + min, batches of 65,536)"}}
+    print(json.dumps(line), flush=True)
+
+
+def run_load(args, rank: int, world: int, local_rank: int) -> None:
+    """Packed file -> device: writes a synthetic packed file of --tokens/512 7B layers (default 4 layers = 28 matrices,
+    177 MB) to a temporary directory, then times load_linears (streamed copies + in-place kernel layouts, l8 and x16).
+    A step = one full load. Metric: file GB per second. N > 1: every rank loads its own shard (tensor parallel kinds)."""
+    import tempfile
+    import torch.distributed as dist
+    from quantexperiments_b200 import loader, packed
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    layers = max(1, args.tokens // 512)
+    kinds = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, f"m{rank}.safetensors")
+        g = torch.Generator().manual_seed(1)
+        mats = {}
+        for li in range(layers):
+            for name, r, c, kind in SHAPES_7B:
+                W = (c // 8 * 12 + 31) // 32
+                t = {"tags": torch.randint(-2**31, 2**31 - 1, (r, W), dtype=torch.int32, generator=g), "table": torch.randn(4096, 8, generator=g).half(),
+                     "row_scale": (torch.rand(r, generator=g) * 0.02 + 0.01).half()}
+                meta = {"R": r, "C": c, "d": 8, "K": 4096, "G": 1, "M": 1, "seed": 0, "perm_crc": 0, "bits": r * W * 32}
+                mats[f"l{li}.{name}"] = (t, meta)
+                kinds[f"l{li}.{name}"] = kind
+        packed.save(path, mats, base_model="synthetic/7b-shapes")
+        del mats
+        nbytes = os.path.getsize(path)
+
+        def step():
+            lins = loader.load_linears(path, device=dev, layouts=("l8", "x16"), rank=rank, world=world, kinds=kinds)
+            return lins.stats
+
+        for _ in range(2):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            stats = step()
+        torch.cuda.synchronize(dev)
+        s = (time.perf_counter() - t0) / args.steps
+        # the reference's way: one tensor at a time (PackedLinear.from_packed), layouts built after each copy
+        from quantexperiments_b200.linear import PackedLinear
+        pf = packed.PackedFile(path)
+        t0 = time.perf_counter()
+        for name in list(pf.meta)[:7]:
+            lin = PackedLinear.from_packed(pf, name, device=dev)
+            lin.l8, lin.x16
+        torch.cuda.synchronize(dev)
+        s_one = (time.perf_counter() - t0) * len(pf.meta) / 7
+    tv = torch.tensor([s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+    s = float(tv[0])
+    if rank != 0:
+        return
+    line = {"metric": "packed_load_gbs", "value": nbytes / s / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": 2,
+            "ms_per_step": s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": f"load of a packed file with {layers} layers of Qwen2.5-7B shapes ({nbytes} bytes, page cache warm) into one arena "
+                                   f"with the l8 and x16 kernel layouts", "parallelism": f"tp{world}" if world > 1 else "single",
+                       "timing": "host wall clock around load_linears (the path is host-driven: file read, pinned copy, H2D, repack kernels)"},
+            "gpu_launches": 3 * len(kinds) * args.steps, "arena_bytes": stats["arena_bytes"], "h2d_bytes_per_step": stats["h2d_bytes"],
+            "tensor_by_tensor_ms": s_one * 1e3}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline_sample() -> dict:
     """The reference's CPU path (oracle port) timed on this host's cores on a bounded sample."""
     from oracle import cbl_oracle as orc
@@ -592,7 +738,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill", "decode"],
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "prefill", "decode", "snap", "load"],
                     help="gemv: decode products (the headline metric); prefill: the same 196 matrices against --tokens tokens; "
                          "decode: end-to-end generation (prompt --tokens, --steps generated tokens, --batch sequences)")
     ap.add_argument("--tokens", type=int, default=2048)
@@ -616,6 +762,10 @@ def main() -> None:
             run_prefill(args, rank, world, local_rank)
         elif args.workload == "decode":
             run_decode(args, rank, world, local_rank)
+        elif args.workload == "snap":
+            run_snap(args, rank, world, local_rank)
+        elif args.workload == "load":
+            run_load(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:
