@@ -663,7 +663,8 @@ def run_load(args, rank: int, world: int, local_rank: int) -> None:
                 W = (c // 8 * 12 + 31) // 32
                 t = {"tags": torch.randint(-2**31, 2**31 - 1, (r, W), dtype=torch.int32, generator=g), "table": torch.randn(4096, 8, generator=g).half(),
                      "row_scale": (torch.rand(r, generator=g) * 0.02 + 0.01).half()}
-                meta = {"R": r, "C": c, "d": 8, "K": 4096, "G": 1, "M": 1, "seed": 0, "perm_crc": 0, "bits": r * W * 32}
+                crc = packed.perm_crc(packed.seeded_perms(c, 1, torch.Generator(device="cpu").manual_seed(0)))
+                meta = {"R": r, "C": c, "d": 8, "K": 4096, "G": 1, "M": 1, "seed": 0, "perm_crc": crc, "bits": r * W * 32}
                 mats[f"l{li}.{name}"] = (t, meta)
                 kinds[f"l{li}.{name}"] = kind
         packed.save(path, mats, base_model="synthetic/7b-shapes")
