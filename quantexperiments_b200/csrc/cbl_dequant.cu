@@ -1,4 +1,6 @@
 // Dense decode, tag unpacking and the load-time re-layouts (file layout -> kernel layouts).
+#include <cstdlib>
+#include <type_traits>
 #include "cbl_common.cuh"
 
 int g_cbl_last_cuda_error = 0;
@@ -109,6 +111,114 @@ __global__ void __launch_bounds__(256) k_dequant(cbl_packed m, OutT* __restrict_
     }
 }
 
+// The benchmark format (d = 8, 12-bit tags, one table per book, one column order) and at least a few hundred rows: the
+// book(s) live in shared memory, a warp walks a row 256 chunks at a time (tags straight from the row's bit stream, one
+// 16-byte codeword read per chunk, one 16- or 32-byte store), same arithmetic as k_dequant.  HBM-write bound.
+constexpr int DQ_THREADS = 512;
+template <typename OutT, int BOOKS>
+__global__ void __launch_bounds__(DQ_THREADS, 2) k_dequant_book(cbl_packed m, OutT* __restrict__ out, int64_t ld, int r0, int r1) {
+    extern __shared__ __align__(16) unsigned char dq_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    {
+        uint4* dst = (uint4*)dq_smem;
+        const uint4* t0 = (const uint4*)m.table;
+        for (int i = tid; i < 4096; i += DQ_THREADS) dst[i] = __ldg(t0 + i);
+        if (BOOKS == 2) {
+            const uint4* t1 = (const uint4*)m.table2;
+            for (int i = tid; i < 4096; i += DQ_THREADS) dst[4096 + i] = __ldg(t1 + i);
+        }
+    }
+    __syncthreads();
+    const uint32_t sb = cbl_smem_u32(dq_smem);
+    const int nch = m.C >> 3;
+    constexpr int NB = (sizeof(OutT) == 2 && BOOKS == 1) ? 8 : 4;   // chunks per lane in flight
+    auto tag_of = [&](const int32_t* rw, int j) {
+        const uint32_t bit = 12u * (uint32_t)j, w = bit >> 5, sh = bit & 31u;
+        const uint32_t lo = (uint32_t)__ldg(rw + w);
+        const uint32_t hi = (sh > 20u && (int)(w + 1) < m.W) ? (uint32_t)__ldg(rw + w + 1) : 0u;
+        return (__funnelshift_r(lo, hi, sh) & 0xFFFu) << 4;
+    };
+    for (int r = r0 + blockIdx.x * (DQ_THREADS / 32) + warp; r < r1; r += gridDim.x * (DQ_THREADS / 32)) {
+        const int32_t* rw = m.tags + (int64_t)r * m.W;
+        const int32_t* rw2 = BOOKS == 2 ? m.tags2 + (int64_t)r * m.W : nullptr;
+        const float rs = __half2float(((const __half*)m.row_scale)[r]);
+        OutT* orow = out + (int64_t)(r - r0) * ld;
+        for (int j0 = 0; j0 < nch; j0 += 32 * NB) {
+            uint4 cw[NB], cw2[BOOKS == 2 ? NB : 1];
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const int j = j0 + 32 * i + lane;
+                cw[i] = make_uint4(0, 0, 0, 0);
+                if (j < nch) {
+                    cw[i] = cbl_lds128(sb + tag_of(rw, j));
+                    if (BOOKS == 2) cw2[i] = cbl_lds128(sb + 65536u + tag_of(rw2, j));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const int j = j0 + 32 * i + lane;
+                if (j >= nch) continue;
+                const __half2* h = (const __half2*)&cw[i];
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(h[e]);
+                    v[2 * e] = f.x;
+                    v[2 * e + 1] = f.y;
+                }
+                if (BOOKS == 2) {
+                    const __half2* h2 = (const __half2*)&cw2[i];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(h2[e]);
+                        v[2 * e] = __fadd_rn(v[2 * e], f.x);
+                        v[2 * e + 1] = __fadd_rn(v[2 * e + 1], f.y);
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = __fmul_rn(v[e], rs);
+                OutT* o = orow + j * 8;
+                if (sizeof(OutT) == 4) {
+                    float4* o4 = (float4*)o;
+                    o4[0] = make_float4(v[0], v[1], v[2], v[3]);
+                    o4[1] = make_float4(v[4], v[5], v[6], v[7]);
+                } else {
+                    uint4 pk;                                      // two values per conversion instruction
+                    uint32_t* pw = (uint32_t*)&pk;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        if (std::is_same<OutT, __half>::value) {
+                            const __half2 h2 = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                            pw[e] = *(const uint32_t*)&h2;
+                        } else {
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                            pw[e] = *(const uint32_t*)&b2;
+                        }
+                    }
+                    *(uint4*)o = pk;
+                }
+            }
+        }
+    }
+}
+
+template <typename OutT, int BOOKS>
+static int launch_dequant_book(const cbl_packed* m, void* out, int64_t ld, int r0, int r1, cudaStream_t st) {
+    const size_t smem = (size_t)BOOKS * 65536;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CBL_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        CBL_CUDA(cudaFuncSetAttribute(k_dequant_book<OutT, BOOKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    int grid = cbl_sm_count() * (BOOKS == 1 ? 2 : 1);
+    const int need = cbl_ceil_div(r1 - r0, DQ_THREADS / 32);
+    if (grid > need) grid = need;
+    k_dequant_book<OutT, BOOKS><<<grid, DQ_THREADS, smem, st>>>(*m, (OutT*)out, ld, r0, r1);
+    return cbl_check_launch();
+}
+
 template <typename OutT>
 static int launch_dequant(const cbl_packed* m, void* out, int64_t ld, int r0, int r1, cudaStream_t st) {
     int64_t n = (int64_t)(r1 - r0) * (m->C / m->d);
@@ -117,6 +227,13 @@ static int launch_dequant(const cbl_packed* m, void* out, int64_t ld, int r0, in
     if (blocks > 0x7fffffffLL) return CBL_EUNSUPPORTED;
     bool vec = m->M == 1 && m->d == 8 && (ld % 8 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)m->table % 16 == 0) &&
                (m->books == 1 || (uintptr_t)m->table2 % 16 == 0);
+    // enough rows to pay for staging the book(s) in every block: the shared-memory kernel
+    static int generic = -1;                                   // CBL_DEQUANT_GENERIC=1: always the generic kernel (comparisons)
+    if (generic < 0) { const char* e = getenv("CBL_DEQUANT_GENERIC"); generic = (e && atoi(e) == 1) ? 1 : 0; }
+    if (!generic && vec && m->bits == 12 && m->G == 1 && !m->row_book && (int64_t)(r1 - r0) * m->C >= (1 << 22)) {
+        if (m->books == 1) return launch_dequant_book<OutT, 1>(m, out, ld, r0, r1, st);
+        return launch_dequant_book<OutT, 2>(m, out, ld, r0, r1, st);
+    }
     if (vec) k_dequant<OutT, 8, true><<<(unsigned)blocks, 256, 0, st>>>(*m, (OutT*)out, ld, r0, n);
     else k_dequant<OutT, 0, false><<<(unsigned)blocks, 256, 0, st>>>(*m, (OutT*)out, ld, r0, n);
     return cbl_check_launch();

@@ -641,3 +641,24 @@ def test_activation_stationary_product_rejects_unsupported_arguments():
     assert _lib.lib.cbl_x16_bytes(100, 264, 2) == 2 * 3 * 2 * 96 * 16
     with pytest.raises(ValueError):
         X16Matrix(_dm(orc.synth_matrix(64, 64, seed=2, M=4)))
+
+
+@pytest.mark.parametrize("R,C,books", [(1200, 3608, 1), (700, 6152, 2)])
+def test_large_decode_with_the_book_in_shared_memory_equals_the_generic_decode(R, C, books):
+    """From 4 M weights on, the benchmark format decodes through the kernel that keeps the book(s) in shared memory:
+    bit-equal to the generic kernel (reached through row ranges below the threshold) and, in fp32, to the oracle."""
+    m = orc.synth_matrix(R, C, seed=R + books, books=books)
+    dm = _dm(m)
+    ref = orc.synth_decode(m)
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        whole = dm.dequant(dtype=dt)
+        parts = torch.cat([dm.dequant(dtype=dt, rows=(r, min(r + 200, R))) for r in range(0, R, 200)])
+        assert torch.equal(whole, parts), dt
+        if dt == torch.float32:
+            assert np.array_equal(whole.cpu().numpy(), ref)
+    big = torch.full((R + 3, C + 8), float("nan"), device="cuda", dtype=torch.bfloat16)      # a row range into a wider scratch
+    from quantexperiments_b200 import _lib
+    import ctypes
+    _lib.check("cbl_dequant", _lib.lib.cbl_dequant(ctypes.byref(dm.struct()), big.data_ptr(), _lib.BF16, C + 8, 0, R,
+                                                   torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(big[:R, :C], dm.dequant(dtype=torch.bfloat16)) and torch.isnan(big[:R, C:]).all() and torch.isnan(big[R:]).all()
