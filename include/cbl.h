@@ -131,42 +131,78 @@ int cbl_prep_x(const void* x, int xdtype, int32_t B, int32_t C, int64_t ldx, con
 int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y, int ydtype, int64_t ldy, cbl_stream s);
 
 /* ------------------------------------------------------------------------------------------
- * Column-tile layout ("l8") for the batch-1 product by activation-side tables: per tile of 8
- * chunk columns the kernel computes T[c][e] = <table[e], x_chunk_c> once (tensor cores) into
- * shared memory and every weight chunk becomes one 4-byte table read and one add.
- * d = 8, bits = 12, G = 1, M = 1; books = 2 is stored as a second run of tiles.
- * replaces shapequant/kernels/gemv.py:142-162 (PackedLinear.gemv) and
- *          shapequant/kernels/proto_runs.py:505-571 (gemv) for batch 1.
+ * Column-tile layout ("l8"): a tile = 8 chunk columns (64 weight columns); the 8 tags of a row and tile
+ * form a 96-bit stream, word k of it stored at [tile][k][row position] (books = 2: a second run of tiles).
+ * Two variants share the struct:
+ *   rot = 0  tags in column order, rows in matrix order, Rpad = R rounded up to 4, one column order:
+ *            read by the tensor-core products cbl_gemm_l8 / cbl_gemm_rows_multi (cbl_repack_l8);
+ *   rot = 1  the batch-1 layout (cbl_repack_l8r): slot s of the stream at row position p holds chunk
+ *            column (s + p) mod 8, so that the lanes of a warp read different columns at the same time;
+ *            rows may be grouped by column order (row_index, seg_off), Rpad is a multiple of 32.
+ * d = 8, bits = 12, G = 1.
+ * replaces shapequant/kernels/proto_runs.py:322-336, 380-388 (pack_lane_major, make_tiles: load-time re-layout
+ *          of the tags into the kernel's order, rows grouped by column order).
  * ------------------------------------------------------------------------------------------ */
+#define CBL_L8_MAX_ORDERS 16
 typedef struct cbl_l8 {
-    int32_t R, C, books, ntile, Rpad;   /* ntile counts both books' tiles; Rpad = R rounded up to 4 */
+    int32_t R, C, books, ntile, Rpad;   /* ntile counts both books' tiles */
+    int32_t rot;                        /* 0 or 1, see above */
+    int32_t M;                          /* column orders (rot = 1; at most CBL_L8_MAX_ORDERS), else 1 */
+    int32_t reserved;
     const void* words;                  /* uint32 [ntile][3][Rpad] */
     const void* frag;                   /* the 4096 x 8 book in tensor-core fragment order (cbl_repack_book) */
     const void* frag2;                  /* second book when books == 2 */
-    const void* row_scale;
+    const void* row_scale;              /* fp16 [R], by source row */
     const void* table;                  /* the book as stored, fp16 [4096, 8] (used by cbl_gemm_l8) */
     const void* table2;
+    const int32_t* row_index;           /* rot = 1: source row of each row position, -1 = padding; NULL = identity */
+    const int32_t* perms;               /* rot = 1, M > 1: int32 [M][C], the activation index of every stored column */
+    int32_t seg_off[CBL_L8_MAX_ORDERS + 1];  /* rot = 1 (read on the HOST): positions [seg_off[m], seg_off[m+1]) hold the rows
+                                           of column order m; multiples of 32, seg_off[0] = 0, seg_off[M] = Rpad */
+    int32_t reserved2;
 } cbl_l8;
 
 size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books);
 int cbl_repack_l8(const cbl_packed* m, void* out, cbl_stream s);
+/* The rot = 1 layout: out = cbl_l8r_bytes(Rpad, C, books) bytes; row_index as in the struct (device pointer or NULL). */
+size_t cbl_l8r_bytes(int32_t Rpad, int32_t C, int32_t books);
+int cbl_repack_l8r(const cbl_packed* m, const int32_t* row_index, int32_t Rpad, void* out, cbl_stream s);
 
 /* A 4096 x 8 fp16 book re-ordered so that one 128-bit load per lane yields the mma.m16n8k8 A fragments
- * of two 16-codeword blocks (64 KB, done once at load time; no counterpart in the reference, whose
- * kernels copy the book to shared memory as stored: shapequant/kernels/cuda_gemv.py:129-141). */
+ * of two 16-codeword blocks, followed by the largest magnitude of the book as one float (64 KB + 16 B, done
+ * once at load time; no counterpart in the reference, whose kernels copy the book to shared memory as stored:
+ * shapequant/kernels/cuda_gemv.py:129-141). */
 size_t cbl_book_frag_bytes(void);
 int cbl_repack_book(const void* table, void* out, cbl_stream s);
 
-/* Work space of cbl_gemv_l8: fp32 row accumulators and a status word.  It must be zero before
- * the first call; every call leaves it zero again.  Calls that share a work space must not
- * overlap on the device. */
+/* Batch-1 product by activation-side tables on the rot = 1 layout:
+ *   y[r] = round_to(ydtype, row_scale[r] * sum_j <table[tag[r, j]], x[perms[m_r][8 j .. 8 j + 7]]>)   (perms = identity for M = 1)
+ * Per tile the kernel computes T[e][c] = <table[e], x_chunk_c> once on the tensor cores (fp16 with a power-of-two
+ * scale per tile, two alternating 64 KB tables in shared memory) and every weight chunk becomes one 2-byte
+ * shared-memory read and one fp32 add.  Blocks that share rows add their fp32 partial sums into 64-bit fixed-point
+ * accumulators (integer addition: the result does not depend on the arrival order, repeated calls agree bit for
+ * bit); the last block of a row range scales, rounds, writes y and clears the accumulators - one kernel per call.
+ * x must be finite (a NaN or infinity anywhere in x turns the whole output into NaN).
+ * Work space: cbl_gemv_l8_workspace_bytes(R) bytes, zero before the first call; every completed call leaves it
+ * zero again.  Calls that share a work space must not overlap on the device.
+ * replaces shapequant/kernels/gemv.py:28-64, 142-162 (_gemv_kernel, PackedLinear.gemv) and
+ *          shapequant/kernels/proto_runs.py:412-473, 505-571 (gemv_additive, gemv) for batch 1, including their
+ *          input-side use of the column orders (proto_runs.py:500-502, prep_x). */
 size_t cbl_gemv_l8_workspace_bytes(int32_t R);
 int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s);
 
-/* Up to 4 matrices that read the same activation vector (q|k|v, gate|up) as ONE launch: their tiles
- * form one work list, so launch, table-build and tail latencies are paid once.  ys[i] receives matrix
- * i's output; the work space must hold the sum of cbl_gemv_l8_workspace_bytes(R_i) bytes, zero on
- * entry, left zero.
+/* The work split cbl_gemv_l8_multi would use for a group on a device of max_blocks SMs, computed on the host
+ * (no device needed; only R, C-derived ntile, M, Rpad and seg_off of the structs are read): every block takes
+ * one rectangle of (row positions x tiles) of one matrix and column order, cut so that the slowest block is
+ * as fast as possible under a cost model of table builds and lookups.  out: int32 [max_blocks][8] =
+ * {matrix, column order, row part, tile splits of that part, first row position, rows, first tile, end tile}.
+ * replaces the launch-shape heuristics of shapequant/kernels/proto_runs.py:505-571 (blocks per SM, split-K). */
+int cbl_gemv_l8_plan(const cbl_l8* mats, int32_t n, int32_t max_blocks, int32_t* out, int32_t* nblocks);
+
+/* Up to 4 matrices that read the same activation vector (q|k|v, gate|up) as ONE launch: the blocks are
+ * shared out over all their (rows x tiles) rectangles, so launch and first-table latencies are paid once.
+ * ys[i] receives matrix i's output; the work space is the matrices' regions back to back
+ * (cbl_gemv_l8_workspace_bytes(R_i) bytes each), zero on entry, left zero.
  * replaces the merged q|k|v and gate|up launches of shapequant/kernels/decode_e2e.py:453-485
  *          (merge_runs) and the per-piece loop of shapequant/vllm_ext/core.py:376-384 (_small). */
 int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
@@ -186,30 +222,35 @@ int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* y, int ydty
                    int32_t world, cbl_stream s);
 /* CBL_ETIMEOUT if, since the last query, a peer's word did not arrive within the bounded wait of a
  * cbl_gemv_l8_ar call on this rank's work space (that call's output is invalid; the GPU context stays
- * usable).  Synchronises the stream and clears the word. */
+ * usable and the next call on the same work space is correct again: every call overwrites the sums it
+ * publishes).  Synchronises the stream and clears the word. */
 int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s);
 
 /* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
- * the work space and leaves.  This call synchronises the stream and returns CBL_OK or CBL_ETIMEOUT.
+ * the work space and leaves (the work space must then be zeroed again before its next use).  This call
+ * synchronises the stream, clears the word and returns CBL_OK or CBL_ETIMEOUT.
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
-int cbl_gemv_l8_status(const void* workspace, int32_t R, cbl_stream s);
+int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s);
 
 /* The same batch-1 product for callers that cannot hand the library any device memory of their
  * own making (hosts that pre-partition the whole GPU into private pools, or plugin contracts that
- * forbid allocator calls while serving).  The accumulators live in a fixed array compiled into the
- * library: at most cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED);
- * 256 KB + 256 B of every GPU that loads the library stay reserved until the process exits.
+ * forbid allocator calls while serving).  The product's work space lives in a fixed array compiled into
+ * the library: at most cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED);
+ * about 776 KB of every GPU that loads the library stay reserved until the process exits.
  * The call allocates and frees nothing.  Its first use on a device looks the array's device address
- * up (cudaGetSymbolAddress), so make that first call before any stream capture.  All calls share
- * the one array: the call clears what it needs on its stream before launching, and two such
+ * up (cudaGetSymbolAddress, under a lock), so make that first call before any stream capture.  All calls
+ * share the one array: the call clears what it needs on its stream before launching, and two such
  * products that overlap on the GPU (different streams, or a replayed graph beside a live call)
- * race on it - serialise them.  Results equal cbl_gemv_l8's up to the order of the fp32 reductions.
+ * race on it - serialise them.  Results equal cbl_gemv_l8's bit for bit.
+ * cbl_gemv_l8_static_status(R, s): the bounded-wait status of such products of R rows since the last query
+ * (CBL_OK or CBL_ETIMEOUT; synchronises the stream, clears the word, allocates nothing).
  * No counterpart in the reference (its launchers allocate through torch / CuPy). */
 int32_t cbl_gemv_l8_static_max_rows(void);
 int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s);
+int cbl_gemv_l8_static_status(int32_t R, cbl_stream s);
 
 /* ------------------------------------------------------------------------------------------
- * Prefill product on the same column-tile layout: y[t*ldy + r] = round_to(ydtype, row_scale[r] *
+ * Prefill product on the column-tile layout (rot = 0): y[t*ldy + r] = round_to(ydtype, row_scale[r] *
  * sum_c W[r, c] * x[t*ldx + c]) for t < ntok.  W tiles are decoded into shared memory and multiplied
  * with tcgen05.mma (fp16 x fp16, fp32 accumulation in tensor memory); x is staged as fp16 with a
  * power-of-two scale per token in `stage` (cbl_gemm_stage_bytes).  `workspace`: at least 4 bytes,

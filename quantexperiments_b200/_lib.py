@@ -44,11 +44,16 @@ class X16(Structure):
                 ("words", c_void_p), ("table", c_void_p), ("table2", c_void_p), ("row_scale", c_void_p)]
 
 
+L8_MAX_ORDERS = 16
+
+
 class L8(Structure):
-    """struct cbl_l8: column-tile layout for the batch-1 product."""
+    """struct cbl_l8: column-tile layout (rot = 1: the batch-1 product; rot = 0: the tensor-core products)."""
     _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("ntile", c_int32), ("Rpad", c_int32),
+                ("rot", c_int32), ("M", c_int32), ("reserved", c_int32),
                 ("words", c_void_p), ("frag", c_void_p), ("frag2", c_void_p), ("row_scale", c_void_p),
-                ("table", c_void_p), ("table2", c_void_p)]
+                ("table", c_void_p), ("table2", c_void_p), ("row_index", c_void_p), ("perms", c_void_p),
+                ("seg_off", c_int32 * (L8_MAX_ORDERS + 1)), ("reserved2", c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/cbl.h declares
@@ -73,12 +78,16 @@ SIGNATURES = {
     "cbl_gemv_x16": (c_int, [POINTER(X16), c_void_p, c_int32, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "cbl_l8_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "cbl_repack_l8": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
+    "cbl_l8r_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
+    "cbl_repack_l8r": (c_int, [POINTER(Packed), c_void_p, c_int32, c_void_p, c_void_p]),
     "cbl_book_frag_bytes": (c_size_t, []),
     "cbl_repack_book": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cbl_gemv_l8_workspace_bytes": (c_size_t, [c_int32]),
     "cbl_gemv_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "cbl_gemv_l8_plan": (c_int, [POINTER(L8), c_int32, c_int32, c_void_p, c_void_p]),
     "cbl_gemv_l8_static_max_rows": (c_int32, []),
     "cbl_gemv_l8_static": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "cbl_gemv_l8_static_status": (c_int, [c_int32, c_void_p]),
     "cbl_gemm_stage_bytes": (c_size_t, [c_int32, c_int32]),
     "cbl_gemm_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "cbl_gemm_l8_2sm": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),

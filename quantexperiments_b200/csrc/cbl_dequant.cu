@@ -228,8 +228,11 @@ static int launch_dequant(const cbl_packed* m, void* out, int64_t ld, int r0, in
     bool vec = m->M == 1 && m->d == 8 && (ld % 8 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)m->table % 16 == 0) &&
                (m->books == 1 || (uintptr_t)m->table2 % 16 == 0);
     // enough rows to pay for staging the book(s) in every block: the shared-memory kernel
-    static int generic = -1;                                   // CBL_DEQUANT_GENERIC=1: always the generic kernel (comparisons)
-    if (generic < 0) { const char* e = getenv("CBL_DEQUANT_GENERIC"); generic = (e && atoi(e) == 1) ? 1 : 0; }
+#ifdef CBL_DEQUANT_GENERIC
+    const bool generic = true;                                 // build option: always the generic kernel (comparisons)
+#else
+    const bool generic = false;
+#endif
     if (!generic && vec && m->bits == 12 && m->G == 1 && !m->row_book && (int64_t)(r1 - r0) * m->C >= (1 << 22)) {
         if (m->books == 1) return launch_dequant_book<OutT, 1>(m, out, ld, r0, r1, st);
         return launch_dequant_book<OutT, 2>(m, out, ld, r0, r1, st);

@@ -15,16 +15,6 @@
 #include <cuda.h>
 #include "cbl_common.cuh"
 
-#ifdef CBL_TRACE
-// Debug builds only: per-block phase timestamps (ns) for offline inspection.
-__device__ unsigned long long g_cbl_trace_gemm[1024 * 16];
-__device__ __forceinline__ unsigned long long cbl_now_gemm() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define CBL_GMARK(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024 && blockIdx.y == 0) g_cbl_trace_gemm[blockIdx.x * 16 + (i)] = cbl_now_gemm(); } while (0)
-extern "C" int cbl_trace_read_gemm(unsigned long long* host) { return (int)cudaMemcpyFromSymbol(host, g_cbl_trace_gemm, sizeof(g_cbl_trace_gemm)); }
-#else
-#define CBL_GMARK(i) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int GM_BM = 256;                 // tokens per tile (2 accumulators of 128)
@@ -743,7 +733,6 @@ k_gemm_rows_ta(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    CBL_GMARK(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int mi = 0;
     while (mi + 1 < P.n && (int)blockIdx.x >= P.tile0[mi + 1]) mi++;
@@ -781,9 +770,7 @@ k_gemm_rows_ta(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
-    CBL_GMARK(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    CBL_GMARK(2);          // the staged activations (and zeroed sums) come from earlier kernels
     // A wait that expires marks the block aborted; every thread then keeps the shape of its loops (the decode
     // warps meet at a named barrier when the book changes) but waits for nothing more.
     auto wait = [&](uint32_t bar, uint32_t parity) {
@@ -881,15 +868,12 @@ k_gemm_rows_ta(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a(s));
-                if (it < 8) CBL_GMARK(3 + it);
                 wa = na; wb = nb; wc = nc;
             }
         }
         // ---------------- epilogue: decode warps 0..3 read TMEM lanes (= W rows) 32 w ..; columns = tokens
-        CBL_GMARK(11);
         if (warp < 4) {
             wait(tmem_full, 0);
-            CBL_GMARK(12);
             const bool ok = *(volatile int*)&s_abort == 0;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int r = r0 + warp * 32 + lane;
@@ -913,10 +897,8 @@ k_gemm_rows_ta(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
         }
     }
-    CBL_GMARK(13);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    CBL_GMARK(14);
     if (s_abort && tid == 0) atomicExch(status, 1u);
     if (warp == GR_DECODE_WARPS) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1262,7 +1244,7 @@ static int gemm_l8_impl(const cbl_l8* m, const void* x, int xdtype, int32_t ntok
     if (m->books != 1 && m->books != 2) return CBL_EINVAL;
     if (m->books == 2 && (!m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
     if (m->books == 2 && two_sm) return CBL_EUNSUPPORTED;      // the two-SM variant executes one book
-    if (m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+    if (m->rot != 0 || m->R <= 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
     if (ntok <= 0 || ldx < m->C || ldy < m->R) return CBL_EINVAL;
     if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
     if (((uintptr_t)stage % 16) || ((uintptr_t)m->table % 16) || ((uintptr_t)workspace % 4)) return CBL_EINVAL;
@@ -1424,8 +1406,11 @@ extern "C" int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void*
     const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
     const int esz = ydtype == CBL_F32 ? 4 : 2;
     const int vec_ok = ((uintptr_t)y % 16 == 0) && ((ldy * esz) % 16 == 0) && ((uintptr_t)row_scale % 16 == 0);
-    static int variant = -1;                                  // CBL_DENSE_1SM=1 selects the one-block kernel (for comparisons)
-    if (variant < 0) { const char* e = getenv("CBL_DENSE_1SM"); variant = (e && atoi(e) == 1) ? 1 : 2; }
+#ifdef CBL_DENSE_1SM
+    const int variant = 1;                                    // build option: the one-block kernel (for comparisons)
+#else
+    const int variant = 2;
+#endif
     if (variant == 2) {
         // box of the pair kernel: 128 tokens / 128 weight rows per block
         {
@@ -1488,7 +1473,7 @@ extern "C" int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x,
         if (!m->words || !m->table || !m->row_scale || !ys[i]) return CBL_EINVAL;
         if (m->books != 1 && m->books != 2) return CBL_EINVAL;
         if (m->books == 2 && (!m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
-        if (m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
+        if (m->rot != 0 || m->R < 0 || m->C <= 0 || m->C % 8 || m->Rpad != (m->R + 3) / 4 * 4 || m->ntile != m->books * cbl_ceil_div(m->C / 8, 8)) return CBL_EINVAL;
         if (m->C != mats[0].C || m->books != mats[0].books || ldx < m->C || ldy < m->R || ((uintptr_t)m->table % 16)) return CBL_EINVAL;
         if (m->R == 0) continue;
         P.m[P.n] = *m;
@@ -1534,8 +1519,11 @@ extern "C" int cbl_gemm_rows_multi(const cbl_l8* mats, int32_t n, const void* x,
         CBL_CUDA(cudaFuncSetAttribute(k_gemm_rows_ta, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM));
         attr_set[dev] = true;
     }
-    static int ta = -1;                                        // CBL_ROWS_SMEM_A=1: the A tile through shared memory (comparisons)
-    if (ta < 0) { const char* e = getenv("CBL_ROWS_SMEM_A"); ta = (e && atoi(e) == 1) ? 0 : 1; }
+#ifdef CBL_ROWS_SMEM_A
+    const int ta = 0;                                          // build option: the A tile through shared memory (comparisons)
+#else
+    const int ta = 1;
+#endif
     const float* xinv = (const float*)((const __half*)stage + (int64_t)Mpad * Cpad);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -359,46 +359,95 @@ class DenseStack:
 
 
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
+_RETIRED: list[torch.Tensor] = []       # outgrown work spaces stay alive: a captured graph may still point at them
 
 
 def l8_workspace(device: torch.device, R: int, nbytes: int = 0) -> torch.Tensor:
-    """Zero-initialised work space shared by every L8 product on (device, current stream): the kernel
-    leaves it zero. Products that may overlap on the device (different streams) get distinct buffers."""
+    """Zero-initialised work space shared by every L8 product on (device, current stream): the kernels
+    leave it zero. Products that may overlap on the device (different streams) get distinct buffers.
+    4 MB to begin with (a group of four 65536-row matrices needs 3.2 MB); a larger request gets a new buffer
+    and the old one is kept, so pointers handed out earlier (CUDA graphs) stay valid."""
     key = (device.index, _stream())
     need = max(lib.cbl_gemv_l8_workspace_bytes(R), nbytes)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
-        ws = _WORKSPACES[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _RETIRED.append(ws)
+        ws = _WORKSPACES[key] = torch.zeros(max(need, 4 << 20), dtype=torch.uint8, device=device)
     return ws
 
 
 class L8Matrix:
-    """Column-tile layout for the batch-1 product by activation-side tables (one column order)."""
+    """Column-tile layouts of one matrix.
+
+    The batch-1 layout (tags rotated by row position, rows grouped by column order; any number of column
+    orders up to 16) is built at construction and read by run() / L8Group.run().  The column-ordered variant
+    that the tensor-core products read (gemm(), L8Group.gemm_rows(); one column order) is built on first use,
+    so a matrix that only ever sees one token keeps a single copy of its tags."""
+
+    MAX_ORDERS = _lib.L8_MAX_ORDERS
 
     def __init__(self, dm: DeviceMatrix, alloc=None):
         _need_fast(dm)
-        if dm.M != 1:
-            raise ValueError("the table-lookup product supports one column order (M = 1)")
-        self.dm, self.R, self.C, self.books, self.device = dm, dm.R, dm.C, dm.books, dm.device
-        self.Rpad = (dm.R + 3) // 4 * 4
+        if dm.M > self.MAX_ORDERS:
+            raise ValueError(f"the table-lookup product supports at most {self.MAX_ORDERS} column orders (got {dm.M})")
+        self.dm, self.R, self.C, self.M, self.books, self.device = dm, dm.R, dm.C, dm.M, dm.books, dm.device
         self.ntile = dm.books * (-(-dm.nch // 8))
-        nbytes = lib.cbl_l8_bytes(dm.R, dm.C, dm.books)
+        self._alloc = alloc
+        # row positions: rows of one column order are contiguous, every order padded to a multiple of 32 rows
+        # (the reference groups rows by order the same way, shapequant/kernels/proto_runs.py:380-388)
+        if dm.M > 1:
+            mask = dm.row_mask.cpu().to(torch.int64)
+            parts, seg = [], [0]
+            for m in range(dm.M):
+                r = torch.nonzero(mask == m).flatten()
+                pad = (-r.numel()) % 32
+                parts.append(torch.cat([r, torch.full((pad,), -1, dtype=torch.int64)]))
+                seg.append(seg[-1] + r.numel() + pad)
+            self.row_index = torch.cat(parts).to(torch.int32).to(dm.device).contiguous()
+            self.seg_off = seg
+        else:
+            self.row_index = None
+            self.seg_off = [0, (dm.R + 31) // 32 * 32]
+        self.Rpad = self.seg_off[-1]
+        nbytes = lib.cbl_l8r_bytes(self.Rpad, dm.C, dm.books)
         self.words = _alloc_i32(max(nbytes, 16) // 4, dm.device, alloc)
         self.frag = _alloc_i32(lib.cbl_book_frag_bytes() // 4, dm.device, alloc)
         self.frag2 = _alloc_i32(lib.cbl_book_frag_bytes() // 4, dm.device, alloc) if dm.books == 2 else None
+        self.words_c = None                     # column-ordered variant, see struct_c()
         with torch.cuda.device(dm.device):
-            _lib.check("cbl_repack_l8", lib.cbl_repack_l8(ctypes.byref(dm.struct()), self.words.data_ptr(), _stream()))
+            _lib.check("cbl_repack_l8r", lib.cbl_repack_l8r(ctypes.byref(dm.struct()), _ptr(self.row_index), self.Rpad,
+                                                            self.words.data_ptr(), _stream()))
             _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table.data_ptr(), self.frag.data_ptr(), _stream()))
             if dm.books == 2:
                 _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table2.data_ptr(), self.frag2.data_ptr(), _stream()))
 
     def struct(self) -> _lib.L8:
+        """The batch-1 layout (rot = 1)."""
         dm = self.dm
-        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, _ptr(self.words), _ptr(self.frag), _ptr(self.frag2),
-                       _ptr(dm.row_scale), _ptr(dm.table), _ptr(dm.table2))
+        seg = (ctypes.c_int32 * (_lib.L8_MAX_ORDERS + 1))(*(self.seg_off + [0] * (_lib.L8_MAX_ORDERS + 1 - len(self.seg_off))))
+        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, 1, self.M, 0, _ptr(self.words), _ptr(self.frag),
+                       _ptr(self.frag2), _ptr(dm.row_scale), _ptr(dm.table), _ptr(dm.table2), _ptr(self.row_index),
+                       _ptr(dm.perms), seg, 0)
+
+    def struct_c(self) -> _lib.L8:
+        """The column-ordered layout (rot = 0) of the tensor-core products; built on first use."""
+        dm = self.dm
+        if dm.M != 1:
+            raise ValueError("the tensor-core products on the column-tile layout support one column order (M = 1)")
+        if self.words_c is None:
+            nbytes = lib.cbl_l8_bytes(dm.R, dm.C, dm.books)
+            self.words_c = _alloc_i32(max(nbytes, 16) // 4, dm.device, None)
+            with torch.cuda.device(dm.device):
+                _lib.check("cbl_repack_l8", lib.cbl_repack_l8(ctypes.byref(dm.struct()), self.words_c.data_ptr(), _stream()))
+        seg = (ctypes.c_int32 * (_lib.L8_MAX_ORDERS + 1))()
+        return _lib.L8(self.R, self.C, self.books, self.ntile, (self.R + 3) // 4 * 4, 0, 1, 0, _ptr(self.words_c), _ptr(self.frag),
+                       _ptr(self.frag2), _ptr(dm.row_scale), _ptr(dm.table), _ptr(dm.table2), None, None, seg, 0)
 
     def nbytes(self) -> int:
-        return self.words.numel() * 4 + self.frag.numel() * 4 * self.books
+        n = self.words.numel() * 4 + self.frag.numel() * 4 * self.books
+        n += self.words_c.numel() * 4 if self.words_c is not None else 0
+        return n + (self.row_index.numel() * 4 if self.row_index is not None else 0)
 
     def run_static(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         """y [R] = W . x using the scratch array built into the library instead of a work-space tensor:
@@ -413,6 +462,11 @@ class L8Matrix:
             _lib.check("cbl_gemv_l8_static", lib.cbl_gemv_l8_static(ctypes.byref(self.struct()), x.data_ptr(), _dt(x.dtype),
                                                                     yv.data_ptr(), _dt(y.dtype), _stream()))
         return y
+
+    def static_status(self) -> None:
+        """Synchronises and raises CblError if a run_static() product gave up on a bounded device-side wait."""
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_l8_static_status", lib.cbl_gemv_l8_static_status(self.R, _stream()))
 
     _stage: dict = {}
 
@@ -439,8 +493,8 @@ class L8Matrix:
         ws = l8_workspace(self.device, self.R)
         with torch.cuda.device(self.device):
             fn = lib.cbl_gemm_l8_2sm if two_sm else lib.cbl_gemm_l8
-            _lib.check("cbl_gemm_l8", fn(ctypes.byref(self.struct()), X.data_ptr(), _dt(X.dtype), T, X.stride(0), Y.data_ptr(),
-                                         _dt(Y.dtype), Y.stride(0), st.data_ptr(), ws.data_ptr() + self.Rpad * 4, _stream()))
+            _lib.check("cbl_gemm_l8", fn(ctypes.byref(self.struct_c()), X.data_ptr(), _dt(X.dtype), T, X.stride(0), Y.data_ptr(),
+                                         _dt(Y.dtype), Y.stride(0), st.data_ptr(), ws.data_ptr() + ws.numel() - 16, _stream()))
         return Y
 
     def status(self, workspace: torch.Tensor | None = None) -> None:
@@ -449,10 +503,13 @@ class L8Matrix:
         with torch.cuda.device(self.device):
             _lib.check("cbl_gemv_l8_status", lib.cbl_gemv_l8_status(ws.data_ptr(), self.R, _stream()))
 
-    def run(self, x: torch.Tensor, y: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
-        """y [R] = W . x for x [C] (f16 / bf16 / f32, contiguous)."""
+    def run(self, x: torch.Tensor, y: torch.Tensor | None = None, workspace: torch.Tensor | None = None, wide: bool = False) -> torch.Tensor:
+        """y [R] = W . x for x [C] (f16 / bf16 / f32, contiguous).  wide=True (matrices with column orders only): x is
+        longer than C and the column orders index into it (a tensor-parallel input shard reading the full vector)."""
         x = x.reshape(-1)
-        if x.numel() != self.C or not x.is_contiguous() or x.device != self.device:
+        if wide and self.M == 1:
+            raise ValueError("wide activations need column orders")
+        if (x.numel() != self.C and not wide) or not x.is_contiguous() or x.device != self.device:
             raise ValueError("x must be a contiguous [C] vector on the matrix's device")
         if y is None:
             y = torch.empty(self.R, dtype=x.dtype, device=self.device)
@@ -479,11 +536,20 @@ class L8Group:
             raise ValueError("grouped matrices share the input size and the device")
         self.mats, self.C, self.device = mats, mats[0].C, mats[0].device
         self.Rs = [m.R for m in mats]
-        self._structs = (_lib.L8 * len(mats))(*[m.struct() for m in mats])
+        self._built = None
+        self._structs_c = None                  # column-ordered variants, built by the first gemm_rows()
         self._ys = (ctypes.c_void_p * len(mats))()
         self.ws_bytes = sum(lib.cbl_gemv_l8_workspace_bytes(m.R) for m in mats)
-        self.rows_ws_bytes = lib.cbl_gemm_rows_workspace_bytes(sum(m.Rpad for m in mats))
+        self.rows_ws_bytes = lib.cbl_gemm_rows_workspace_bytes(sum((m.R + 3) // 4 * 4 for m in mats))
         self._rows_stage: dict = {}
+
+    @property
+    def _structs(self):
+        """The matrices' batch-1 descriptors; rebuilt when a matrix's buffers have moved (loader.pool_layouts)."""
+        key = tuple(m.words.data_ptr() for m in self.mats)
+        if self._built is None or self._built[0] != key:
+            self._built = (key, (_lib.L8 * len(self.mats))(*[m.struct() for m in self.mats]))
+        return self._built[1]
 
     def gemm_rows(self, X: torch.Tensor, ys: list[torch.Tensor]) -> list[torch.Tensor]:
         """A few dozen tokens on the tensor cores with the weight rows as the M side: ys[i] [B, R_i] = X [B, C] . W_i^T.
@@ -510,8 +576,10 @@ class L8Group:
             st = self._rows_stage[key] = torch.empty(lib.cbl_gemm_stage_bytes(lib.cbl_gemm_rows_max_tokens(), self.C), dtype=torch.uint8,
                                                      device=self.device)
         ws = l8_workspace(self.device, 0, self.rows_ws_bytes)
+        if self._structs_c is None:
+            self._structs_c = (_lib.L8 * len(self.mats))(*[m.struct_c() for m in self.mats])
         with torch.cuda.device(self.device):
-            _lib.check("cbl_gemm_rows_multi", lib.cbl_gemm_rows_multi(self._structs, len(self.mats), X.data_ptr(), _dt(X.dtype), B, X.stride(0),
+            _lib.check("cbl_gemm_rows_multi", lib.cbl_gemm_rows_multi(self._structs_c, len(self.mats), X.data_ptr(), _dt(X.dtype), B, X.stride(0),
                                                                       self._ys, _dt(ys[0].dtype), ldy, st.data_ptr(), ws.data_ptr(), _stream()))
         return ys
 

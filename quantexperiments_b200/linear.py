@@ -104,7 +104,8 @@ class PackedLinear(torch.nn.Module):
         return self._rows_group
 
     def use_l8(self) -> bool:
-        return self.dm.M == 1 and self.R >= L8_MIN_ROWS
+        """One token runs on the table-lookup kernel (any number of column orders up to its limit)."""
+        return self.dm.M <= L8Matrix.MAX_ORDERS and self.R >= L8_MIN_ROWS
 
     def use_gemm(self) -> bool:
         """The tensor-core kernel that decodes weight tiles on the fly executes one column order (one or two

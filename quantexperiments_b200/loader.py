@@ -72,7 +72,15 @@ def _t16_tiles(R: int, M: int, row_mask: torch.Tensor | None) -> int:
     return int(sum(-(-int(c) // 16) for c in counts if int(c) > 0))
 
 
-def matrix_bytes(m: dict, R: int, C: int, layouts, ntile16: int) -> dict:
+def _l8_positions(R: int, M: int, row_mask: torch.Tensor | None) -> int:
+    """Row positions of the batch-1 layout: every column order padded to a multiple of 32 rows."""
+    if M == 1 or row_mask is None:
+        return (R + 31) // 32 * 32
+    counts = torch.bincount(row_mask.to(torch.int64).flatten(), minlength=M)
+    return int(sum((int(c) + 31) // 32 * 32 for c in counts))
+
+
+def matrix_bytes(m: dict, R: int, C: int, layouts, ntile16: int, rpad8: int | None = None) -> dict:
     """Aligned device bytes of one matrix piece: file-order tensors and each requested layout."""
     bits = int(math.log2(m["K"]))
     W = pk.words_per_row(C // m["d"], bits)
@@ -86,10 +94,11 @@ def matrix_bytes(m: dict, R: int, C: int, layouts, ntile16: int) -> dict:
     for lay in layouts:
         if lay not in LAYOUTS:
             raise ValueError(f"unknown layout {lay!r}")
-        if not fast or (lay in ("l8", "x16") and m["M"] > 1):
+        if not fast or (lay == "x16" and m["M"] > 1) or (lay == "l8" and m["M"] > L8Matrix.MAX_ORDERS):
             continue
         if lay == "l8":
-            out["l8"] = _al(max(lib.cbl_l8_bytes(R, C, 1), 16)) + _al(lib.cbl_book_frag_bytes())
+            rp = rpad8 if rpad8 is not None else (R + 31) // 32 * 32
+            out["l8"] = _al(max(lib.cbl_l8r_bytes(rp, C, 1), 16)) + _al(lib.cbl_book_frag_bytes())
         elif lay == "x16":
             out["x16"] = _al(max(lib.cbl_x16_bytes(R, C, 1), 16))
         else:
@@ -110,12 +119,12 @@ def plan_arena(pf: pk.PackedFile, names=None, layouts=("l8",), rank: int = 0, wo
                                       "activation vector; build it with tp.RowParallelLinear")
         R, C = _shard_meta(m, kind, rank, world)
         mask = None
-        if m["M"] > 1 and "t16" in layouts:
+        if m["M"] > 1 and ("t16" in layouts or "l8" in layouts):
             mask = pf.f.get_tensor(f"{name}.row_mask")
             if world > 1 and kind == "col":
                 r0, r1 = tp.row_range(m["R"], rank, world)
                 mask = mask[r0:r1]
-        plan[name] = matrix_bytes(m, R, C, layouts, _t16_tiles(R, m["M"], mask))
+        plan[name] = matrix_bytes(m, R, C, layouts, _t16_tiles(R, m["M"], mask), _l8_positions(R, m["M"], mask))
     return plan
 
 
@@ -212,7 +221,9 @@ def load_linears(path_or_file, names=None, device="cuda", layouts=("l8",), rank:
 def pool_layouts(linears) -> int:
     """Move the kernel layouts (and file-order tensors) of PackedLinears that were built one by one into one exact-size
     buffer per device and repoint them; the per-tensor allocations are released. Call before capturing CUDA graphs
-    that use these matrices (the launchers read the pointers at every call). Returns the bytes now pooled."""
+    that use these matrices: single-matrix launchers and L8Group read the pointers at every call, but a captured
+    graph, a PeerReduceGemv or a decode engine built earlier keeps the old addresses (build those afterwards).
+    Returns the bytes now pooled."""
     lins = [l for l in linears if not getattr(l, "_pooled", False)]
     pooled = 0
     for dev in {l.dm.device for l in lins}:
@@ -220,8 +231,8 @@ def pool_layouts(linears) -> int:
         for l in (x for x in lins if x.dm.device == dev):
             objs = [l.dm] + [o for o in (l._l8, l._t16, getattr(l, "_x16", None)) if o is not None]
             for o in objs:
-                for attr in ("tags", "tags2", "table", "table2", "row_scale", "row_book", "row_mask", "perms", "words", "frag", "frag2",
-                             "tile_rows", "tile_mask"):
+                for attr in ("tags", "tags2", "table", "table2", "row_scale", "row_book", "row_mask", "perms", "words", "words_c", "frag", "frag2",
+                             "row_index", "tile_rows", "tile_mask"):
                     v = getattr(o, attr, None)
                     if isinstance(v, torch.Tensor):
                         slots.append((o, attr, v))

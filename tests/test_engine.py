@@ -2,6 +2,7 @@
 restatement of one Qwen2 decode step (weights decoded by the CPU oracle). The restatement rounds to the
 model's 16-bit type at the same places as the reference engine (shapequant/kernels/decode_e2e.py:63-309),
 so the operator tests are tight (a 16-bit ulp) and the end-to-end logits agree to 2e-2 of their range."""
+import ctypes
 import math
 
 import numpy as np
@@ -277,7 +278,8 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
     # shapes the fused forms refuse
     assert L.lib.cbl_gemv_l8_rope_kv(grp._structs, xq.data_ptr(), dtc, None, pos.data_ptr(), NH + 1, NKV, HD, 1e6, max_len, qo.data_ptr(),
                                      kc.data_ptr(), vc.data_ptr(), dtc, ws, s) == L.EINVAL
-    big = (L.L8 * 1)(L.L8(8196, 64, 1, 1, 8196, 16, 16, None, 16, None, None))
+    seg = (ctypes.c_int32 * (L.L8_MAX_ORDERS + 1))(0, 8224)
+    big = (L.L8 * 1)(L.L8(8196, 64, 1, 1, 8224, 1, 1, 0, 16, 16, None, 16, None, None, None, None, seg, 0))
     assert L.lib.cbl_gemv_l8_add_norm(big, xq.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s) == L.EUNSUPPORTED
 
 

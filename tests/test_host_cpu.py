@@ -41,7 +41,61 @@ def test_size_queries_match_the_layout_arithmetic():
     assert lib.cbl_l8_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
     assert lib.cbl_l8_bytes(4863, 896, 2) == 2 * 14 * 3 * 4864 * 4
     assert lib.cbl_prep_x_bytes(3, 896, 16) == 16 * 8 * 1024 * 2 + 16 * 8 * 4
-    assert lib.cbl_gemv_l8_workspace_bytes(18944) >= 18944 * 4 + 4
+    # batch-1 layout: rows padded to 32 positions; work space = int64 + fp32 sums per position, counters, status
+    assert lib.cbl_l8r_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
+    assert lib.cbl_l8r_bytes(4864 + 32, 896, 2) == 2 * 14 * 3 * 4896 * 4
+    assert lib.cbl_book_frag_bytes() == 65536 + 16
+    assert lib.cbl_gemv_l8_workspace_bytes(18944) == (18944 + 512) * 12 + 1024
+    assert lib.cbl_gemv_l8_static_max_rows() == 65536
+
+
+def _l8_shape(R, C, books=1, seg=None):
+    Rpad = (R + 31) // 32 * 32 if seg is None else seg[-1]
+    seg = seg or [0, Rpad]
+    arr = (ctypes.c_int32 * (_lib.L8_MAX_ORDERS + 1))(*(seg + [0] * (_lib.L8_MAX_ORDERS + 1 - len(seg))))
+    return _lib.L8(R, C, books, books * (-(-(C // 8) // 8)), Rpad, 1, len(seg) - 1, 0, None, None, None, None, None, None, None, None, arr, 0)
+
+
+@pytest.mark.parametrize("shapes,sms", [
+    ([(3584, 3584), (512, 3584), (512, 3584)], 148), ([(18944, 3584), (18944, 3584)], 148), ([(3584, 18944)], 148),
+    ([(4864, 896)], 148), ([(4, 64)], 148), ([(27648, 5120, 2), (27648, 5120, 2)], 148), ([(3584, 3584)], 20),
+    ([(5120, 5120, 2, [0, 320, 672, 960, 1312, 1600, 1952, 2240, 2592, 2880, 3232, 3520, 3872, 4160, 4512, 4800, 5152])], 148),
+    ([(70000, 128)], 132)])
+def test_batch1_work_split_covers_every_row_and_tile_exactly_once(shapes, sms):
+    """The host plan of the table-lookup product: rectangles (row positions x tiles) that partition every
+    (matrix, column order); at most 4096 rows per block; one wave of blocks."""
+    lib = _lib.lib
+    mats = [_l8_shape(*sh) for sh in shapes]
+    arr = (_lib.L8 * len(mats))(*mats)
+    out = np.zeros((160, 8), np.int32)
+    nb = ctypes.c_int32(0)
+    assert lib.cbl_gemv_l8_plan(arr, len(mats), sms, out.ctypes.data, ctypes.byref(nb)) == _lib.OK
+    assert 1 <= nb.value <= min(sms, 160)
+    cover = [np.zeros((m.Rpad // 32, m.ntile), np.int32) for m in mats]
+    parts = {}
+    for mi, order, part, splits, row0, rows, t0, t1 in out[:nb.value]:
+        m = mats[mi]
+        assert rows > 0 and rows % 32 == 0 and row0 % 32 == 0 and rows <= 4096 and 0 <= t0 < t1 <= m.ntile
+        assert m.seg_off[order] <= row0 and row0 + rows <= m.seg_off[order + 1]      # one column order per block
+        cover[mi][row0 // 32:(row0 + rows) // 32, t0:t1] += 1
+        parts.setdefault(part, []).append((mi, row0, rows, splits))
+    for c in cover:
+        assert (c == 1).all()
+    for part, blocks in parts.items():                # the blocks of a part share rows and know how many they are
+        assert len({b[:3] for b in blocks}) == 1 and all(b[3] == len(blocks) for b in blocks)
+    assert len(parts) <= 192                          # one arrival counter each
+
+
+def test_batch1_work_split_rejects_what_it_cannot_place():
+    lib = _lib.lib
+    out = np.zeros((160, 8), np.int32)
+    nb = ctypes.c_int32(0)
+    m = (_lib.L8 * 1)(_l8_shape(70000, 128))
+    assert lib.cbl_gemv_l8_plan(m, 1, 8, out.ctypes.data, ctypes.byref(nb)) == _lib.EUNSUPPORTED    # 18 row parts of <= 4096 rows need 18 blocks
+    assert lib.cbl_gemv_l8_plan(None, 1, 8, out.ctypes.data, ctypes.byref(nb)) == _lib.EINVAL
+    bad = _l8_shape(64, 64)
+    bad.rot = 0
+    assert lib.cbl_gemv_l8_plan((_lib.L8 * 1)(bad), 1, 8, out.ctypes.data, ctypes.byref(nb)) == _lib.EINVAL
 
 
 def test_null_and_bad_arguments_are_rejected_without_a_device():
