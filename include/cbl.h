@@ -137,7 +137,7 @@ int cbl_gemv_t16(const cbl_t16* m, const void* xp, int32_t B, void* y, int ydtyp
  *   rot = 0  tags in column order, rows in matrix order, Rpad = R rounded up to 4, one column order:
  *            read by the tensor-core products cbl_gemm_l8 / cbl_gemm_rows_multi (cbl_repack_l8);
  *   rot = 1  the batch-1 layout (cbl_repack_l8r): slot s of the stream at row position p holds chunk
- *            column (s + p) mod 8, so that the lanes of a warp read different columns at the same time;
+ *            column (s + p / 4) mod 8, so that the lanes of a warp (4 rows each) read different columns at the same time;
  *            rows may be grouped by column order (row_index, seg_off), Rpad is a multiple of 32.
  * d = 8, bits = 12, G = 1.
  * replaces shapequant/kernels/proto_runs.py:322-336, 380-388 (pack_lane_major, make_tiles: load-time re-layout
@@ -179,15 +179,16 @@ int cbl_repack_book(const void* table, void* out, cbl_stream s);
  *   y[r] = round_to(ydtype, row_scale[r] * sum_j <table[tag[r, j]], x[perms[m_r][8 j .. 8 j + 7]]>)   (perms = identity for M = 1)
  * Per tile the kernel computes T[e][c] = <table[e], x_chunk_c> once on the tensor cores (fp16 with a power-of-two
  * scale per tile, two alternating 64 KB tables in shared memory) and every weight chunk becomes one 2-byte
- * shared-memory read and one fp32 add.  Blocks that share rows add their fp32 partial sums into 64-bit fixed-point
- * accumulators (integer addition: the result does not depend on the arrival order, repeated calls agree bit for
- * bit); the last block of a row range scales, rounds, writes y and clears the accumulators - one kernel per call.
- * x must be finite (a NaN or infinity anywhere in x turns the whole output into NaN).
- * Work space: cbl_gemv_l8_workspace_bytes(R) bytes, zero before the first call; every completed call leaves it
- * zero again.  Calls that share a work space must not overlap on the device.
+ * shared-memory read and one fp32 add.  Blocks that share rows store their fp32 partial sums into slots of the
+ * work space, meet at a counter (bounded wait) and then each sums a slice of the rows over the blocks in a fixed
+ * order, scales, rounds and writes y: one kernel per call, and repeated calls agree bit for bit.
+ * Work space: cbl_gemv_l8_workspace_bytes(R) bytes, zero before the first call; every completed call leaves its
+ * counters zero again (the rest may hold anything).  Calls that share a work space must not overlap on the device.
+ * Codeword magnitudes up to 2^13 are supported (larger ones may overflow the fp16 tables).
  * replaces shapequant/kernels/gemv.py:28-64, 142-162 (_gemv_kernel, PackedLinear.gemv) and
  *          shapequant/kernels/proto_runs.py:412-473, 505-571 (gemv_additive, gemv) for batch 1, including their
- *          input-side use of the column orders (proto_runs.py:500-502, prep_x). */
+ *          input-side use of the column orders (proto_runs.py:500-502, prep_x) and the ordered split-K sum of
+ *          shapequant/kernels/batched_runs.py:328-356. */
 size_t cbl_gemv_l8_workspace_bytes(int32_t R);
 int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, void* workspace, cbl_stream s);
 
@@ -201,8 +202,8 @@ int cbl_gemv_l8_plan(const cbl_l8* mats, int32_t n, int32_t max_blocks, int32_t*
 
 /* Up to 4 matrices that read the same activation vector (q|k|v, gate|up) as ONE launch: the blocks are
  * shared out over all their (rows x tiles) rectangles, so launch and first-table latencies are paid once.
- * ys[i] receives matrix i's output; the work space is the matrices' regions back to back
- * (cbl_gemv_l8_workspace_bytes(R_i) bytes each), zero on entry, left zero.
+ * ys[i] receives matrix i's output; the work space holds the sum of cbl_gemv_l8_workspace_bytes(R_i) bytes
+ * (zero before the first call).
  * replaces the merged q|k|v and gate|up launches of shapequant/kernels/decode_e2e.py:453-485
  *          (merge_runs) and the per-piece loop of shapequant/vllm_ext/core.py:376-384 (_small). */
 int cbl_gemv_l8_multi(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype,
@@ -226,28 +227,31 @@ int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* y, int ydty
  * publishes).  Synchronises the stream and clears the word. */
 int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s);
 
-/* The kernel's waits on its staged copies are bounded; if one ever expires it sets a status word in
- * the work space and leaves (the work space must then be zeroed again before its next use).  This call
- * synchronises the stream, clears the word and returns CBL_OK or CBL_ETIMEOUT.
+/* The kernel's waits (on its staged copies, on the other blocks of a row part) are bounded; if one ever
+ * expires the kernel sets a status word in the work space and leaves.  This call synchronises the stream and
+ * returns CBL_OK or CBL_ETIMEOUT; after a time-out it also clears the word and the counters, so the work space
+ * can be used again.  R is not used (kept for the signature of earlier versions).
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
 int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s);
 
 /* The same batch-1 product for callers that cannot hand the library any device memory of their
  * own making (hosts that pre-partition the whole GPU into private pools, or plugin contracts that
  * forbid allocator calls while serving).  The product's work space lives in a fixed array compiled into
- * the library: at most cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED);
- * about 776 KB of every GPU that loads the library stay reserved until the process exits.
+ * the library: 770 KB of every GPU that loads the library stay reserved until the process exits, and the
+ * launch uses at most 48 thread blocks so that their partial sums fit (slower than cbl_gemv_l8 on large
+ * matrices, same results bit for bit when the work split is the same, within fp32 summation order otherwise).
+ * Limit: cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED).
  * The call allocates and frees nothing.  Its first use on a device looks the array's device address
  * up (cudaGetSymbolAddress, under a lock), so make that first call before any stream capture.  All calls
- * share the one array: the call clears what it needs on its stream before launching, and two such
+ * share the one array: the call clears the counters it needs on its stream before launching, and two such
  * products that overlap on the GPU (different streams, or a replayed graph beside a live call)
- * race on it - serialise them.  Results equal cbl_gemv_l8's bit for bit.
- * cbl_gemv_l8_static_status(R, s): the bounded-wait status of such products of R rows since the last query
- * (CBL_OK or CBL_ETIMEOUT; synchronises the stream, clears the word, allocates nothing).
+ * race on it - serialise them.
+ * cbl_gemv_l8_static_status(s): the bounded-wait status of such products on the current device since the last
+ * query (CBL_OK or CBL_ETIMEOUT; synchronises the stream, clears the word, allocates nothing).
  * No counterpart in the reference (its launchers allocate through torch / CuPy). */
 int32_t cbl_gemv_l8_static_max_rows(void);
 int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s);
-int cbl_gemv_l8_static_status(int32_t R, cbl_stream s);
+int cbl_gemv_l8_static_status(cbl_stream s);
 
 /* ------------------------------------------------------------------------------------------
  * Prefill product on the column-tile layout (rot = 0): y[t*ldy + r] = round_to(ydtype, row_scale[r] *

@@ -87,7 +87,7 @@ SIGNATURES = {
     "cbl_gemv_l8_plan": (c_int, [POINTER(L8), c_int32, c_int32, c_void_p, c_void_p]),
     "cbl_gemv_l8_static_max_rows": (c_int32, []),
     "cbl_gemv_l8_static": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p]),
-    "cbl_gemv_l8_static_status": (c_int, [c_int32, c_void_p]),
+    "cbl_gemv_l8_static_status": (c_int, [c_void_p]),
     "cbl_gemm_stage_bytes": (c_size_t, [c_int32, c_int32]),
     "cbl_gemm_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "cbl_gemm_l8_2sm": (c_int, [POINTER(L8), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),

@@ -2,50 +2,61 @@
 //
 // For a tile of 8 chunk columns (64 weight columns) a thread block computes the table
 //     T[e][c] = <book[e], x_chunk_c>          e = 0..4095, c = 0..7        (mma.sync m16n8k8, 256 per tile)
-// once, as fp16 with a power-of-two scale per tile, into 64 KB of shared memory; after that every weight
-// chunk (8 weights, 12 bits in HBM) costs ONE 2-byte shared-memory read and one add.  Two tables
+// once, as 16-bit integers with a power-of-two scale per tile (the scale comes from a Cauchy-Schwarz bound, so no
+// entry can saturate), into 64 KB of shared memory; after that every weight chunk (8 weights, 12 bits in HBM)
+// costs ONE 2-byte shared-memory read and half an integer add (three-input adds; a row's 8 entries sum exactly).  Two tables
 // alternate: while the block looks tile t up, its warps build tile t + 1, so only a block's first build
 // is exposed.  The tags of the block's rows stream through a ring of shared-memory stages filled by bulk
 // copies (cp.async.bulk + mbarrier, up to 15 stages = 90 KB in flight, started before the kernel waits
 // for its predecessor).  A block owns a rectangle (rows x tiles) of one matrix; a thread owns up to 8 rows
 // of it and keeps their fp32 sums in registers over all the block's tiles.
 //
-// Row sums of blocks that share rows (different tile ranges) meet in 64-bit FIXED-POINT accumulators
-// (red.global.add.u64): integer addition is associative, so the result does not depend on the order in
-// which blocks arrive - two runs agree bit for bit - and the scale 2^S is derived from a bound that every
-// block computes identically (largest |x|, largest |codeword value|, number of terms).  The last block to
-// arrive for a group of rows (a counter per row part) converts, applies the row scale, rounds, writes y and
-// clears accumulators and counter: no second kernel, and the work space is left zero.
+// Row sums of blocks that share rows (different tile ranges) meet without atomics and in a FIXED order, so two
+// runs agree bit for bit: every block stores its fp32 partial sums into its own slot of the work space, the
+// blocks of a row part meet at a counter (bounded wait; all blocks of a launch are resident at once: one block
+// per SM, at most as many blocks as SMs), and then EVERY block of the part sums a slice of the part's rows over
+// the splits, in split order, applies the row scale, rounds and writes y - one kernel per call, the finishing
+// work spread over all SMs.
 //
 // Shared-memory gathers bound this kernel, not HBM: a warp's 32 random 2-byte reads take as many cycles
 // as the most loaded bank has requests, 3.3 on average.  Per lane the column it reads rotates with the lane
-// index ((slot + lane) mod 8; the tags are stored in that rotated order), which keeps same-column lanes from
-// piling on the few banks one column's entries occupy.
+// index ((slot + row position / 4) mod 8; the tags are stored in that rotated order), which keeps same-column lanes from
+// piling on the few banks one column's entries occupy.  A thread takes 4 consecutive rows per step (one 16-byte
+// read per tag plane, 32 independent table reads in flight): the loop is bound by latency, not by issue slots.
 #include <map>
 #include <mutex>
 #include <vector>
 #include "cbl_common.cuh"
 
-constexpr int L8_NT = 512;                       // threads per block = rows per ring stage
+
+constexpr int L8_NT = 512;                       // consumer threads per block; a thread handles 4 consecutive rows per ring stage
 constexpr int L8_NWARP = L8_NT / 32;
+constexpr int L8_THREADS = L8_NT + 32;           // + one producer warp
 constexpr int L8_RPT = 8;                        // rows per thread: a block covers at most 4096 rows
-constexpr int L8_STAGE_BYTES = 3 * L8_NT * 4;    // three tag planes of 512 rows
-constexpr int L8_MAX_STAGES = 16;
+constexpr int L8_STEP_ROWS = 4 * L8_NT;           // 2048 rows per step of the block
+constexpr int L8_STAGE_ROWS = L8_STEP_ROWS / 2;   // a ring stage holds half a step: the rows of 8 consumer warps
+constexpr int L8_STAGE_WARPS = L8_NWARP / 2;
+constexpr int L8_STAGE_BYTES = 3 * L8_STAGE_ROWS * 4;   // three tag planes
+constexpr int L8_MAX_STAGES = 8;
 constexpr int L8_DYN_SMEM = 231424;              // all of an SM's shared memory but 1 KB for the static part
-constexpr int L8_REFILL_LAG = 2;                 // the producer refills the stage consumed two iterations ago
+constexpr int L8_ACC_BYTES = L8_NT * L8_RPT * 4;  // fp32 row sums of a block between tiles
 constexpr uint32_t L8_WAIT_LIMIT = 1u << 20;     // mbarrier polls before a wait gives up
 constexpr int L8_MAX_GROUP = 4;
 constexpr int L8_MAX_BLOCKS = 160;
 constexpr int L8_MAX_ORDERS = 16;
-constexpr int L8_CTL_WORDS = 256;                // counters [0, 192), status word at 192
-constexpr int L8_STATUS_WORD = 192;
+constexpr int L8_SLOT_FLOATS = L8_NT * L8_RPT;    // partial-sum slot of one block
+constexpr size_t L8_PART_BYTES = (size_t)L8_MAX_BLOCKS * L8_SLOT_FLOATS * 4;
+constexpr int L8_CTL_WORDS = 512;                // arrivals [0, 160), departures [160, 320), status word at 320
+constexpr int L8_STATUS_WORD = 320;
+constexpr uint32_t L8_MEET_LIMIT = 1u << 20;     // polls of a part's arrival counter before a block gives up (~1 s)
 
 static inline size_t l8_rows_max(int32_t R) { return ((size_t)R + 31) / 32 * 32 + 32 * L8_MAX_ORDERS; }
 
-// Work space of one matrix: int64 sums by row position | fp32 sums by source row | counters + status.
+// Work space of a launch: partial-sum slots of the blocks | counters + status | fp32 sums by source row of each
+// matrix (mode 1).  The per-matrix figure covers a launch of that matrix alone; a group needs no more than the sum.
 extern "C" size_t cbl_gemv_l8_workspace_bytes(int32_t R) {
     if (R < 0) return 0;
-    return l8_rows_max(R) * 12 + L8_CTL_WORDS * 4;
+    return L8_PART_BYTES + L8_CTL_WORDS * 4 + l8_rows_max(R) * 4;
 }
 
 __device__ __forceinline__ void l8_mbar_init(uint32_t bar, uint32_t count) {
@@ -77,33 +88,46 @@ __device__ __forceinline__ uint32_t l8_lds32(uint32_t addr) {
     return v;
 }
 __device__ __forceinline__ void l8_sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
-// acc += fp16 table entry at a shared-memory address (one 2-byte read, one mixed-precision add).
-__device__ __forceinline__ void l8_add_entry(float& acc, uint32_t addr) {
-    unsigned short h;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
-    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(h));
+// D = A(16x8, row) * B(8x8, col), fp16 inputs, fp32 result; not volatile: the compiler may issue several back to back.
+__device__ __forceinline__ void l8_mma1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.0f));
 }
 
-// Sum of a row's 8 table entries of one tile.  (w0, w1, w2) is the row's 96-bit stream of 8 tags, slot s at bit
-// 12 s; col[s] = table base | 2 * column of slot s for this lane.  Entry address = base + tag * 16 + column * 2:
-// the base is 64 KB aligned, so the three fields are merged with one logic operation per tag.
-__device__ __forceinline__ float l8_row8(uint32_t w0, uint32_t w1, uint32_t w2, const uint32_t (&col)[8]) {
-    float s0 = 0.f, s1 = 0.f;
-    l8_add_entry(s0, ((w0 << 4) & 0xFFF0u) | col[0]);
-    l8_add_entry(s1, ((w0 >> 8) & 0xFFF0u) | col[1]);
-    l8_add_entry(s0, (__funnelshift_r(w0, w1, 20) & 0xFFF0u) | col[2]);
-    l8_add_entry(s1, (w1 & 0xFFF0u) | col[3]);
-    l8_add_entry(s0, ((w1 >> 12) & 0xFFF0u) | col[4]);
-    l8_add_entry(s1, (__funnelshift_r(w1, w2, 24) & 0xFFF0u) | col[5]);
-    l8_add_entry(s0, ((w2 >> 4) & 0xFFF0u) | col[6]);
-    l8_add_entry(s1, ((w2 >> 16) & 0xFFF0u) | col[7]);
-    return s0 + s1;
+// One signed 16-bit table entry (sign-extended) from a shared-memory address.
+__device__ __forceinline__ int l8_entry(uint32_t addr) {
+    int v;
+    asm volatile("ld.shared.s16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Sum of a row's 8 table entries of one tile (exact: the entries are 16-bit integers).  (w0, w1, w2) is the row's
+// 96-bit stream of 8 tags, slot s at bit 12 s; col[s] = table base | 2 * column of slot s for this lane.  Entry
+// address = base + tag * 16 + column * 2: the base is 64 KB aligned, so the three fields are merged with one logic
+// operation per tag.
+__device__ __forceinline__ int l8_row8(uint32_t w0, uint32_t w1, uint32_t w2, const uint32_t (&col)[8]) {
+    const int e0 = l8_entry(((w0 << 4) & 0xFFF0u) | col[0]);
+    const int e1 = l8_entry(((w0 >> 8) & 0xFFF0u) | col[1]);
+    const int e2 = l8_entry((__funnelshift_r(w0, w1, 20) & 0xFFF0u) | col[2]);
+    const int e3 = l8_entry((w1 & 0xFFF0u) | col[3]);
+    const int e4 = l8_entry(((w1 >> 12) & 0xFFF0u) | col[4]);
+    const int e5 = l8_entry((__funnelshift_r(w1, w2, 24) & 0xFFF0u) | col[5]);
+    const int e6 = l8_entry(((w2 >> 4) & 0xFFF0u) | col[6]);
+    const int e7 = l8_entry(((w2 >> 16) & 0xFFF0u) | col[7]);
+    return ((e0 + e1) + (e2 + e3)) + ((e4 + e5) + (e6 + e7));
+}
+
+// 2^e as a float, e clamped to the normal range.
+__device__ __forceinline__ float l8_pow2(int e) {
+    e = e < -126 ? -126 : (e > 127 ? 127 : e);
+    return __int_as_float((e + 127) << 23);
 }
 
 // Power-of-two exponent k such that |v| * 2^-k < 2^14 for the largest magnitude mx (k may be negative).
 __device__ __forceinline__ int l8_scale_exp(float mx) {
     if (!(mx > 0.f) || !(mx < 3.0e38f)) return 0;
-    int k = ilogbf(mx) - 13;
+    int k = ((__float_as_int(mx) >> 23) & 0xFF) - 127 - 13;      // exponent field (subnormals land on the clamp below)
     return k < -100 ? -100 : (k > 110 ? 110 : k);
 }
 
@@ -113,10 +137,10 @@ struct L8Launch {
     int ydtype;
     int mode;                          // 0: y = round(row_scale * sum); 1: fsum[source row] = sum (an epilogue kernel follows)
     cbl_l8 m[L8_MAX_GROUP];
-    unsigned long long* iacc[L8_MAX_GROUP];   // fixed-point sums by row position (zero on entry, left zero)
+    float* partial;                    // L8_MAX_BLOCKS slots of L8_SLOT_FLOATS fp32 partial sums (any contents)
     float* fsum[L8_MAX_GROUP];         // mode 1: fp32 sums by source row
     void* y[L8_MAX_GROUP];
-    unsigned int* counters;            // one arrival counter per row part (zero on entry, left zero)
+    unsigned int* counters;            // per row part: arrivals [part], departures [L8_MAX_BLOCKS + part] (zero on entry, left zero)
     unsigned int* status;              // set to 1 when a bounded wait expired
     const uint32_t* calls;             // optional: completed-call counter; call e = *calls + 1 writes its sums to
     int64_t fsum_stride;               // fsum[0] + (e & 1) * fsum_stride (two alternating buffers, see cbl_gemv_l8_ar)
@@ -126,11 +150,15 @@ struct L8Launch {
 // 32) x tiles [tile_lo, tile_hi) of matrix mi, all rows of one column order.
 struct L8Plan {
     int nblocks;
-    int4 r[L8_MAX_BLOCKS];   // x = mi | order << 2 | part << 8 | splits << 16, y = row_lo, z = nrows, w = tile_lo | tile_hi << 16
+    int4 r[L8_MAX_BLOCKS];   // x = mi | order << 2 | part << 8 | splits << 16 | first block of the part << 24, y = row_lo, z = nrows,
+                             // w = tile_lo | tile_hi << 16; the blocks of a part are consecutive, in split order
 };
 
-__global__ void __launch_bounds__(L8_NT, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan,
-                                                      const void* __restrict__ x, int xdtype) {
+// Barrier among the 512 consumer threads only (the producer warp runs ahead on its own).
+__device__ __forceinline__ void l8_sync_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(L8_NT) : "memory"); }
+
+__global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan,
+                                                           const void* __restrict__ x, int xdtype) {
     extern __shared__ __align__(128) unsigned char l8_smem[];
     __shared__ __align__(8) unsigned long long s_bar[2 * L8_MAX_STAGES];   // full[stage] (tags landed), empty[stage] (every warp has read them)
     __shared__ float s_red[L8_NWARP];
@@ -140,74 +168,82 @@ __global__ void __launch_bounds__(L8_NT, 1) k_gemv_l8(const __grid_constant__ L8
     const int g = lane >> 2, t = lane & 3;
     if ((int)blockIdx.x >= plan.nblocks) return;
     const int4 d = plan.r[blockIdx.x];
-    const int mi = d.x & 3, order = (d.x >> 2) & 15, part = (d.x >> 8) & 255, splits = (d.x >> 16) & 255;
+    const int mi = d.x & 3, order = (d.x >> 2) & 15, part = (d.x >> 8) & 255, splits = (d.x >> 16) & 255, first = (int)((uint32_t)d.x >> 24);
     const int row_lo = d.y, nrows = d.z, tile_lo = d.w & 0xFFFF, tile_hi = (int)((uint32_t)d.w >> 16);
     const cbl_l8& mm = P.m[mi];
     // Programmatic dependent launch: the next kernel of the stream may become resident now; this kernel itself
     // waits for its predecessor only where it first touches data that depends on it (x, accumulators, y).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // ---- shared memory: two 64 KB tables on a 64 KB boundary, ring stages in what is left below and above them
+    // ---- shared memory: two 64 KB tables on a 64 KB boundary; below and above them the fp32 row sums of the
+    // block (16 KB) and the ring stages
     const uint32_t base = cbl_smem_u32(l8_smem), end = base + (uint32_t)L8_DYN_SMEM;
     const uint32_t tbl0 = (base + 65535u) & ~65535u;
-    const uint32_t lo0 = (base + 127u) & ~127u, hi0 = tbl0 + 131072u;
+    const uint32_t hi0 = tbl0 + 131072u;
+    uint32_t lo0 = (base + 127u) & ~127u, hi1 = hi0, sacc;
+    if (end >= hi0 + L8_ACC_BYTES) { sacc = hi0; hi1 += L8_ACC_BYTES; } else { sacc = lo0; lo0 += L8_ACC_BYTES; }
     const int n_lo = tbl0 > lo0 ? (int)((tbl0 - lo0) / L8_STAGE_BYTES) : 0;
-    const int n_hi = end > hi0 ? (int)((end - hi0) / L8_STAGE_BYTES) : 0;
+    const int n_hi = end > hi1 ? (int)((end - hi1) / L8_STAGE_BYTES) : 0;
     const int S = min(L8_MAX_STAGES, n_lo + n_hi);
-    if (hi0 > end || S < L8_REFILL_LAG + 1) {          // cannot happen with the launch configuration of this file
+    if (hi1 > end || S < 2) {                          // cannot happen with the launch configuration of this file
         if (tid == 0) atomicExch(P.status, 2u);
         return;
     }
-    auto stage_addr = [&](int s) { return s < n_lo ? lo0 + (uint32_t)s * L8_STAGE_BYTES : hi0 + (uint32_t)(s - n_lo) * L8_STAGE_BYTES; };
+    auto stage_addr = [&](int s) { return s < n_lo ? lo0 + (uint32_t)s * L8_STAGE_BYTES : hi1 + (uint32_t)(s - n_lo) * L8_STAGE_BYTES; };
     const uint32_t bar0 = cbl_smem_u32(s_bar);
 
-    const int nrow_it = (nrows + L8_NT - 1) / L8_NT;   // <= L8_RPT
+    const int nrow_it = (nrows + L8_STEP_ROWS - 1) / L8_STEP_ROWS;     // <= 2
     const int ntl = tile_hi - tile_lo;
-    const int nit = ntl * nrow_it;                     // ring iterations of this block
-    if (tid == 0) {
-        s_abort = 0;
-        for (int i = 0; i < S; i++) {
-            l8_mbar_init(bar0 + 8 * i, 1);                           // full: the producer's arrive + the bytes of three copies
-            l8_mbar_init(bar0 + 8 * (L8_MAX_STAGES + i), L8_NWARP);  // empty: one arrival per consuming warp
-        }
+    const int nit = ntl * nrow_it;                     // iterations of this block: (tile, row step), tile-major; two ring stages each
+    if (tid < S) {
+        l8_mbar_init(bar0 + 8 * tid, 1);                             // full: the producer's arrive + the bytes of three copies
+        l8_mbar_init(bar0 + 8 * (L8_MAX_STAGES + tid), L8_STAGE_WARPS);   // empty: one arrival per consuming warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid == 0) s_abort = 0;
     __syncthreads();
 
-    // ---- producer (thread 0): iteration i = (tile, row step) in tile-major order
-    const uint32_t* words = (const uint32_t*)mm.words;
-    int pit = 0, ptile = tile_lo, pk = 0, pstage = 0, puse = 0;
-    auto issue = [&]() {
-        const int n = min(L8_NT, nrows - pk * L8_NT);
-        const uint32_t bar = bar0 + 8 * pstage, dst = stage_addr(pstage);
-        l8_mbar_expect_tx(bar, 12u * (uint32_t)n);
-        const uint32_t* src = words + (int64_t)ptile * 3 * mm.Rpad + row_lo + pk * L8_NT;
-#pragma unroll
-        for (int p = 0; p < 3; p++) l8_bulk_g2s(dst + p * (L8_NT * 4), src + (int64_t)p * mm.Rpad, 4u * (uint32_t)n, bar);
-        pit++;
-        if (++pk == nrow_it) { pk = 0; ptile++; }
-        if (++pstage == S) { pstage = 0; puse++; }
-    };
-    if (tid == 0) {
-        const int n0 = min(S, nit);
-        for (int i = 0; i < n0; i++) issue();          // weights do not depend on the previous kernel: start streaming now
+    if (warp == L8_NWARP) {
+        // ---- producer warp: lanes 0..2 stage the three tag planes of one iteration, lane 0 announces the bytes.
+        // Weights do not depend on the previous kernel: streaming starts at once and runs up to S stages ahead.
+        const uint32_t* src = (const uint32_t*)mm.words + (int64_t)tile_lo * 3 * mm.Rpad + row_lo + (int64_t)lane * mm.Rpad;
+        int k = 0, stage = 0;
+        uint32_t use = 0;
+        for (int i = 0; i < 2 * nit; i++) {             // stage i: half (i & 1) of iteration i / 2
+            if (use > 0) {
+                int ok = 1;
+                if (lane == 0) ok = l8_mbar_wait(bar0 + 8 * (L8_MAX_STAGES + stage), (use - 1u) & 1u);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) { s_abort = 1; return; }
+            }
+            const int r0 = k * L8_STEP_ROWS + (i & 1) * L8_STAGE_ROWS;
+            const int n = max(0, min(L8_STAGE_ROWS, nrows - r0));
+            const uint32_t bar = bar0 + 8 * stage;
+            if (lane == 0) {
+                if (n > 0) l8_mbar_expect_tx(bar, 12u * (uint32_t)n);
+                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");      // an empty half completes at once
+            }
+            __syncwarp();
+            if (lane < 3 && n > 0) l8_bulk_g2s(stage_addr(stage) + lane * (L8_STAGE_ROWS * 4), src + r0, 4u * (uint32_t)n, bar);
+            if ((i & 1) && ++k == nrow_it) { k = 0; src += 3 * (int64_t)mm.Rpad; }
+            if (++stage == S) { stage = 0; use++; }
+        }
+        return;
     }
 
-    // ---- the book's mma A fragments stay in registers for all tiles of a book (one 16-byte load per two 16-codeword blocks)
+    // ---- consumers.  A build reads its share of the book's mma A fragments from global memory (L2-resident: 64 KB
+    // per book, one 16-byte load per two 16-codeword blocks) - kept in registers they would crowd the lookup loop.
     const int ntile1 = mm.ntile / mm.books;
-    uint4 af[8];
-    int cur_book = -1, jexp = 0;
-    auto load_book = [&](int book) {
-        const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
-#pragma unroll
-        for (int i = 0; i < 8; i++) af[i] = __ldg(fr + (warp + i * L8_NWARP) * 32 + lane);
-        const float mb = __ldg((const float*)(fr + 4096));          // largest |value| of the book
-        jexp = (mb > 0.f && mb < 3.0e38f) ? ilogbf(mb) + 3 : 0;      // 8 * mb * 2^14 * 2^-jexp < 2^16
+    const uint4* frag = nullptr;
+    int cur_book = -1, jx = 0;
+    auto set_book = [&](int book) {
+        frag = (const uint4*)(book ? mm.frag2 : mm.frag) + warp * 32 + lane;
+        const float nb = __ldg((const float*)((const uint4*)(book ? mm.frag2 : mm.frag) + 4096) + 1);   // largest Euclidean norm of a codeword
+        // |<codeword, x_chunk>| <= nb * |x_chunk| < 2^(jx + 1) * 2^(13 - jx) = 2^14: every entry fits 16 bits with room to spare
+        jx = (nb > 0.f && nb < 3.0e38f) ? ilogbf(nb) : 0;
+        jx = jx < -8 ? -8 : (jx > 24 ? 24 : jx);
         cur_book = book;
     };
-    load_book(tile_lo / ntile1);
-    float mbmax = __ldg((const float*)((const uint4*)mm.frag + 4096));
-    if (mm.books == 2) mbmax = fmaxf(mbmax, __ldg((const float*)((const uint4*)mm.frag2 + 4096)));
+    set_book(tile_lo / ntile1);
 
     asm volatile("griddepcontrol.wait;" ::: "memory");              // x, accumulators and outputs belong to earlier kernels until here
     float* fsum = P.fsum[mi];
@@ -225,152 +261,233 @@ __global__ void __launch_bounds__(L8_NT, 1) k_gemv_l8(const __grid_constant__ L8
     float xa, xb;
     load_x(tile_lo, xa, xb);
 
-    // ---- largest |x| over the whole vector: the common fixed-point scale of every block of this matrix and order
-    float mx = 0.f;
-    int bad = 0;
-    for (int c = tid; c < mm.C; c += L8_NT) {
-        const float a = fabsf(cbl_load_in(x, xdtype, perm ? perm[c] : c));
-        bad |= !(a <= 3.0e38f);                        // NaN or infinity
-        mx = fmaxf(mx, a);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) s_red[warp] = mx;
-    bad = __syncthreads_or(bad);
-#pragma unroll
-    for (int i = 0; i < L8_NWARP; i++) mx = fmaxf(mx, s_red[i]);
-    // |row sum| <= ntile * 64 * mbmax * mx * (1 + 2^-10) < 2^(ec + eb + ex): scaled by 2^sfx it stays below 2^60
-    int sfx = 0;
-    if (mx > 0.f && mbmax > 0.f && mbmax < 3.0e38f && !bad)
-        sfx = 60 - ((ilogbf(mbmax) + 1) + (ilogbf(mx) + 1) + (32 - __clz(mm.ntile * 64)));
-    const double fx_scale = ldexp(1.0, sfx), fx_inv = ldexp(1.0, -sfx);
-
     // ---- table build: 16 codeword blocks per warp; the tile's 64 activations are this warp's B fragment
-    // (lane (g, t) holds k = 2t, 2t+1 of chunk column g = elements 2 lane, 2 lane + 1 of the tile)
+    // (lane (g, t) holds k = 2t, 2t+1 of chunk column g = elements 2 lane, 2 lane + 1 of the tile).  The activations
+    // are scaled by a power of two that brings the largest Euclidean norm of the tile's 8 chunks below
+    // 2^13 * 2^-jx: the products then stay below 2^14 in magnitude whatever the inputs (Cauchy-Schwarz) and
+    // are stored as rounded 16-bit integers; the returned factor undoes the scale on the integer sum of a row.
     auto build = [&](uint32_t tbl, float va, float vb) -> float {
-        float mt = fmaxf(fabsf(va), fabsf(vb));
+        uint4 af[8];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
-        const int k = l8_scale_exp(mt);
-        const float sc = ldexpf(1.f, -k), sj = ldexpf(1.f, -jexp);
+        for (int i = 0; i < 8; i++) af[i] = __ldg(frag + i * (L8_NWARP * 32));
+        float me = fmaxf(fabsf(va), fabsf(vb));          // largest element of the tile: a first scale, so that squares cannot overflow
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
+        const int k1 = l8_scale_exp(me);
+        const float s1 = l8_pow2(-k1), ua = va * s1, ub = vb * s1;
+        float n2 = ua * ua + ub * ub;                    // squared norm of chunk g over its four lanes
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
+#pragma unroll
+        for (int o = 16; o > 2; o >>= 1) n2 = fmaxf(n2, __shfl_xor_sync(0xffffffffu, n2, o));
+        // largest chunk norm -> [2^12, 2^13) * 2^-jx: one bit of head room for the rounding of the fp16 activations
+        // (floor(log2(sqrt(n2))) is half the exponent of n2, which is at least 2^26 here)
+        const int k2 = n2 > 0.f ? ((((__float_as_int(n2) >> 23) & 0xFF) - 127) >> 1) - 12 : 0;
+        const int k = k1 + (k2 > 0 ? k2 : 0) + jx;
+        // a NaN or infinity among the tile's activations must reach every output, as it would in a matrix product
+        const bool nonfinite = __any_sync(0xffffffffu, !(fabsf(va) <= 3.0e38f) || !(fabsf(vb) <= 3.0e38f));
+        const float sc = l8_pow2(-k);
         const __half2 xh = __floats2half2_rn(va * sc, vb * sc);
         const uint32_t b0 = *(const uint32_t*)&xh;
+        const uint32_t a0 = tbl + (uint32_t)g * 16u + (uint32_t)t * 4u + (uint32_t)warp * 512u;
+        // four products in flight at a time (their latencies overlap), then the eight stores of the group
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < 8; i += 2) {
+            float c[4][4];
+            l8_mma1688(c[0], af[i].x, af[i].y, b0);
+            l8_mma1688(c[1], af[i].z, af[i].w, b0);
+            l8_mma1688(c[2], af[i + 1].x, af[i + 1].y, b0);
+            l8_mma1688(c[3], af[i + 1].z, af[i + 1].w, b0);
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int e0 = ((warp + i * L8_NWARP) * 2 + h) * 16;
-                float c[4];
-                cbl_mma1688(c, h ? af[i].z : af[i].x, h ? af[i].w : af[i].y, b0);
-                const __half2 lo = __floats2half2_rn(c[0] * sj, c[1] * sj), hi = __floats2half2_rn(c[2] * sj, c[3] * sj);
-                const uint32_t a = tbl + (uint32_t)(e0 + g) * 16u + (uint32_t)t * 4u;
-                l8_sts32(a, *(const uint32_t*)&lo);
-                l8_sts32(a + 128u, *(const uint32_t*)&hi);
+            for (int q = 0; q < 4; q++) {
+                // round to integer by adding 1.5 * 2^23: the low 16 bits of the sum's pattern are the two's-complement value
+                const uint32_t lo = __byte_perm(__float_as_uint(c[q][0] + 12582912.f), __float_as_uint(c[q][1] + 12582912.f), 0x5410);
+                const uint32_t hi = __byte_perm(__float_as_uint(c[q][2] + 12582912.f), __float_as_uint(c[q][3] + 12582912.f), 0x5410);
+                const uint32_t a = a0 + (uint32_t)((i + (q >> 1)) * L8_NWARP * 512 + (q & 1) * 256);   // codeword block ((warp + 16 i') * 2 + h) * 16
+                l8_sts32(a, lo);
+                l8_sts32(a + 128u, hi);
             }
         }
-        return ldexpf(1.f, k + jexp);                   // undoes both scales on the fp32 sum
+        return nonfinite ? __int_as_float(0x7fc00000) : l8_pow2(k);
     };
 
     uint32_t col[8];
 #pragma unroll
     for (int s = 0; s < 8; s++) col[s] = tbl0 | (uint32_t)(((s + lane) & 7) << 1);
-    float acc[L8_RPT];
-#pragma unroll
-    for (int k = 0; k < L8_RPT; k++) acc[k] = 0.f;
 
     float inv_cur = build(tbl0, xa, xb), inv_nxt = 0.f;
     if (ntl > 1) load_x(tile_lo + 1, xa, xb);
-    __syncthreads();
 
-    int cstage = 0, it = 0;
+    l8_sync_consumers();                                // the first table is complete
+
+    // ---- main loop over the ring iterations.  Warps run through the ring on their own; the tags of iteration i + 1
+    // are fetched from the ring before the lookups of iteration i; a row's fp32 sum lives in shared memory between
+    // tiles (each row belongs to one thread).  After a wait has expired the loop only keeps its shape (it contains
+    // barriers) and does no more work.
+    const int half = warp / L8_STAGE_WARPS, tih = tid - half * (L8_NT / 2);    // this thread's half step and index in it
+    int cstage = half, kf = 0;
     uint32_t cphase = 0;
     bool dead = false;
-    for (int ti = 0; ti < ntl; ti++) {
-        if (ti + 1 < ntl) {
-            // the next tile's table goes into the other buffer while this tile is looked up
+    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
+    auto fetch = [&]() {                                // tags of the next ring iteration (row step kf) -> w0..w2
+        if (!dead && !l8_mbar_wait(bar0 + 8 * cstage, cphase)) { s_abort = 1; dead = true; }
+        w0 = w1 = w2 = make_uint4(0, 0, 0, 0);
+        if (!dead && kf * L8_STEP_ROWS + 4 * tid < nrows) {
+            const uint32_t a = stage_addr(cstage) + (uint32_t)tih * 16u;
+            w0 = cbl_lds128(a);
+            w1 = cbl_lds128(a + L8_STAGE_ROWS * 4);
+            w2 = cbl_lds128(a + 2 * L8_STAGE_ROWS * 4);
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * (L8_MAX_STAGES + cstage)) : "memory");
+        cstage += 2;
+        if (cstage >= S) { cstage -= S; cphase ^= 1u; }
+        if (++kf == nrow_it) kf = 0;
+    };
+    fetch();
+    float acc[2][4];                                    // this thread's 4 rows of row step 0 and of row step 1
+#pragma unroll
+    for (int u = 0; u < 4; u++) acc[0][u] = acc[1][u] = 0.f;
+    int k = 0, ti = 0;
+    for (int it = 0; it < nit; it++) {
+        // The next tile's table goes into the other buffer while this tile is looked up: one half of the warps builds
+        // its share before its lookups of the tile, the other half after them, so that at any time some warps keep the
+        // shared-memory pipe busy with lookups while others run the tensor-core products of the build.
+        const bool build_now = ti + 1 < ntl && (half == 0 ? k == 0 : k == nrow_it - 1);
+        if (build_now && half == 0) {
             const int nb = (tile_lo + ti + 1) / ntile1;
-            if (nb != cur_book) load_book(nb);
+            if (nb != cur_book) set_book(nb);
             inv_nxt = build(tbl0 + (uint32_t)(((ti + 1) & 1) << 16), xa, xb);
             if (ti + 2 < ntl) load_x(tile_lo + ti + 2, xa, xb);
         }
-#pragma unroll
-        for (int k = 0; k < L8_RPT; k++) {
-            if (k < nrow_it) {
-                // Warps run through the stages on their own.  After a wait has expired the loops only keep their
-                // shape (they contain block-wide barriers) and do no more work.
-                dead = dead || *(volatile int*)&s_abort != 0;
-                if (tid == 0 && !dead && it >= L8_REFILL_LAG && pit < nit) {
-                    if (l8_mbar_wait(bar0 + 8 * (L8_MAX_STAGES + pstage), (uint32_t)(puse - 1) & 1u)) issue();
-                    else { s_abort = 1; dead = true; }
-                }
-                if (!dead && !l8_mbar_wait(bar0 + 8 * cstage, cphase)) { s_abort = 1; dead = true; }
-                const bool act = !dead && k * L8_NT + tid < nrows;
-                uint32_t w0 = 0, w1 = 0, w2 = 0;
-                if (act) {
-                    const uint32_t a = stage_addr(cstage) + (uint32_t)tid * 4u;
-                    w0 = l8_lds32(a);
-                    w1 = l8_lds32(a + L8_NT * 4);
-                    w2 = l8_lds32(a + 2 * L8_NT * 4);
-                }
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * (L8_MAX_STAGES + cstage)) : "memory");
-                if (act) acc[k] = fmaf(l8_row8(w0, w1, w2, col), inv_cur, acc[k]);
-                it++;
-                if (++cstage == S) { cstage = 0; cphase ^= 1u; }
-            }
+        const uint4 c0 = w0, c1 = w1, c2 = w2;
+        dead = dead || *(volatile int*)&s_abort != 0;
+        const bool act = !dead && k * L8_STEP_ROWS + 4 * tid < nrows;
+        if (it + 1 < nit) fetch();
+        if (act) {
+            const float r0 = (float)l8_row8(c0.x, c1.x, c2.x, col) * inv_cur, r1 = (float)l8_row8(c0.y, c1.y, c2.y, col) * inv_cur;
+            const float r2 = (float)l8_row8(c0.z, c1.z, c2.z, col) * inv_cur, r3 = (float)l8_row8(c0.w, c1.w, c2.w, col) * inv_cur;
+            if (k == 0) { acc[0][0] += r0; acc[0][1] += r1; acc[0][2] += r2; acc[0][3] += r3; }
+            else { acc[1][0] += r0; acc[1][1] += r1; acc[1][2] += r2; acc[1][3] += r3; }
         }
-        const uint32_t tn = tbl0 + (uint32_t)(((ti + 1) & 1) << 16);
+        if (build_now && half == 1) {
+            const int nb = (tile_lo + ti + 1) / ntile1;
+            if (nb != cur_book) set_book(nb);
+            inv_nxt = build(tbl0 + (uint32_t)(((ti + 1) & 1) << 16), xa, xb);
+            if (ti + 2 < ntl) load_x(tile_lo + ti + 2, xa, xb);
+        }
+        if (++k == nrow_it) {
+            k = 0;
+            ti++;
+            const uint32_t tn = tbl0 + (uint32_t)((ti & 1) << 16);
 #pragma unroll
-        for (int s = 0; s < 8; s++) col[s] = (col[s] & 0xFFFFu) | tn;
-        inv_cur = inv_nxt;
-        __syncthreads();                                // next table complete; every reader of this one is done
+            for (int s = 0; s < 8; s++) col[s] = (col[s] & 0xFFFFu) | tn;
+            inv_cur = inv_nxt;
+            l8_sync_consumers();                        // next table complete; every reader of this one is done
+        }
     }
-    if (s_abort) {
-        // a staged copy never completed: report, give the copies still in flight a bounded time, leave
-        if (tid == 0) {
-            atomicExch(P.status, 1u);
-            for (int i = 0; i < S; i++) (void)l8_mbar_wait(bar0 + 8 * i, (i < cstage ? cphase : cphase ^ 1u));
-        }
+    // the row sums go to shared memory, indexed by row of the block, for the output phase
+#pragma unroll
+    for (int kk = 0; kk < 2; kk++)
+        if (kk * L8_STEP_ROWS + 4 * tid < nrows)
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(sacc + (uint32_t)(kk * L8_STEP_ROWS + 4 * tid) * 4u), "f"(acc[kk][0]),
+                         "f"(acc[kk][1]), "f"(acc[kk][2]), "f"(acc[kk][3])
+                         : "memory");
+    l8_sync_consumers();
+    if (*(volatile int*)&s_abort) {
+        // a staged copy never completed: report and leave (the waits that gave up were bounded)
+        if (tid == 0) atomicExch(P.status, 1u);
         return;
     }
 
     // ---- row sums -> outputs
-    const cbl_l8& mo = P.m[mi];
-    const int32_t* rix = mo.row_index;
-    auto emit = [&](int p, float v) {
-        const int src = rix ? rix[p] : p;
-        if (src < 0 || src >= mo.R) return;
-        if (bad) v = __int_as_float(0x7fc00000);
-        if (P.mode == 0) cbl_store_out(P.y[mi], P.ydtype, src, v * __half2float(((const __half*)mo.row_scale)[src]));
-        else fsum[src] = v;
+    const int32_t* rix = mm.row_index;
+    auto source_row = [&](int p) {                      // source row of row position p, -1 for padding
+        const int r = rix ? rix[p] : p;
+        return r < mm.R ? r : -1;
     };
+    auto emit = [&](int r, float v) {
+        if (P.mode == 0) cbl_store_out(P.y[mi], P.ydtype, r, v * __half2float(((const __half*)mm.row_scale)[r]));
+        else fsum[r] = v;
+    };
+    const int n512 = (nrows + L8_NT - 1) / L8_NT;
     if (splits <= 1) {
-#pragma unroll
-        for (int k = 0; k < L8_RPT; k++)
-            if (k * L8_NT + tid < nrows) emit(row_lo + k * L8_NT + tid, acc[k]);
+        for (int j = 0; j < n512; j++) {
+            const int q = j * L8_NT + tid;
+            if (q >= nrows) break;
+            const int r = source_row(row_lo + q);
+            if (r >= 0) emit(r, __uint_as_float(l8_lds32(sacc + (uint32_t)q * 4u)));
+        }
         return;
     }
-    unsigned long long* ia = P.iacc[mi] + row_lo;
-#pragma unroll
-    for (int k = 0; k < L8_RPT; k++)
-        if (k * L8_NT + tid < nrows) {
-            const long long q = __double2ll_rn((double)acc[k] * fx_scale);
-            atomicAdd(ia + k * L8_NT + tid, (unsigned long long)q);
-        }
+    // this block's partial sums -> its slot; then meet the other blocks of the part
+    float* slot = P.partial + (size_t)blockIdx.x * L8_SLOT_FLOATS;
+    for (int j = 0; j < n512; j++) {
+        const int q = j * L8_NT + tid;
+        if (q < nrows) __stcg(slot + q, __uint_as_float(l8_lds32(sacc + (uint32_t)q * 4u)));
+    }
     __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = atomicAdd(P.counters + part, 1u) == (unsigned)(splits - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-#pragma unroll
-    for (int k = 0; k < L8_RPT; k++)
-        if (k * L8_NT + tid < nrows) {
-            const long long q = (long long)__ldcg(ia + k * L8_NT + tid);
-            __stcg(ia + k * L8_NT + tid, 0ull);
-            emit(row_lo + k * L8_NT + tid, (float)((double)q * fx_inv));
+    l8_sync_consumers();
+    if (tid == 0) {
+        atomicAdd(P.counters + part, 1u);
+        uint32_t seen = 0;
+        for (uint32_t i = 0; i < L8_MEET_LIMIT && seen < (uint32_t)splits; i++)
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.counters + part) : "memory");
+        s_last = seen >= (uint32_t)splits;
+    }
+    l8_sync_consumers();
+    if (!s_last) {                                      // the others never came (cannot happen while all blocks are resident)
+        if (tid == 0) atomicExch(P.status, 3u);
+        return;
+    }
+    // every block sums its share of the part's rows over the splits: thread (row, group) adds the splits
+    // group, group + G, ... in order, the groups are added in order through shared memory
+    const int s_me = (int)blockIdx.x - first;
+    const int q_lo = (int)((int64_t)nrows * s_me / splits), q_hi = (int)((int64_t)nrows * (s_me + 1) / splits);
+    const int nq = q_hi - q_lo;
+    const float* slots = P.partial + (size_t)first * L8_SLOT_FLOATS;
+    for (int q0 = 0; q0 < nq; q0 += L8_NT) {
+        const int nqq = min(L8_NT, nq - q0);
+        int G = L8_NT / nqq;
+        if (G > splits) G = splits;
+        const int r = tid % nqq, grp = tid / nqq;
+        // the output row and its scale are requested before the partial sums, not after them
+        int rr = -1;
+        float rsc = 0.f;
+        if (grp == 0) {
+            rr = source_row(row_lo + q_lo + q0 + r);
+            if (rr >= 0 && P.mode == 0) rsc = __half2float(((const __half*)mm.row_scale)[rr]);
         }
-    if (tid == 0) P.counters[part] = 0u;
+        float sum = 0.f;
+        if (grp < G) {
+            const float* src = slots + q_lo + q0 + r;
+            float v[8];
+            for (int j0 = grp; j0 < splits; j0 += 8 * G) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = (j0 + u * G < splits) ? __ldcg(src + (size_t)(j0 + u * G) * L8_SLOT_FLOATS) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; u++) sum += v[u];
+            }
+        }
+        if (G > 1) {
+            l8_sync_consumers();                        // previous readers of the staging rows
+            if (grp < G) l8_sts32(sacc + (uint32_t)(grp * nqq + r) * 4u, __float_as_uint(sum));
+            l8_sync_consumers();
+            if (grp == 0) {
+                sum = 0.f;
+                for (int gq = 0; gq < G; gq++) sum += __uint_as_float(l8_lds32(sacc + (uint32_t)(gq * nqq + r) * 4u));
+            }
+        }
+        if (grp == 0 && rr >= 0) {
+            if (P.mode == 0) cbl_store_out(P.y[mi], P.ydtype, rr, sum * rsc);
+            else fsum[rr] = sum;
+        }
+    }
+    // the last block to leave resets the part's counters for the next call
+    if (tid == 0 && atomicAdd(P.counters + L8_MAX_BLOCKS + part, 1u) == (unsigned)(splits - 1)) {
+        P.counters[part] = 0u;
+        P.counters[L8_MAX_BLOCKS + part] = 0u;
+    }
 }
 
 // ------------------------------------------------------------------------------------ work split (host)
@@ -429,12 +546,15 @@ static int l8_make_plan(const std::vector<L8Seg>& segs, int maxb, L8Plan* plan) 
         int pr = 1, ks = 1;
         l8_seg_blocks(s, hi, &pr, &ks);
         const int u = s.nrows / 32;
+        if (ks > s.ntile) ks = s.ntile;
+        if (pr > u) pr = u;
         for (int p = 0; p < pr; p++) {
             const int u0 = (int)((int64_t)u * p / pr), u1 = (int)((int64_t)u * (p + 1) / pr);
+            const int first = nb;
             for (int k = 0; k < ks; k++) {
                 const int t0 = (int)((int64_t)s.ntile * k / ks), t1 = (int)((int64_t)s.ntile * (k + 1) / ks);
-                if (u1 > u0 && t1 > t0)
-                    plan->r[nb++] = make_int4(s.mi | (s.order << 2) | (part << 8) | (ks << 16), s.row0 + u0 * 32, (u1 - u0) * 32, t0 | (t1 << 16));
+                plan->r[nb++] = make_int4(s.mi | (s.order << 2) | (part << 8) | (ks << 16) | (first << 24), s.row0 + u0 * 32, (u1 - u0) * 32,
+                                          t0 | (t1 << 16));
             }
             part++;
         }
@@ -447,7 +567,8 @@ static int l8_make_plan(const std::vector<L8Seg>& segs, int maxb, L8Plan* plan) 
 //
 // Book in mma.m16n8k8 A-fragment order: uint4 [128][32] = {a0, a1 of codeword block 2p, a0, a1 of block 2p+1}
 // for lane (g, t): a0 = codeword (16*blk + g) values 2t, 2t+1; a1 = codeword (16*blk + g + 8) values 2t, 2t+1;
-// followed by one float: the largest |value| of the book (bounds the table entries).
+// followed by two floats: the largest |value| of the book and the largest Euclidean norm of a codeword (rounded up;
+// it bounds every table entry).
 __global__ void __launch_bounds__(256) k_repack_book(const uint32_t* __restrict__ table, uint4* __restrict__ out, unsigned int* __restrict__ maxbits) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;       // 0 .. 4095
     const int lane = i & 31, p = i >> 5, g = lane >> 2, t = lane & 3;
@@ -458,15 +579,26 @@ __global__ void __launch_bounds__(256) k_repack_book(const uint32_t* __restrict_
     v.w = table[((2 * p + 1) * 16 + g + 8) * 4 + t];
     out[i] = v;
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    float m = 0.f;
+    float m = 0.f, nrm = 0.f;
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         const float2 f = __half22float2(*(const __half2*)&w[k]);
         m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));             // NaN entries are ignored, infinities kept
+        float q = f.x * f.x + f.y * f.y;                         // this lane's quarter of one codeword's squared norm
+        q += __shfl_xor_sync(0xffffffffu, q, 1);
+        q += __shfl_xor_sync(0xffffffffu, q, 2);
+        nrm = fmaxf(nrm, q);
     }
+    nrm = sqrtf(nrm) * 1.0001f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) atomicMax(maxbits, __float_as_uint(m));     // non-negative floats order like their bit patterns
+    for (int o = 16; o > 0; o >>= 1) {
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        nrm = fmaxf(nrm, __shfl_xor_sync(0xffffffffu, nrm, o));
+    }
+    if (lane == 0) {
+        atomicMax(maxbits, __float_as_uint(m));                  // non-negative floats order like their bit patterns
+        atomicMax(maxbits + 1, __float_as_uint(nrm));
+    }
 }
 
 extern "C" size_t cbl_book_frag_bytes(void) { return 65536 + 16; }
@@ -480,7 +612,7 @@ extern "C" int cbl_repack_book(const void* table, void* out, cbl_stream s) {
 
 // Rotated column-tile layout: uint32 [ntile][3][Rpad].  Position p of the row order holds source row row_index[p]
 // (or p itself when row_index is NULL; -1 and p >= R are padding rows of zero tags).  The 8 tags of a row and tile
-// form a 96-bit stream whose slot s holds chunk column (s + p) mod 8; word k of that stream is stored at [tile][k][p].
+// form a 96-bit stream whose slot s holds chunk column (s + p / 4) mod 8; word k of that stream is stored at [tile][k][p].
 extern "C" size_t cbl_l8r_bytes(int32_t Rpad, int32_t C, int32_t books) {
     if (Rpad < 0 || C <= 0 || books < 1) return 0;
     return (size_t)books * cbl_ceil_div(C / 8, 8) * 3 * (size_t)Rpad * 4;
@@ -500,7 +632,7 @@ __global__ void __launch_bounds__(256) k_repack_l8r(cbl_packed m, const int32_t*
     if (r >= 0) {
 #pragma unroll
         for (int s = 0; s < 8; s++) {
-            const int chunk = tile * 8 + ((s + p) & 7);
+            const int chunk = tile * 8 + ((s + (p >> 2)) & 7);
             const uint32_t tag = chunk < nch ? cbl_read_tag(words + (int64_t)r * m.W, m.W, chunk, 12) : 0u;
             const int bit = 12 * s;
             w[bit >> 5] |= tag << (bit & 31);
@@ -587,14 +719,14 @@ extern "C" int cbl_gemv_l8_plan(const cbl_l8* mats, int32_t n, int32_t max_block
     return CBL_OK;
 }
 
-static int launch_l8(const L8Launch& P, const void* x, int xdtype, cudaStream_t st) {
+static int launch_l8(const L8Launch& P, const void* x, int xdtype, cudaStream_t st, int max_blocks = L8_MAX_BLOCKS) {
     static bool attr_set[64] = {};
     static std::mutex mu;
     int dev = 0;
     CBL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return CBL_EUNSUPPORTED;
-    int grid = cbl_sm_count();
-    if (grid > L8_MAX_BLOCKS) grid = L8_MAX_BLOCKS;
+    int grid = cbl_sm_count();                          // one block per SM: every block of the launch is resident at once
+    if (grid > max_blocks) grid = max_blocks;
     // plan cache: the cut depends only on the shapes of the group
     static std::map<std::vector<int>, L8Plan> cache;
     std::vector<int> key = {grid, P.n};
@@ -629,14 +761,14 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, cudaStream_t 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(plan.nblocks);
-    cfg.blockDim = dim3(L8_NT);
+    cfg.blockDim = dim3(L8_THREADS);
     cfg.dynamicSmemBytes = L8_DYN_SMEM;
     CBL_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_l8, P, plan, x, xdtype));
     return cbl_check_launch();
 }
 
-// Fills the launch descriptor of a group: each matrix's region of `workspace` in order (cbl_gemv_l8_workspace_bytes(R_i)
-// bytes each); counters and status word are those of the first region.
+// Fills the launch descriptor of a group.  Work space: partial-sum slots | counters + status | fp32 sums of matrix 0,
+// matrix 1, ... (l8_rows_max(R_i) floats each).
 static int l8_group(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype, int mode, void* workspace,
                     L8Launch& P) {
     if (!mats || !x || !workspace || n < 1) return CBL_EINVAL;
@@ -646,24 +778,20 @@ static int l8_group(const cbl_l8* mats, int32_t n, const void* x, int xdtype, vo
     P.n = 0;
     P.ydtype = ydtype;
     P.mode = mode;
-    P.counters = nullptr;
-    size_t off = 0;
+    P.partial = (float*)workspace;
+    P.counters = (unsigned int*)((char*)workspace + L8_PART_BYTES);
+    P.status = P.counters + L8_STATUS_WORD;
+    size_t off = L8_PART_BYTES + L8_CTL_WORDS * 4;
     for (int i = 0; i < n; i++) {
         int rc = check_l8r(mats + i);
         if (rc) return rc;
         if (mats[i].C != mats[0].C) return CBL_EINVAL;          // one shared activation vector
         if (ys && !ys[i]) return CBL_EINVAL;
         char* reg = (char*)workspace + off;
-        const size_t rmax = l8_rows_max(mats[i].R);
-        if (!P.counters) {
-            P.counters = (unsigned int*)(reg + rmax * 12);
-            P.status = P.counters + L8_STATUS_WORD;
-        }
-        off += cbl_gemv_l8_workspace_bytes(mats[i].R);
+        off += l8_rows_max(mats[i].R) * 4;
         if (mats[i].R == 0) continue;
         P.m[P.n] = mats[i];
-        P.iacc[P.n] = (unsigned long long*)reg;
-        P.fsum[P.n] = (float*)(reg + rmax * 8);
+        P.fsum[P.n] = (float*)reg;
         P.y[P.n] = ys ? ys[i] : nullptr;
         P.n++;
     }
@@ -693,11 +821,11 @@ extern "C" int cbl_gemv_l8(const cbl_l8* m, const void* x, int xdtype, void* y, 
 // wait expired and the output is invalid).  Synchronises the stream.
 extern "C" int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s) {
     if (!workspace || R < 0) return CBL_EINVAL;
-    char* p = (char*)workspace + l8_rows_max(R) * 12 + L8_STATUS_WORD * 4;
+    char* p = (char*)workspace + L8_PART_BYTES + L8_STATUS_WORD * 4;
     unsigned int v = 0;
     CBL_CUDA(cudaMemcpyAsync(&v, p, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
-    if (v) CBL_CUDA(cudaMemsetAsync(p, 0, 4, (cudaStream_t)s));
+    if (v) CBL_CUDA(cudaMemsetAsync((char*)workspace + L8_PART_BYTES, 0, L8_CTL_WORDS * 4, (cudaStream_t)s));   // counters too
     return v ? CBL_ETIMEOUT : CBL_OK;
 }
 
@@ -922,7 +1050,7 @@ extern "C" int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype,
 //
 // Work space of each rank (the same layout everywhere, allocated as symmetric memory by the caller,
 // zero before the first call): sums[0] | sums[1] (rmax fp32 each) | flags (uint32 per rank) | status |
-// completed calls | block ticket | the product's own fixed-point sums and counters.
+// completed calls | block ticket | the product's own partial-sum slots and counters.
 constexpr int L8_AR_MAX_RANKS = 8;
 constexpr uint32_t L8_AR_SPIN_LIMIT = 1u << 22;      // polls of a peer's flag before giving up (~1 s)
 
@@ -938,7 +1066,7 @@ struct L8AllReduce {
 
 extern "C" size_t cbl_gemv_l8_ar_workspace_bytes(int32_t R) {
     if (R < 0) return 0;
-    return l8_rows_max(R) * 16 + L8_AR_MAX_RANKS * 4 + 32 + L8_CTL_WORDS * 4;
+    return l8_rows_max(R) * 8 + L8_AR_MAX_RANKS * 4 + 32 + L8_PART_BYTES + L8_CTL_WORDS * 4;
 }
 
 __global__ void __launch_bounds__(256) k_l8_finish_allreduce(const __grid_constant__ L8AllReduce A) {
@@ -1013,9 +1141,9 @@ extern "C" int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* 
     P.mode = 1;
     P.m[0] = *m;
     P.fsum[0] = (float*)own;
-    P.iacc[0] = (unsigned long long*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32);
+    P.partial = (float*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32);
     P.y[0] = y;
-    P.counters = (unsigned int*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32 + rmax * 8);
+    P.counters = (unsigned int*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32 + L8_PART_BYTES);
     P.status = ctl;
     P.calls = ctl + 1;
     P.fsum_stride = (int64_t)rmax;
@@ -1063,11 +1191,13 @@ extern "C" int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s) {
 // Some hosts may not give this library a way to obtain device memory: a serving runtime that carves
 // all of HBM into its own pools at start-up, or a plugin slot whose contract forbids allocator calls
 // on the request path (an allocation can synchronise the device and fragments a pre-sized pool).
-// For them the product's work space (fixed-point row sums, counters, status word) lives in a fixed array
-// inside the library image instead of a caller buffer.  The array is part of every CUDA context that loads
-// the library (about 776 KB per GPU, held until the process exits).
+// For them the product's work space (partial-sum slots, counters, status word) lives in a fixed array
+// inside the library image instead of a caller buffer; the launch is limited to L8_STATIC_BLOCKS thread
+// blocks so that the array stays small (770 KB per GPU, part of every CUDA context that loads the library,
+// held until the process exits).
 constexpr int L8_STATIC_MAX_ROWS = 65536;
-constexpr size_t L8_STATIC_BYTES = ((size_t)L8_STATIC_MAX_ROWS + 32 * L8_MAX_ORDERS) * 12 + L8_CTL_WORDS * 4;
+constexpr int L8_STATIC_BLOCKS = 48;
+constexpr size_t L8_STATIC_BYTES = (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4 + L8_CTL_WORDS * 4;
 static __device__ __align__(256) unsigned char g_l8_static_scratch[L8_STATIC_BYTES];
 
 extern "C" int32_t cbl_gemv_l8_static_max_rows(void) { return L8_STATIC_MAX_ROWS; }
@@ -1091,25 +1221,48 @@ static int l8_static_addr(void** out) {
 }
 
 extern "C" int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s) {
-    if (!m) return CBL_EINVAL;
-    if (m->R > L8_STATIC_MAX_ROWS) return CBL_EUNSUPPORTED;      // the built-in scratch holds 65536 rows at most
+    if (!m || !y) return CBL_EINVAL;
+    if (m->R > L8_STATIC_MAX_ROWS) return CBL_EUNSUPPORTED;      // stated limit of this entry point
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
     void* scratch = nullptr;
     int rc = l8_static_addr(&scratch);                           // (the first call per device should happen outside stream capture)
     if (rc) return rc;
+    int nrc = check_l8r(m);
+    if (nrc) return nrc;
+    if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
+    if (!x) return CBL_EINVAL;
+    if (m->R == 0) return CBL_OK;
     // Every call shares the array and finds whatever the previous call left.  A product that ran to its end left
-    // sums and counters zero; one that gave up (status word set) did not, so the part this call accumulates into
-    // is cleared on the caller's stream first - all but the status word, which only cbl_gemv_l8_static_status clears.
-    const size_t body = l8_rows_max(m->R) * 12;
-    CBL_CUDA(cudaMemsetAsync(scratch, 0, body + L8_STATUS_WORD * 4, (cudaStream_t)s));
-    return cbl_gemv_l8(m, x, xdtype, y, ydtype, scratch, s);
+    // its counters zero; one that gave up (status word set) did not, so the counters are cleared on the caller's
+    // stream first - not the status word, which only cbl_gemv_l8_static_status clears.  The partial-sum slots
+    // need no clearing: every block overwrites its own before anyone reads it.
+    unsigned int* ctl = (unsigned int*)((char*)scratch + (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4);
+    CBL_CUDA(cudaMemsetAsync(ctl, 0, L8_STATUS_WORD * 4, (cudaStream_t)s));
+    L8Launch P;
+    P.n = 1;
+    P.ydtype = ydtype;
+    P.mode = 0;
+    P.m[0] = *m;
+    P.partial = (float*)scratch;
+    P.fsum[0] = nullptr;
+    P.y[0] = y;
+    P.counters = ctl;
+    P.status = ctl + L8_STATUS_WORD;
+    P.calls = nullptr;
+    P.fsum_stride = 0;
+    return launch_l8(P, x, xdtype, (cudaStream_t)s, L8_STATIC_BLOCKS);
 }
 
-// CBL_ETIMEOUT if a cbl_gemv_l8_static product of R rows on the current device gave up on a bounded wait since the
-// last query (its output is invalid).  Synchronises the stream and clears the word; allocates nothing.
-extern "C" int cbl_gemv_l8_static_status(int32_t R, cbl_stream s) {
-    if (R < 0 || R > L8_STATIC_MAX_ROWS) return CBL_EINVAL;
+// CBL_ETIMEOUT if a cbl_gemv_l8_static product on the current device gave up on a bounded wait since the last
+// query (its output is invalid).  Synchronises the stream and clears the word; allocates nothing.
+extern "C" int cbl_gemv_l8_static_status(cbl_stream s) {
     void* scratch = nullptr;
     int rc = l8_static_addr(&scratch);
     if (rc) return rc;
-    return cbl_gemv_l8_status(scratch, R, s);
+    char* p = (char*)scratch + (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4 + L8_STATUS_WORD * 4;
+    unsigned int v = 0;
+    CBL_CUDA(cudaMemcpyAsync(&v, p, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
+    if (v) CBL_CUDA(cudaMemsetAsync(p, 0, 4, (cudaStream_t)s));
+    return v ? CBL_ETIMEOUT : CBL_OK;
 }

@@ -466,7 +466,7 @@ class L8Matrix:
     def static_status(self) -> None:
         """Synchronises and raises CblError if a run_static() product gave up on a bounded device-side wait."""
         with torch.cuda.device(self.device):
-            _lib.check("cbl_gemv_l8_static_status", lib.cbl_gemv_l8_static_status(self.R, _stream()))
+            _lib.check("cbl_gemv_l8_static_status", lib.cbl_gemv_l8_static_status(_stream()))
 
     _stage: dict = {}
 

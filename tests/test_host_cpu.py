@@ -45,7 +45,8 @@ def test_size_queries_match_the_layout_arithmetic():
     assert lib.cbl_l8r_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
     assert lib.cbl_l8r_bytes(4864 + 32, 896, 2) == 2 * 14 * 3 * 4896 * 4
     assert lib.cbl_book_frag_bytes() == 65536 + 16
-    assert lib.cbl_gemv_l8_workspace_bytes(18944) == (18944 + 512) * 12 + 1024
+    # work space: 160 partial-sum slots of 4096 floats, 512 control words, fp32 sums per (padded) row
+    assert lib.cbl_gemv_l8_workspace_bytes(18944) == 160 * 4096 * 4 + 2048 + (18944 + 512) * 4
     assert lib.cbl_gemv_l8_static_max_rows() == 65536
 
 
@@ -83,7 +84,9 @@ def test_batch1_work_split_covers_every_row_and_tile_exactly_once(shapes, sms):
         assert (c == 1).all()
     for part, blocks in parts.items():                # the blocks of a part share rows and know how many they are
         assert len({b[:3] for b in blocks}) == 1 and all(b[3] == len(blocks) for b in blocks)
-    assert len(parts) <= 192                          # one arrival counter each
+    assert len(parts) <= 160                          # one arrival counter each
+    firsts = sorted(min(i for i, row in enumerate(out[:nb.value]) if row[2] == part) for part in parts)
+    assert firsts == sorted(set(firsts))
 
 
 def test_batch1_work_split_rejects_what_it_cannot_place():
