@@ -148,7 +148,7 @@ typedef struct cbl_l8 {
     int32_t R, C, books, ntile, Rpad;   /* ntile counts both books' tiles */
     int32_t rot;                        /* 0 or 1, see above */
     int32_t M;                          /* column orders (rot = 1; at most CBL_L8_MAX_ORDERS), else 1 */
-    int32_t reserved;
+    int32_t book_exp;                   /* rot = 1: cbl_book_norm_exp of frag (host-known, so that the kernel need not fetch it) */
     const void* words;                  /* uint32 [ntile][3][Rpad] */
     const void* frag;                   /* the 4096 x 8 book in tensor-core fragment order (cbl_repack_book) */
     const void* frag2;                  /* second book when books == 2 */
@@ -159,7 +159,7 @@ typedef struct cbl_l8 {
     const int32_t* perms;               /* rot = 1, M > 1: int32 [M][C], the activation index of every stored column */
     int32_t seg_off[CBL_L8_MAX_ORDERS + 1];  /* rot = 1 (read on the HOST): positions [seg_off[m], seg_off[m+1]) hold the rows
                                            of column order m; multiples of 32, seg_off[0] = 0, seg_off[M] = Rpad */
-    int32_t reserved2;
+    int32_t book_exp2;                  /* the same for frag2 when books == 2 */
 } cbl_l8;
 
 size_t cbl_l8_bytes(int32_t R, int32_t C, int32_t books);
@@ -174,16 +174,20 @@ int cbl_repack_l8r(const cbl_packed* m, const int32_t* row_index, int32_t Rpad, 
  * shapequant/kernels/cuda_gemv.py:129-141). */
 size_t cbl_book_frag_bytes(void);
 int cbl_repack_book(const void* table, void* out, cbl_stream s);
+/* floor(log2(largest Euclidean norm of a codeword)) of a book re-ordered by cbl_repack_book (clamped to -8 .. 24):
+ * the exponent that scales the batch-1 kernel's tables.  Synchronises the stream (a load-time call). */
+int cbl_book_norm_exp(const void* frag, int32_t* exp_out, cbl_stream s);
 
 /* Batch-1 product by activation-side tables on the rot = 1 layout:
  *   y[r] = round_to(ydtype, row_scale[r] * sum_j <table[tag[r, j]], x[perms[m_r][8 j .. 8 j + 7]]>)   (perms = identity for M = 1)
  * Per tile the kernel computes T[e][c] = <table[e], x_chunk_c> once on the tensor cores (fp16 with a power-of-two
  * scale per tile, two alternating 64 KB tables in shared memory) and every weight chunk becomes one 2-byte
- * shared-memory read and one fp32 add.  Blocks that share rows store their fp32 partial sums into slots of the
- * work space, meet at a counter (bounded wait) and then each sums a slice of the rows over the blocks in a fixed
- * order, scales, rounds and writes y: one kernel per call, and repeated calls agree bit for bit.
- * Work space: cbl_gemv_l8_workspace_bytes(R) bytes, zero before the first call; every completed call leaves its
- * counters zero again (the rest may hold anything).  Calls that share a work space must not overlap on the device.
+ * shared-memory read and an integer add (the entries are 16-bit integers with a power-of-two scale per tile).
+ * Blocks that share rows store their fp32 partial sums into slots of the work space as {valid flag, value}
+ * words; each block then sums a slice of the rows over the blocks in a fixed order (polling, with a bound, words
+ * that have not landed yet), scales, rounds and writes y: one kernel per call, and repeated calls agree bit for bit.
+ * Work space: cbl_gemv_l8_workspace_bytes(R) bytes, zero before the first call; every completed call leaves it
+ * as it found it (slots zero).  Calls that share a work space must not overlap on the device.
  * Codeword magnitudes up to 2^13 are supported (larger ones may overflow the fp16 tables).
  * replaces shapequant/kernels/gemv.py:28-64, 142-162 (_gemv_kernel, PackedLinear.gemv) and
  *          shapequant/kernels/proto_runs.py:412-473, 505-571 (gemv_additive, gemv) for batch 1, including their
@@ -229,7 +233,7 @@ int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s);
 
 /* The kernel's waits (on its staged copies, on the other blocks of a row part) are bounded; if one ever
  * expires the kernel sets a status word in the work space and leaves.  This call synchronises the stream and
- * returns CBL_OK or CBL_ETIMEOUT; after a time-out it also clears the word and the counters, so the work space
+ * returns CBL_OK or CBL_ETIMEOUT; after a time-out it also clears the work space (on that stream), so it
  * can be used again.  R is not used (kept for the signature of earlier versions).
  * (The reference's kernels spin without a bound, shapequant/kernels/proto_runs.py:234-243.) */
 int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s);
@@ -237,17 +241,18 @@ int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s);
 /* The same batch-1 product for callers that cannot hand the library any device memory of their
  * own making (hosts that pre-partition the whole GPU into private pools, or plugin contracts that
  * forbid allocator calls while serving).  The product's work space lives in a fixed array compiled into
- * the library: 770 KB of every GPU that loads the library stay reserved until the process exits, and the
- * launch uses at most 48 thread blocks so that their partial sums fit (slower than cbl_gemv_l8 on large
+ * the library: 1 MB + 256 B of every GPU that loads the library stay reserved until the process exits, and the
+ * launch uses at most 32 thread blocks so that their partial sums fit (slower than cbl_gemv_l8 on large
  * matrices, same results bit for bit when the work split is the same, within fp32 summation order otherwise).
  * Limit: cbl_gemv_l8_static_max_rows() = 65536 output rows (larger R: CBL_EUNSUPPORTED).
  * The call allocates and frees nothing.  Its first use on a device looks the array's device address
  * up (cudaGetSymbolAddress, under a lock), so make that first call before any stream capture.  All calls
- * share the one array: the call clears the counters it needs on its stream before launching, and two such
- * products that overlap on the GPU (different streams, or a replayed graph beside a live call)
- * race on it - serialise them.
+ * share the one array, which keeps the last call's contents: a product that runs to its end clears every word
+ * it used (the array starts zero), one that gave up leaves words behind until cbl_gemv_l8_static_status clears
+ * them; two such products that overlap on the GPU (different streams, or a replayed graph beside a live call)
+ * race on the array - serialise them.
  * cbl_gemv_l8_static_status(s): the bounded-wait status of such products on the current device since the last
- * query (CBL_OK or CBL_ETIMEOUT; synchronises the stream, clears the word, allocates nothing).
+ * query (CBL_OK or CBL_ETIMEOUT; synchronises the stream, after a time-out clears the array, allocates nothing).
  * No counterpart in the reference (its launchers allocate through torch / CuPy). */
 int32_t cbl_gemv_l8_static_max_rows(void);
 int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s);

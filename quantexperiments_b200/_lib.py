@@ -50,10 +50,10 @@ L8_MAX_ORDERS = 16
 class L8(Structure):
     """struct cbl_l8: column-tile layout (rot = 1: the batch-1 product; rot = 0: the tensor-core products)."""
     _fields_ = [("R", c_int32), ("C", c_int32), ("books", c_int32), ("ntile", c_int32), ("Rpad", c_int32),
-                ("rot", c_int32), ("M", c_int32), ("reserved", c_int32),
+                ("rot", c_int32), ("M", c_int32), ("book_exp", c_int32),
                 ("words", c_void_p), ("frag", c_void_p), ("frag2", c_void_p), ("row_scale", c_void_p),
                 ("table", c_void_p), ("table2", c_void_p), ("row_index", c_void_p), ("perms", c_void_p),
-                ("seg_off", c_int32 * (L8_MAX_ORDERS + 1)), ("reserved2", c_int32)]
+                ("seg_off", c_int32 * (L8_MAX_ORDERS + 1)), ("book_exp2", c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/cbl.h declares
@@ -82,6 +82,7 @@ SIGNATURES = {
     "cbl_repack_l8r": (c_int, [POINTER(Packed), c_void_p, c_int32, c_void_p, c_void_p]),
     "cbl_book_frag_bytes": (c_size_t, []),
     "cbl_repack_book": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "cbl_book_norm_exp": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "cbl_gemv_l8_workspace_bytes": (c_size_t, [c_int32]),
     "cbl_gemv_l8": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "cbl_gemv_l8_plan": (c_int, [POINTER(L8), c_int32, c_int32, c_void_p, c_void_p]),

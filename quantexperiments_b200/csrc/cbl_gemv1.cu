@@ -11,12 +11,14 @@
 // for its predecessor).  A block owns a rectangle (rows x tiles) of one matrix; a thread owns up to 8 rows
 // of it and keeps their fp32 sums in registers over all the block's tiles.
 //
-// Row sums of blocks that share rows (different tile ranges) meet without atomics and in a FIXED order, so two
-// runs agree bit for bit: every block stores its fp32 partial sums into its own slot of the work space, the
-// blocks of a row part meet at a counter (bounded wait; all blocks of a launch are resident at once: one block
-// per SM, at most as many blocks as SMs), and then EVERY block of the part sums a slice of the part's rows over
-// the splits, in split order, applies the row scale, rounds and writes y - one kernel per call, the finishing
-// work spread over all SMs.
+// Row sums of blocks that share rows (different tile ranges) meet without atomics, fences or counters, and in a
+// FIXED order, so two runs agree bit for bit: every block stores its fp32 partial sums into its own slot of the
+// work space as 64-bit words {valid flag, value} (a 64-bit store is indivisible: whoever sees the flag sees the
+// value).  Then EVERY block of the row part sums a slice of the part's rows over the splits, in split order -
+// polling, with a bound, the words that have not landed yet and clearing each word it has consumed - applies the
+// row scale, rounds and writes y.  One kernel per call, the finishing work spread over all SMs, two memory round
+// trips after the last lookup.  (All blocks of a launch are resident at once - one block per SM, at most as many
+// blocks as SMs - so the poll cannot starve the block it waits for.)
 //
 // Shared-memory gathers bound this kernel, not HBM: a warp's 32 random 2-byte reads take as many cycles
 // as the most loaded bank has requests, 3.3 on average.  Per lane the column it reads rotates with the lane
@@ -44,15 +46,15 @@ constexpr uint32_t L8_WAIT_LIMIT = 1u << 20;     // mbarrier polls before a wait
 constexpr int L8_MAX_GROUP = 4;
 constexpr int L8_MAX_BLOCKS = 160;
 constexpr int L8_MAX_ORDERS = 16;
-constexpr int L8_SLOT_FLOATS = L8_NT * L8_RPT;    // partial-sum slot of one block
-constexpr size_t L8_PART_BYTES = (size_t)L8_MAX_BLOCKS * L8_SLOT_FLOATS * 4;
-constexpr int L8_CTL_WORDS = 512;                // arrivals [0, 160), departures [160, 320), status word at 320
-constexpr int L8_STATUS_WORD = 320;
-constexpr uint32_t L8_MEET_LIMIT = 1u << 20;     // polls of a part's arrival counter before a block gives up (~1 s)
+constexpr int L8_SLOT_ROWS = L8_NT * L8_RPT;      // partial-sum slot of one block: one 64-bit word per row
+constexpr size_t L8_PART_BYTES = (size_t)L8_MAX_BLOCKS * L8_SLOT_ROWS * 8;
+constexpr int L8_CTL_WORDS = 64;                 // status word at 0
+constexpr int L8_STATUS_WORD = 0;
+constexpr uint32_t L8_MEET_LIMIT = 1u << 20;     // polls of another block's partial sums before a block gives up (~1 s)
 
 static inline size_t l8_rows_max(int32_t R) { return ((size_t)R + 31) / 32 * 32 + 32 * L8_MAX_ORDERS; }
 
-// Work space of a launch: partial-sum slots of the blocks | counters + status | fp32 sums by source row of each
+// Work space of a launch: partial-sum slots of the blocks | status word | fp32 sums by source row of each
 // matrix (mode 1).  The per-matrix figure covers a launch of that matrix alone; a group needs no more than the sum.
 extern "C" size_t cbl_gemv_l8_workspace_bytes(int32_t R) {
     if (R < 0) return 0;
@@ -137,10 +139,9 @@ struct L8Launch {
     int ydtype;
     int mode;                          // 0: y = round(row_scale * sum); 1: fsum[source row] = sum (an epilogue kernel follows)
     cbl_l8 m[L8_MAX_GROUP];
-    float* partial;                    // L8_MAX_BLOCKS slots of L8_SLOT_FLOATS fp32 partial sums (any contents)
+    unsigned long long* partial;       // L8_MAX_BLOCKS slots of L8_SLOT_ROWS words {valid << 32 | fp32 partial sum} (zero on entry, left zero)
     float* fsum[L8_MAX_GROUP];         // mode 1: fp32 sums by source row
     void* y[L8_MAX_GROUP];
-    unsigned int* counters;            // per row part: arrivals [part], departures [L8_MAX_BLOCKS + part] (zero on entry, left zero)
     unsigned int* status;              // set to 1 when a bounded wait expired
     const uint32_t* calls;             // optional: completed-call counter; call e = *calls + 1 writes its sums to
     int64_t fsum_stride;               // fsum[0] + (e & 1) * fsum_stride (two alternating buffers, see cbl_gemv_l8_ar)
@@ -230,17 +231,17 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
         return;
     }
 
-    // ---- consumers.  A build reads its share of the book's mma A fragments from global memory (L2-resident: 64 KB
-    // per book, one 16-byte load per two 16-codeword blocks) - kept in registers they would crowd the lookup loop.
+    // ---- consumers.  The book's mma A fragments stay in registers for all tiles of a book (one 16-byte load per two
+    // 16-codeword blocks); everything that does not depend on the previous kernel is requested before the wait.
     const int ntile1 = mm.ntile / mm.books;
-    const uint4* frag = nullptr;
+    uint4 af[8];
     int cur_book = -1, jx = 0;
     auto set_book = [&](int book) {
-        frag = (const uint4*)(book ? mm.frag2 : mm.frag) + warp * 32 + lane;
-        const float nb = __ldg((const float*)((const uint4*)(book ? mm.frag2 : mm.frag) + 4096) + 1);   // largest Euclidean norm of a codeword
-        // |<codeword, x_chunk>| <= nb * |x_chunk| < 2^(jx + 1) * 2^(13 - jx) = 2^14: every entry fits 16 bits with room to spare
-        jx = (nb > 0.f && nb < 3.0e38f) ? ilogbf(nb) : 0;
-        jx = jx < -8 ? -8 : (jx > 24 ? 24 : jx);
+        const uint4* fr = (const uint4*)(book ? mm.frag2 : mm.frag);
+#pragma unroll
+        for (int i = 0; i < 8; i++) af[i] = __ldg(fr + (warp + i * L8_NWARP) * 32 + lane);
+        // |<codeword, x_chunk>| <= norm * |x_chunk| < 2^(jx + 1) * 2^(13 - jx) = 2^14: every entry fits 16 bits with room to spare
+        jx = book ? mm.book_exp2 : mm.book_exp;
         cur_book = book;
     };
     set_book(tile_lo / ntile1);
@@ -267,9 +268,6 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
     // 2^13 * 2^-jx: the products then stay below 2^14 in magnitude whatever the inputs (Cauchy-Schwarz) and
     // are stored as rounded 16-bit integers; the returned factor undoes the scale on the integer sum of a row.
     auto build = [&](uint32_t tbl, float va, float vb) -> float {
-        uint4 af[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) af[i] = __ldg(frag + i * (L8_NWARP * 32));
         float me = fmaxf(fabsf(va), fabsf(vb));          // largest element of the tile: a first scale, so that squares cannot overflow
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) me = fmaxf(me, __shfl_xor_sync(0xffffffffu, me, o));
@@ -420,32 +418,20 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
         }
         return;
     }
-    // this block's partial sums -> its slot; then meet the other blocks of the part
-    float* slot = P.partial + (size_t)blockIdx.x * L8_SLOT_FLOATS;
+    // this block's partial sums -> its slot, each with its valid flag
+    unsigned long long* slot = P.partial + (size_t)blockIdx.x * L8_SLOT_ROWS;
     for (int j = 0; j < n512; j++) {
         const int q = j * L8_NT + tid;
-        if (q < nrows) __stcg(slot + q, __uint_as_float(l8_lds32(sacc + (uint32_t)q * 4u)));
+        if (q < nrows) __stcg(slot + q, (1ull << 32) | (unsigned long long)l8_lds32(sacc + (uint32_t)q * 4u));
     }
-    __threadfence();
-    l8_sync_consumers();
-    if (tid == 0) {
-        atomicAdd(P.counters + part, 1u);
-        uint32_t seen = 0;
-        for (uint32_t i = 0; i < L8_MEET_LIMIT && seen < (uint32_t)splits; i++)
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.counters + part) : "memory");
-        s_last = seen >= (uint32_t)splits;
-    }
-    l8_sync_consumers();
-    if (!s_last) {                                      // the others never came (cannot happen while all blocks are resident)
-        if (tid == 0) atomicExch(P.status, 3u);
-        return;
-    }
+    l8_sync_consumers();                                // the row sums in shared memory have been read: the space is staging now
     // every block sums its share of the part's rows over the splits: thread (row, group) adds the splits
     // group, group + G, ... in order, the groups are added in order through shared memory
     const int s_me = (int)blockIdx.x - first;
     const int q_lo = (int)((int64_t)nrows * s_me / splits), q_hi = (int)((int64_t)nrows * (s_me + 1) / splits);
     const int nq = q_hi - q_lo;
-    const float* slots = P.partial + (size_t)first * L8_SLOT_FLOATS;
+    unsigned long long* slots = P.partial + (size_t)first * L8_SLOT_ROWS;
+    bool late = false;
     for (int q0 = 0; q0 < nq; q0 += L8_NT) {
         const int nqq = min(L8_NT, nq - q0);
         int G = L8_NT / nqq;
@@ -460,13 +446,30 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
         }
         float sum = 0.f;
         if (grp < G) {
-            const float* src = slots + q_lo + q0 + r;
-            float v[8];
+            unsigned long long* src = slots + q_lo + q0 + r;
             for (int j0 = grp; j0 < splits; j0 += 8 * G) {
+                float v[8];
+                uint32_t need = 0;
 #pragma unroll
-                for (int u = 0; u < 8; u++) v[u] = (j0 + u * G < splits) ? __ldcg(src + (size_t)(j0 + u * G) * L8_SLOT_FLOATS) : 0.f;
+                for (int u = 0; u < 8; u++)
+                    if (j0 + u * G < splits) need |= 1u << u;
+                for (uint32_t poll = 0; need && poll < L8_MEET_LIMIT; poll++) {
+                    unsigned long long w[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) sum += v[u];
+                    for (int u = 0; u < 8; u++)
+                        if (need >> u & 1u) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[u]) : "l"(src + (size_t)(j0 + u * G) * L8_SLOT_ROWS) : "memory");
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+                        if ((need >> u & 1u) && (w[u] >> 32)) {
+                            v[u] = __uint_as_float((uint32_t)w[u]);
+                            need &= ~(1u << u);
+                            __stcg(src + (size_t)(j0 + u * G) * L8_SLOT_ROWS, 0ull);     // consumed: clear it for the next call
+                        }
+                }
+                if (need) late = true;
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (j0 + u * G < splits) sum += v[u];
             }
         }
         if (G > 1) {
@@ -478,16 +481,12 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
                 for (int gq = 0; gq < G; gq++) sum += __uint_as_float(l8_lds32(sacc + (uint32_t)(gq * nqq + r) * 4u));
             }
         }
-        if (grp == 0 && rr >= 0) {
+        if (grp == 0 && rr >= 0 && !late) {
             if (P.mode == 0) cbl_store_out(P.y[mi], P.ydtype, rr, sum * rsc);
             else fsum[rr] = sum;
         }
     }
-    // the last block to leave resets the part's counters for the next call
-    if (tid == 0 && atomicAdd(P.counters + L8_MAX_BLOCKS + part, 1u) == (unsigned)(splits - 1)) {
-        P.counters[part] = 0u;
-        P.counters[L8_MAX_BLOCKS + part] = 0u;
-    }
+    if (late) atomicExch(P.status, 3u);                 // another block's sums never came (cannot happen while all blocks are resident)
 }
 
 // ------------------------------------------------------------------------------------ work split (host)
@@ -603,6 +602,16 @@ __global__ void __launch_bounds__(256) k_repack_book(const uint32_t* __restrict_
 
 extern "C" size_t cbl_book_frag_bytes(void) { return 65536 + 16; }
 
+extern "C" int cbl_book_norm_exp(const void* frag, int32_t* exp_out, cbl_stream s) {
+    if (!frag || !exp_out) return CBL_EINVAL;
+    float nb = 0.f;
+    CBL_CUDA(cudaMemcpyAsync(&nb, (const char*)frag + 65536 + 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
+    int e = (nb > 0.f && nb < 3.0e38f) ? ilogbf(nb) : 0;
+    *exp_out = e < -8 ? -8 : (e > 24 ? 24 : e);
+    return CBL_OK;
+}
+
 extern "C" int cbl_repack_book(const void* table, void* out, cbl_stream s) {
     if (!table || !out || ((uintptr_t)table % 4) || ((uintptr_t)out % 16)) return CBL_EINVAL;
     CBL_CUDA(cudaMemsetAsync((char*)out + 65536, 0, 16, (cudaStream_t)s));
@@ -670,6 +679,7 @@ static int check_l8r(const cbl_l8* m) {
     if (m->ntile != m->books * cbl_ceil_div(m->C / 8, 8) || m->ntile >= 65536) return CBL_EINVAL;
     if (m->M < 1 || m->M > L8_MAX_ORDERS) return CBL_EUNSUPPORTED;
     if (m->M > 1 && (!m->perms || !m->row_index)) return CBL_EINVAL;
+    if (m->book_exp < -8 || m->book_exp > 24 || (m->books == 2 && (m->book_exp2 < -8 || m->book_exp2 > 24))) return CBL_EINVAL;
     if (!m->row_index && m->Rpad < m->R) return CBL_EINVAL;
     if ((size_t)m->Rpad > l8_rows_max(m->R)) return CBL_EINVAL;
     if (m->seg_off[0] != 0 || m->seg_off[m->M] != m->Rpad) return CBL_EINVAL;
@@ -767,7 +777,7 @@ static int launch_l8(const L8Launch& P, const void* x, int xdtype, cudaStream_t 
     return cbl_check_launch();
 }
 
-// Fills the launch descriptor of a group.  Work space: partial-sum slots | counters + status | fp32 sums of matrix 0,
+// Fills the launch descriptor of a group.  Work space: partial-sum slots | status word | fp32 sums of matrix 0,
 // matrix 1, ... (l8_rows_max(R_i) floats each).
 static int l8_group(const cbl_l8* mats, int32_t n, const void* x, int xdtype, void* const* ys, int ydtype, int mode, void* workspace,
                     L8Launch& P) {
@@ -778,9 +788,8 @@ static int l8_group(const cbl_l8* mats, int32_t n, const void* x, int xdtype, vo
     P.n = 0;
     P.ydtype = ydtype;
     P.mode = mode;
-    P.partial = (float*)workspace;
-    P.counters = (unsigned int*)((char*)workspace + L8_PART_BYTES);
-    P.status = P.counters + L8_STATUS_WORD;
+    P.partial = (unsigned long long*)workspace;
+    P.status = (unsigned int*)((char*)workspace + L8_PART_BYTES) + L8_STATUS_WORD;
     size_t off = L8_PART_BYTES + L8_CTL_WORDS * 4;
     for (int i = 0; i < n; i++) {
         int rc = check_l8r(mats + i);
@@ -825,7 +834,7 @@ extern "C" int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s) {
     unsigned int v = 0;
     CBL_CUDA(cudaMemcpyAsync(&v, p, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
-    if (v) CBL_CUDA(cudaMemsetAsync((char*)workspace + L8_PART_BYTES, 0, L8_CTL_WORDS * 4, (cudaStream_t)s));   // counters too
+    if (v) CBL_CUDA(cudaMemsetAsync(workspace, 0, L8_PART_BYTES + L8_CTL_WORDS * 4, (cudaStream_t)s));   // and whatever the slots still hold
     return v ? CBL_ETIMEOUT : CBL_OK;
 }
 
@@ -1050,7 +1059,7 @@ extern "C" int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype,
 //
 // Work space of each rank (the same layout everywhere, allocated as symmetric memory by the caller,
 // zero before the first call): sums[0] | sums[1] (rmax fp32 each) | flags (uint32 per rank) | status |
-// completed calls | block ticket | the product's own partial-sum slots and counters.
+// completed calls | block ticket | the product's own partial-sum slots.
 constexpr int L8_AR_MAX_RANKS = 8;
 constexpr uint32_t L8_AR_SPIN_LIMIT = 1u << 22;      // polls of a peer's flag before giving up (~1 s)
 
@@ -1141,9 +1150,8 @@ extern "C" int cbl_gemv_l8_ar(const cbl_l8* m, const void* x, int xdtype, void* 
     P.mode = 1;
     P.m[0] = *m;
     P.fsum[0] = (float*)own;
-    P.partial = (float*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32);
+    P.partial = (unsigned long long*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32);
     P.y[0] = y;
-    P.counters = (unsigned int*)(own + 2 * rmax * 4 + L8_AR_MAX_RANKS * 4 + 32 + L8_PART_BYTES);
     P.status = ctl;
     P.calls = ctl + 1;
     P.fsum_stride = (int64_t)rmax;
@@ -1191,14 +1199,14 @@ extern "C" int cbl_gemv_l8_ar_status(void* workspace, int32_t R, cbl_stream s) {
 // Some hosts may not give this library a way to obtain device memory: a serving runtime that carves
 // all of HBM into its own pools at start-up, or a plugin slot whose contract forbids allocator calls
 // on the request path (an allocation can synchronise the device and fragments a pre-sized pool).
-// For them the product's work space (partial-sum slots, counters, status word) lives in a fixed array
-// inside the library image instead of a caller buffer; the launch is limited to L8_STATIC_BLOCKS thread
-// blocks so that the array stays small (770 KB per GPU, part of every CUDA context that loads the library,
-// held until the process exits).
+// For them the product's work space (partial-sum slots, status word) lives in a fixed array inside the
+// library image instead of a caller buffer; the launch is limited to L8_STATIC_BLOCKS thread blocks so that
+// the array stays small (1 MB + 256 B per GPU, part of every CUDA context that loads the library, held until
+// the process exits).
 constexpr int L8_STATIC_MAX_ROWS = 65536;
-constexpr int L8_STATIC_BLOCKS = 48;
-constexpr size_t L8_STATIC_BYTES = (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4 + L8_CTL_WORDS * 4;
-static __device__ __align__(256) unsigned char g_l8_static_scratch[L8_STATIC_BYTES];
+constexpr int L8_STATIC_BLOCKS = 32;
+constexpr size_t L8_STATIC_SLOT_BYTES = (size_t)L8_STATIC_BLOCKS * L8_SLOT_ROWS * 8;
+static __device__ __align__(256) unsigned char g_l8_static_scratch[L8_STATIC_SLOT_BYTES + L8_CTL_WORDS * 4];
 
 extern "C" int32_t cbl_gemv_l8_static_max_rows(void) { return L8_STATIC_MAX_ROWS; }
 
@@ -1221,48 +1229,43 @@ static int l8_static_addr(void** out) {
 }
 
 extern "C" int cbl_gemv_l8_static(const cbl_l8* m, const void* x, int xdtype, void* y, int ydtype, cbl_stream s) {
-    if (!m || !y) return CBL_EINVAL;
+    if (!m || !x || !y) return CBL_EINVAL;
     if (m->R > L8_STATIC_MAX_ROWS) return CBL_EUNSUPPORTED;      // stated limit of this entry point
     if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
     void* scratch = nullptr;
     int rc = l8_static_addr(&scratch);                           // (the first call per device should happen outside stream capture)
     if (rc) return rc;
-    int nrc = check_l8r(m);
-    if (nrc) return nrc;
-    if (xdtype != CBL_F16 && xdtype != CBL_BF16 && xdtype != CBL_F32) return CBL_EINVAL;
-    if (!x) return CBL_EINVAL;
+    rc = check_l8r(m);
+    if (rc) return rc;
     if (m->R == 0) return CBL_OK;
-    // Every call shares the array and finds whatever the previous call left.  A product that ran to its end left
-    // its counters zero; one that gave up (status word set) did not, so the counters are cleared on the caller's
-    // stream first - not the status word, which only cbl_gemv_l8_static_status clears.  The partial-sum slots
-    // need no clearing: every block overwrites its own before anyone reads it.
-    unsigned int* ctl = (unsigned int*)((char*)scratch + (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4);
-    CBL_CUDA(cudaMemsetAsync(ctl, 0, L8_STATUS_WORD * 4, (cudaStream_t)s));
+    // Every call shares the array and finds whatever the previous call left.  The array starts zero (static
+    // storage) and a product that ran to its end has cleared every word it used, so nothing needs clearing here;
+    // a product that gave up (status word set) leaves words behind, which cbl_gemv_l8_static_status clears.
     L8Launch P;
     P.n = 1;
     P.ydtype = ydtype;
     P.mode = 0;
     P.m[0] = *m;
-    P.partial = (float*)scratch;
+    P.partial = (unsigned long long*)scratch;
     P.fsum[0] = nullptr;
     P.y[0] = y;
-    P.counters = ctl;
-    P.status = ctl + L8_STATUS_WORD;
+    P.status = (unsigned int*)((char*)scratch + L8_STATIC_SLOT_BYTES) + L8_STATUS_WORD;
     P.calls = nullptr;
     P.fsum_stride = 0;
     return launch_l8(P, x, xdtype, (cudaStream_t)s, L8_STATIC_BLOCKS);
 }
 
 // CBL_ETIMEOUT if a cbl_gemv_l8_static product on the current device gave up on a bounded wait since the last
-// query (its output is invalid).  Synchronises the stream and clears the word; allocates nothing.
+// query (its output is invalid).  Synchronises the stream; after a time-out it also clears the array on that
+// stream, so the next product starts clean.  Allocates nothing.
 extern "C" int cbl_gemv_l8_static_status(cbl_stream s) {
     void* scratch = nullptr;
     int rc = l8_static_addr(&scratch);
     if (rc) return rc;
-    char* p = (char*)scratch + (size_t)L8_STATIC_BLOCKS * L8_SLOT_FLOATS * 4 + L8_STATUS_WORD * 4;
     unsigned int v = 0;
-    CBL_CUDA(cudaMemcpyAsync(&v, p, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    CBL_CUDA(cudaMemcpyAsync(&v, (char*)scratch + L8_STATIC_SLOT_BYTES + L8_STATUS_WORD * 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)s));
     CBL_CUDA(cudaStreamSynchronize((cudaStream_t)s));
-    if (v) CBL_CUDA(cudaMemsetAsync(p, 0, 4, (cudaStream_t)s));
+    if (v) CBL_CUDA(cudaMemsetAsync(scratch, 0, L8_STATIC_SLOT_BYTES + L8_CTL_WORDS * 4, (cudaStream_t)s));
     return v ? CBL_ETIMEOUT : CBL_OK;
 }

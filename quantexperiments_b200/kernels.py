@@ -421,14 +421,21 @@ class L8Matrix:
             _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table.data_ptr(), self.frag.data_ptr(), _stream()))
             if dm.books == 2:
                 _lib.check("cbl_repack_book", lib.cbl_repack_book(dm.table2.data_ptr(), self.frag2.data_ptr(), _stream()))
+            # the exponent that scales the kernel's tables, read back once so that no launch has to fetch it
+            e = ctypes.c_int32(0)
+            _lib.check("cbl_book_norm_exp", lib.cbl_book_norm_exp(self.frag.data_ptr(), ctypes.byref(e), _stream()))
+            self.book_exp, self.book_exp2 = e.value, 0
+            if dm.books == 2:
+                _lib.check("cbl_book_norm_exp", lib.cbl_book_norm_exp(self.frag2.data_ptr(), ctypes.byref(e), _stream()))
+                self.book_exp2 = e.value
 
     def struct(self) -> _lib.L8:
         """The batch-1 layout (rot = 1)."""
         dm = self.dm
         seg = (ctypes.c_int32 * (_lib.L8_MAX_ORDERS + 1))(*(self.seg_off + [0] * (_lib.L8_MAX_ORDERS + 1 - len(self.seg_off))))
-        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, 1, self.M, 0, _ptr(self.words), _ptr(self.frag),
+        return _lib.L8(self.R, self.C, self.books, self.ntile, self.Rpad, 1, self.M, self.book_exp, _ptr(self.words), _ptr(self.frag),
                        _ptr(self.frag2), _ptr(dm.row_scale), _ptr(dm.table), _ptr(dm.table2), _ptr(self.row_index),
-                       _ptr(dm.perms), seg, 0)
+                       _ptr(dm.perms), seg, self.book_exp2)
 
     def struct_c(self) -> _lib.L8:
         """The column-ordered layout (rot = 0) of the tensor-core products; built on first use."""

@@ -29,8 +29,8 @@ def _dm(m, device="cuda"):
 
 
 def _l8_counters(ws):
-    """The counters and status word of a batch-1 work space (after 160 partial-sum slots of 4096 floats)."""
-    return ws[160 * 4096 * 4:160 * 4096 * 4 + 2048]
+    """The partial-sum slots (160 x 4096 64-bit words) and the status word of a batch-1 work space: zero between calls."""
+    return ws[:160 * 4096 * 8 + 256]
 
 
 def _out_tol(dtype):
@@ -472,7 +472,7 @@ def test_peer_reduce_entry_point_with_one_rank_and_graph_replay():
     rmax = (3584 + 31) // 32 * 32 + 32 * 16                              # rows of a sum buffer (row positions incl. padding)
     ctl = ws[2 * rmax * 4 + 32:].view(torch.int32)[:3].cpu().tolist()
     assert ctl[0] == 0 and ctl[1] == 3 + 1 + 6 and ctl[2] == 0           # status, completed calls (capture itself runs nothing), ticket
-    assert int(_l8_counters(ws[2 * rmax * 4 + 64:]).count_nonzero()) == 0   # the product's counters are zero again
+    assert int(_l8_counters(ws[2 * rmax * 4 + 64:]).count_nonzero()) == 0   # the product's slots are zero again
 
 
 def test_peer_reduce_reports_a_missing_peer_instead_of_hanging():

@@ -45,8 +45,8 @@ def test_size_queries_match_the_layout_arithmetic():
     assert lib.cbl_l8r_bytes(3584, 3584, 1) == 56 * 3 * 3584 * 4
     assert lib.cbl_l8r_bytes(4864 + 32, 896, 2) == 2 * 14 * 3 * 4896 * 4
     assert lib.cbl_book_frag_bytes() == 65536 + 16
-    # work space: 160 partial-sum slots of 4096 floats, 512 control words, fp32 sums per (padded) row
-    assert lib.cbl_gemv_l8_workspace_bytes(18944) == 160 * 4096 * 4 + 2048 + (18944 + 512) * 4
+    # work space: 160 partial-sum slots of 4096 64-bit words, 64 control words, fp32 sums per (padded) row
+    assert lib.cbl_gemv_l8_workspace_bytes(18944) == 160 * 4096 * 8 + 256 + (18944 + 512) * 4
     assert lib.cbl_gemv_l8_static_max_rows() == 65536
 
 
