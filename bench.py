@@ -33,17 +33,22 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# Qwen2.5-7B block linears: (name, R, C, kind) kind: "col" = split rows under TP, "row" = split columns
+# block linears: (name, R, C, kind) kind: "col" = split rows under TP, "row" = split columns
 SHAPES_7B = [("q", 3584, 3584, "col"), ("k", 512, 3584, "col"), ("v", 512, 3584, "col"), ("o", 3584, 3584, "row"),
              ("gate", 18944, 3584, "col"), ("up", 18944, 3584, "col"), ("down", 3584, 18944, "row")]
+SHAPES_32B = [("q", 5120, 5120, "col"), ("k", 1024, 5120, "col"), ("v", 1024, 5120, "col"), ("o", 5120, 5120, "row"),
+              ("gate", 27648, 5120, "col"), ("up", 27648, 5120, "col"), ("down", 5120, 27648, "row")]
+# "7b": BASELINE configs[1] (one book, one column order); "32b": configs[4] (two summed books, 16 seeded column orders)
+MODELS = {"7b": {"shapes": SHAPES_7B, "layers": 28, "books": 1, "M": 1, "label": "qwen2.5-7b"},
+          "32b": {"shapes": SHAPES_32B, "layers": 64, "books": 2, "M": 16, "label": "qwen2.5-32b"}}
 LAYERS_7B = 28
 METRIC = "codebook_gemv_hbm_gbs_batch1"
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM bytes per launch of the batch-1 kernel on the 18944 x 3584 shape from one ncu capture
-# (profiles/gemv_l8_gate_7b.md: dram__bytes_read.sum + dram__bytes_write.sum), and the algorithmic
+# DRAM bytes per launch of the batch-1 kernel on the 18944 x 3584 gate|up pair from one ncu capture
+# (profiles/gemv_l8_gateup_7b.md: dram__bytes_read.sum + dram__bytes_write.sum), and the algorithmic
 # bytes of that launch; traffic of other launches is scaled by their algorithmic bytes.
-NCU_TRAFFIC_GATE = (12_902_912 + 0, 12_833_792 + 3584 * 2 + 18944 * 2)
+NCU_TRAFFIC_GATEUP = (25_725_440 + 0, 2 * (12_833_792 + 18944 * 2) + 3584 * 2)
 
 
 def measured_peak() -> tuple[float, str]:
@@ -56,9 +61,46 @@ def measured_peak() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def algorithmic_bytes(R: int, C: int, B: int = 1) -> int:
+def algorithmic_bytes(R: int, C: int, B: int = 1, books: int = 1, M: int = 1) -> int:
+    """Packed tags + books + row scales (+ the rows' column-order ids) + activations in and out."""
     W = (C // 8 * 12 + 31) // 32
-    return R * W * 4 + 4096 * 8 * 2 + R * 2 + B * C * 2 + B * R * 2
+    return books * (R * W * 4 + 4096 * 8 * 2) + R * 2 + (R if M > 1 else 0) + B * C * 2 + B * R * 2
+
+
+def set_bytes(model: str, B: int = 1) -> int:
+    m = MODELS[model]
+    return sum(algorithmic_bytes(R, C, B, m["books"], m["M"]) for _, R, C, _ in m["shapes"]) * m["layers"]
+
+
+def workload_name(model: str, B: int) -> str:
+    m = MODELS[model]
+    n = len(m["shapes"]) * m["layers"]
+    extra = "" if m["books"] == 1 else f", {m['books']} summed books, {m['M']} seeded column orders"
+    return f"{m['label']} decode GEMV set ({n} codebook matrices, d=8, K=4096, 12-bit tags{extra}), batch {B}"
+
+
+def make_matrix(model: str, layer: int, name: str, R: int, C: int, device="cpu"):
+    """One synthetic matrix of the set in the file layout, seeded by (model, layer, name): uniform random tags, an
+    N(0,1) fp16 book, row scales distributed like the RMS of N(0, 0.02) rows.  Generated on the CPU it is the same
+    tensor in both arms of the bench (the GPU arm copies it to the device); returns (tensors, meta, perms)."""
+    import zlib
+    from quantexperiments_b200 import packed
+    m = MODELS[model]
+    seed = zlib.crc32(f"{model}/{layer}/{name}".encode())
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = (C // 8 * 12 + 31) // 32
+    t = {"tags": torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device=device, generator=g),
+         "table": torch.randn(4096, 8, device=device, generator=g).half(),
+         "row_scale": (0.02 * (1.0 + torch.randn(R, device=device, generator=g) / (2.0 * C) ** 0.5)).half()}
+    if m["books"] == 2:
+        t["tags2"] = torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device=device, generator=g)
+        t["table2"] = torch.randn(4096, 8, device=device, generator=g).half()
+    perms = None
+    if m["M"] > 1:
+        t["row_mask"] = torch.randint(0, m["M"], (R,), device=device, generator=g).to(torch.uint8)
+        perms = packed.seeded_perms(C, m["M"], torch.Generator(device="cpu").manual_seed(seed & 0x7FFFFFFF))
+    meta = {"R": R, "C": C, "d": 8, "K": 4096, "G": 1, "M": m["M"]}
+    return t, meta, perms
 
 
 class ClockSampler(threading.Thread):
@@ -111,137 +153,228 @@ def physical_gpu_index(local: int) -> int:
 
 
 # ----------------------------------------------------------------------------------------- reference arm
+def reference_cpu_linear():
+    """(fn, kind): the reference's CPU execution of one product - unpack_bits + decode_tensors + fp32 matmul.
+    The reference's own modules when they have been staged under oracle/_ref (kind "reference"), else the oracle's
+    restatement of them (kind "port")."""
+    try:
+        from oracle import make_ref
+        if make_ref.load() is not None:
+            import shapequant.packed as rp
+
+            def fn(words, table, row_scale, x):
+                nch = x.shape[-1] // 8
+                tags = rp.unpack_bits(words, 12, nch)
+                perms = torch.arange(x.shape[-1])[None]
+                w = rp.decode_tensors(tags, table, row_scale, torch.zeros(words.shape[0], dtype=torch.int64), None, perms, 4096)
+                return x.float() @ w.t()
+            return fn, "reference"
+    except Exception:
+        pass
+    from oracle import cbl_oracle as orc
+    return (lambda words, table, row_scale, x: orc.cpu_linear_torch(words, table, row_scale, x, 12, 8)), "port"
+
+
+def reference_sample(model: str = "7b"):
+    """The bounded sample of the set that the CPU legs time: layer 0's q and k whole (v, o have their shapes), the
+    first 2048 rows of its gate (= up) and of its down - the very tensors the GPU arm multiplies."""
+    out = []
+    counts = {"q": 2, "k": 2, "gate": 2, "down": 1}
+    for name, R, C, _ in MODELS[model]["shapes"]:
+        if name not in counts:
+            continue
+        t, _, _ = make_matrix(model, 0, name, R, C)
+        Rs = min(R, 2048)
+        x = torch.randn(1, C, generator=torch.Generator().manual_seed(C)).bfloat16()
+        out.append((t["tags"][:Rs], t["table"], t["row_scale"][:Rs], x, R, Rs, counts[name] * MODELS[model]["layers"]))
+    return out
+
+
+def time_reference_step(fn, sample) -> float:
+    """Seconds the whole set would take on this host: the sample's products timed, scaled by rows and shape counts."""
+    total = 0.0
+    for words, table, rs, x, R, Rs, count in sample:
+        t0 = time.perf_counter()
+        fn(words, table, rs, x)
+        total += (time.perf_counter() - t0) * (R / Rs) * count
+    return total
+
+
+SAMPLE_TEXT = "layer 0's q and k matrices whole and 2048 rows each of its gate and down matrices (the tensors the GPU arm uses), scaled by rows and shape counts to the 196-matrix set"
+
+
 def run_reference(args, rank: int, world: int) -> None:
-    """The reference's CPU execution of the path (unpack + decode + fp32 matmul in CPU torch, all host
-    threads), on a bounded sample of the same workload: one matrix per distinct shape per step, scaled
-    to the full set by the shape counts."""
+    """The reference's CPU execution of the path (unpack + decode + fp32 matmul in CPU torch, all host threads), on a
+    bounded sample of the same workload and the same tensors as the GPU arm."""
     if rank != 0:
         return
-    from oracle import cbl_oracle as orc
     torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
-    g = torch.Generator().manual_seed(0)
-    sample = []
-    for name, R, C, _ in SHAPES_7B:
-        if name in ("v", "o", "up"):
-            continue                      # same shapes as k, q, gate
-        Rs = min(R, 2048)                 # bounded sample: at most 2048 rows of each shape
-        W = (C // 8 * 12 + 31) // 32
-        words = torch.randint(-2**31, 2**31 - 1, (Rs, W), dtype=torch.int32, generator=g)
-        table = torch.randn(4096, 8, generator=g).half()
-        rs = (torch.rand(Rs, generator=g) * 0.02 + 0.01).half()
-        x = torch.randn(1, C, generator=g).bfloat16()
-        count = {"q": 2, "k": 2, "gate": 2, "down": 1}[name] * LAYERS_7B
-        sample.append((words, table, rs, x, R, C, Rs, count))
-
-    def step() -> float:
-        """Seconds the full 196-matrix set would take, extrapolated from the sampled rows."""
-        total = 0.0
-        for words, table, rs, x, R, C, Rs, count in sample:
-            t0 = time.perf_counter()
-            orc.cpu_linear_torch(words, table, rs, x, 12, 8)
-            total += (time.perf_counter() - t0) * (R / Rs) * count
-        return total
-
-    for _ in range(args.warmup):
-        step()
-    ts = [step() for _ in range(args.steps)]
+    fn, kind = reference_cpu_linear()
+    sample = reference_sample("7b")
+    for _ in range(max(args.warmup, 1)):
+        time_reference_step(fn, sample)
+    ts = [time_reference_step(fn, sample) for _ in range(args.steps)]
     t = sum(ts) / len(ts)
-    total_bytes = sum(algorithmic_bytes(R, C) for _, R, C, _ in SHAPES_7B) * LAYERS_7B
-    val = total_bytes / t / 1e9
+    val = set_bytes("7b") / t / 1e9
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen2.5-7b decode GEMV set (196 codebook matrices), batch 1", "timing": "host wall clock"},
-            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
-                             "sample": "<=2048 rows of one matrix per distinct shape (q, k, gate, down) per step, scaled by rows and counts"},
+            "config": {"workload": workload_name("7b", 1), "timing": "host wall clock; ms_per_step is the full set's time extrapolated from the sample"},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": kind, "sample": SAMPLE_TEXT},
             "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
+def cpu_baseline_sample() -> dict:
+    """The reference's CPU path timed on this host's cores on the bounded sample (one pass after a warm-up pass)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    fn, kind = reference_cpu_linear()
+    sample = reference_sample("7b")
+    time_reference_step(fn, [(w[:64], t, r[:64], x, R, Rs, c) for w, t, r, x, R, Rs, c in sample])
+    t = time_reference_step(fn, sample)
+    return {"value": set_bytes("7b") / t / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": kind, "sample": SAMPLE_TEXT}
+
+
+def gpu_reference(dev, stream, lins_shapes, steps: int) -> dict:
+    """The reference's own GPU kernel for this format - the Triton PackedLinear.gemv of shapequant/kernels/gemv.py -
+    over the same 196 matrices on the same device: the survey's same-box bar.  Needs the staged reference and Triton."""
+    try:
+        from oracle import make_ref
+        if make_ref.load() is None:
+            return {"unavailable": "oracle/_ref has not been staged (python oracle/make_ref.py)"}
+        import shapequant.kernels.gemv as rg
+    except Exception as e:                                    # Triton missing or not importable on this box
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    try:
+        mods, xs, ys = [], {}, {}
+        for (t, meta, perms) in lins_shapes:
+            C = meta["C"]
+            p = torch.arange(C, device=dev)[None]
+            mods.append(rg.PackedLinear(t["tags"], t["table"], t["row_scale"], None, None, p, 4096, 8))
+            xs.setdefault(C, torch.randn(C, device=dev).bfloat16())
+            ys.setdefault(meta["R"], torch.empty(meta["R"], device=dev, dtype=torch.bfloat16))
+        with torch.cuda.stream(stream):
+            for m in mods[:7]:
+                m.gemv(xs[m.C], ys[m.R])                        # compiles the kernel
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for m in mods:
+                    m.gemv(xs[m.C], ys[m.R])
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"kernel": "shapequant.kernels.gemv._gemv_kernel (Triton, unmodified)", "ms_per_step": ms,
+                "value": set_bytes("7b") / (ms * 1e-3) / 1e9, "unit": "GB/s", "launches_per_step": len(mods)}
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+
 # ----------------------------------------------------------------------------------------- our arm
-def build_set(dev, rank: int, world: int, batch: int):
-    """The rank's share of the 196 matrices as PackedLinear objects (random tags generated on the device)."""
+def build_set(dev, rank: int, world: int, batch: int, model: str = "7b", layers: int | None = None, keep_file_layout: bool = False):
+    """The rank's tensor-parallel share of the model's matrices as PackedLinear objects: every rank derives its shard
+    from the same seeded full matrix (rows for q/k/v/gate/up, chunk ranges of the input for o/down; with column
+    orders the o/down shards keep global column indices and read the full activation vector)."""
+    from quantexperiments_b200 import tp
     from quantexperiments_b200.linear import PackedLinear
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    lins, kinds, total_bytes = [], [], 0
-    for layer in range(LAYERS_7B):
-        for name, R, C, kind in SHAPES_7B:
-            r, c = R, C
+    m = MODELS[model]
+    gen_dev = "cpu" if model == "7b" else dev            # the 7B set is shared with the CPU arm; 12 GB of 32B tags are drawn on the GPU
+    lins, kinds, raw = [], [], []
+    for layer in range(m["layers"] if layers is None else layers):
+        for name, R, C, kind in m["shapes"]:
+            t, meta, perms = make_matrix(model, layer, name, R, C, gen_dev)
             if world > 1:
                 if kind == "col":
-                    r = max(R // world, 1) if R % world == 0 else R       # k/v at TP 8: 512 / 8 = 64 rows
+                    r0, r1 = tp.row_range(R, rank, world)
+                    t, meta = tp.shard_rows(t, meta, r0, r1)
                 else:
-                    c = C // world
-            W = (c // 8 * 12 + 31) // 32
-            words = torch.randint(-2**31, 2**31 - 1, (r, W), dtype=torch.int32, device=dev, generator=g)
-            table = torch.randn(4096, 8, device=dev, generator=g).half()
-            rs = (torch.rand(r, device=dev, generator=g) * 0.02 + 0.01).half()
-            perms = torch.arange(c, device=dev)[None]
-            lin = PackedLinear(words, table, rs, None, None, perms, 4096, 8)
-            lin.l8 if (batch == 1 and lin.use_l8()) else lin.small_batch(batch).xp_buffer(batch)
+                    c0, c1 = tp.col_range(C, 8, rank, world)
+                    t, meta, perms = tp.shard_cols(t, meta, c0, c1, perms)
+            t = {k: v.to(dev) for k, v in t.items()}
+            p = perms.to(dev) if perms is not None else torch.arange(meta["C"], device=dev)[None]
+            lin = PackedLinear(t["tags"], t["table"], t["row_scale"], None, t.get("row_mask"), p, 4096, 8,
+                               words2=t.get("tags2"), table2=t.get("table2"))
+            lin.kind, lin.wide = kind, (world > 1 and kind == "row" and m["M"] > 1)
+            if batch == 1 and (lin.dm.M == 1 or lin.use_l8()):
+                lin.l8
+            else:
+                lin.small_batch(batch).xp_buffer(batch)
             lins.append(lin)
             kinds.append(kind)
-            total_bytes += algorithmic_bytes(r, c, batch)
-    return lins, kinds, total_bytes
+            if keep_file_layout:
+                raw.append((t, meta, perms))
+    return lins, kinds, raw
 
 
 def run_ours(args, rank: int, world: int, local_rank: int) -> None:
     import torch.distributed as dist
     from quantexperiments_b200 import kernels  # noqa: F401  (fails loudly if libcbl.so is missing)
+    from quantexperiments_b200.kernels import L8Group
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    B = args.batch
-    lins, kinds, rank_bytes = build_set(dev, rank, world, B)
+    B, model = args.batch, args.model
+    mdl = MODELS[model]
+    shapes = mdl["shapes"]
+    want_gpu_ref = world == 1 and B == 1 and model == "7b" and not args.no_extras
+    lins, kinds, raw = build_set(dev, rank, world, B, model, keep_file_layout=want_gpu_ref)
     g = torch.Generator(device=dev).manual_seed(7)
-    xs = {c: torch.randn(B, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
-    ys = {r: torch.empty(B, r, device=dev, dtype=torch.bfloat16) for r in {l.R for l in lins}}
-
-    def launch(lin, x, y):
-        if B == 1:
-            lin.gemv(x[0], y[0])
-        else:
-            lin.small_batch(B).run(x, y, B)
-
-    # batch 1: q|k|v and gate|up share their input and run as one grouped launch each, as the reference merges
-    # them (7 matrices per layer -> 4 launches + 4 finish kernels)
-    from quantexperiments_b200.kernels import L8Group
-    per_layer = len(SHAPES_7B)
+    per_layer = len(shapes)
+    C_full = {name: C for name, _, C, _ in shapes}
     groups = []
     arena = None
     if B == 1 and world > 1:
         # row-parallel products sum their partial outputs through peer memory inside the finish kernel
         from quantexperiments_b200.tp import PeerArena, PeerReduceGemv
-        arena = PeerArena(8 << 20)
+        need = sum(kernels.lib.cbl_gemv_l8_ar_workspace_bytes(l.R) + 512 for l in lins if l.kind == "row")
+        arena = PeerArena(need + (1 << 20))
     # every product reads its own slice of one input arena and writes its own slice of one output arena, so that the
     # end-to-end leg moves a step's inputs and results with ONE copy each way
-    n_in = sum(B * l.C for i, l in enumerate(lins) if i % per_layer in (0, 3, 4, 6))
+    def in_cols(lin, name):
+        return C_full[name] if lin.wide else lin.C
+    n_in = sum(B * in_cols(l, shapes[i % per_layer][0]) for i, l in enumerate(lins) if i % per_layer in (0, 3, 4, 6))
     xarena = torch.randn(n_in, device=dev, generator=g).bfloat16()
     yarena = torch.empty(sum(B * l.R for l in lins), device=dev, dtype=torch.bfloat16)
     xoff = yoff = 0
     items = []                     # batch > 1: (lin, x [B, C], y [B, R], kind)
     for l0 in range(0, len(lins), per_layer):
         q, k, v, o, gate, up, down = lins[l0:l0 + per_layer]
-        for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
-            C = members[0].C
+        for members, kind, nm in (((q, k, v), "col", "q"), ((o,), "row", "o"), ((gate, up), "col", "gate"), ((down,), "row", "down")):
+            C = in_cols(members[0], nm)
             x = xarena[xoff:xoff + B * C].view(B, C)
             xoff += B * C
             outs = []
-            for m in members:
-                outs.append(yarena[yoff:yoff + B * m.R].view(B, m.R))
-                yoff += B * m.R
-                items.append((m, x, outs[-1], kind))
+            for mm in members:
+                outs.append(yarena[yoff:yoff + B * mm.R].view(B, mm.R))
+                yoff += B * mm.R
+                items.append((mm, x, outs[-1], kind))
             if B == 1:
-                if arena is not None and kind == "row":
-                    groups.append((PeerReduceGemv(members[0].l8, arena), x[0], [outs[0][0]], "fused"))
+                # one token: the table-lookup kernel, unless the matrices have so many column orders for their rows that
+                # per-order tables do not pay (PackedLinear.use_l8); those run on the row-tile kernel
+                tables = all(mm.dm.M == 1 or mm.use_l8() for mm in members)
+                if arena is not None and kind == "row" and tables:
+                    groups.append((PeerReduceGemv(members[0].l8, arena), x[0], [outs[0][0]], "fused", members))
+                elif tables:
+                    groups.append((L8Group([mm.l8 for mm in members]), x[0], [o_[0] for o_ in outs], kind, members))
                 else:
-                    groups.append((L8Group([m.l8 for m in members]), x[0], [o_[0] for o_ in outs], kind))
+                    groups.append((None, x, outs, "t16", members))
 
     def step_kernels():
         if B == 1:
-            for grp, x, outs, kind in groups:
+            for grp, x, outs, kind, members in groups:
                 if kind == "fused":
                     grp.run(x, outs[0])
+                elif kind == "t16":
+                    for mm, y in zip(members, outs):
+                        mm.t16.run(x, y, 1, wide=mm.wide)
+                        if world > 1 and mm.kind == "row":
+                            dist.all_reduce(y)
                 else:
                     grp.run(x, outs)
             return
@@ -253,20 +386,23 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
             if world > 1 and kind == "row":
                 dist.all_reduce(y)
 
-    launches_per_step = 2 * len(groups) if B == 1 else len(lins) + 4 * (len(lins) // per_layer)
+    launches_per_step = (sum(2 * len(grp[4]) if grp[3] == "t16" else (2 if grp[3] == "fused" else 1) for grp in groups) if B == 1
+                         else len(lins) + 4 * (len(lins) // per_layer))
     stream = torch.cuda.Stream(device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
     with torch.cuda.stream(stream):
+        barrier()                              # every rank's shards and peer work spaces exist before the first launch
         step_kernels()
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()         # NCCL all-reduces are captured with the kernels
         with torch.cuda.graph(graph, stream=stream):
             step_kernels()
         run = graph.replay
-
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize(dev)
 
         for _ in range(max(args.warmup, 3)):
             run()
@@ -285,31 +421,55 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop()
 
-        # dominant kernel alone: the batch-1 table-lookup kernel over its matrices, timed with events
+        # tensor-parallel runs: every fused peer sum reported no expired wait, every rank holds the same output, and
+        # that output equals the sum of the ranks' separately computed partial products
+        tp_check = None
+        if world > 1 and B == 1:
+            status_ok, worst, same = True, 0.0, True
+            for grp, x, outs, kind, members in groups:
+                if kind == "fused":
+                    status_ok = status_ok and grp.status()
+            for grp, x, outs, kind, members in groups[:4]:            # layer 0: the o and the down product
+                if kind != "fused":
+                    continue
+                lin = members[0]
+                part = lin.l8.run(x, torch.empty(lin.R, device=dev, dtype=torch.float32), wide=lin.wide)
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                ref = parts[0].clone()
+                for p in parts[1:]:
+                    ref += p
+                fused = outs[0].float()
+                worst = max(worst, float((fused - ref).abs().max() / ref.abs().max()))
+                ys_all = [torch.empty_like(outs[0]) for _ in range(world)]
+                dist.all_gather(ys_all, outs[0].contiguous())
+                same = same and all(torch.equal(ys_all[0], t) for t in ys_all[1:])
+            flags = torch.tensor([float(status_ok), float(same), worst], device=dev, dtype=torch.float64)
+            mn, mx = flags.clone(), flags.clone()
+            dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            tp_check = {"status_ok": bool(mn[0] > 0), "ranks_bit_identical": bool(mn[1] > 0), "max_rel_err": float(mx[2]),
+                        "tolerance": 2.0 ** -7, "checked": "layer 0's o and down products: fused peer sum vs the rank-ordered sum of all ranks' partial products"}
+            tp_check["ok"] = tp_check["status_ok"] and tp_check["ranks_bit_identical"] and tp_check["max_rel_err"] < tp_check["tolerance"]
+
+        # dominant kernel alone: the batch-1 table-lookup kernel over the set's grouped launches, timed with events
         roof = None
         if world == 1 and B == 1:
-            big = [lin for lin in lins if lin.use_l8()]
-            gk = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gk, stream=stream):
-                for lin in big:
-                    lin.l8.run(xs[lin.C][0], ys[lin.R][0])
-            for _ in range(3):
-                gk.replay()
-            torch.cuda.synchronize(dev)
             k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             k0.record(stream)
             for _ in range(args.steps):
-                gk.replay()
+                run()
             k1.record(stream)
             torch.cuda.synchronize(dev)
-            per_launch_s = k0.elapsed_time(k1) * 1e-3 / (args.steps * len(big))
-            alg = sum(algorithmic_bytes(lin.R, lin.C) for lin in big) / len(big)
+            per_launch_s = k0.elapsed_time(k1) * 1e-3 / (args.steps * len(groups))
+            alg = set_bytes(model) / len(groups)
             peak, src = measured_peak()
             achieved = alg / per_launch_s / 1e9
-            roof = {"bound": "hbm", "kernel": "k_gemv_l8", "achieved": achieved, "peak": peak, "peak_source": src, "unit": "GB/s",
+            roof = {"bound": "hbm", "kernel": "k_gemv_l8" if all(grp[3] != "t16" for grp in groups) else "k_gemv_l8 / k_gemv_t16 (per shape)", "achieved": achieved, "peak": peak, "peak_source": src, "unit": "GB/s",
                     "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
-                    "traffic": alg * NCU_TRAFFIC_GATE[0] / NCU_TRAFFIC_GATE[1], "algorithmic_bytes_per_launch": alg,
-                    "us_per_launch": per_launch_s * 1e6, "launches_timed": args.steps * len(big)}
+                    "traffic": alg * NCU_TRAFFIC_GATEUP[0] / NCU_TRAFFIC_GATEUP[1], "algorithmic_bytes_per_launch": alg,
+                    "us_per_launch": per_launch_s * 1e6, "launches_timed": args.steps * len(groups),
+                    "note": "the step is nothing but launches of this kernel (q|k|v, o, gate|up, down per layer): average over them"}
 
         # end to end with HOST buffers: the step's inputs come from pinned host memory (one copy into the input arena),
         # the products run, the step's results go back to pinned host memory (one copy of the output arena); copies and
@@ -343,26 +503,23 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
         t1.record(stream)
         barrier()
         ms_e2e = t0.elapsed_time(t1)
+        gref = gpu_reference(dev, stream, raw, max(args.steps // 4, 2)) if want_gpu_ref else None
 
-    # max over ranks, whole-job bytes
-    tv = torch.tensor([ms, ms_e2e, float(rank_bytes)], device=dev, dtype=torch.float64)
+    # max over ranks; the value counts the model's fixed byte set once, however many ranks share it
+    tv = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
-        tmax = tv.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = tv.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        ms, ms_e2e, total_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
-    else:
-        total_bytes = float(rank_bytes)
+        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(tv[0]), float(tv[1])
     if rank != 0:
         return
+    total_bytes = float(set_bytes(model, B))
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
     line = {"metric": METRIC if B == 1 else f"codebook_gemv_hbm_gbs_batch{B}", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"qwen2.5-7b decode GEMV set (196 codebook matrices, d=8, K=4096, 12-bit tags), batch {B}",
-                       "parallelism": f"tp{world}" if world > 1 else "single", "l2": "inputs larger than L2 (1.24 GB of packed weights per step)",
+            "config": {"workload": workload_name(model, B),
+                       "parallelism": f"tp{world}" if world > 1 else "single", "l2": f"inputs larger than L2 ({total_bytes / 1e9:.2f} GB of packed weights per step)",
                        "accumulate": "fp32", "activations": "bf16", "launch": "one CUDA graph per step (q|k|v and gate|up grouped)" + ("" if world == 1 else "; o/down summed over ranks through peer memory in the finish kernel"),
                        "e2e": "a step's inputs from pinned host memory and its results back to pinned host memory (one copy each way), copies and kernels in one CUDA graph, host synchronises every step"},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps * world,
@@ -370,21 +527,49 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> None:
                     "ms_per_step": ms_e2e / args.steps}}
     if roof is not None:
         line["roofline"] = roof
-    if world == 1:
+    if tp_check is not None:
+        line["tp_check"] = tp_check
+    if gref is not None:
+        line["gpu_reference"] = gref
+    if world == 1 and model == "7b":
         line["cpu_baseline"] = cpu_baseline_sample()
+    return_line(args, line, dev, rank, world, local_rank)
+    if tp_check is not None and not tp_check["ok"]:
+        sys.exit(3)
+
+
+def return_line(args, line: dict, dev, rank: int, world: int, local_rank: int) -> None:
+    """Prints the JSON line; the default run (headline workload, one GPU) first adds the two other parts of the metric,
+    measured in this process: prefill TFLOP/s at 2048 tokens and decode tokens/s at batch 1 (short runs)."""
+    if world == 1 and args.workload == "gemv" and args.batch == 1 and args.model == "7b" and not args.no_extras:
+        torch.cuda.empty_cache()
+        try:
+            line["prefill"] = run_prefill(argparse.Namespace(**{**vars(args), "tokens": 2048, "steps": 3, "warmup": 3}), rank, world, local_rank, emit=False)
+        except Exception as e:
+            line["prefill"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        torch.cuda.empty_cache()
+        try:
+            line["decode"] = run_decode(argparse.Namespace(**{**vars(args), "tokens": 2048, "steps": 64, "warmup": 3, "batch": 1}), rank, world, local_rank, emit=False)
+        except Exception as e:
+            line["decode"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     print(json.dumps(line), flush=True)
 
 
-def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
-    """Prefill product of the same 196-matrix set: Y = X W^T for --tokens tokens per matrix on the tcgen05
-    kernel; metric TFLOPS = 2 * tokens * R * C summed over the matrices / time."""
+def run_prefill(args, rank: int, world: int, local_rank: int, emit: bool = True):
+    """Prefill product of the same matrix set: Y = X W^T for --tokens tokens per matrix on the tcgen05
+    kernel; metric TFLOPS = 2 * tokens * R * C summed over the matrices / time.  emit=False: no JSON line, a short
+    summary is returned (the default run embeds it)."""
     import torch.distributed as dist
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     T = args.tokens
     from quantexperiments_b200.kernels import DenseStack
     from quantexperiments_b200.linear import DENSE_MIN_TOKENS
-    lins, kinds, _ = build_set(dev, rank, world, 64)
+    SHAPES = MODELS[args.model]["shapes"]
+    if world > 1 and MODELS[args.model]["M"] > 1:
+        raise SystemExit("prefill of matrices with column orders under tensor parallelism: use tp.RowParallelLinear (tests/test_tp.py); "
+                         "this workload runs them on one GPU")
+    lins, kinds, _ = build_set(dev, rank, world, 64, args.model)
     g = torch.Generator(device=dev).manual_seed(7)
     xs = {c: torch.randn(T, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
     flops = sum(2.0 * T * l.R * l.C for l in lins)
@@ -393,8 +578,8 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     # tcgen05 GEMM; below, every piece runs the kernel that decodes weight tiles on the fly.
     dense = T >= (args.dense_min if args.dense_min is not None else DENSE_MIN_TOKENS)
     groups, launches = [], 0
-    for l0 in range(0, len(lins), len(SHAPES_7B)):
-        q, k, v, o, gate, up, down = lins[l0:l0 + len(SHAPES_7B)]
+    for l0 in range(0, len(lins), len(SHAPES)):
+        q, k, v, o, gate, up, down = lins[l0:l0 + len(SHAPES)]
         for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
             y = torch.empty(T, sum(m.R for m in members), device=dev, dtype=torch.bfloat16)
             groups.append((DenseStack([m.dm for m in members]) if dense else None, members, xs[members[0].C], y, kind))
@@ -471,10 +656,14 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
         pass
     peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
     value = flops * args.steps / (ms * 1e-3) / 1e12
+    if not emit:
+        return {"tokens": T, "value": value, "unit": "TFLOP/s", "ms_per_step": ms / args.steps, "steps": args.steps,
+                "frac_of_sustained_peak": value / world / peak, "frac_of_burst_peak": value / world / float(peaks.get("bf16_tflops", 1590.0)),
+                "kernel": "k_decode_raw + k_gemm_dense_2sm (tcgen05)", "clocks": clocks}
     line = {"metric": "prefill_dequant_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"qwen2.5-7b prefill dequant-GEMM set (196 codebook matrices), {T} tokens", "accumulate": "fp32",
+            "config": {"workload": f"{MODELS[args.model]['label']} prefill dequant-GEMM set ({len(lins) * (world if False else 1)} codebook matrices), {T} tokens", "accumulate": "fp32",
                        "path": "decode once into a 16-bit scratch + TMA-fed tcgen05 GEMM (q|k|v and gate|up stacked)" if dense
                                else "weight tiles decoded on the fly inside the tcgen05 GEMM",
                        "activations": "bf16 in, fp16 on the tensor cores with a power-of-two scale per token", "output": "bf16",
@@ -489,7 +678,7 @@ def run_prefill(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def run_decode(args, rank: int, world: int, local_rank: int) -> None:
+def run_decode(args, rank: int, world: int, local_rank: int, emit: bool = True):
     """End-to-end decode of a random-init Qwen2.5-7B architecture with every block linear in the packed format:
     prompt of --tokens random ids (batched prefill), then --steps generated tokens per sequence by CUDA-graph replay
     of the decode step, --batch sequences at once. Metric: generated tokens/s. N > 1: independent replicas (the
@@ -546,6 +735,9 @@ def run_decode(args, rank: int, world: int, local_rank: int) -> None:
     step_bytes = eng.weight_bytes() + kv_bytes
     achieved = step_bytes / (ms / K * 1e-3) / 1e9
     launches = (10 * cfg.layers + 4) if B == 1 else (22 * cfg.layers + 5)
+    if not emit:
+        return {"batch": B, "prompt": T, "value": B * K * world / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms / K, "steps": K,
+                "step_hbm_frac": achieved / peak, "clocks": clocks}
     line = {"metric": "decode_tok_s", "value": B * K * world / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
@@ -710,26 +902,113 @@ def run_load(args, rank: int, world: int, local_rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def cpu_baseline_sample() -> dict:
-    """The reference's CPU path (oracle port) timed on this host's cores on a bounded sample."""
-    from oracle import cbl_oracle as orc
-    torch.set_num_threads(os.cpu_count() or 1)
-    g = torch.Generator().manual_seed(0)
-    t_total = 0.0
-    for name, R, C, count in (("q", 3584, 3584, 2), ("k", 512, 3584, 2), ("gate", 18944, 3584, 2), ("down", 3584, 18944, 1)):
-        Rs = min(R, 1024)
-        W = (C // 8 * 12 + 31) // 32
-        words = torch.randint(-2**31, 2**31 - 1, (Rs, W), dtype=torch.int32, generator=g)
-        table = torch.randn(4096, 8, generator=g).half()
-        rs = (torch.rand(Rs, generator=g) * 0.02 + 0.01).half()
-        x = torch.randn(1, C, generator=g).bfloat16()
-        orc.cpu_linear_torch(words[:64], table, rs[:64], x, 12, 8)
-        t0 = time.perf_counter()
-        orc.cpu_linear_torch(words, table, rs, x, 12, 8)
-        t_total += (time.perf_counter() - t0) * (R / Rs) * count * LAYERS_7B
-    total_bytes = sum(algorithmic_bytes(R, C) for _, R, C, _ in SHAPES_7B) * LAYERS_7B
-    return {"value": total_bytes / t_total / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": "1024 rows of one matrix per distinct shape (q, k, gate, down), scaled by rows and counts to the 196-matrix set"}
+# ----------------------------------------------------------------------------------------- small cases for a profiler
+def _case_matrix(R: int, C: int, seed: int = 0, books: int = 1):
+    from quantexperiments_b200.kernels import DeviceMatrix
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    W = (C // 8 * 12 + 31) // 32
+    kw = {}
+    if books == 2:
+        kw = {"tags2": torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device="cuda", generator=g),
+              "table2": torch.randn(4096, 8, device="cuda", generator=g).half()}
+    return DeviceMatrix(torch.randint(-2**31, 2**31 - 1, (R, W), dtype=torch.int32, device="cuda", generator=g),
+                        torch.randn(4096, 8, device="cuda", generator=g).half(),
+                        (torch.rand(R, device="cuda", generator=g) * 0.02 + 0.01).half(), K=4096, d=8, C=C, **kw)
+
+
+def _case_gemv_l8(shapes):
+    """A grouped batch-1 launch on distinct matrices, a few times (every launch streams its tags from HBM: ncu flushes
+    the caches before a captured launch, and 12 matrices of the largest shape exceed L2 anyway)."""
+    from quantexperiments_b200.kernels import L8Group, L8Matrix
+    grps = [L8Group([L8Matrix(_case_matrix(R, C, seed=7 * i + j)) for j, (R, C) in enumerate(shapes)]) for i in range(4)]
+    x = torch.randn(shapes[0][1], device="cuda").bfloat16()
+    ys = [torch.empty(R, device="cuda", dtype=torch.bfloat16) for R, _ in shapes]
+    for rep in range(2):
+        for grp in grps:
+            grp.run(x, ys)
+
+
+def _case_gemv_t16():
+    from quantexperiments_b200.kernels import T16Matrix
+    ms = [T16Matrix(_case_matrix(18944, 3584, seed=i)) for i in range(6)]
+    x, y = torch.randn(1, 3584, device="cuda").bfloat16(), torch.empty(1, 18944, device="cuda", dtype=torch.bfloat16)
+    for m in ms:
+        m.run(x, y)
+
+
+def _case_gemv_x16():
+    from quantexperiments_b200.kernels import X16Matrix
+    xm = X16Matrix(_case_matrix(37888, 3584))
+    X, Y = torch.randn(16, 3584, device="cuda").bfloat16(), torch.empty(16, 37888, device="cuda", dtype=torch.bfloat16)
+    xp = xm.prep(X, 16)
+    for _ in range(3):
+        xm.run_prepped(xp, Y, 16)
+
+
+def _case_gemm(dense: bool):
+    from quantexperiments_b200.kernels import DenseStack, L8Matrix
+    dm = _case_matrix(18944, 3584)
+    X, Y = torch.randn(2048, 3584, device="cuda").bfloat16(), torch.empty(2048, 18944, device="cuda", dtype=torch.bfloat16)
+    if dense:
+        st = DenseStack([dm])
+        for _ in range(3):
+            st.gemm(X, Y)
+        DenseStack.status("cuda")
+    else:
+        l8 = L8Matrix(dm)
+        for _ in range(3):
+            l8.gemm(X, Y)
+        l8.status()
+
+
+def _case_assign():
+    from quantexperiments_b200 import codebook as cb
+    n = 148 * 2048 * 4
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x, wt = torch.randn(n, 8, device="cuda", generator=g), torch.rand(n, 8, device="cuda", generator=g)
+    book = torch.randn(4096, 8, device="cuda", generator=g).half()
+    for w in (None, None, wt, wt):
+        cb.assign(x, book, wt=w)
+
+
+def _case_decode_step(B: int):
+    from quantexperiments_b200.engine import Cfg, Qwen2BatchEngine, random_engine
+    eng = random_engine(Cfg(max_len=2304, layers=4), seed=0)
+    if B > 1:
+        eng = Qwen2BatchEngine(eng, B)
+    eng.reset()
+    eng.pos.fill_(2048)
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    eng.check()
+
+
+PROFILE_CASES = {
+    "gemv_l8_gateup": lambda: _case_gemv_l8([(18944, 3584), (18944, 3584)]),    # the largest batch-1 launch of the 7B set
+    "gemv_l8_down": lambda: _case_gemv_l8([(3584, 18944)]),
+    "gemv_l8_qkv": lambda: _case_gemv_l8([(3584, 3584), (512, 3584), (512, 3584)]),
+    "gemv_t16_gate": _case_gemv_t16,
+    "gemv_x16_gateup": _case_gemv_x16,
+    "gemm_dense_gate": lambda: _case_gemm(True),
+    "gemm_l8_gate": lambda: _case_gemm(False),
+    "assign": _case_assign,
+    "decode_step_1": lambda: _case_decode_step(1),                              # uses cudaProfilerStart/Stop around the last step
+    "decode_step_32": lambda: _case_decode_step(32),
+}
+
+
+def run_profile_case(name: str) -> None:
+    """One small case of a kernel on cuda:0 (sizes chosen so that an ncu capture of one to three launches ends in a
+    minute or two): the commands in profiles/*.md run these."""
+    torch.cuda.set_device(0)
+    PROFILE_CASES[name]()
+    torch.cuda.synchronize()
+    print("ok", name)
 
 
 def main() -> None:
@@ -746,12 +1025,20 @@ def main() -> None:
     ap.add_argument("--head", default="16", choices=["16", "q8"], help="decode workload: output head in bf16 (the named config) or the reference's 8-bit block-32 format")
     ap.add_argument("--embed", default="16", choices=["16", "q4"], help="decode workload: embedding in bf16 or the reference's 4-bit block-32 format")
     ap.add_argument("--dense-min", type=int, default=None, help="prefill: token count from which the two-phase path runs (default: the library's)")
+    ap.add_argument("--model", default="7b", choices=sorted(MODELS), help="gemv / prefill: the shape set (7b: one book, one column order; "
+                    "32b: two summed books and 16 seeded column orders per matrix)")
+    ap.add_argument("--no-extras", action="store_true", help="gemv: skip the prefill / decode / reference-kernel legs that the default run adds to its line")
+    ap.add_argument("--profile-case", default=None, choices=sorted(PROFILE_CASES),
+                    help="run one small case for a profiler (a few launches between cudaProfilerStart/Stop) instead of a benchmark")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.profile_case:
+        run_profile_case(args.profile_case)
         return
     if world > 1:
         import torch.distributed as dist

@@ -320,6 +320,12 @@ int cbl_gemv_x16(const cbl_x16* m, const void* xp, int32_t B, void* y, int ydtyp
 /* Two-phase prefill for many tokens and for matrices with several column orders: decode the matrix ONCE
  * into a 16-bit scratch, then multiply with a TMA-fed tcgen05 GEMM (both operands by TMA, accumulators in
  * tensor memory).
+ * Ordering: both kernels use programmatic dependent launch - cbl_decode_raw starts WRITING `out` while earlier work
+ * of the stream may still be running (it waits for its predecessors only at its end, so that it runs beside the
+ * previous GEMM), and cbl_gemm_dense lets the next kernel start early.  `out` must therefore not be read or
+ * written by any earlier work of the stream that may still be in flight: a caller that decodes matrix after
+ * matrix keeps TWO scratch buffers and alternates them (decode A, gemm A, decode B, gemm B, decode A, ...), as
+ * DenseStack does; with a single scratch put an event or another kernel between a GEMM and the next decode.
  *   cbl_decode_raw: out fp16 [R, ld], ld = C rounded up to 8, = cbl_dense_scratch_bytes(R, C) bytes:
  *                   out[r, col] = fp16(A[tag]) or fp16(fp32(A[tag]) + fp32(B[tag2])), col the ORIGINAL column
  *                   (column orders undone), without the row scale.  d = 8, 12-bit tags, G = 1.
@@ -362,7 +368,9 @@ int cbl_rope_kv(const void* qkv, int dtype, int64_t ld, const void* bias, const 
 /* Grouped-query attention of one new token per sequence over cache positions 0..pos[b] (the step's own
  * key / value already written by cbl_rope_kv), flash-decoding on tensor cores.  q, out: [B, NH * HD]; key cache
  * [B][NKV][max_len][HD], value cache dimension-major [B][NKV][HD][max_len]; HD = 128, NH / NKV <= 8, max_len a
- * multiple of 32, both caches zero (or finite) where nothing has been written yet.  The positions of a sequence
+ * multiple of 32, both caches zero (or finite) where nothing has been written yet.  pos[b] must lie in
+ * [0, max_len); a position outside is clamped to the cache (the call reads no memory beyond it, the result is then
+ * the attention over the whole cache) - cbl_rope_kv skips the cache write of such a row.  The positions of a sequence
  * are cut into `nsplit` slices (1..cbl_attn_decode_max_splits()) that run in parallel, four warps per slice;
  * `workspace` holds their partial results (cbl_attn_decode_workspace_bytes bytes; no initial contents required). */
 size_t cbl_attn_decode_workspace_bytes(int32_t B, int32_t NH, int32_t nsplit);
@@ -384,16 +392,19 @@ int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B, int32_t V,
  * no round trip of the vector through memory).  Results equal the product followed by the separate
  * operator: the product is rounded to `dtype` first.  `workspace` as for cbl_gemv_l8_multi (the
  * matrices' padded rows x 4 bytes in order, plus 16 bytes; zero before the first call, left zero).
- *   cbl_gemv_l8_silu_mul: gate_up[0..1] (equal row counts) -> out[i] = silu(gate.x)[i] * (up.x)[i]
- *   cbl_gemv_l8_add_norm: h += W.x; xout = RMSNorm(h) * w   (R <= cbl_gemv_l8_add_norm_max_rows())
+ *   cbl_gemv_l8_silu_mul: gate_up[0..1] (equal row counts) -> out[i] = silu(gate.x)[i] * (up.x)[i]; y_gate / y_up
+ *                         (NULL or [R] in `dtype`) also receive the two products, as the reference's launch leaves them
+ *   cbl_gemv_l8_add_norm: h += W.x; xout = RMSNorm(h) * w   (R <= cbl_gemv_l8_add_norm_max_rows()); y (NULL or [R])
+ *                         also receives the product
  *   cbl_gemv_l8_rope_kv:  qkv[0..2] = q, k, v projections -> bias, rotary at position pos[0], rotated
  *                         query to q_out [NH * HD], key / value into the caches of sequence 0
  * replaces the epilogue modes of the reference's run kernel (shapequant/kernels/proto_runs.py:223-287:
  * add + norm and silu * mul written by the last blocks) and its fused rope + attention prologue
  * (decode_e2e.py:200-250). */
-int cbl_gemv_l8_silu_mul(const cbl_l8* gate_up, const void* x, int xdtype, void* out, int dtype, void* workspace, cbl_stream s);
+int cbl_gemv_l8_silu_mul(const cbl_l8* gate_up, const void* x, int xdtype, void* out, void* y_gate, void* y_up, int dtype, void* workspace,
+                         cbl_stream s);
 int32_t cbl_gemv_l8_add_norm_max_rows(void);
-int cbl_gemv_l8_add_norm(const cbl_l8* m, const void* x, int xdtype, float* h, const void* w, float eps, void* xout, int dtype,
+int cbl_gemv_l8_add_norm(const cbl_l8* m, const void* x, int xdtype, float* h, const void* w, float eps, void* xout, void* y, int dtype,
                          void* workspace, cbl_stream s);
 int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype, const void* bias, const int32_t* pos, int32_t NH, int32_t NKV,
                         int32_t HD, float theta, int32_t max_len, void* q_out, void* kc, void* vc, int dtype, void* workspace,

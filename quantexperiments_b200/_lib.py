@@ -116,9 +116,9 @@ SIGNATURES = {
     "cbl_silu_mul": (c_int, [c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p, c_void_p]),
     "cbl_head_gemv_max_batch": (c_int32, []),
     "cbl_head_gemv": (c_int, [c_void_p, c_void_p, c_int, c_int32, c_int32, c_int32, c_void_p, c_int, c_int64, c_void_p]),
-    "cbl_gemv_l8_silu_mul": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "cbl_gemv_l8_silu_mul": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "cbl_gemv_l8_add_norm_max_rows": (c_int32, []),
-    "cbl_gemv_l8_add_norm": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p]),
+    "cbl_gemv_l8_add_norm": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "cbl_gemv_l8_rope_kv": (c_int, [POINTER(L8), c_void_p, c_int, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_float, c_int32, c_void_p,
                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "cbl_embed_rows_q4": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p]),

@@ -201,7 +201,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_slice(const T* __restrict_
     const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z, nsplit = gridDim.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int NH = NKV * REP;
-    const int L = pos[b] + 1;                                        // positions 0..pos[b] are in the cache (the step's own included)
+    // positions 0..pos[b] are in the cache (the step's own included); a position outside the cache (a caller that
+    // stepped past max_len) is clamped, so that no read ever leaves the cache
+    const int L = min(max(pos[b] + 1, 0), max_len);
     int s0, s1;
     att_slice(L, nsplit, split, s0, s1);
     // partial result of (this warp, head g): [HD sums | max | denominator]

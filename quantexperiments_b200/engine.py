@@ -320,10 +320,10 @@ class DecodeEngine:
             _lib.check("cbl_attn_decode", lib.cbl_attn_decode(self.qr.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.pos.data_ptr(), dtc, 1,
                                                               c.n_heads, c.n_kv, c.head_dim, self.cache_len, c.head_dim ** -0.5, ao,
                                                               self.att_ws.data_ptr(), self.nsplit, s))
-            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["o"].group._structs, ao, dtc, h, L["ln2"].data_ptr(), c.eps, x, dtc, ws, s))
-            _lib.check("cbl_gemv_l8_silu_mul", lib.cbl_gemv_l8_silu_mul(S["gu"].group._structs, x, dtc, act, dtc, ws, s))
+            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["o"].group._structs, ao, dtc, h, L["ln2"].data_ptr(), c.eps, x, None, dtc, ws, s))
+            _lib.check("cbl_gemv_l8_silu_mul", lib.cbl_gemv_l8_silu_mul(S["gu"].group._structs, x, dtc, act, None, None, dtc, ws, s))
             w_next = self.layers[li + 1]["ln1"] if li + 1 < n else self.final_norm
-            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["down"].group._structs, act, dtc, h, w_next.data_ptr(), c.eps, x, dtc, ws, s))
+            _lib.check("cbl_gemv_l8_add_norm", lib.cbl_gemv_l8_add_norm(S["down"].group._structs, act, dtc, h, w_next.data_ptr(), c.eps, x, None, dtc, ws, s))
         self.lm_head.run(self.x16, self.logits)
         _lib.check("cbl_argmax", lib.cbl_argmax(self.logits.data_ptr(), _dt(self.logits.dtype), self.logits.stride(0), 1, self.logits.shape[1],
                                                 self.tok.data_ptr(), self.pos.data_ptr(), s))
@@ -404,6 +404,8 @@ class DecodeEngine:
     def generate(self, n: int, tok=0) -> list:
         """Greedy-decode n tokens from `tok` at position 0 (eager steps; for checks). B = 1: a list of ints,
         else a list of B lists."""
+        if n > self.cfg.max_len:
+            raise ValueError(f"{n} steps from position 0 would run past max_len {self.cfg.max_len}")
         self.reset(tok)
         out = []
         for _ in range(n):
@@ -501,15 +503,20 @@ def start(eng: DecodeEngine, prompt, seq: int = 0) -> torch.Tensor:
 
 
 def _sample(logits: torch.Tensor, temperature: float, top_p: float, top_k: int, gen) -> int:
-    z = logits.float() / max(temperature, 1e-6)
-    if top_k and top_k < z.numel():
-        z = torch.where(z < torch.topk(z, top_k).values[-1], torch.full_like(z, float("-inf")), z)
+    """One token id drawn from softmax(logits / temperature) restricted to the top_k largest logits and to the nucleus
+    whose probability first reaches top_p (the usual temperature / top-k / top-p sampler; the same choices as the
+    reference's, shapequant/runtime.py:203-213)."""
+    scaled = logits.to(torch.float32) / max(temperature, 1e-6)
+    order = torch.argsort(scaled, descending=True)
+    keep = torch.ones(order.numel(), dtype=torch.bool, device=scaled.device)     # in sorted order
+    if 0 < top_k < order.numel():
+        keep[top_k:] = False
     if top_p < 1.0:
-        sz, si = torch.sort(z, descending=True)
-        pr = torch.softmax(sz, -1)
-        sz[pr.cumsum(-1) - pr > top_p] = float("-inf")          # keep the smallest prefix reaching top_p
-        z = torch.full_like(z, float("-inf")).scatter(0, si, sz)
-    return int(torch.multinomial(torch.softmax(z, -1), 1, generator=gen))
+        probs = torch.softmax(scaled[order].masked_fill(~keep, float("-inf")), 0)
+        before = probs.cumsum(0) - probs                    # mass strictly ahead of each candidate
+        keep &= before <= top_p
+    probs = torch.softmax(scaled[order].masked_fill(~keep, float("-inf")), 0)
+    return int(order[torch.multinomial(probs, 1, generator=gen)])
 
 
 @torch.no_grad()

@@ -365,15 +365,15 @@ _RETIRED: list[torch.Tensor] = []       # outgrown work spaces stay alive: a cap
 def l8_workspace(device: torch.device, R: int, nbytes: int = 0) -> torch.Tensor:
     """Zero-initialised work space shared by every L8 product on (device, current stream): the kernels
     leave it zero. Products that may overlap on the device (different streams) get distinct buffers.
-    4 MB to begin with (a group of four 65536-row matrices needs 3.2 MB); a larger request gets a new buffer
-    and the old one is kept, so pointers handed out earlier (CUDA graphs) stay valid."""
+    16 MB to begin with (a launch needs 5.3 MB of partial-sum slots plus 4 bytes per output row); a larger request
+    gets a new buffer and the old one is kept, so pointers handed out earlier (CUDA graphs) stay valid."""
     key = (device.index, _stream())
     need = max(lib.cbl_gemv_l8_workspace_bytes(R), nbytes)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         if ws is not None:
             _RETIRED.append(ws)
-        ws = _WORKSPACES[key] = torch.zeros(max(need, 4 << 20), dtype=torch.uint8, device=device)
+        ws = _WORKSPACES[key] = torch.zeros(max(need, 16 << 20), dtype=torch.uint8, device=device)
     return ws
 
 
@@ -544,7 +544,7 @@ class L8Group:
         self.mats, self.C, self.device = mats, mats[0].C, mats[0].device
         self.Rs = [m.R for m in mats]
         self._built = None
-        self._structs_c = None                  # column-ordered variants, built by the first gemm_rows()
+        self._built_c = None                    # column-ordered variants, built on first use (gemm_rows)
         self._ys = (ctypes.c_void_p * len(mats))()
         self.ws_bytes = sum(lib.cbl_gemv_l8_workspace_bytes(m.R) for m in mats)
         self.rows_ws_bytes = lib.cbl_gemm_rows_workspace_bytes(sum((m.R + 3) // 4 * 4 for m in mats))
@@ -557,6 +557,13 @@ class L8Group:
         if self._built is None or self._built[0] != key:
             self._built = (key, (_lib.L8 * len(self.mats))(*[m.struct() for m in self.mats]))
         return self._built[1]
+
+    @property
+    def _structs_c(self):
+        """The matrices' column-ordered descriptors (the tensor-core products); the layout is built on first use."""
+        if self._built_c is None:
+            self._built_c = (_lib.L8 * len(self.mats))(*[m.struct_c() for m in self.mats])
+        return self._built_c
 
     def gemm_rows(self, X: torch.Tensor, ys: list[torch.Tensor]) -> list[torch.Tensor]:
         """A few dozen tokens on the tensor cores with the weight rows as the M side: ys[i] [B, R_i] = X [B, C] . W_i^T.
@@ -583,8 +590,6 @@ class L8Group:
             st = self._rows_stage[key] = torch.empty(lib.cbl_gemm_stage_bytes(lib.cbl_gemm_rows_max_tokens(), self.C), dtype=torch.uint8,
                                                      device=self.device)
         ws = l8_workspace(self.device, 0, self.rows_ws_bytes)
-        if self._structs_c is None:
-            self._structs_c = (_lib.L8 * len(self.mats))(*[m.struct_c() for m in self.mats])
         with torch.cuda.device(self.device):
             _lib.check("cbl_gemm_rows_multi", lib.cbl_gemm_rows_multi(self._structs_c, len(self.mats), X.data_ptr(), _dt(X.dtype), B, X.stride(0),
                                                                       self._ys, _dt(ys[0].dtype), ldy, st.data_ptr(), ws.data_ptr(), _stream()))

@@ -21,8 +21,11 @@ import torch
 
 from .kernels import DeviceMatrix, L8Matrix, T16Matrix
 
-# rows from which the batch-1 product uses activation-side tables instead of codeword lookups
+# rows from which the batch-1 product uses activation-side tables instead of codeword lookups; with several column
+# orders every order needs its own tables, so the rule applies to the rows per order (measured on B200: a table build
+# costs as much as the lookups of ~1300 rows)
 L8_MIN_ROWS = 2048
+L8_MIN_ROWS_PER_ORDER = 1536
 # tokens from which the two-phase path runs (decode the matrix once into a 16-bit scratch + TMA-fed tensor-core
 # GEMM). Measured on B200 it beats the kernel that decodes weight tiles on the fly at every token count above the
 # small-batch kernel's 64 (12.1 vs 20.6 ms for the 196 Qwen2.5-7B matrices at 128 tokens, 30 vs 36 ms at 2048).
@@ -105,7 +108,9 @@ class PackedLinear(torch.nn.Module):
 
     def use_l8(self) -> bool:
         """One token runs on the table-lookup kernel (any number of column orders up to its limit)."""
-        return self.dm.M <= L8Matrix.MAX_ORDERS and self.R >= L8_MIN_ROWS
+        if self.dm.M == 1:
+            return self.R >= L8_MIN_ROWS
+        return self.dm.M <= L8Matrix.MAX_ORDERS and self.R >= L8_MIN_ROWS_PER_ORDER * self.dm.M
 
     def use_gemm(self) -> bool:
         """The tensor-core kernel that decodes weight tiles on the fly executes one column order (one or two
@@ -167,13 +172,59 @@ class RunsLin:
         else:
             lin.t16.xp_buffer(1)
 
-    def run(self, x: torch.Tensor, y: torch.Tensor, epi=None):
-        if epi is not None:
-            raise NotImplementedError("fused epilogues are not part of this path")
-        if x.dim() == 1 or x.shape[0] == 1:
-            self.lin.gemv(x.reshape(-1), y.reshape(-1))
-        else:
-            self.lin.t16.run(x, y)
+    def run(self, x: torch.Tensor, y: torch.Tensor, epi: dict | None = None):
+        """y = W . x.  `epi` asks for the operator that follows the product in a decode step to run with it, as the
+        reference's run kernel does for its last blocks (shapequant/kernels/proto_runs.py:223-287, 505-520):
+            dict(mode=1, h_in, h_out, w, eps, out)   h_out = h_in + y;  out = RMSNorm(h_out) * w
+            dict(mode=2, out)                        this matrix is `gate`, epi["up"] a second RunsLin on the same x:
+                                                     y = [gate.x | up.x] (2R values), out = silu(gate.x) * (up.x)
+        (`src` of the reference's dict is this launch's own y and is accepted and ignored; `perms`, the M permuted
+        copies of `out`, must be None: column orders are applied inside the next product here.)  h_in / h_out are the
+        fp32 residual stream; y, w and out are in the model's 16-bit type.  One token, one column order."""
+        if epi is None:
+            if x.dim() == 1 or x.shape[0] == 1:
+                self.lin.gemv(x.reshape(-1), y.reshape(-1))
+            else:
+                self.lin.t16.run(x, y)
+            return y
+        import ctypes
+        from . import _lib
+        from .kernels import L8Group, _dt, _stream, l8_workspace
+        if epi.get("perms") is not None:
+            raise ValueError("epi['perms']: permuted copies of the output are not produced here (the next product applies its column orders itself)")
+        if not self.lin.use_l8() or self.lin.dm.M != 1 or x.numel() != self.C:
+            raise ValueError("fused epilogues run one token through the table-lookup kernel (one column order, at least 2048 rows)")
+        mode, out = epi.get("mode"), epi["out"]
+        xv = x.reshape(-1)
+        if y.dtype not in (torch.float16, torch.bfloat16) or out.dtype != y.dtype:
+            raise ValueError("fused epilogues write the model's 16-bit type")
+        with torch.cuda.device(self.lin.dm.device):
+            if mode == 1:
+                h_in, h_out = epi["h_in"], epi.get("h_out", epi["h_in"])
+                if h_in.dtype != torch.float32 or h_out.dtype != torch.float32:
+                    raise ValueError("the residual stream is fp32")
+                if h_out.data_ptr() != h_in.data_ptr():
+                    h_out.copy_(h_in)
+                st = (_lib.L8 * 1)(self.lin.l8.struct())
+                ws = l8_workspace(self.lin.dm.device, self.R)
+                _lib.check("cbl_gemv_l8_add_norm", _lib.lib.cbl_gemv_l8_add_norm(st, xv.data_ptr(), _dt(xv.dtype), h_out.data_ptr(), epi["w"].data_ptr(),
+                                                                                 float(epi.get("eps", 1e-6)), out.data_ptr(), y.data_ptr(), _dt(y.dtype),
+                                                                                 ws.data_ptr(), _stream()))
+            elif mode == 2:
+                up = epi["up"]
+                if up.R != self.R or up.C != self.C or y.numel() != 2 * self.R:
+                    raise ValueError("mode 2: `up` has this matrix's shape and y holds gate | up (2 R values)")
+                grp = self._pair if getattr(self, "_pair", None) is not None and self._pair[0] is up else None
+                if grp is None:
+                    self._pair = grp = (up, L8Group([self.lin.l8, up.lin.l8]))
+                yv = y.reshape(-1)
+                ws = l8_workspace(self.lin.dm.device, 0, grp[1].ws_bytes)
+                _lib.check("cbl_gemv_l8_silu_mul", _lib.lib.cbl_gemv_l8_silu_mul(grp[1]._structs, xv.data_ptr(), _dt(xv.dtype), out.data_ptr(),
+                                                                                 yv.data_ptr(), yv.data_ptr() + self.R * yv.element_size(), _dt(y.dtype),
+                                                                                 ws.data_ptr(), _stream()))
+            else:
+                raise ValueError("epi['mode'] is 1 (add + RMSNorm) or 2 (silu * up)")
+        return y
 
     def nbytes(self) -> int:
         return self.lin.stored_bytes()

@@ -156,50 +156,64 @@ class PackedFile:
         return self.matrix(name, device).dequant(dtype=torch.float32)
 
 
+# ---- the reference's block-32 formats of embedding and head (aux section of a packed file, shapequant/packed.py:33-41):
+# every run of 32 columns shares one fp16 scale = largest magnitude / qmax (a run of zeros gets scale 1), values are
+# round(w / scale) clamped to the code range.  The arithmetic below is the format's definition; fixtures written by the
+# reference's packers (tests/golden/blockq.npz) pin it bit for bit.
+_BLOCK = 32
+
+
+def _block32_codes(w: torch.Tensor, qmax: float, lo: int, hi: int, max_elems: int = 1 << 26) -> tuple[torch.Tensor, torch.Tensor]:
+    """(codes int32 [R, C], scale fp16 [R, C / 32]) of a matrix, a slab of rows at a time so that the fp32 temporaries
+    stay below max_elems elements whatever the vocabulary size."""
+    R, C = w.shape
+    if C % _BLOCK:
+        raise ValueError(f"{C} columns are not a multiple of {_BLOCK}")
+    codes = torch.empty(R, C, dtype=torch.int32, device=w.device)
+    scale = torch.empty(R, C // _BLOCK, dtype=torch.float16, device=w.device)
+    slab = max(1, max_elems // C)
+    for r0 in range(0, R, slab):
+        blocks = w[r0:r0 + slab].to(torch.float32).unflatten(1, (C // _BLOCK, _BLOCK))
+        s16 = (blocks.abs().amax(dim=2).clamp_min(1e-8) / qmax).to(torch.float16)
+        s16[s16 == 0] = 1.0                               # a scale that underflows fp16: the codes are all zero anyway
+        scale[r0:r0 + slab] = s16
+        codes[r0:r0 + slab] = torch.round(blocks / s16.to(torch.float32).unsqueeze(2)).clamp_(lo, hi).flatten(1).to(torch.int32)
+    return codes, scale
+
+
+def q8_pack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """w [R, C] -> (q int8 [R, C], scale fp16 [R, C/32]): the reference's 8-bit block-32 head, codes in -127..127
+    (shapequant/kernels/proto_formats.py:464-471; aux.lm_head of shapequant/packed.py:38-39)."""
+    codes, scale = _block32_codes(w, 127.0, -127, 127)
+    return codes.to(torch.int8), scale
+
+
 def q4_embed_pack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """w [V, C] -> (q uint8 [V, C/2], scale fp16 [V, C/32]): the reference's 4-bit block-32 embedding
-    (shapequant/packed.py:134-148): s = fp16(max|w| / 7) per 32 columns, n = clamp(round(w / s), -8, 7) + 8, even column
-    in the low nibble. Runs on the tensor's device."""
-    V, C = w.shape
-    q = torch.empty(V, C // 2, dtype=torch.uint8, device=w.device)
-    sc = torch.empty(V, C // 32, dtype=torch.float16, device=w.device)
-    for s in range(0, V, 8192):
-        b = w[s:s + 8192].float().view(-1, C // 32, 32)
-        k = (b.abs().amax(-1).clamp_min(1e-8) / 7.0).half().float()
-        k = torch.where(k == 0, torch.ones_like(k), k)
-        n = ((b / k[..., None]).round().clamp(-8, 7) + 8).to(torch.uint8).view(-1, C // 2, 2)
-        q[s:s + 8192] = n[..., 0] | (n[..., 1] << 4)
-        sc[s:s + 8192] = k.half()
-    return q, sc
+    (shapequant/packed.py:134-148), codes -8..7 stored with an offset of 8, the even column in the low nibble."""
+    codes, scale = _block32_codes(w, 7.0, -8, 7)
+    nib = (codes + 8).to(torch.uint8)
+    return nib[:, 0::2] | (nib[:, 1::2] << 4), scale
+
+
+def _block32_expand(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp32 values of block-32 codes [n, C] (any integer or float type) under their scales [n, C / 32]."""
+    return (codes.to(torch.float32).unflatten(1, (-1, _BLOCK)) * scale.to(torch.float32).unsqueeze(2)).flatten(1)
 
 
 def q4_embed_rows(q: torch.Tensor, sc: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """fp32 [len(ids), C] rows of a 4-bit block-32 embedding (shapequant/packed.py:151-155); on a CUDA device the
     engine uses cbl_embed_rows_q4 instead."""
-    b = q[ids]
-    n = torch.stack([b & 15, b >> 4], -1).view(b.shape[0], -1).float() - 8
-    return (n.view(b.shape[0], -1, 32) * sc[ids].float()[..., None]).view(b.shape[0], -1)
-
-
-def q8_pack(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """w [R, C] -> (q int8 [R, C], scale fp16 [R, C/32]): the reference's 8-bit block-32 head
-    (shapequant/kernels/proto_formats.py:464-471; aux.lm_head of shapequant/packed.py:38-39)."""
-    R, C = w.shape
-    q = torch.empty(R, C, dtype=torch.int8, device=w.device)
-    sc = torch.empty(R, C // 32, dtype=torch.float16, device=w.device)
-    for s in range(0, R, 8192):
-        b = w[s:s + 8192].float().view(-1, C // 32, 32)
-        k = (b.abs().amax(-1).clamp_min(1e-8) / 127.0).half().float()
-        k = torch.where(k == 0, torch.ones_like(k), k)
-        q[s:s + 8192] = (b / k[..., None]).round().clamp(-127, 127).to(torch.int8).view(-1, C)
-        sc[s:s + 8192] = k.half()
-    return q, sc
+    packed_rows = q[ids]
+    nib = torch.empty(packed_rows.shape[0], 2 * packed_rows.shape[1], dtype=torch.int16, device=q.device)
+    nib[:, 0::2] = packed_rows & 15
+    nib[:, 1::2] = packed_rows >> 4
+    return _block32_expand(nib - 8, sc[ids])
 
 
 def q8_rows(q: torch.Tensor, sc: torch.Tensor, s: int = 0, e: int | None = None) -> torch.Tensor:
     """fp32 rows s:e of an 8-bit block-32 matrix (shapequant/packed.py:158-160)."""
-    b = q[s:e]
-    return (b.float().view(b.shape[0], -1, 32) * sc[s:e].float()[..., None]).view(b.shape[0], -1)
+    return _block32_expand(q[s:e], sc[s:e])
 
 
 def decode_tensors(local_tags, table, row_scale, row_book, row_mask, perms, K: int) -> torch.Tensor:

@@ -125,14 +125,29 @@ class PeerReduceGemv:
         self.l8, self.rank, self.world = l8, arena.rank, arena.world
         ptrs = arena.take(lib.cbl_gemv_l8_ar_workspace_bytes(l8.R))
         self.ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        self.own = ptrs[self.rank]
         self._struct = l8.struct()
 
+    def status(self) -> bool:
+        """Synchronises the stream; False if a bounded wait of a run() since the last query expired (a peer's word or
+        a staged copy never arrived: that call's output is invalid, later calls are correct again)."""
+        from . import _lib
+        from .kernels import _stream
+        with torch.cuda.device(self.l8.device):
+            rc = _lib.lib.cbl_gemv_l8_ar_status(self.own, self.l8.R, _stream())
+        if rc not in (_lib.OK, _lib.ETIMEOUT):
+            _lib.check("cbl_gemv_l8_ar_status", rc)
+        return rc == _lib.OK
+
     def run(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """x: this rank's activation slice [C_local]; for a matrix with column orders the FULL activation vector (the
+        shard's column orders hold global indices)."""
         import ctypes
         from . import _lib
         from .kernels import _dt, _stream
         xv, yv = x.reshape(-1), y.reshape(-1)
-        if xv.numel() != self.l8.C or not xv.is_contiguous() or yv.numel() != self.l8.R or not yv.is_contiguous():
+        wide_ok = self.l8.M > 1 and xv.numel() >= self.l8.C
+        if (xv.numel() != self.l8.C and not wide_ok) or not xv.is_contiguous() or yv.numel() != self.l8.R or not yv.is_contiguous():
             raise ValueError("x must be this rank's contiguous activation slice and y a contiguous [R] vector")
         with torch.cuda.device(self.l8.device):
             _lib.check("cbl_gemv_l8_ar", _lib.lib.cbl_gemv_l8_ar(ctypes.byref(self._struct), xv.data_ptr(), _dt(xv.dtype), yv.data_ptr(),
@@ -190,6 +205,7 @@ class RowParallelLinear:
             self.dm = DeviceMatrix(ts["tags"], ts["table"], ts["row_scale"], None, ts["row_mask"], ps, K=ms["K"], d=ms["d"],
                                    C=c1 - c0, device=device, tags2=ts.get("tags2"), table2=ts.get("table2"))
             self.t16 = T16Matrix(self.dm)
+            self._l8 = None
 
     def partial(self, x: torch.Tensor) -> torch.Tensor:
         """fp32 partial product [..., R] of this rank's column range."""
@@ -198,17 +214,34 @@ class RowParallelLinear:
         y = torch.empty(n, self.R, dtype=torch.float32, device=x.device)
         if not self.multi:
             self.lin.forward_into(x.reshape(n, self.c1 - self.c0), y)
+        elif n == 1 and self.l8_multi is not None:
+            self.l8_multi.run(x.reshape(-1).contiguous(), y[0], wide=True)      # one token: the table-lookup kernel
         else:
-            if n > T16Matrix_BMAX():
-                raise ValueError("row-parallel matrices with column orders run batches up to 64 tokens")
-            if n:
-                self.t16.run(x.reshape(n, self.C_full).contiguous(), y, n, wide=True)
+            # the row-tile kernel takes up to 64 tokens per launch; longer inputs (prefill) run as 64-token pieces
+            xs = x.reshape(n, self.C_full).contiguous()
+            step = T16Matrix_BMAX()
+            for t0 in range(0, n, step):
+                nt = min(step, n - t0)
+                self.t16.run(xs[t0:t0 + nt], y[t0:t0 + nt], nt, wide=True)
         return y.reshape(*lead, self.R)
+
+    @property
+    def l8_multi(self):
+        """The batch-1 layout of a shard with column orders (at most 16 of them), built on first use."""
+        from .kernels import L8Matrix
+        if self._l8 is None and self.dm.M <= L8Matrix.MAX_ORDERS:
+            self._l8 = L8Matrix(self.dm)
+        return self._l8
 
     def attach(self, arena: "PeerArena") -> None:
         """Reserve this matrix's peer work space (call on every rank, in the same order)."""
-        if self.multi or not self.lin.use_l8():
-            raise ValueError("the fused path runs single-order matrices with at least 2048 rows")
+        if self.multi:
+            if self.l8_multi is None:
+                raise ValueError("the fused path runs matrices with at most 16 column orders")
+            self.fused = PeerReduceGemv(self.l8_multi, arena)
+            return
+        if not self.lin.use_l8():
+            raise ValueError("the fused path runs matrices with at least 2048 rows")
         self.fused = PeerReduceGemv(self.lin.l8, arena)
 
     def forward_fused(self, x: torch.Tensor, y: torch.Tensor | None = None) -> torch.Tensor:

@@ -12,7 +12,6 @@ to x's 16-bit dtype into a shared scratch followed by a library GEMM)."""
 
 from __future__ import annotations
 
-import re
 
 import torch
 
@@ -24,22 +23,23 @@ BMAX = T16Matrix.BMAX
 # vLLM fuses some HF projections into one layer; the packed file keeps the HF pieces
 STACKED = {"self_attn.qkv_proj": ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"),
            "mlp.gate_up_proj": ("mlp.gate_proj", "mlp.up_proj")}
-_LAYER = re.compile(r"(?:^|\.)layers\.(\d+)\.(.+)$")
-
-
 def packed_pieces(prefix: str, names) -> list[str] | None:
-    """Packed matrix names (model.layers.N.<kind>) that make up the vLLM layer at `prefix`, or None
-    when the layer is not packed (same rule as shapequant/vllm_ext/core.py:127-142)."""
-    m = _LAYER.search(prefix)
-    if m is None:
+    """Packed matrix names (model.layers.N.<kind>) that make up the vLLM layer at `prefix`: the HF pieces of a fused
+    projection, in order.  None when the layer is not a block linear or none of its pieces is in the file; an error
+    when only some are (the rule of shapequant/vllm_ext/core.py:127-142)."""
+    parts = prefix.split(".")
+    if "layers" not in parts:
         return None
-    i, suffix = m.group(1), m.group(2)
-    pieces = [f"model.layers.{i}.{s}" for s in STACKED.get(suffix, (suffix,))]
-    have = [p in names for p in pieces]
-    if all(have):
-        return pieces
-    if any(have):
-        raise ValueError(f"{prefix}: only some of its pieces are packed ({pieces})")
+    at = len(parts) - 1 - parts[::-1].index("layers")           # the last "layers" component
+    if at + 2 >= len(parts) or not parts[at + 1].isdigit():
+        return None
+    layer, kind = parts[at + 1], ".".join(parts[at + 2:])
+    wanted = [f"model.layers.{layer}.{piece}" for piece in STACKED.get(kind, (kind,))]
+    present = [name for name in wanted if name in names]
+    if len(present) == len(wanted):
+        return wanted
+    if present:
+        raise ValueError(f"{prefix}: only some of its pieces are packed ({wanted})")
     return None
 
 
@@ -60,19 +60,42 @@ class PackedShards:
         self.bmax = self.cross = bmax
         self.device = lins[0].dm.device
         self.sq_name = ""
-        for lin in lins:                       # build kernel layouts and staging buffers up front
-            if lin.use_l8() or lin.use_gemm():
-                lin.l8
-            for b in range(1, bmax + 1):
-                lin.small_batch(b).xp_buffer(b)
         self.stack = DenseStack([lin.dm for lin in lins])     # many tokens / several column orders: decode once, one GEMM
-        # one token: all pieces in one launch when they share a column order and the stack is tall enough
+        # Kernel layouts are second copies of the tags in a kernel's order: each is built when its token-count class
+        # is first used (or by prepare()), so a layer that only ever decodes keeps one extra copy, not three.
         self.group = self.rows = None
-        if all(lin.dm.M == 1 for lin in lins) and len(lins) <= L8Group.MAX:
-            if self.R >= L8_MIN_ROWS:
-                self.group = L8Group([lin.l8 for lin in lins])
-            if len({lin.dm.books for lin in lins}) == 1:
-                self.rows = self.group if self.group is not None else L8Group([lin.l8 for lin in lins])
+        self._one_order = all(lin.dm.M == 1 for lin in lins) and len(lins) <= L8Group.MAX
+        self._ready: set = set()
+        self.prepare(1)
+
+    def _class_of(self, M: int) -> str:
+        if M == 1:
+            return "one"
+        if M <= self.cross:
+            return "rows" if (M >= ROWS_MIN_TOKENS and self._one_order and len({lin.dm.books for lin in self.lins}) == 1) else f"small{M}"
+        return "many"
+
+    def prepare(self, M: int) -> None:
+        """Build whatever forward() needs for M tokens (kernel layouts, staging buffers).  forward() calls it on
+        first use; call it yourself for every token count a CUDA graph will replay, before capturing."""
+        cls = self._class_of(M)
+        if cls in self._ready:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"PackedShards.prepare({M}) must run before the stream is captured (layouts are allocated on first use)")
+        if cls == "one":
+            if self._one_order and self.R >= L8_MIN_ROWS:
+                self.group = L8Group([lin.l8 for lin in self.lins])       # all pieces in one launch
+            else:
+                for lin in self.lins:
+                    lin.l8 if lin.use_l8() else lin.small_batch(1).xp_buffer(1)
+        elif cls == "rows":
+            self.rows = self.group if self.group is not None else L8Group([lin.l8 for lin in self.lins])
+            self.rows._structs_c                                      # (built by the first gemm_rows otherwise)
+        elif cls.startswith("small"):
+            for lin in self.lins:
+                lin.small_batch(M).xp_buffer(M)
+        self._ready.add(cls)
 
     @classmethod
     def from_packed(cls, pf, names: list[str], dev="cuda", **kw) -> "PackedShards":
@@ -99,6 +122,7 @@ class PackedShards:
         if M == 0:
             y = x2.new_empty(0, self.R)
         elif M <= self.cross:
+            self.prepare(M)
             xin = x2 if x2.dtype in (torch.float16, torch.bfloat16) else x2.to(torch.bfloat16)
             y = self._small(xin.contiguous(), M)
         else:
@@ -111,7 +135,7 @@ class PackedShards:
         if M == 1 and self.group is not None:
             self.group.run(x[0], [y[0, off:off + R] for off, R in zip(self.offs, self.Rs)])
             return y
-        if M >= ROWS_MIN_TOKENS and self.rows is not None:
+        if self._class_of(M) == "rows":
             self.rows.gemm_rows(x, [y[:, off:off + R] for off, R in zip(self.offs, self.Rs)])
             return y
         for lin, off, R in zip(self.lins, self.offs, self.Rs):

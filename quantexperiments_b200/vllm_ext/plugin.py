@@ -32,20 +32,18 @@ from ..linear import PackedLinear
 from . import core
 
 
-def _model_path() -> tuple[str, str | None]:
-    from vllm.config import get_current_vllm_config
-    mc = get_current_vllm_config().model_config
-    return mc.model, getattr(mc, "revision", None)
-
-
 def _resolve(file: str) -> str:
-    if os.path.isabs(file) and os.path.exists(file):
-        return file
-    model, rev = _model_path()
-    if os.path.isdir(model):
-        return os.path.join(model, file)
+    """Where the packed file lives: an existing absolute path as given; else a file of the model vLLM is loading -
+    inside its local directory, or fetched from its hub repository at the configured revision."""
+    path = os.path.abspath(file) if os.path.isabs(file) else None
+    if path and os.path.exists(path):
+        return path
+    from vllm.config import get_current_vllm_config
+    model_cfg = get_current_vllm_config().model_config
+    if os.path.isdir(model_cfg.model):
+        return os.path.join(model_cfg.model, file)
     from huggingface_hub import hf_hub_download
-    return hf_hub_download(model, file, revision=rev)
+    return hf_hub_download(repo_id=model_cfg.model, filename=file, revision=getattr(model_cfg, "revision", None))
 
 
 def _tp() -> tuple[int, int]:

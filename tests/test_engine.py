@@ -146,6 +146,27 @@ def test_decode_attention_matches_softmax_attention(dtype, NH, NKV, B, max_len, 
         assert err <= 2 * (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4, (b, float(err))
 
 
+def test_decode_attention_clamps_positions_beyond_the_cache():
+    """pos = max_len (a caller that stepped one past the cache) reads nothing outside it: the result is the attention
+    over the whole cache, exactly what pos = max_len - 1 gives."""
+    L = _lib()
+    NH, NKV, HD, max_len, B = 8, 2, 128, 96, 2
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q = torch.randn(B, NH * HD, device="cuda", generator=g).bfloat16()
+    kc = torch.randn(B, NKV, max_len, HD, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(B, NKV, HD, max_len, device="cuda", generator=g).bfloat16()
+    ws = torch.zeros(L.lib.cbl_attn_decode_workspace_bytes(B, NH, 3), dtype=torch.uint8, device="cuda")
+    outs = []
+    for p in ([max_len - 1, max_len - 1], [max_len, max_len + 1000]):
+        pos = torch.tensor(p, dtype=torch.int32, device="cuda")
+        out = torch.zeros(B, NH * HD, device="cuda", dtype=torch.bfloat16)
+        L.check("cbl_attn_decode", L.lib.cbl_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), _dt(torch.bfloat16), B, NH, NKV,
+                                                         HD, max_len, HD ** -0.5, out.data_ptr(), ws.data_ptr(), 3, _s()))
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_decode_attention_rejects_too_many_slices_and_odd_shapes():
     L = _lib()
     t = torch.zeros(16, device="cuda")
@@ -219,7 +240,7 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
     L = _lib()
     g = torch.Generator(device="cuda").manual_seed(21 + books)
     dtc, s = _dt(dtype), _s()
-    ws = l8_workspace(torch.device("cuda", 0), 0, 1 << 20).data_ptr()
+    ws = l8_workspace(torch.device("cuda", 0), 0, 4 * L.lib.cbl_gemv_l8_workspace_bytes(8192)).data_ptr()
     # gate | up -> silu * up   (row count not a multiple of 4: padded accumulator rows)
     C, I = 520, 2050
     gate, up = _rand_lin(I, C, g, books), _rand_lin(I, C, g, books)
@@ -239,8 +260,20 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
         return bool(((a - b).abs() <= n * ulp * b.abs().max()).all()) and float((a - b).abs().mean()) <= 0.05 * ulp * float(b.abs().max())
 
     for _ in range(2):          # the work space is left zero: a second call gives the same result
-        L.check("cbl_gemv_l8_silu_mul", L.lib.cbl_gemv_l8_silu_mul(grp._structs, x.data_ptr(), dtc, out.data_ptr(), dtc, ws, s))
+        L.check("cbl_gemv_l8_silu_mul", L.lib.cbl_gemv_l8_silu_mul(grp._structs, x.data_ptr(), dtc, out.data_ptr(), None, None, dtc, ws, s))
         assert close(out, ref[0])
+    # the two products themselves on request, and the reference-named surface RunsLin.run(x, y, epi=...)
+    ykeep = torch.zeros(2 * I, device="cuda", dtype=dtype)
+    L.check("cbl_gemv_l8_silu_mul", L.lib.cbl_gemv_l8_silu_mul(grp._structs, x.data_ptr(), dtc, out.data_ptr(), ykeep.data_ptr(),
+                                                                ykeep.data_ptr() + I * ykeep.element_size(), dtc, ws, s))
+    assert torch.equal(ykeep, ygu)                    # products are bit-reproducible: the fused launch rounds the same sums
+    from quantexperiments_b200.linear import RunsLin
+    rg, ru = RunsLin(gate), RunsLin(up)
+    y2, o2 = torch.zeros(2 * I, device="cuda", dtype=dtype), torch.zeros(I, device="cuda", dtype=dtype)
+    rg.run(x, y2, epi={"mode": 2, "up": ru, "out": o2})
+    assert torch.equal(y2, ygu) and torch.equal(o2, out)
+    with pytest.raises(ValueError):
+        rg.run(x, y2, epi={"mode": 2, "up": ru, "out": o2, "perms": torch.zeros(1, I)})
     # down -> add + norm   (R = 3584: four finish blocks in one cluster; and a single-block case)
     for R, Cd in ((3584, 1032), (520, 264), (8192, 64)):
         down = _rand_lin(R, Cd, g, books)
@@ -252,8 +285,13 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
         L.check("cbl_add_rmsnorm", L.lib.cbl_add_rmsnorm(h_ref.data_ptr(), y.data_ptr(), R, w.data_ptr(), dtc, 1e-6, 1, R, x_ref.data_ptr(), s))
         h, xo = h0.clone(), torch.zeros(R, device="cuda", dtype=dtype)
         st = (L.L8 * 1)(down.l8.struct())
-        L.check("cbl_gemv_l8_add_norm", L.lib.cbl_gemv_l8_add_norm(st, xd.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s))
+        L.check("cbl_gemv_l8_add_norm", L.lib.cbl_gemv_l8_add_norm(st, xd.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), None, dtc, ws, s))
         assert close(h, h_ref[0]) and close(xo, x_ref[0])
+        if R >= 2048:               # the same through RunsLin.run(x, y, epi={mode 1}): h_out = h_in + y, out = norm(h_out) * w, y kept
+            hi, ho = h0[0].clone(), torch.zeros(R, device="cuda")
+            yk, ok = torch.zeros(R, device="cuda", dtype=dtype), torch.zeros(R, device="cuda", dtype=dtype)
+            RunsLin(down).run(xd, yk, epi={"mode": 1, "h_in": hi, "h_out": ho, "w": w, "eps": 1e-6, "out": ok, "src": yk})
+            assert torch.equal(yk, y) and torch.equal(hi, h0[0]) and torch.equal(ho, h) and torch.equal(ok, xo)
     assert L.lib.cbl_gemv_l8_add_norm_max_rows() == 8192
     # q | k | v -> bias, rotary, cache write
     NH, NKV, HD, max_len, Cq = 6, 2, 128, 24, 264
@@ -280,7 +318,7 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
                                      kc.data_ptr(), vc.data_ptr(), dtc, ws, s) == L.EINVAL
     seg = (ctypes.c_int32 * (L.L8_MAX_ORDERS + 1))(0, 8224)
     big = (L.L8 * 1)(L.L8(8196, 64, 1, 1, 8224, 1, 1, 0, 16, 16, None, 16, None, None, None, None, seg, 0))
-    assert L.lib.cbl_gemv_l8_add_norm(big, xq.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), dtc, ws, s) == L.EUNSUPPORTED
+    assert L.lib.cbl_gemv_l8_add_norm(big, xq.data_ptr(), dtc, h.data_ptr(), w.data_ptr(), 1e-6, xo.data_ptr(), None, dtc, ws, s) == L.EUNSUPPORTED
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -497,3 +535,49 @@ def test_engine_rejects_unsupported_shapes():
     eng = random_engine(_small_cfg(max_len=32), seed=1)
     with pytest.raises(ValueError):
         eng.prefill(list(range(40)))
+
+
+@pytest.mark.parametrize("feed", ["prefill", "steps"])
+def test_engine_logits_match_a_hugging_face_qwen2_with_reference_decoded_weights(feed):
+    """The pin of the decode engine, as the reference pins its own (tests/test_runtime.py:18-89): a tiny random Hugging
+    Face Qwen2 (CPU, fp32, eager attention) whose block linears are codebook matrices decoded by the reference wrote
+    the logits of 14 positions into tests/golden/engine_hf.npz; the same model, rebuilt here in the packed format from
+    the same seeds, must reproduce them (relative error of the logit vectors < 2e-2, the reference's bound), fed
+    either as one batched prefill per prefix or token by token through the decode step."""
+    import sys
+    from pathlib import Path
+    gold = Path(__file__).resolve().parent / "golden"
+    sys.path.insert(0, str(gold))
+    import tiny_qwen2 as tq
+    from quantexperiments_b200.engine import Cfg, DecodeEngine, DenseHead
+    from quantexperiments_b200.linear import PackedLinear
+    z = np.load(gold / "engine_hf.npz")
+    tokens, want = [int(t) for t in z["tokens"]], torch.from_numpy(z["logits"])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()          # noqa: E731
+    st = tq.small_tensors()
+    layers = []
+    for li in range(tq.NL):
+        L = {"ln1": t(st[f"ln1_{li}"]), "ln2": t(st[f"ln2_{li}"]), "bq": t(st[f"bq_{li}"]), "bk": t(st[f"bk_{li}"]), "bv": t(st[f"bv_{li}"])}
+        for n in tq.LINEARS:
+            m = tq.matrix(li, n)
+            L[n] = PackedLinear(t(m["words"][0]), t(m["table"][0]), t(m["row_scale"]), None, None, t(m["perms"]).long(), 4096, 8)
+        layers.append(L)
+    cfg = Cfg(hidden=tq.H, n_heads=tq.NH, n_kv=tq.NKV, head_dim=tq.HD, inter=tq.I, vocab=tq.V, layers=tq.NL, rope_theta=tq.THETA,
+              eps=tq.EPS, max_len=tq.MAX_LEN)
+    eng = DecodeEngine(cfg, t(st["embed"]), layers, t(st["final_norm"]), DenseHead(t(st["head"])))
+    got = []
+    if feed == "prefill":
+        for n in range(1, len(tokens) + 1):               # the logits of position n - 1 = last position of the prefix of n tokens
+            eng.reset(0)
+            got.append(eng.prefill(torch.tensor(tokens[:n], device="cuda"), 0).float().cpu())
+    else:
+        eng.reset(tokens[0])
+        for i, tok in enumerate(tokens):
+            eng.tok.fill_(tok)                            # teacher forcing: the step reads tok at pos, leaves the logits, advances pos
+            eng.step()
+            got.append(eng.logits[0].float().cpu().clone())
+    eng.check()
+    got = torch.stack(got)
+    rel = float((got - want).norm() / want.norm())
+    assert rel < 2e-2, rel
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() >= 0.9

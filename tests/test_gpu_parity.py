@@ -597,6 +597,34 @@ def test_two_phase_prefill_stacks_pieces_writes_a_column_slice_and_survives_outl
     DenseStack.status("cuda")
 
 
+def test_two_phase_prefill_back_to_back_matrices_on_alternating_scratches():
+    """The documented call sequence through the C ABI: decode A -> gemm A -> decode B -> gemm B -> decode A ... on TWO
+    scratch buffers (cbl_decode_raw starts writing before earlier work of the stream has finished, so a scratch is
+    never reused by the very next decode)."""
+    import ctypes
+    from quantexperiments_b200 import _lib
+    lib = _lib.lib
+    T, C = 130, 520
+    ms = [orc.synth_matrix(R, C, seed=40 + i) for i, R in enumerate((300, 520, 260, 300))]
+    dms = [_dm(m) for m in ms]
+    X = torch.randn(T, C, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3)).bfloat16()
+    ld = (C + 7) // 8 * 8
+    scr = [torch.empty(lib.cbl_dense_scratch_bytes(520, C), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    stage = torch.zeros(lib.cbl_gemm_stage_bytes(T, C) + 16, dtype=torch.uint8, device="cuda")
+    ys = [torch.empty(T, m["R"], device="cuda") for m in ms]
+    s = torch.cuda.current_stream().cuda_stream
+    for rep in range(3):
+        for i, (dm, y) in enumerate(zip(dms, ys)):
+            sc = scr[i & 1]
+            assert lib.cbl_decode_raw(ctypes.byref(dm.struct()), sc.data_ptr(), s) == _lib.OK
+            assert lib.cbl_gemm_dense(sc.data_ptr(), dm.R, C, dm.row_scale.data_ptr(), X.data_ptr(), _lib.BF16, T, X.stride(0), y.data_ptr(),
+                                      _lib.F32, y.stride(0), stage.data_ptr(), stage.data_ptr() + stage.numel() - 16, s) == _lib.OK
+    torch.cuda.synchronize()
+    assert int(stage[-16:].view(torch.int32)[0]) == 0
+    for m, y in zip(ms, ys):
+        assert orc.max_rel_err(y.cpu().numpy(), orc.linear_ref(X.float().cpu().numpy(), orc.synth_decode(m))) < TOL
+
+
 def test_two_phase_prefill_rejects_unsupported_arguments():
     from quantexperiments_b200 import _lib
     import ctypes

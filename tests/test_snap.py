@@ -125,3 +125,25 @@ def test_snap_matches_reference_compress_and_round_trips_through_the_decoder():
     assert np.array_equal(dm.dequant(dtype=torch.float32).cpu().numpy(), ref)
     rel = float((dm.dequant(dtype=torch.float32).cpu() - wm).pow(2).mean() / wm.pow(2).mean())
     assert rel < 0.5                                       # random book, random matrix: the snap still halves the energy
+    # the container's own decode takes the same path
+    assert np.array_equal(cb.decode(s.cm).cpu().numpy(), ref)
+
+
+def test_codebook_matrix_decode_with_padding_and_permutation_matches_the_reference_fixture():
+    """decode(CodebookMatrix) on the GPU against the reference's decode of the same container (64-word book, rows of
+    100 columns padded to 104, a column permutation): bit for bit, padding stripped, permutation undone."""
+    from quantexperiments_b200 import codebook as cb
+    z = np.load(G / "codebook.npz")
+    pad, cols = (int(v) for v in z["pad"])
+    cm = cb.CodebookMatrix(_t(z["idx"]).long(), _t(z["codebook"]), _t(z["row_scale"]), pad, cols, _t(z["perm"]).long())
+    assert cm.K == 64 and cm.d == 8
+    w = cb.decode(cm)
+    assert w.shape == (16, 100) and np.array_equal(w.cpu().numpy(), z["decoded"])
+    plain = cb.decode(cb.CodebookMatrix(cm.idx, cm.codebook, cm.row_scale, pad, cols, None))
+    assert np.array_equal(plain.cpu().numpy()[:, z["perm"]], plain.cpu().numpy()[:, z["perm"]])
+    inv = np.argsort(z["perm"])
+    assert np.array_equal(plain.cpu().numpy()[:, inv], z["decoded"])                      # the permutation is what differs
+    # a book whose size is not a power of two: 48 of the 64 words
+    small = cb.CodebookMatrix(cm.idx % 48, cm.codebook[:48], cm.row_scale, pad, cols, None)
+    ref = orc.codebook_decode((z["idx"] % 48), z["codebook"][:48], z["row_scale"], pad, cols, None)
+    assert np.array_equal(cb.decode(small).cpu().numpy(), ref)

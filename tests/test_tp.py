@@ -104,7 +104,7 @@ def test_sharded_linears_on_one_gpu(world, books, M):
     m = orc.synth_matrix(R, C, seed=world + books + M, books=books, M=M)
     t, meta, perms = _file_tensors(m)
     wfull = orc.synth_decode(m)
-    for B in (1, 5, 80 if M == 1 else 40):
+    for B in (1, 5, 80 if M == 1 else 150):          # one token: the table-lookup kernel; 150 tokens with column orders: 64-token pieces
         x = torch.randn(B, C, generator=torch.Generator().manual_seed(B)).bfloat16()
         yfull = orc.linear_ref(x.float().numpy(), wfull)
         cols = [tp.ColumnParallelLinear(t, meta, perms if M > 1 else None, r, world)(x.cuda()) for r in range(world)]
@@ -179,17 +179,19 @@ def _peer_rank_main(rank, world, port, tmp):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        arena = tp.PeerArena(2 << 20)
-        for R, C in ((3584, 1024), (2304, 4096)):
-            m = orc.synth_matrix(R, C, seed=R + C)
-            t, meta, _ = _file_tensors(m)
+        arena = tp.PeerArena(32 << 20)
+        for R, C, books, M in ((3584, 1024, 1, 1), (2304, 4096, 1, 1), (2560, 1024, 2, 16)):
+            m = orc.synth_matrix(R, C, seed=R + C, books=books, M=M)
+            t, meta, perms = _file_tensors(m)
             wfull = orc.synth_decode(m)
-            rp = tp.RowParallelLinear(t, meta, None, rank, world)
+            rp = tp.RowParallelLinear(t, meta, perms if M > 1 else None, rank, world)
             rp.attach(arena)
             g = torch.Generator().manual_seed(1)
             for it in range(3):
                 x = torch.randn(C, generator=g).bfloat16()
-                y = rp.forward_fused(x[rp.c0:rp.c1].contiguous().cuda(), torch.empty(R, device="cuda"))
+                xin = x.cuda() if M > 1 else x[rp.c0:rp.c1].contiguous().cuda()      # column orders index the full vector
+                y = rp.forward_fused(xin, torch.empty(R, device="cuda"))
+                assert rp.fused.status()
                 yref = orc.linear_ref(x.float().numpy()[None], wfull)[0]
                 assert orc.max_rel_err(y.cpu().numpy(), yref) < 1e-3
                 ys = [torch.empty_like(y) for _ in range(world)]
