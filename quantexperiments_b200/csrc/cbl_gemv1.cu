@@ -875,11 +875,12 @@ __device__ __forceinline__ void l8_take(const L8Launch& P, const L8Plan& plan, i
     for (int u = 0; u < N; u++) v[u] = 0.f;
     int b = 0;
     int4 d = plan.r[0];
-    for (; b < plan.nblocks; b++) {                     // the leading block of the row part that holds r0
+    while (b < plan.nblocks) {                          // the leading block of the row part that holds r0: step from part to part
         d = plan.r[b];
-        if ((d.x & 3) == mi && (int)((uint32_t)d.x >> 24) == b && r0 >= d.y && r0 < d.y + d.z) break;
+        if ((d.x & 3) == mi && r0 >= d.y && r0 < d.y + d.z) break;
+        b += max(1, (d.x >> 16) & 255);
     }
-    if (b == plan.nblocks) return;
+    if (b >= plan.nblocks) return;
     const int splits = (d.x >> 16) & 255;
     unsigned long long* p = P.partial + (size_t)b * L8_SLOT_ROWS + (r0 - d.y);
     // eight splits' words are requested at once (the loads do not wait for each other), added in split order, cleared

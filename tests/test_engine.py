@@ -291,7 +291,7 @@ def test_fused_epilogues_equal_the_product_followed_by_the_operator(dtype, books
             hi, ho = h0[0].clone(), torch.zeros(R, device="cuda")
             yk, ok = torch.zeros(R, device="cuda", dtype=dtype), torch.zeros(R, device="cuda", dtype=dtype)
             RunsLin(down).run(xd, yk, epi={"mode": 1, "h_in": hi, "h_out": ho, "w": w, "eps": 1e-6, "out": ok, "src": yk})
-            assert torch.equal(yk, y) and torch.equal(hi, h0[0]) and torch.equal(ho, h) and torch.equal(ok, xo)
+            assert torch.equal(yk, y) and torch.equal(hi, h0[0]) and torch.equal(ho, h.reshape(-1)) and torch.equal(ok, xo)
     assert L.lib.cbl_gemv_l8_add_norm_max_rows() == 8192
     # q | k | v -> bias, rotary, cache write
     NH, NKV, HD, max_len, Cq = 6, 2, 128, 24, 264
