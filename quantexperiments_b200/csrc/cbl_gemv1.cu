@@ -137,8 +137,7 @@ __device__ __forceinline__ int l8_scale_exp(float mx) {
 struct L8Launch {
     int n;                             // matrices in the group
     int ydtype;
-    int mode;                          // 0: y = round(row_scale * sum); 1: fsum[source row] = sum (another kernel follows);
-                                       // 2: partial sums left in the slots, the epilogue kernel that follows adds them up (M = 1)
+    int mode;                          // 0: y = round(row_scale * sum); 1: fsum[source row] = sum (another kernel follows)
     cbl_l8 m[L8_MAX_GROUP];
     unsigned long long* partial;       // L8_MAX_BLOCKS slots of L8_SLOT_ROWS words {valid << 32 | fp32 partial sum} (zero on entry, left zero)
     float* fsum[L8_MAX_GROUP];         // mode 1: fp32 sums by source row
@@ -163,19 +162,16 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
                                                            const void* __restrict__ x, int xdtype) {
     extern __shared__ __align__(128) unsigned char l8_smem[];
     __shared__ __align__(8) unsigned long long s_bar[2 * L8_MAX_STAGES];   // full[stage] (tags landed), empty[stage] (every warp has read them)
-    __shared__ float s_red[L8_NWARP];
     __shared__ int s_abort;
-    __shared__ unsigned int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     if ((int)blockIdx.x >= plan.nblocks) return;
     const int4 d = plan.r[blockIdx.x];
-    const int mi = d.x & 3, order = (d.x >> 2) & 15, part = (d.x >> 8) & 255, splits = (d.x >> 16) & 255, first = (int)((uint32_t)d.x >> 24);
+    const int mi = d.x & 3, order = (d.x >> 2) & 15, splits = (d.x >> 16) & 255, first = (int)((uint32_t)d.x >> 24);
     const int row_lo = d.y, nrows = d.z, tile_lo = d.w & 0xFFFF, tile_hi = (int)((uint32_t)d.w >> 16);
     const cbl_l8& mm = P.m[mi];
-    // Programmatic dependent launch: the next kernel of the stream may become resident now; this kernel itself
-    // waits for its predecessor only where it first touches data that depends on it (x, accumulators, y).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Programmatic dependent launch: this kernel waits for its predecessor only where it first touches data that
+    // depends on it (x, the work space, y), and lets its successor in when its own lookups are done (below).
 
     // ---- shared memory: two 64 KB tables on a 64 KB boundary; below and above them the fp32 row sums of the
     // block (16 KB) and the ring stages
@@ -385,6 +381,10 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
             l8_sync_consumers();                        // next table complete; every reader of this one is done
         }
     }
+    // The next kernel of the stream may become resident from here on.  (Not earlier: a block of this kernel fills its
+    // SM, so an early successor would be packed onto the few SMs this launch leaves free instead of spreading
+    // over the SMs as they empty.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // the row sums go to shared memory, indexed by row of the block, for the output phase
 #pragma unroll
     for (int kk = 0; kk < 2; kk++)
@@ -410,16 +410,6 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
         else fsum[r] = v;
     };
     const int n512 = (nrows + L8_NT - 1) / L8_NT;
-    if (P.mode == 2) {
-        // the epilogue kernel behind this one sums the blocks' partial sums (l8_take): leave them in the slot and go
-        unsigned long long* slot = P.partial + (size_t)blockIdx.x * L8_SLOT_ROWS;
-        for (int j = 0; j < n512; j++) {
-            const int q = j * L8_NT + tid;
-            if (q < nrows && row_lo + q < mm.R)         // (padding rows would never be consumed, hence never cleared)
-                __stcg(slot + q, (1ull << 32) | (unsigned long long)l8_lds32(sacc + (uint32_t)q * 4u));
-        }
-        return;
-    }
     if (splits <= 1) {
         for (int j = 0; j < n512; j++) {
             const int q = j * L8_NT + tid;
@@ -775,12 +765,6 @@ static int launch_l8(L8Launch& P, const void* x, int xdtype, cudaStream_t st, in
     }
     if (plan_out) *plan_out = plan;
     if (plan.nblocks == 0) return CBL_OK;
-    if (P.mode == 2) {
-        // an epilogue thread adds a row's partial sums one after the other: worth it for a dozen splits, not for a
-        // hundred - there the product kernel's own distributed sum is the faster way (mode 1)
-        for (int b = 0; b < plan.nblocks; b++)
-            if (((plan.r[b].x >> 16) & 255) > 16) P.mode = 1;
-    }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -867,57 +851,6 @@ extern "C" int cbl_gemv_l8_status(void* workspace, int32_t R, cbl_stream s) {
 //   o / down -> residual add + RMSNorm               (cbl_add_rmsnorm): the kernel's blocks form one
 //               cluster and exchange their sums of squares through distributed shared memory
 //   q|k|v    -> bias, rotary embedding, cache write  (cbl_rope_kv, decode form, sequence 0)
-// Sum of the blocks' partial sums of n consecutive rows (n = 1 or 4, starting at a multiple of n; one column order,
-// so row position = row) of matrix mi left by a mode-2 product, added in split order; the words are cleared.
-template <int N>
-__device__ __forceinline__ void l8_take(const L8Launch& P, const L8Plan& plan, int mi, int r0, float (&v)[N]) {
-#pragma unroll
-    for (int u = 0; u < N; u++) v[u] = 0.f;
-    int b = 0;
-    int4 d = plan.r[0];
-    while (b < plan.nblocks) {                          // the leading block of the row part that holds r0: step from part to part
-        d = plan.r[b];
-        if ((d.x & 3) == mi && r0 >= d.y && r0 < d.y + d.z) break;
-        b += max(1, (d.x >> 16) & 255);
-    }
-    if (b >= plan.nblocks) return;
-    const int splits = (d.x >> 16) & 255;
-    unsigned long long* p = P.partial + (size_t)b * L8_SLOT_ROWS + (r0 - d.y);
-    // eight splits' words are requested at once (the loads do not wait for each other), added in split order, cleared
-    for (int j0 = 0; j0 < splits; j0 += 8) {
-        if constexpr (N == 4) {
-            ulonglong2 a[8], c[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++)
-                if (j0 + u < splits) {
-                    a[u] = __ldcg((const ulonglong2*)(p + (size_t)(j0 + u) * L8_SLOT_ROWS));
-                    c[u] = __ldcg((const ulonglong2*)(p + (size_t)(j0 + u) * L8_SLOT_ROWS) + 1);
-                }
-#pragma unroll
-            for (int u = 0; u < 8; u++)
-                if (j0 + u < splits) {
-                    v[0] += __uint_as_float((uint32_t)a[u].x);
-                    v[1] += __uint_as_float((uint32_t)a[u].y);
-                    v[2] += __uint_as_float((uint32_t)c[u].x);
-                    v[3] += __uint_as_float((uint32_t)c[u].y);
-                    __stcg((ulonglong2*)(p + (size_t)(j0 + u) * L8_SLOT_ROWS), make_ulonglong2(0ull, 0ull));
-                    __stcg((ulonglong2*)(p + (size_t)(j0 + u) * L8_SLOT_ROWS) + 1, make_ulonglong2(0ull, 0ull));
-                }
-        } else {
-            unsigned long long a[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++)
-                if (j0 + u < splits) a[u] = __ldcg(p + (size_t)(j0 + u) * L8_SLOT_ROWS);
-#pragma unroll
-            for (int u = 0; u < 8; u++)
-                if (j0 + u < splits) {
-                    v[0] += __uint_as_float((uint32_t)a[u]);
-                    __stcg(p + (size_t)(j0 + u) * L8_SLOT_ROWS, 0ull);
-                }
-        }
-    }
-}
-
 template <typename T> __device__ __forceinline__ float l8_f(T v);
 template <> __device__ __forceinline__ float l8_f<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float l8_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -928,21 +861,14 @@ __device__ __forceinline__ void l8_pdl_enter() {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) k_l8_finish_silu(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan, T* __restrict__ out) {
+__global__ void __launch_bounds__(256) k_l8_finish_silu(const __grid_constant__ L8Launch P, T* __restrict__ out) {
     l8_pdl_enter();
     const cbl_l8& mg = P.m[0];
     const cbl_l8& mu = P.m[1];
     const int gi = blockIdx.x * blockDim.x + threadIdx.x;
     if (gi * 4 >= mg.R) return;
-    float gv[4], uv[4];
-    if (P.mode == 2) {
-        l8_take<4>(P, plan, 0, gi * 4, gv);
-        l8_take<4>(P, plan, 1, gi * 4, uv);
-    } else {
-        const float4 g = __ldcg((const float4*)P.fsum[0] + gi), u = __ldcg((const float4*)P.fsum[1] + gi);
-        gv[0] = g.x; gv[1] = g.y; gv[2] = g.z; gv[3] = g.w;
-        uv[0] = u.x; uv[1] = u.y; uv[2] = u.z; uv[3] = u.w;
-    }
+    const float4 g = __ldcg((const float4*)P.fsum[0] + gi), u = __ldcg((const float4*)P.fsum[1] + gi);
+    const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         const int r = gi * 4 + k;
@@ -960,7 +886,7 @@ __global__ void __launch_bounds__(256) k_l8_finish_silu(const __grid_constant__ 
 
 constexpr int L8_NORM_MAX_CTAS = 8;          // portable cluster size: up to 8 x 1024 rows
 template <typename T>
-__global__ void __launch_bounds__(256) k_l8_finish_addnorm(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan,
+__global__ void __launch_bounds__(256) k_l8_finish_addnorm(const __grid_constant__ L8Launch P,
                                                            float* __restrict__ h, const T* __restrict__ w, float eps, T* __restrict__ xout) {
     l8_pdl_enter();
     __shared__ float s_warp[8];
@@ -970,12 +896,8 @@ __global__ void __launch_bounds__(256) k_l8_finish_addnorm(const __grid_constant
     float hv[4] = {0.f, 0.f, 0.f, 0.f};
     float ss = 0.f;
     if (gi * 4 < mm.R) {
-        float vv[4];
-        if (P.mode == 2) l8_take<4>(P, plan, 0, gi * 4, vv);
-        else {
-            const float4 v = __ldcg((const float4*)P.fsum[0] + gi);
-            vv[0] = v.x; vv[1] = v.y; vv[2] = v.z; vv[3] = v.w;
-        }
+        const float4 v = __ldcg((const float4*)P.fsum[0] + gi);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const int r = gi * 4 + k;
@@ -1021,7 +943,7 @@ __global__ void __launch_bounds__(256) k_l8_finish_addnorm(const __grid_constant
 }
 
 template <typename T>
-__global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan, const T* __restrict__ bias,
+__global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L8Launch P, const T* __restrict__ bias,
                                                        const int32_t* __restrict__ pos, int NH, int NKV, int HD, float theta, int max_len,
                                                        T* __restrict__ qo, T* __restrict__ kc, T* __restrict__ vc) {
     l8_pdl_enter();
@@ -1034,10 +956,7 @@ __global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L
     const float c = l8_f(cbl_cvt_out<T>(cosf(ang))), sn = l8_f(cbl_cvt_out<T>(sinf(ang)));
     // one output element of matrix mi: take the sum, scale, round, add the bias in the 16-bit type
     auto take = [&](int mi, int r, int bcol) {
-        float v1[1];
-        if (P.mode == 2) l8_take<1>(P, plan, mi, r, v1);
-        else v1[0] = __ldcg(P.fsum[mi] + r);
-        const float y = l8_f(cbl_cvt_out<T>(v1[0] * __half2float(((const __half*)P.m[mi].row_scale)[r])));
+        const float y = l8_f(cbl_cvt_out<T>(__ldcg(P.fsum[mi] + r) * __half2float(((const __half*)P.m[mi].row_scale)[r])));
         return bias ? l8_f(cbl_cvt_out<T>(y + l8_f(bias[bcol]))) : y;
     };
     const bool isq = hd < NH;
@@ -1058,14 +977,6 @@ __global__ void __launch_bounds__(64) k_l8_finish_rope(const __grid_constant__ L
             vc[vo + (int64_t)(i + half) * max_len] = cbl_cvt_out<T>(v2);
         }
     }
-}
-
-// Epilogue kernels add the blocks' partial sums up themselves when every matrix has one column order (row position =
-// row); otherwise the product finishes its sums into the fp32 buffer first.
-static int l8_epilogue_mode(const cbl_l8* mats, int n) {
-    for (int i = 0; mats && i < n; i++)
-        if (mats[i].M != 1 || mats[i].row_index) return 1;
-    return 2;
 }
 
 template <typename... KA, typename... A>
@@ -1091,19 +1002,18 @@ extern "C" int cbl_gemv_l8_silu_mul(const cbl_l8* gate_up, const void* x, int xd
                                     void* workspace, cbl_stream s) {
     if (!out || (dtype != CBL_F16 && dtype != CBL_BF16)) return CBL_EINVAL;
     L8Launch P;
-    int rc = l8_group(gate_up, 2, x, xdtype, nullptr, dtype, l8_epilogue_mode(gate_up, 2), workspace, P);
+    int rc = l8_group(gate_up, 2, x, xdtype, nullptr, dtype, 1, workspace, P);
     P.y[0] = y_gate;
     P.y[1] = y_up;
     if (rc) return rc;
     if (gate_up[0].R != gate_up[1].R) return CBL_EINVAL;
     if (P.n == 0) return CBL_OK;
     const cudaStream_t st = (cudaStream_t)s;
-    L8Plan plan;
-    rc = launch_l8(P, x, xdtype, st, L8_MAX_BLOCKS, &plan);
+    rc = launch_l8(P, x, xdtype, st);
     if (rc) return rc;
     const dim3 grid(cbl_ceil_div(cbl_ceil_div(P.m[0].R, 4), 256));
-    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_silu<__half>, grid, dim3(256), 1, st, P, plan, (__half*)out);
-    return l8_finish_launch(k_l8_finish_silu<__nv_bfloat16>, grid, dim3(256), 1, st, P, plan, (__nv_bfloat16*)out);
+    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_silu<__half>, grid, dim3(256), 1, st, P, (__half*)out);
+    return l8_finish_launch(k_l8_finish_silu<__nv_bfloat16>, grid, dim3(256), 1, st, P, (__nv_bfloat16*)out);
 }
 
 extern "C" int32_t cbl_gemv_l8_add_norm_max_rows(void) { return L8_NORM_MAX_CTAS * 1024; }
@@ -1112,18 +1022,17 @@ extern "C" int cbl_gemv_l8_add_norm(const cbl_l8* m, const void* x, int xdtype, 
                                     int dtype, void* workspace, cbl_stream s) {
     if (!h || !w || !xout || (dtype != CBL_F16 && dtype != CBL_BF16)) return CBL_EINVAL;
     L8Launch P;
-    int rc = l8_group(m, 1, x, xdtype, nullptr, dtype, l8_epilogue_mode(m, 1), workspace, P);
+    int rc = l8_group(m, 1, x, xdtype, nullptr, dtype, 1, workspace, P);
     P.y[0] = y;
     if (rc) return rc;
     if (m->R < 1) return CBL_EINVAL;
     if (m->R > L8_NORM_MAX_CTAS * 1024) return CBL_EUNSUPPORTED;
     const cudaStream_t st = (cudaStream_t)s;
-    L8Plan plan;
-    rc = launch_l8(P, x, xdtype, st, L8_MAX_BLOCKS, &plan);
+    rc = launch_l8(P, x, xdtype, st);
     if (rc) return rc;
     const int nb = cbl_ceil_div(cbl_ceil_div(P.m[0].R, 4), 256);
-    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_addnorm<__half>, dim3(nb), dim3(256), nb, st, P, plan, h, (const __half*)w, eps, (__half*)xout);
-    return l8_finish_launch(k_l8_finish_addnorm<__nv_bfloat16>, dim3(nb), dim3(256), nb, st, P, plan, h, (const __nv_bfloat16*)w, eps,
+    if (dtype == CBL_F16) return l8_finish_launch(k_l8_finish_addnorm<__half>, dim3(nb), dim3(256), nb, st, P, h, (const __half*)w, eps, (__half*)xout);
+    return l8_finish_launch(k_l8_finish_addnorm<__nv_bfloat16>, dim3(nb), dim3(256), nb, st, P, h, (const __nv_bfloat16*)w, eps,
                             (__nv_bfloat16*)xout);
 }
 
@@ -1133,18 +1042,17 @@ extern "C" int cbl_gemv_l8_rope_kv(const cbl_l8* qkv, const void* x, int xdtype,
     if (!pos || !q_out || !kc || !vc || (dtype != CBL_F16 && dtype != CBL_BF16) || NH < 1 || NKV < 1 || max_len < 1) return CBL_EINVAL;
     if (HD < 2 || HD > 128 || (HD & 1)) return CBL_EUNSUPPORTED;
     L8Launch P;
-    int rc = l8_group(qkv, 3, x, xdtype, nullptr, dtype, l8_epilogue_mode(qkv, 3), workspace, P);
+    int rc = l8_group(qkv, 3, x, xdtype, nullptr, dtype, 1, workspace, P);
     if (rc) return rc;
     if (qkv[0].R != NH * HD || qkv[1].R != NKV * HD || qkv[2].R != NKV * HD) return CBL_EINVAL;
     const cudaStream_t st = (cudaStream_t)s;
-    L8Plan plan;
-    rc = launch_l8(P, x, xdtype, st, L8_MAX_BLOCKS, &plan);
+    rc = launch_l8(P, x, xdtype, st);
     if (rc) return rc;
     const dim3 grid(NH + NKV);
     if (dtype == CBL_F16)
-        return l8_finish_launch(k_l8_finish_rope<__half>, grid, dim3(64), 1, st, P, plan, (const __half*)bias, pos, (int)NH, (int)NKV, (int)HD, theta,
+        return l8_finish_launch(k_l8_finish_rope<__half>, grid, dim3(64), 1, st, P, (const __half*)bias, pos, (int)NH, (int)NKV, (int)HD, theta,
                                 (int)max_len, (__half*)q_out, (__half*)kc, (__half*)vc);
-    return l8_finish_launch(k_l8_finish_rope<__nv_bfloat16>, grid, dim3(64), 1, st, P, plan, (const __nv_bfloat16*)bias, pos, (int)NH, (int)NKV, (int)HD,
+    return l8_finish_launch(k_l8_finish_rope<__nv_bfloat16>, grid, dim3(64), 1, st, P, (const __nv_bfloat16*)bias, pos, (int)NH, (int)NKV, (int)HD,
                             theta, (int)max_len, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc);
 }
 
