@@ -1098,10 +1098,8 @@ __global__ void __launch_bounds__(256) k_l8_finish_allreduce(const __grid_consta
     __syncthreads();
     if (tid < A.world) {
         // publish (one block does it), then wait for every peer's word of this call
-        if (blockIdx.x == 0) {
-            __threadfence_system();
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(A.flags[tid] + A.rank), "r"(epoch) : "memory");
-        }
+        // (the sums were written by the kernel before this one; the release store orders them before the word)
+        if (blockIdx.x == 0) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(A.flags[tid] + A.rank), "r"(epoch) : "memory");
         const uint32_t* f = A.flags[A.rank] + tid;
         bool seen = false;
         for (uint32_t i = 0; i < L8_AR_SPIN_LIMIT && !seen; i++) {
@@ -1117,11 +1115,16 @@ __global__ void __launch_bounds__(256) k_l8_finish_allreduce(const __grid_consta
         if (tid == 0) atomicExch(A.ctl, 1u);
     } else if (gi * 4 < A.R) {
         const int64_t cur = (int64_t)(epoch & 1u) * A.stride;
+        // all ranks' values are requested before the first one is used (one NVLink round trip, not one per rank),
+        // then added in rank order
+        float4 v[L8_AR_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < L8_AR_MAX_RANKS; r++)
+            if (r < A.world) v[r] = __ldcg((const float4*)(A.sums[r] + cur) + gi);
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < A.world; r++) {
-            const float4 v = __ldcg((const float4*)(A.sums[r] + cur) + gi);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
+#pragma unroll
+        for (int r = 0; r < L8_AR_MAX_RANKS; r++)
+            if (r < A.world) { sum.x += v[r].x; sum.y += v[r].y; sum.z += v[r].z; sum.w += v[r].w; }
         const float vv[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
         for (int u = 0; u < 4; u++) {
