@@ -388,10 +388,11 @@ int32_t cbl_head_gemv_max_batch(void);
 int cbl_head_gemv(const void* W, const void* x, int dtype, int32_t B, int32_t V, int32_t H, void* logits, int ldtype, int64_t ldl,
                   cbl_stream s);
 
-/* Batch-1 products whose finish kernel also runs the step operator that follows them (one launch less,
- * no round trip of the vector through memory).  Results equal the product followed by the separate
- * operator: the product is rounded to `dtype` first.  `workspace` as for cbl_gemv_l8_multi (the
- * matrices' padded rows x 4 bytes in order, plus 16 bytes; zero before the first call, left zero).
+/* Batch-1 products followed by the step operator that consumes them, applied by one small kernel to the product's
+ * finished fp32 sums (one launch less than product + operator on a stored vector, no round trip of the rounded vector
+ * through memory).  Results equal the product followed by the separate
+ * operator: the product is rounded to `dtype` first.  `workspace` as for cbl_gemv_l8_multi (the sum of
+ * cbl_gemv_l8_workspace_bytes(R_i) bytes; zero before the first call, left zero).
  *   cbl_gemv_l8_silu_mul: gate_up[0..1] (equal row counts) -> out[i] = silu(gate.x)[i] * (up.x)[i]; y_gate / y_up
  *                         (NULL or [R] in `dtype`) also receive the two products, as the reference's launch leaves them
  *   cbl_gemv_l8_add_norm: h += W.x; xout = RMSNorm(h) * w   (R <= cbl_gemv_l8_add_norm_max_rows()); y (NULL or [R])

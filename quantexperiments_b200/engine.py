@@ -227,7 +227,7 @@ class DecodeEngine:
                        for L in layers]
         self.graph = None
         self.only_linears = False
-        # one token, one column order everywhere: the operators that follow a product run in its finish kernel
+        # one token, one column order everywhere: the operator that follows a product runs on its fp32 sums (one small kernel)
         self.fused = B == 1 and all(st.group is not None for S in self.stages for st in S.values()) and H <= lib.cbl_gemv_l8_add_norm_max_rows()
 
     # -- operators (thin wrappers over the C ABI; all on the current stream)
@@ -303,7 +303,7 @@ class DecodeEngine:
             o += l.R
 
     def _step_fused(self, s: int) -> None:
-        """Batch-1 layers with the step operators inside the products' finish kernels: q|k|v + rotary + cache
+        """Batch-1 layers, each product followed by its step operator on the fp32 sums: q|k|v + rotary + cache
         write, attention, o + add + norm, gate|up + silu * up, down + add + norm (of the next layer)."""
         from .kernels import l8_workspace
         c, dtc = self.cfg, _dt(self.dtype)
