@@ -335,6 +335,13 @@ int cbl_gemv_x16(const cbl_x16* m, const void* xp, int32_t B, void* y, int ydtyp
  *          multi-token branch of shapequant/kernels/gemv.py:164-170 (dense() + F.linear). */
 size_t cbl_dense_scratch_bytes(int32_t R, int32_t C);
 int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s);
+/* The same for a column shard (tensor parallelism) of a matrix with several column orders: the shard's orders name
+ * positions of the FULL activation vector, so a row of `out` is C_out >= m->C wide (ld = C_out rounded up to 8,
+ * cbl_dense_scratch_bytes(R, C_out) bytes) and the shard's weights land at out[r, perms[row_mask[r]][c]]; every other
+ * element must be ZERO on entry (the call writes only the shard's positions; every index in perms must be below
+ * C_out).  The product is then cbl_gemm_dense over C_out columns against the full activations.
+ * no counterpart in the reference (which refuses tensor parallelism, shapequant/vllm_ext/plugin.py:198-199). */
+int cbl_decode_raw_wide(const cbl_packed* m, void* out, int32_t C_out, cbl_stream s);
 int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void* row_scale, const void* x, int xdtype, int32_t ntok, int64_t ldx,
                    void* y, int ydtype, int64_t ldy, void* stage, void* workspace, cbl_stream s);
 

@@ -103,6 +103,7 @@ SIGNATURES = {
                                     c_void_p, c_void_p]),
     "cbl_dense_scratch_bytes": (c_size_t, [c_int32, c_int32]),
     "cbl_decode_raw": (c_int, [POINTER(Packed), c_void_p, c_void_p]),
+    "cbl_decode_raw_wide": (c_int, [POINTER(Packed), c_void_p, c_int32, c_void_p]),
     "cbl_gemm_dense": (c_int, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p,
                                c_void_p, c_void_p]),
     "cbl_embed_rows": (c_int, [c_void_p, c_int, c_int64, c_int32, c_void_p, c_int32, c_void_p, c_void_p]),

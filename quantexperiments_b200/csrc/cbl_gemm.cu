@@ -1319,15 +1319,16 @@ extern "C" size_t cbl_dense_scratch_bytes(int32_t R, int32_t C) {
     return (size_t)R * ((size_t)(C + 7) / 8 * 8) * 2;
 }
 
-extern "C" int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s) {
+static int decode_raw_impl(const cbl_packed* m, void* out, int32_t C_out, cbl_stream s) {
     if (!m || !m->tags || !m->table || !out || ((uintptr_t)out % 16) || ((uintptr_t)m->table % 16)) return CBL_EINVAL;
+    if (C_out < m->C || (C_out > m->C && m->M <= 1)) return CBL_EINVAL;      // a wider output only makes sense with column orders
     if (m->d != 8 || m->bits != 12 || m->G != 1) return CBL_EUNSUPPORTED;
     if (m->R < 0 || m->C <= 0 || m->C % 8 || (int64_t)m->W * 32 < (int64_t)(m->C / 8) * 12) return CBL_EINVAL;
     if (m->books != 1 && m->books != 2) return CBL_EINVAL;
     if (m->books == 2 && (!m->tags2 || !m->table2 || ((uintptr_t)m->table2 % 16))) return CBL_EINVAL;
     if (m->M > 1 && (!m->row_mask || !m->perms)) return CBL_EINVAL;
     if (m->R == 0) return CBL_OK;
-    const int64_t ld = (m->C + 7) / 8 * 8;
+    const int64_t ld = ((int64_t)C_out + 7) / 8 * 8;
     const size_t smem = (size_t)65536 * m->books;
     int grid = cbl_sm_count();
     if (grid > cbl_ceil_div(m->R, DR_THREADS / 32)) grid = cbl_ceil_div(m->R, DR_THREADS / 32);
@@ -1360,6 +1361,12 @@ extern "C" int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s) {
 #undef CBL_RAW
     return cbl_check_launch();
 }
+
+extern "C" int cbl_decode_raw(const cbl_packed* m, void* out, cbl_stream s) { return decode_raw_impl(m, out, m ? m->C : 0, s); }
+
+// The same for a column shard of a matrix with several column orders, whose orders name positions of the FULL
+// activation vector (C_out of them): the scratch row is C_out wide and the shard's weights land at their positions.
+extern "C" int cbl_decode_raw_wide(const cbl_packed* m, void* out, int32_t C_out, cbl_stream s) { return decode_raw_impl(m, out, C_out, s); }
 
 extern "C" int cbl_gemm_dense(const void* w16, int32_t R, int32_t C, const void* row_scale, const void* x, int xdtype, int32_t ntok,
                               int64_t ldx, void* y, int ydtype, int64_t ldy, void* stage, void* workspace, cbl_stream s) {

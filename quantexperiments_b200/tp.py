@@ -216,14 +216,41 @@ class RowParallelLinear:
             self.lin.forward_into(x.reshape(n, self.c1 - self.c0), y)
         elif n == 1 and self.l8_multi is not None:
             self.l8_multi.run(x.reshape(-1).contiguous(), y[0], wide=True)      # one token: the table-lookup kernel
+        elif n <= T16Matrix_BMAX():
+            self.t16.run(x.reshape(n, self.C_full).contiguous(), y, n, wide=True)   # the row-tile kernel: up to 64 tokens
         else:
-            # the row-tile kernel takes up to 64 tokens per launch; longer inputs (prefill) run as 64-token pieces
-            xs = x.reshape(n, self.C_full).contiguous()
-            step = T16Matrix_BMAX()
-            for t0 in range(0, n, step):
-                nt = min(step, n - t0)
-                self.t16.run(xs[t0:t0 + nt], y[t0:t0 + nt], nt, wide=True)
+            self._dense_wide(x.reshape(n, self.C_full), y)                          # prefill: decode once, tensor-core GEMM
         return y.reshape(*lead, self.R)
+
+    def _dense_wide(self, X: torch.Tensor, Y: torch.Tensor) -> None:
+        """Many tokens against a column shard with column orders: the shard is decoded once into a zeroed 16-bit
+        scratch as wide as the full activation vector (its orders name positions of that vector), then one TMA-fed
+        tensor-core GEMM over all C columns.  Every rank multiplies the full width (its rows are 1 / world dense), so
+        this path buys correctness and tensor-core speed for long inputs, not a per-rank saving."""
+        import ctypes
+        from . import _lib
+        from .kernels import DenseStack, _dt, _stream
+        lib = _lib.lib
+        dev, T = self.dm.device, X.shape[0]
+        key = (dev.index, _stream(), "wide")
+        need = lib.cbl_dense_scratch_bytes(self.R, self.C_full)
+        pair = DenseStack._scratch.setdefault(key, [None, None, 0])     # two scratches alternate, as in DenseStack
+        pair[2] ^= 1
+        sc = pair[pair[2]]
+        if sc is None or sc.numel() < need:
+            sc = pair[pair[2]] = torch.empty(need, dtype=torch.uint8, device=dev)
+        need = lib.cbl_gemm_stage_bytes(T, self.C_full) + 16
+        st = DenseStack._stage.get(key)
+        if st is None or st.numel() < need:
+            st = DenseStack._stage[key] = torch.zeros(need, dtype=torch.uint8, device=dev)
+        X = X if X.stride(1) == 1 else X.contiguous()
+        with torch.cuda.device(dev):
+            sc[:lib.cbl_dense_scratch_bytes(self.R, self.C_full)].zero_()
+            s = _stream()
+            _lib.check("cbl_decode_raw_wide", lib.cbl_decode_raw_wide(ctypes.byref(self.dm.struct()), sc.data_ptr(), self.C_full, s))
+            _lib.check("cbl_gemm_dense", lib.cbl_gemm_dense(sc.data_ptr(), self.R, self.C_full, self.dm.row_scale.data_ptr(), X.data_ptr(), _dt(X.dtype),
+                                                            T, X.stride(0), Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
+                                                            st.data_ptr() + st.numel() - 16, s))
 
     @property
     def l8_multi(self):
