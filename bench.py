@@ -299,9 +299,10 @@ def build_set(dev, rank: int, world: int, batch: int, model: str = "7b", layers:
                     t, meta, perms = tp.shard_cols(t, meta, c0, c1, perms)
             t = {k: v.to(dev) for k, v in t.items()}
             p = perms.to(dev) if perms is not None else torch.arange(meta["C"], device=dev)[None]
+            wide = world > 1 and kind == "row" and m["M"] > 1         # the shard's column orders name positions of the full vector
             lin = PackedLinear(t["tags"], t["table"], t["row_scale"], None, t.get("row_mask"), p, 4096, 8,
-                               words2=t.get("tags2"), table2=t.get("table2"))
-            lin.kind, lin.wide = kind, (world > 1 and kind == "row" and m["M"] > 1)
+                               words2=t.get("tags2"), table2=t.get("table2"), x_cols=C if wide else None)
+            lin.kind = kind
             if batch == 1 and (lin.dm.M == 1 or lin.use_l8()):
                 lin.l8
             else:

@@ -42,7 +42,7 @@ class DeviceMatrix:
     optional second tag plane + table for two summed books)."""
 
     def __init__(self, tags, table, row_scale, row_book=None, row_mask=None, perms=None, *, K: int, d: int,
-                 C: int | None = None, device="cuda", tags2=None, table2=None):
+                 C: int | None = None, device="cuda", tags2=None, table2=None, x_cols: int | None = None):
         dev = torch.device(device)
         if dev.type != "cuda":
             raise ValueError("DeviceMatrix lives on a CUDA device; there is no CPU path")
@@ -74,6 +74,11 @@ class DeviceMatrix:
         self.table2 = None if table2 is None else table2.to(dev, torch.float16).contiguous()
         if self.books == 2 and (self.table2 is None or self.tags2.shape != self.tags.shape or self.G != 1):
             raise ValueError("two summed books need tags2 and table2 of matching shape and G = 1")
+        # A column shard (tensor parallelism) of a matrix with several column orders keeps orders that name positions
+        # of the FULL activation vector: x_cols is that vector's length (None: the activations are C long).
+        self.x_cols = None if x_cols is None or int(x_cols) == self.C else int(x_cols)
+        if self.x_cols is not None and (self.M == 1 or self.x_cols < self.C):
+            raise ValueError("x_cols (wider activations than columns) needs several column orders and x_cols >= C")
 
     @classmethod
     def tags_only(cls, words: torch.Tensor, bits: int, n: int) -> "DeviceMatrix":
@@ -97,6 +102,9 @@ class DeviceMatrix:
                 rows: tuple[int, int] | None = None) -> torch.Tensor:
         """Dense [r1 - r0, C] decode, bit-exact with the reference decode (fp32) or one rounding of
         it (fp16 / bf16). `out` may be a larger flat scratch buffer (its first (r1-r0)*C elements are used)."""
+        if self.x_cols is not None:
+            raise ValueError("a column shard whose column orders index the full activation vector has no [R, C] decode "
+                             "(its weights are positions of that vector: gemm_dense decodes it x_cols wide)")
         r0, r1 = rows if rows is not None else (0, self.R)
         n = (r1 - r0) * self.C
         if out is None:
@@ -111,8 +119,41 @@ class DeviceMatrix:
         return res
 
     def gemm_dense(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
-        """Y [T, R] = X [T, C] . W^T through the two-phase path (see DenseStack)."""
-        return DenseStack([self]).gemm(X, Y)
+        """Y [T, R] = X [T, C] . W^T through the two-phase path (see DenseStack).  A shard with x_cols takes X
+        [T, x_cols]: it is decoded once into a zeroed 16-bit scratch as wide as the activation vector (its orders name
+        positions of that vector) and multiplied over all x_cols columns - every rank multiplies the full width, its rows
+        being 1 / world dense, so for such shards this path buys tensor-core speed on long inputs, not a per-rank saving."""
+        if self.x_cols is None:
+            return DenseStack([self]).gemm(X, Y)
+        _need_fast(self)
+        T, Cx = X.shape[0], self.x_cols
+        if X.dim() != 2 or X.shape[1] != Cx or X.stride(1) != 1 or X.device != self.device:
+            raise ValueError("X must be [T, x_cols] with unit column stride on the matrix's device")
+        if Y is None:
+            Y = torch.empty(T, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape != (T, self.R) or Y.stride(1) != 1:
+            raise ValueError("Y must be [T, R] with unit column stride")
+        if T == 0 or self.R == 0:
+            return Y
+        key = (self.device.index, _stream())
+        need = lib.cbl_dense_scratch_bytes(self.R, Cx)
+        pair = DenseStack._scratch.setdefault(key, [None, None, 0])     # the two alternating scratches of the device and stream
+        pair[2] ^= 1
+        sc = pair[pair[2]]
+        if sc is None or sc.numel() < need:
+            sc = pair[pair[2]] = torch.empty(need, dtype=torch.uint8, device=self.device)
+        nst = lib.cbl_gemm_stage_bytes(T, Cx) + 16
+        st = DenseStack._stage.get(key)
+        if st is None or st.numel() < nst:
+            st = DenseStack._stage[key] = torch.zeros(nst, dtype=torch.uint8, device=self.device)
+        with torch.cuda.device(self.device):
+            sc[:need].zero_()
+            s = _stream()
+            _lib.check("cbl_decode_raw_wide", lib.cbl_decode_raw_wide(ctypes.byref(self.struct()), sc.data_ptr(), Cx, s))
+            _lib.check("cbl_gemm_dense", lib.cbl_gemm_dense(sc.data_ptr(), self.R, Cx, self.row_scale.data_ptr(), X.data_ptr(), _dt(X.dtype), T,
+                                                            X.stride(0), Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
+                                                            st.data_ptr() + st.numel() - 16, s))
+        return Y
 
     def unpack(self, plane: int = 0) -> torch.Tensor:
         out = torch.empty(self.R, self.nch, dtype=torch.int32, device=self.device)

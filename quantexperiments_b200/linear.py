@@ -50,7 +50,7 @@ class PackedLinear(torch.nn.Module):
     reference (words, table, row_scale, row_book, row_mask, perms, K, d, bias)."""
 
     def __init__(self, words, table, row_scale, row_book, row_mask, perms, K: int, d: int, bias=None,
-                 words2=None, table2=None):
+                 words2=None, table2=None, x_cols: int | None = None):
         super().__init__()
         dev = words.device
         if dev.type != "cuda":
@@ -58,7 +58,11 @@ class PackedLinear(torch.nn.Module):
         C = perms.shape[1] if perms is not None else None
         has_mask = row_mask is not None and perms is not None and perms.shape[0] > 1
         self.dm = DeviceMatrix(words, table, row_scale, row_book, row_mask if has_mask else None,
-                               perms if has_mask else None, K=K, d=d, C=C, device=dev, tags2=words2, table2=table2)
+                               perms if has_mask else None, K=K, d=d, C=C, device=dev, tags2=words2, table2=table2, x_cols=x_cols)
+        # x_cols: this is a column shard (tensor parallelism) of a matrix with several column orders; its orders name
+        # positions of the full activation vector of that length, which forward() then expects
+        self.wide = self.dm.x_cols is not None
+        self.in_features = self.dm.x_cols if self.wide else self.dm.C
         self.R, self.C, self.K, self.d, self.W = self.dm.R, self.dm.C, K, d, self.dm.W
         self.bits, self.nch, self.has_mask = self.dm.bits, self.dm.nch, has_mask
         self.bias = bias
@@ -120,9 +124,9 @@ class PackedLinear(torch.nn.Module):
     def gemv(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [C] (fp16 / bf16 / fp32, contiguous) -> y [R] in x's dtype (or `out`'s)."""
         if self.use_l8():
-            return self.l8.run(x, out)
+            return self.l8.run(x, out, wide=self.wide)
         y = out if out is not None else torch.empty(self.R, dtype=x.dtype, device=x.device)
-        self.t16.run(x.reshape(1, -1), y.reshape(1, -1), 1)
+        self.t16.run(x.reshape(1, -1), y.reshape(1, -1), 1, wide=self.wide)
         return y
 
     def dense(self) -> torch.Tensor:
@@ -135,11 +139,11 @@ class PackedLinear(torch.nn.Module):
         if n == 0:
             return y
         if n == 1 and self.use_l8() and y.is_contiguous():
-            self.l8.run(x2[0].contiguous(), y[0])
+            self.l8.run(x2[0].contiguous(), y[0], wide=self.wide)
         elif X16_MIN_TOKENS <= n <= X16_MAX_TOKENS and self.dm.M == 1:
             self.x16.run(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
         elif n <= T16Matrix.BMAX and (n < ROWS_MIN_TOKENS or self.dm.M > 1):
-            self.t16.run(x2.contiguous(), y, n)
+            self.t16.run(x2.contiguous(), y, n, wide=self.wide)
         elif n <= T16Matrix.BMAX:
             self.rows_group.gemm_rows(x2 if x2.stride(1) == 1 else x2.contiguous(), [y])
         elif self.use_gemm() and n < DENSE_MIN_TOKENS:
@@ -152,7 +156,7 @@ class PackedLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         n = math.prod(lead)
-        y = self.forward_into(x.reshape(n, self.C), torch.empty(n, self.R, dtype=x.dtype, device=x.device))
+        y = self.forward_into(x.reshape(n, self.in_features), torch.empty(n, self.R, dtype=x.dtype, device=x.device))
         y = y.reshape(*lead, self.R)
         return y if self.bias is None else y + self.bias
 
@@ -185,7 +189,7 @@ class RunsLin:
             if x.dim() == 1 or x.shape[0] == 1:
                 self.lin.gemv(x.reshape(-1), y.reshape(-1))
             else:
-                self.lin.t16.run(x, y)
+                self.lin.t16.run(x, y, wide=self.lin.wide)
             return y
         import ctypes
         from . import _lib
@@ -259,4 +263,4 @@ class RunsBatch:
             raise ValueError("RunsBatch.run: B <= bmax, X contiguous, X and Y fp16 or bf16")
         if Y.stride(-1) != 1 or Y.shape[-1] != self.R:
             raise ValueError("RunsBatch.run: Y must be [B, R] with unit column stride")
-        return self.lin.small_batch(B).run(X, Y, B)
+        return self.lin.t16.run(X, Y, B, wide=True) if self.lin.wide else self.lin.small_batch(B).run(X, Y, B)

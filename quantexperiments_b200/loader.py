@@ -7,7 +7,8 @@ staging buffers into ONE exact-size arena per device and re-laid out for the ker
 While the copy engine moves matrix i to the device and the repack kernels of matrix i - 1 run, the host reads
 matrix i + 1 from the file into the other staging buffer. Column orders are regenerated from the stored seed and
 checked against the stored CRC (`PackedFile.perms`). With world > 1 each rank keeps its row range ("col" kind,
-output sharded) or column range ("row" kind, input sharded) of every matrix, cut before the copy.
+output sharded) or column range ("row" kind, input sharded) of every matrix, cut before the copy; an input shard of a
+matrix with several column orders keeps `perms[:, c0:c1]` and reads the full activation vector (`PackedLinear.wide`).
 
 Everything a matrix needs on the device (file-order tags for the dense decode, tables, scales, kernel layouts)
 lies back to back in the arena, 256-byte aligned, instead of one caching-allocator block per tensor: the
@@ -114,9 +115,6 @@ def plan_arena(pf: pk.PackedFile, names=None, layouts=("l8",), rank: int = 0, wo
     for name in names:
         m = pf.meta[name]
         kind = (kinds or {}).get(name)
-        if world > 1 and kind == "row" and m["M"] > 1:
-            raise NotImplementedError(f"{name}: an input shard of a matrix with several column orders reads the full "
-                                      "activation vector; build it with tp.RowParallelLinear")
         R, C = _shard_meta(m, kind, rank, world)
         mask = None
         if m["M"] > 1 and ("t16" in layouts or "l8" in layouts):
@@ -197,8 +195,10 @@ def load_linears(path_or_file, names=None, device="cuda", layouts=("l8",), rank:
             copied[i % 2] = ev
             main.wait_event(ev)
             C = meta["C"]
+            # an input shard of a matrix with several column orders keeps orders that name positions of the full vector
+            wide = m["C"] if (world > 1 and kind == "row" and m["M"] > 1) else None
             lin = PackedLinear(views["tags"], views["table"], views["row_scale"], views.get("row_book"), views.get("row_mask"),
-                               views["perms"] if "perms" in views else torch.empty((1, C), device="meta"), meta["K"], meta["d"])
+                               views["perms"] if "perms" in views else torch.empty((1, C), device="meta"), meta["K"], meta["d"], x_cols=wide)
             for lay in layouts:
                 if lay not in plan[name]:
                     continue

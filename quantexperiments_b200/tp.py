@@ -186,7 +186,6 @@ class RowParallelLinear:
 
     def __init__(self, t: dict, meta: dict, perms: torch.Tensor | None, rank: int, world: int, device="cuda", group=None,
                  arena: "PeerArena | None" = None):
-        from .kernels import DeviceMatrix, T16Matrix
         from .linear import PackedLinear
         self.rank, self.fused = rank, None
         c0, c1 = col_range(meta["C"], meta["d"], rank, world)
@@ -194,71 +193,27 @@ class RowParallelLinear:
         ts, ms, ps = shard_cols(t, meta, c0, c1, perms if multi else None)
         self.c0, self.c1, self.group, self.world, self.multi = c0, c1, group, world, multi
         self.R, self.C_full = meta["R"], meta["C"]
-        if not multi:
-            self.lin = PackedLinear(ts["tags"].to(device), ts["table"].to(device), ts["row_scale"].to(device),
-                                    ts["row_book"].to(device) if "row_book" in ts else None, None,
-                                    torch.arange(c1 - c0)[None].to(device), ms["K"], ms["d"],
-                                    words2=ts["tags2"].to(device) if "tags2" in ts else None,
-                                    table2=ts["table2"].to(device) if "table2" in ts else None)
-        else:
-            # column orders: the small-batch kernel gathers x through perms[:, c0:c1] from the full vector
-            self.dm = DeviceMatrix(ts["tags"], ts["table"], ts["row_scale"], None, ts["row_mask"], ps, K=ms["K"], d=ms["d"],
-                                   C=c1 - c0, device=device, tags2=ts.get("tags2"), table2=ts.get("table2"))
-            self.t16 = T16Matrix(self.dm)
-            self._l8 = None
+        self.lin = PackedLinear(ts["tags"].to(device), ts["table"].to(device), ts["row_scale"].to(device),
+                                ts["row_book"].to(device) if "row_book" in ts else None, ts["row_mask"].to(device) if multi else None,
+                                ps.to(device) if multi else torch.arange(c1 - c0)[None].to(device), ms["K"], ms["d"],
+                                words2=ts["tags2"].to(device) if "tags2" in ts else None,
+                                table2=ts["table2"].to(device) if "table2" in ts else None, x_cols=meta["C"] if multi else None)
+        if multi:       # column orders: every kernel gathers x through perms[:, c0:c1] from the full vector
+            self.dm = self.lin.dm
 
     def partial(self, x: torch.Tensor) -> torch.Tensor:
         """fp32 partial product [..., R] of this rank's column range."""
         lead = x.shape[:-1]
         n = math.prod(lead)
         y = torch.empty(n, self.R, dtype=torch.float32, device=x.device)
-        if not self.multi:
-            self.lin.forward_into(x.reshape(n, self.c1 - self.c0), y)
-        elif n == 1 and self.l8_multi is not None:
-            self.l8_multi.run(x.reshape(-1).contiguous(), y[0], wide=True)      # one token: the table-lookup kernel
-        elif n <= T16Matrix_BMAX():
-            self.t16.run(x.reshape(n, self.C_full).contiguous(), y, n, wide=True)   # the row-tile kernel: up to 64 tokens
-        else:
-            self._dense_wide(x.reshape(n, self.C_full), y)                          # prefill: decode once, tensor-core GEMM
+        self.lin.forward_into(x.reshape(n, self.lin.in_features), y)    # one token: table lookups; <= 64: row tiles; more: decode + GEMM
         return y.reshape(*lead, self.R)
-
-    def _dense_wide(self, X: torch.Tensor, Y: torch.Tensor) -> None:
-        """Many tokens against a column shard with column orders: the shard is decoded once into a zeroed 16-bit
-        scratch as wide as the full activation vector (its orders name positions of that vector), then one TMA-fed
-        tensor-core GEMM over all C columns.  Every rank multiplies the full width (its rows are 1 / world dense), so
-        this path buys correctness and tensor-core speed for long inputs, not a per-rank saving."""
-        import ctypes
-        from . import _lib
-        from .kernels import DenseStack, _dt, _stream
-        lib = _lib.lib
-        dev, T = self.dm.device, X.shape[0]
-        key = (dev.index, _stream(), "wide")
-        need = lib.cbl_dense_scratch_bytes(self.R, self.C_full)
-        pair = DenseStack._scratch.setdefault(key, [None, None, 0])     # two scratches alternate, as in DenseStack
-        pair[2] ^= 1
-        sc = pair[pair[2]]
-        if sc is None or sc.numel() < need:
-            sc = pair[pair[2]] = torch.empty(need, dtype=torch.uint8, device=dev)
-        need = lib.cbl_gemm_stage_bytes(T, self.C_full) + 16
-        st = DenseStack._stage.get(key)
-        if st is None or st.numel() < need:
-            st = DenseStack._stage[key] = torch.zeros(need, dtype=torch.uint8, device=dev)
-        X = X if X.stride(1) == 1 else X.contiguous()
-        with torch.cuda.device(dev):
-            sc[:lib.cbl_dense_scratch_bytes(self.R, self.C_full)].zero_()
-            s = _stream()
-            _lib.check("cbl_decode_raw_wide", lib.cbl_decode_raw_wide(ctypes.byref(self.dm.struct()), sc.data_ptr(), self.C_full, s))
-            _lib.check("cbl_gemm_dense", lib.cbl_gemm_dense(sc.data_ptr(), self.R, self.C_full, self.dm.row_scale.data_ptr(), X.data_ptr(), _dt(X.dtype),
-                                                            T, X.stride(0), Y.data_ptr(), _dt(Y.dtype), Y.stride(0), st.data_ptr(),
-                                                            st.data_ptr() + st.numel() - 16, s))
 
     @property
     def l8_multi(self):
         """The batch-1 layout of a shard with column orders (at most 16 of them), built on first use."""
         from .kernels import L8Matrix
-        if self._l8 is None and self.dm.M <= L8Matrix.MAX_ORDERS:
-            self._l8 = L8Matrix(self.dm)
-        return self._l8
+        return self.lin.l8 if self.lin.dm.M <= L8Matrix.MAX_ORDERS else None
 
     def attach(self, arena: "PeerArena") -> None:
         """Reserve this matrix's peer work space (call on every rank, in the same order)."""
@@ -289,7 +244,3 @@ class RowParallelLinear:
 
     __call__ = forward
 
-
-def T16Matrix_BMAX() -> int:
-    from .kernels import T16Matrix
-    return T16Matrix.BMAX

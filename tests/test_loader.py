@@ -98,8 +98,22 @@ def test_rank_shards_and_pooling(tmp_path):
         y = lins["a.gate"](x[None])[0]
         ref = full["a.gate"][:, rank * 512:(rank + 1) * 512] @ x.float()
         assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
-    with pytest.raises(NotImplementedError):
-        loader.load_linears(pf, ["b.masks"], rank=0, world=2, kinds={"b.masks": "row"})
+    # an input shard of a matrix with several column orders keeps orders that name positions of the full activation
+    # vector: the ranks' partial products (1, 5 and 100 tokens: table lookups, row tiles, wide decode + GEMM) add up
+    masks_full = PackedLinear.from_packed(pf, "b.masks")
+    Cm = masks_full.C
+    for T in (1, 5, 100):
+        xm = torch.randn(T, Cm, device="cuda").bfloat16()
+        want = xm.float() @ masks_full.dense().T
+        got = torch.zeros_like(want)
+        for rank in range(3):                            # 33 chunks: three ranks of 11
+            sh = loader.load_linears(pf, ["b.masks"], rank=rank, world=3, kinds={"b.masks": "row"})["b.masks"]
+            assert sh.wide and sh.in_features == Cm and sh.C < Cm
+            y = torch.empty(T, sh.R, device="cuda", dtype=torch.float32)
+            got += sh.forward_into(xm, y)
+            with pytest.raises(ValueError):
+                sh.dense()
+        assert (got - want).abs().max() <= 2e-3 * want.abs().max(), T
     # matrices built tensor by tensor, then pooled: same answers, new addresses inside one buffer, second call is a no-op
     built = [PackedLinear.from_packed(pf, n) for n in ("a.q", "a.gate", "b.masks")]
     x = torch.randn(1, 896, device="cuda").bfloat16()
