@@ -567,12 +567,10 @@ def run_prefill(args, rank: int, world: int, local_rank: int, emit: bool = True)
     from quantexperiments_b200.kernels import DenseStack
     from quantexperiments_b200.linear import DENSE_MIN_TOKENS
     SHAPES = MODELS[args.model]["shapes"]
-    if world > 1 and MODELS[args.model]["M"] > 1:
-        raise SystemExit("prefill of matrices with column orders under tensor parallelism: use tp.RowParallelLinear (tests/test_tp.py); "
-                         "this workload runs them on one GPU")
     lins, kinds, _ = build_set(dev, rank, world, 64, args.model)
     g = torch.Generator(device=dev).manual_seed(7)
-    xs = {c: torch.randn(T, c, device=dev, generator=g).bfloat16() for c in {l.C for l in lins}}
+    # (an input shard of a matrix with several column orders reads the full activation vector: in_features > C)
+    xs = {c: torch.randn(T, c, device=dev, generator=g).bfloat16() for c in sorted({l.in_features for l in lins})}
     flops = sum(2.0 * T * l.R * l.C for l in lins)
     # q|k|v and gate|up share their activations: one stacked product each, as the reference's gemm(x, [pieces]) does.
     # From DENSE_MIN_TOKENS tokens on the stack is decoded once into a 16-bit scratch and multiplied by the TMA-fed
@@ -583,12 +581,14 @@ def run_prefill(args, rank: int, world: int, local_rank: int, emit: bool = True)
         q, k, v, o, gate, up, down = lins[l0:l0 + len(SHAPES)]
         for members, kind in (((q, k, v), "col"), ((o,), "row"), ((gate, up), "col"), ((down,), "row")):
             y = torch.empty(T, sum(m.R for m in members), device=dev, dtype=torch.bfloat16)
-            groups.append((DenseStack([m.dm for m in members]) if dense else None, members, xs[members[0].C], y, kind))
+            groups.append((DenseStack([m.dm for m in members]) if dense and not members[0].wide else None, members, xs[members[0].in_features], y, kind))
             launches += (len(members) + 2) if dense else 2 * len(members)
 
     def run_group(stack, members, x, y, kind):
         if stack is not None:
             stack.gemm(x, y)
+        elif members[0].wide:
+            members[0].forward_into(x, y)              # wide decode into a zeroed scratch + the same GEMM over all columns
         else:
             off = 0
             for m in members:
