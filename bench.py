@@ -238,7 +238,7 @@ def cpu_baseline_sample() -> dict:
 
 def gpu_reference(dev, stream, lins_shapes, steps: int) -> dict:
     """The reference's own GPU kernel for this format - the Triton PackedLinear.gemv of shapequant/kernels/gemv.py -
-    over the same 196 matrices on the same device: the survey's same-box bar.  Needs the staged reference and Triton."""
+    over the same 196 matrices on the same device (the GPU-versus-GPU comparison).  Needs the staged reference and Triton."""
     try:
         from oracle import make_ref
         if make_ref.load() is None:

@@ -1,6 +1,6 @@
 """Stages the reference's own implementation of the path under oracle/_ref/ (git-ignored, travels to the GPU box).
 
-    python oracle/make_ref.py [REFERENCE_ROOT]        # default: /root/reference
+    python oracle/make_ref.py [REFERENCE_ROOT]        # default: the checkout named by DEFAULT_ROOT below
 
 The reference (angryslavemerchant/QuantExperiments, package `shapequant`) is pure Python, so there is nothing to
 compile: the recipe copies, unmodified, the four modules that define and execute the packed format -
@@ -19,9 +19,10 @@ FILES = ["shapequant/__init__.py", "shapequant/codebook.py", "shapequant/masks.p
          "shapequant/kernels/__init__.py", "shapequant/kernels/gemv.py"]
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
+DEFAULT_ROOT = Path("/root/reference")
 
 
-def make(ref_root: str | Path = "/root/reference") -> Path | None:
+def make(ref_root: str | Path = DEFAULT_ROOT) -> Path | None:
     """Copy the files if the reference is present; returns the destination (or None when it is absent)."""
     root = Path(ref_root)
     if not (root / FILES[1]).exists():
@@ -47,5 +48,5 @@ def load():
 
 
 if __name__ == "__main__":
-    out = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = make(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_ROOT)
     print(out if out else "reference not found: nothing staged")
