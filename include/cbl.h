@@ -78,6 +78,17 @@ typedef struct cbl_packed {
  *          shapequant/kernels/batched_runs.py:935-961 (dequant_tile, fp16 / bf16 output). */
 int cbl_dequant(const cbl_packed* m, void* out, int dtype, int64_t ld, int32_t r0, int32_t r1, cbl_stream s);
 
+/* Product for EVERY format the file layout can hold (any d <= 16, tags of up to 16 bits, several books per matrix
+ * through row_book, one or two summed books, several column orders), the formats outside the benchmark's d = 8 /
+ * 12-bit / one-book-per-matrix that the table-lookup and tensor-core kernels execute:
+ *   y[t * ldy + r] = round(row_scale[r] * sum_c W[r, c] * x[t * ldx + c]),  W = the decode above without the row scale
+ * fp32 accumulate; x f32 / f16 / bf16 (a column shard with column orders may index beyond C: ldx covers the vector),
+ * y f32 / f16 / bf16.  A correctness path (a warp per row, codewords from the cache-resident table), not a bandwidth
+ * kernel.
+ * replaces shapequant/kernels/gemv.py:28-64 (_gemv_kernel: any d, book_off, row_mask / perms) for those formats. */
+int cbl_gemv_generic(const cbl_packed* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                     cbl_stream s);
+
 /* Encoder side ("snap"): index of the nearest codeword of every chunk and its squared error,
  *   idx[i] = argmin_k (|c_k|^2 - 2 x_i . c_k)   (first k on ties),   err[i] = max(min + |x_i|^2, 0),
  * all in fp32 (8 FMAs per codeword from |c_k|^2, no reduced-precision contraction).  wt (optional, same shape as x):

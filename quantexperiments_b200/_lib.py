@@ -63,6 +63,7 @@ SIGNATURES = {
     "cbl_status_string": (c_char_p, [c_int]),
     "cbl_last_cuda_error": (c_int, []),
     "cbl_dequant": (c_int, [POINTER(Packed), c_void_p, c_int, c_int64, c_int32, c_int32, c_void_p]),
+    "cbl_gemv_generic": (c_int, [POINTER(Packed), c_void_p, c_int, c_int32, c_int64, c_void_p, c_int, c_int64, c_void_p]),
     "cbl_unpack_tags": (c_int, [POINTER(Packed), c_int, c_void_p, c_void_p]),
     "cbl_assign_max_codewords": (c_int, []),
     "cbl_assign": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int, c_int32, c_void_p, c_void_p, c_void_p]),

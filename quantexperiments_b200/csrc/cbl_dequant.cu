@@ -435,3 +435,60 @@ extern "C" int cbl_repack_l8(const cbl_packed* m, void* out, cbl_stream s) {
     k_repack_l8<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)s>>>(*m, ntile1, Rpad, (uint32_t*)out, n);
     return cbl_check_launch();
 }
+
+// ------------------------------------------------------------------------------------ product for every format the file layout can hold
+//
+// y[t, r] = round(row_scale[r] * sum_j <table[row_book[r] * K + tag(r, j)] (+ table2[tag2(r, j)]), x[t, perms[row_mask[r]][j d .. j d + d)]>)
+// for any chunk length d <= 16, tag width <= 16 bits, several books per matrix (row_book) and several column orders:
+// the formats the reference's generic kernel executes and the table-lookup / tensor-core kernels here do not.  A
+// warp per row: its lanes take every 32nd chunk, read the codeword from the L1/L2-resident table and the chunk's
+// activations through the row's column order, and accumulate up to GEN_TOK tokens in fp32; shuffles add the lanes.
+// Not a bandwidth kernel: correctness for the formats outside the benchmark's.
+constexpr int GEN_TOK = 4;
+__global__ void __launch_bounds__(256) k_gemv_generic(cbl_packed m, const void* __restrict__ x, int xdtype, int ntok, int64_t ldx,
+                                                      void* __restrict__ y, int ydtype, int64_t ldy) {
+    const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= m.R) return;
+    const int d = m.d, nch = m.C / d;
+    const uint32_t K = 1u << m.bits, boff = m.row_book ? (uint32_t)m.row_book[r] * K : 0u;
+    const int32_t* rw = m.tags + (int64_t)r * m.W;
+    const int32_t* rw2 = m.books == 2 ? m.tags2 + (int64_t)r * m.W : nullptr;
+    const int32_t* perm = m.M > 1 ? m.perms + (int64_t)m.row_mask[r] * m.C : nullptr;
+    const float rs = __half2float(((const __half*)m.row_scale)[r]);
+    for (int t0 = 0; t0 < ntok; t0 += GEN_TOK) {
+        float acc[GEN_TOK];
+#pragma unroll
+        for (int t = 0; t < GEN_TOK; t++) acc[t] = 0.f;
+        for (int j = lane; j < nch; j += 32) {
+            const __half* cw = (const __half*)m.table + (int64_t)(boff + cbl_read_tag(rw, m.W, j, m.bits)) * d;
+            const __half* cw2 = rw2 ? (const __half*)m.table2 + (int64_t)cbl_read_tag(rw2, m.W, j, m.bits) * d : nullptr;
+            for (int i = 0; i < d; i++) {
+                float w = __half2float(cw[i]);
+                if (cw2) w = __fadd_rn(w, __half2float(cw2[i]));          // the decode's order: the two codewords are added first
+                const int c = perm ? perm[j * d + i] : j * d + i;
+#pragma unroll
+                for (int t = 0; t < GEN_TOK; t++)
+                    if (t0 + t < ntok) acc[t] = fmaf(w, cbl_load_in(x, xdtype, (int64_t)(t0 + t) * ldx + c), acc[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < GEN_TOK; t++) {
+            float v = acc[t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && t0 + t < ntok) cbl_store_out(y, ydtype, (int64_t)(t0 + t) * ldy + r, v * rs);
+        }
+    }
+}
+
+extern "C" int cbl_gemv_generic(const cbl_packed* m, const void* x, int xdtype, int32_t ntok, int64_t ldx, void* y, int ydtype, int64_t ldy,
+                                cbl_stream s) {
+    int rc = check_packed(m);
+    if (rc) return rc;
+    if (!x || !y || ntok < 0 || ldy < m->R) return CBL_EINVAL;
+    if (xdtype != CBL_F32 && xdtype != CBL_F16 && xdtype != CBL_BF16) return CBL_EINVAL;
+    if (ydtype != CBL_F32 && ydtype != CBL_F16 && ydtype != CBL_BF16) return CBL_EINVAL;
+    if (m->R == 0 || ntok == 0) return CBL_OK;
+    k_gemv_generic<<<cbl_ceil_div(m->R, 8), 256, 0, (cudaStream_t)s>>>(*m, x, xdtype, ntok, ldx, y, ydtype, ldy);
+    return cbl_check_launch();
+}

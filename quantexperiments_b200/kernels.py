@@ -155,6 +155,29 @@ class DeviceMatrix:
                                                             st.data_ptr() + st.numel() - 16, s))
         return Y
 
+    @property
+    def fast(self) -> bool:
+        """The format the table-lookup and tensor-core kernels execute (d = 8, 12-bit tags, one book per matrix)."""
+        return self.d == 8 and self.bits == 12 and self.G == 1
+
+    def gemv_generic(self, X: torch.Tensor, Y: torch.Tensor | None = None) -> torch.Tensor:
+        """Y [T, R] = X [T, C] . W^T for any format the layout holds (any d, tag width, books per matrix, column orders):
+        the correctness path for formats outside the benchmark's; fp32 accumulate."""
+        if X.dim() == 1:
+            X = X[None]
+        width = self.x_cols if self.x_cols is not None else self.C
+        if X.dim() != 2 or X.shape[1] != width or X.stride(1) != 1 or X.device != self.device:
+            raise ValueError("X must be [T, C] with unit column stride on the matrix's device")
+        T = X.shape[0]
+        if Y is None:
+            Y = torch.empty(T, self.R, dtype=X.dtype, device=self.device)
+        if Y.shape != (T, self.R) or Y.stride(1) != 1:
+            raise ValueError("Y must be [T, R] with unit column stride")
+        with torch.cuda.device(self.device):
+            _lib.check("cbl_gemv_generic", lib.cbl_gemv_generic(ctypes.byref(self.struct()), X.data_ptr(), _dt(X.dtype), T, X.stride(0) if T > 1 else width,
+                                                                Y.data_ptr(), _dt(Y.dtype), Y.stride(0) if T > 1 else self.R, _stream()))
+        return Y
+
     def unpack(self, plane: int = 0) -> torch.Tensor:
         out = torch.empty(self.R, self.nch, dtype=torch.int32, device=self.device)
         with torch.cuda.device(self.device):

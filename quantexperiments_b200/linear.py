@@ -112,6 +112,8 @@ class PackedLinear(torch.nn.Module):
 
     def use_l8(self) -> bool:
         """One token runs on the table-lookup kernel (any number of column orders up to its limit)."""
+        if not self.dm.fast:
+            return False
         if self.dm.M == 1:
             return self.R >= L8_MIN_ROWS
         return self.dm.M <= L8Matrix.MAX_ORDERS and self.R >= L8_MIN_ROWS_PER_ORDER * self.dm.M
@@ -123,6 +125,10 @@ class PackedLinear(torch.nn.Module):
 
     def gemv(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [C] (fp16 / bf16 / fp32, contiguous) -> y [R] in x's dtype (or `out`'s)."""
+        if not self.dm.fast:            # any d / tag width / several books per matrix: the generic product
+            y = out if out is not None else torch.empty(self.R, dtype=x.dtype, device=x.device)
+            self.dm.gemv_generic(x.reshape(1, -1), y.reshape(1, -1))
+            return y
         if self.use_l8():
             return self.l8.run(x, out, wide=self.wide)
         y = out if out is not None else torch.empty(self.R, dtype=x.dtype, device=x.device)
@@ -137,6 +143,11 @@ class PackedLinear(torch.nn.Module):
         """y [n, R] (any of fp32 / fp16 / bf16, unit column stride) = x2 [n, C] . W^T, dispatched by n."""
         n = x2.shape[0]
         if n == 0:
+            return y
+        if not self.dm.fast:
+            # formats outside d = 8 / 12-bit tags / one book per matrix: the generic product (a warp per row), which is
+            # what the reference's own kernel is for them; a correctness path, whatever the token count
+            self.dm.gemv_generic(x2 if x2.stride(1) == 1 else x2.contiguous(), y)
             return y
         if n == 1 and self.use_l8() and y.is_contiguous():
             self.l8.run(x2[0].contiguous(), y[0], wide=self.wide)

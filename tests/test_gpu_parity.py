@@ -33,6 +33,11 @@ def _l8_counters(ws):
     return ws[:160 * 4096 * 8 + 256]
 
 
+def _lib_mod():
+    from quantexperiments_b200 import _lib
+    return _lib
+
+
 def _out_tol(dtype):
     return TOL + {torch.float32: 0.0, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}[dtype]
 
@@ -51,6 +56,44 @@ def test_decode_matches_reference_fixtures_bit_for_bit():
         assert torch.equal(w.cpu(), _t(z[f"w_{i}"])), f"case {i}: G={Gb} M={M} K={K} d={d}"
         bits = int(K).bit_length() - 1
         assert np.array_equal(dm.unpack().cpu().numpy(), orc.unpack_bits(z[f"words_{i}"], bits, C // int(d)))
+
+
+def test_product_of_every_format_in_the_reference_grid():
+    """Formats outside d = 8 / 12-bit tags / one book per matrix (the reference's (G, M, K, d) grid, written by its own
+    decoder): the generic product and PackedLinear's dispatch to it, 1 / 3 / 9 tokens, against an fp32 matmul on the
+    reference-decoded weights."""
+    from quantexperiments_b200.kernels import DeviceMatrix
+    from quantexperiments_b200.linear import PackedLinear
+    z = np.load(G / "decode.npz")
+    seen_generic = 0
+    for i, (Gb, M, K, d) in enumerate(z["grid"]):
+        seed, R, C = (int(v) for v in z[f"seed_{i}"])
+        rb = _t(z[f"rb_{i}"]) if f"rb_{i}" in z else None
+        rm = _t(z[f"rm_{i}"]) if f"rm_{i}" in z else None
+        perms = _t(orc.seeded_perms(C, int(M), seed)) if M > 1 else None
+        dm = DeviceMatrix(_t(z[f"words_{i}"]), _t(z[f"table_{i}"]), _t(z[f"rs_{i}"]), rb, rm, perms, K=int(K), d=int(d), C=C)
+        w = z[f"w_{i}"]
+        lin = PackedLinear(_t(z[f"words_{i}"]).cuda(), _t(z[f"table_{i}"]).cuda(), _t(z[f"rs_{i}"]).cuda(), None if rb is None else rb.cuda(),
+                           None if rm is None else rm.cuda(), (perms if perms is not None else torch.arange(C)[None]).cuda(), int(K), int(d))
+        seen_generic += not dm.fast
+        for T in (1, 3, 9):
+            x = torch.randn(T, C, generator=torch.Generator().manual_seed(T + i)).bfloat16()
+            yref = orc.linear_ref(x.float().numpy(), w)
+            y = dm.gemv_generic(x.cuda(), torch.empty(T, R, device="cuda")).cpu().numpy()
+            assert orc.max_rel_err(y, yref) < TOL, (i, T)
+            y2 = lin(x.cuda()).float().cpu().numpy()
+            assert orc.max_rel_err(y2, yref) < TOL + 2.0 ** -8, (i, T)
+        if not dm.fast:
+            y1 = lin.gemv(x[0].cuda()).float().cpu().numpy()
+            assert orc.max_rel_err(y1, yref[0]) < TOL + 2.0 ** -8
+    assert seen_generic >= 2
+    # two summed books in a format the fast kernels do not run (d = 4, 8-bit tags)
+    m = orc.synth_matrix(96, 64, seed=12, d=4, bits=8, books=2, M=3)
+    dm = DeviceMatrix(_t(m["words"][0]), _t(m["table"][0]), _t(m["row_scale"]), None, _t(m["row_mask"]), _t(m["perms"]), K=256, d=4, C=64,
+                      tags2=_t(m["words"][1]), table2=_t(m["table"][1]))
+    x = torch.randn(5, 64, generator=torch.Generator().manual_seed(1))
+    assert orc.max_rel_err(dm.gemv_generic(x.cuda()).cpu().numpy(), orc.linear_ref(x.numpy(), orc.synth_decode(m))) < TOL
+    assert _lib_mod().lib.cbl_gemv_generic(None, None, 0, 1, 0, None, 0, 0, None) == _lib_mod().EINVAL
 
 
 def test_two_book_decode_matches_reference_fixture():
