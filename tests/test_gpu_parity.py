@@ -236,7 +236,7 @@ def test_batch1_product_survives_outliers_and_extreme_scales():
         assert orc.max_rel_err(y.cpu().numpy(), yref) < TOL
 
 
-@pytest.mark.parametrize("R,C,books,M", [(2304, 1024, 2, 16), (1000, 520, 1, 3), (4100, 896, 1, 16), (37, 64, 2, 2)])
+@pytest.mark.parametrize("R,C,books,M", [(2304, 1024, 2, 16), (1000, 520, 1, 3), (4100, 896, 1, 16), (37, 64, 2, 2), (20, 128, 1, 16)])
 def test_batch1_product_with_column_orders_matches_fp32_matmul(R, C, books, M):
     """Rows grouped by column order, one table per (tile, order) built from the permuted activations:
     y[r] = rs[r] * sum_j <table[tag[r, j]], x[perm_{m_r}[8j .. 8j+7]]> (shapequant/kernels/gemv.py:3)."""
