@@ -7,8 +7,8 @@
 // costs ONE 2-byte shared-memory read and half an integer add (three-input adds; a row's 8 entries sum exactly).  Two tables
 // alternate: while the block looks tile t up, its warps build tile t + 1, so only a block's first build
 // is exposed.  The tags of the block's rows stream through a ring of shared-memory stages filled by bulk
-// copies (cp.async.bulk + mbarrier, up to 15 stages = 90 KB in flight, started before the kernel waits
-// for its predecessor).  A block owns a rectangle (rows x tiles) of one matrix; a thread owns up to 8 rows
+// copies (cp.async.bulk + mbarrier, 8 stages = 96 KB in flight, started before the kernel waits for its
+// predecessor); nobody is the producer: the last warp to read a stage issues the copies that refill it.  A block owns a rectangle (rows x tiles) of one matrix; a thread owns up to 8 rows
 // of it and keeps their fp32 sums in registers over all the block's tiles.
 //
 // Row sums of blocks that share rows (different tile ranges) meet without atomics, fences or counters, and in a
@@ -31,12 +31,12 @@
 #include "cbl_common.cuh"
 
 
-constexpr int L8_NT = 512;                       // consumer threads per block; a thread handles 4 consecutive rows per ring stage
+constexpr int L8_NT = 512;                       // threads per block; a thread handles 4 consecutive rows per ring stage
 constexpr int L8_NWARP = L8_NT / 32;
-constexpr int L8_THREADS = L8_NT + 32;           // + one producer warp
+constexpr int L8_THREADS = L8_NT;                // the last warp to read a ring stage refills it
 constexpr int L8_RPT = 8;                        // rows per thread: a block covers at most 4096 rows
 constexpr int L8_STEP_ROWS = 4 * L8_NT;           // 2048 rows per step of the block
-constexpr int L8_STAGE_ROWS = L8_STEP_ROWS / 2;   // a ring stage holds half a step: the rows of 8 consumer warps
+constexpr int L8_STAGE_ROWS = L8_STEP_ROWS / 2;   // a ring stage holds half a step: the rows of 8 warps
 constexpr int L8_STAGE_WARPS = L8_NWARP / 2;
 constexpr int L8_STAGE_BYTES = 3 * L8_STAGE_ROWS * 4;   // three tag planes
 constexpr int L8_MAX_STAGES = 8;
@@ -155,14 +155,15 @@ struct L8Plan {
                              // w = tile_lo | tile_hi << 16; the blocks of a part are consecutive, in split order
 };
 
-// Barrier among the 512 consumer threads only (the producer warp runs ahead on its own).
-__device__ __forceinline__ void l8_sync_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(L8_NT) : "memory"); }
+// Barrier among the block's 512 threads.
+__device__ __forceinline__ void l8_sync_block() { asm volatile("bar.sync 1, %0;" ::"n"(L8_NT) : "memory"); }
 
 __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant__ L8Launch P, const __grid_constant__ L8Plan plan,
                                                            const void* __restrict__ x, int xdtype) {
     extern __shared__ __align__(128) unsigned char l8_smem[];
-    __shared__ __align__(8) unsigned long long s_bar[2 * L8_MAX_STAGES];   // full[stage] (tags landed), empty[stage] (every warp has read them)
+    __shared__ __align__(8) unsigned long long s_bar[L8_MAX_STAGES];       // full[stage]: the stage's tags have landed
     __shared__ int s_abort;
+    __shared__ unsigned int s_readers[L8_MAX_STAGES];   // warps that have read the stage's current contents
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     if ((int)blockIdx.x >= plan.nblocks) return;
@@ -194,41 +195,36 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
     const int ntl = tile_hi - tile_lo;
     const int nit = ntl * nrow_it;                     // iterations of this block: (tile, row step), tile-major; two ring stages each
     if (tid < S) {
-        l8_mbar_init(bar0 + 8 * tid, 1);                             // full: the producer's arrive + the bytes of three copies
-        l8_mbar_init(bar0 + 8 * (L8_MAX_STAGES + tid), L8_STAGE_WARPS);   // empty: one arrival per consuming warp
+        l8_mbar_init(bar0 + 8 * tid, 1);                             // full: the issuing lane's arrive + the bytes of three copies
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid == 0) s_abort = 0;
+    if (tid < L8_MAX_STAGES) s_readers[tid] = 0u;
     __syncthreads();
 
-    if (warp == L8_NWARP) {
-        // ---- producer warp: lanes 0..2 stage the three tag planes of one iteration, lane 0 announces the bytes.
-        // Weights do not depend on the previous kernel: streaming starts at once and runs up to S stages ahead.
-        const uint32_t* src = (const uint32_t*)mm.words + (int64_t)tile_lo * 3 * mm.Rpad + row_lo + (int64_t)lane * mm.Rpad;
-        int k = 0, stage = 0;
-        uint32_t use = 0;
-        for (int i = 0; i < 2 * nit; i++) {             // stage i: half (i & 1) of iteration i / 2
-            if (use > 0) {
-                int ok = 1;
-                if (lane == 0) ok = l8_mbar_wait(bar0 + 8 * (L8_MAX_STAGES + stage), (use - 1u) & 1u);
-                if (!__shfl_sync(0xffffffffu, ok, 0)) { s_abort = 1; return; }
-            }
-            const int r0 = k * L8_STEP_ROWS + (i & 1) * L8_STAGE_ROWS;
-            const int n = max(0, min(L8_STAGE_ROWS, nrows - r0));
-            const uint32_t bar = bar0 + 8 * stage;
-            if (lane == 0) {
-                if (n > 0) l8_mbar_expect_tx(bar, 12u * (uint32_t)n);
-                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");      // an empty half completes at once
-            }
-            __syncwarp();
-            if (lane < 3 && n > 0) l8_bulk_g2s(stage_addr(stage) + lane * (L8_STAGE_ROWS * 4), src + r0, 4u * (uint32_t)n, bar);
-            if ((i & 1) && ++k == nrow_it) { k = 0; src += 3 * (int64_t)mm.Rpad; }
-            if (++stage == S) { stage = 0; use++; }
+    // ---- tag ring.  Stage n (half n & 1 of iteration n / 2) lives in ring slot n mod S.  Nobody is the producer: the
+    // warp that is the LAST of a stage's 8 readers issues the copies of stage n + S into the slot (lanes 0..2 the three
+    // tag planes, lane 0 announces the bytes), without waiting for anything.  Weights do not depend on the previous
+    // kernel: warp 0 fills the ring before the wait below.
+    auto issue = [&](int n) {                           // whole warp; stage n -> slot n mod S
+        const int i = n >> 1, ti = i / nrow_it, k = i - ti * nrow_it;
+        const int r0 = k * L8_STEP_ROWS + (n & 1) * L8_STAGE_ROWS;
+        const int cnt = max(0, min(L8_STAGE_ROWS, nrows - r0));
+        const int slot = n % S;
+        const uint32_t bar = bar0 + 8 * slot;
+        if (lane == 0) {
+            if (cnt > 0) l8_mbar_expect_tx(bar, 12u * (uint32_t)cnt);
+            else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");      // an empty half completes at once
         }
-        return;
-    }
+        __syncwarp();
+        if (lane < 3 && cnt > 0)
+            l8_bulk_g2s(stage_addr(slot) + lane * (L8_STAGE_ROWS * 4),
+                        (const uint32_t*)mm.words + ((int64_t)(tile_lo + ti) * 3 + lane) * mm.Rpad + row_lo + r0, 4u * (uint32_t)cnt, bar);
+    };
+    if (warp == 0)
+        for (int n = 0; n < S && n < 2 * nit; n++) issue(n);
 
-    // ---- consumers.  The book's mma A fragments stay in registers for all tiles of a book (one 16-byte load per two
+    // ---- tables.  The book's mma A fragments stay in registers for all tiles of a book (one 16-byte load per two
     // 16-codeword blocks); everything that does not depend on the previous kernel is requested before the wait.
     const int ntile1 = mm.ntile / mm.books;
     uint4 af[8];
@@ -313,14 +309,14 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
     float inv_cur = build(tbl0, xa, xb), inv_nxt = 0.f;
     if (ntl > 1) load_x(tile_lo + 1, xa, xb);
 
-    l8_sync_consumers();                                // the first table is complete
+    l8_sync_block();                                // the first table is complete
 
     // ---- main loop over the ring iterations.  Warps run through the ring on their own; the tags of iteration i + 1
     // are fetched from the ring before the lookups of iteration i; a row's fp32 sum lives in shared memory between
     // tiles (each row belongs to one thread).  After a wait has expired the loop only keeps its shape (it contains
     // barriers) and does no more work.
     const int half = warp / L8_STAGE_WARPS, tih = tid - half * (L8_NT / 2);    // this thread's half step and index in it
-    int cstage = half, kf = 0;
+    int cstage = half, kf = 0, cn = half;              // ring slot, row step and stage number of the next fetch
     uint32_t cphase = 0;
     bool dead = false;
     uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0, w2 = w0;
@@ -334,7 +330,14 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
             w2 = cbl_lds128(a + 2 * L8_STAGE_ROWS * 4);
         }
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar0 + 8 * (L8_MAX_STAGES + cstage)) : "memory");
+        // the last of the stage's readers refills its slot with the stage S further on
+        unsigned int last = 0;
+        if (lane == 0 && atomicAdd(&s_readers[cstage], 1u) == L8_STAGE_WARPS - 1) {
+            atomicExch(&s_readers[cstage], 0u);
+            last = 1;
+        }
+        if (__shfl_sync(0xffffffffu, last, 0) && cn + S < 2 * nit && !dead) issue(cn + S);
+        cn += 2;
         cstage += 2;
         if (cstage >= S) { cstage -= S; cphase ^= 1u; }
         if (++kf == nrow_it) kf = 0;
@@ -378,7 +381,7 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
 #pragma unroll
             for (int s = 0; s < 8; s++) col[s] = (col[s] & 0xFFFFu) | tn;
             inv_cur = inv_nxt;
-            l8_sync_consumers();                        // next table complete; every reader of this one is done
+            l8_sync_block();                        // next table complete; every reader of this one is done
         }
     }
     // The next kernel of the stream may become resident from here on.  (Not earlier: a block of this kernel fills its
@@ -392,7 +395,7 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
             asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(sacc + (uint32_t)(kk * L8_STEP_ROWS + 4 * tid) * 4u), "f"(acc[kk][0]),
                          "f"(acc[kk][1]), "f"(acc[kk][2]), "f"(acc[kk][3])
                          : "memory");
-    l8_sync_consumers();
+    l8_sync_block();
     if (*(volatile int*)&s_abort) {
         // a staged copy never completed: report and leave (the waits that gave up were bounded)
         if (tid == 0) atomicExch(P.status, 1u);
@@ -425,7 +428,7 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
         const int q = j * L8_NT + tid;
         if (q < nrows) __stcg(slot + q, (1ull << 32) | (unsigned long long)l8_lds32(sacc + (uint32_t)q * 4u));
     }
-    l8_sync_consumers();                                // the row sums in shared memory have been read: the space is staging now
+    l8_sync_block();                                // the row sums in shared memory have been read: the space is staging now
     // every block sums its share of the part's rows over the splits: thread (row, group) adds the splits
     // group, group + G, ... in order, the groups are added in order through shared memory
     const int s_me = (int)blockIdx.x - first;
@@ -474,9 +477,9 @@ __global__ void __launch_bounds__(L8_THREADS, 1) k_gemv_l8(const __grid_constant
             }
         }
         if (G > 1) {
-            l8_sync_consumers();                        // previous readers of the staging rows
+            l8_sync_block();                        // previous readers of the staging rows
             if (grp < G) l8_sts32(sacc + (uint32_t)(grp * nqq + r) * 4u, __float_as_uint(sum));
-            l8_sync_consumers();
+            l8_sync_block();
             if (grp == 0) {
                 sum = 0.f;
                 for (int gq = 0; gq < G; gq++) sum += __uint_as_float(l8_lds32(sacc + (uint32_t)(gq * nqq + r) * 4u));
