@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the batch-1 kernel on the 18944 x 3584 gate|up pair from one ncu capture
 # (profiles/gemv_l8_gateup_7b.md: dram__bytes_read.sum + dram__bytes_write.sum), and the algorithmic
 # bytes of that launch; traffic of other launches is scaled by their algorithmic bytes.
-NCU_TRAFFIC_GATEUP = (25_730_304 + 1_280, 2 * (12_833_792 + 18944 * 2) + 3584 * 2)
+NCU_TRAFFIC_GATEUP = (25_732_608 + 0, 2 * (12_833_792 + 18944 * 2) + 3584 * 2)
 
 
 def measured_peak() -> tuple[float, str]:
